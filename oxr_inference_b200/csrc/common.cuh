@@ -1,0 +1,70 @@
+// Shared device helpers for the sm_100a kernels of this engine.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define OXR_API extern "C" __attribute__((visibility("default")))
+
+// Error codes written to the engine's device status word (first error wins) and returned by launchers.
+enum OxrStatus : int {
+    OXR_OK = 0,
+    OXR_BAD_TOKEN_ID = 1,     // embedding: id outside [0, vocab)
+    OXR_BAD_SLOT = 2,         // cache store: slot outside the pool
+    OXR_BAD_POSITION = 3,     // position outside the rotary table
+    OXR_BAD_PAGE = 4,         // attention: block table names a page outside the pool
+    OXR_WAIT_EXPIRED = 5,     // a bounded wait on an mbarrier ran out
+    OXR_BAD_ARGUMENT = 100,   // launcher refused its arguments (host side)
+};
+
+__device__ __forceinline__ void oxr_report(int* status, int code, int detail) {
+    if (status != nullptr && atomicCAS(status, 0, code) == 0) status[1] = detail;
+}
+
+template <typename T> struct Num;
+template <> struct Num<float> {
+    static __device__ __forceinline__ float to_f32(float v) { return v; }
+    static __device__ __forceinline__ float from_f32(float v) { return v; }
+};
+template <> struct Num<__nv_bfloat16> {
+    static __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+    static __device__ __forceinline__ __nv_bfloat16 from_f32(float v) { return __float2bfloat16_rn(v); }
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Block-wide sum in a fixed order (warp butterflies, then warp 0 over the per-warp partials), so that the
+// result for a row does not depend on what else runs. `scratch` holds 32 floats. All threads get the result.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();  // scratch may still be read from a previous call
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float t = (lane < nwarps) ? scratch[lane] : 0.f;
+    return warp_sum(t);
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float t = (lane < nwarps) ? scratch[lane] : -INFINITY;
+    return warp_max(t);
+}
+
+static inline int oxr_launch_status() {
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : 1000 + (int)e;
+}

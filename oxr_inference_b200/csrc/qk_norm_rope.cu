@@ -1,0 +1,126 @@
+// Fused per-head q/k RMSNorm + rotary position encoding + store of K and V into the paged cache.
+//
+// Takes the place of the reference's one hand-written GPU kernel, the Triton
+// `_qk_norm_rope_store_kernel` (oxr_runtime/kernels.py:66-99): for each token, every q head and k head is
+// RMS-normalised over head_dim with a weight shared by all heads (kernels.py:48-60), rotated by the
+// half-split (GPT-NeoX) rule out = (y1*c - y2*s, y1*s + y2*c) (kernels.py:61-63), q is written out and k, v go
+// to `cache + slot * KV * D` (kernels.py:84-99). Unlike the reference it takes any even head_dim, gathers
+// cos/sin by position itself, keeps the whole computation in fp32 and rounds once.
+#include "common.cuh"
+
+// One warp per (token, head); heads 0..H-1 are q, H..H+KV-1 are k, H+KV..H+2KV-1 are v.
+// Lane l handles the pairs (j, j + D/2) for j = l, l + 32, ...
+template <typename T, int MAX_PAIRS_PER_LANE>
+__global__ void qk_norm_rope_store_kernel(
+    T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache, const T* __restrict__ qkv,
+    const float* __restrict__ q_weight, const float* __restrict__ k_weight, const float* __restrict__ cos_table,
+    const float* __restrict__ sin_table, const int* __restrict__ positions, const int* __restrict__ slots,
+    int n_tokens, int H, int KV, int D, float eps, int max_positions, long long num_slots, int norm_q, int norm_k,
+    int rotate, int* status) {
+    const int warps_per_block = blockDim.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const long long unit = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+    const int heads = H + 2 * KV;
+    if (unit >= (long long)n_tokens * heads) return;
+    const int t = (int)(unit / heads), head = (int)(unit % heads);
+    const int half = D >> 1;
+    const T* src = qkv + (size_t)t * heads * D + (size_t)head * D;
+
+    T* dst;
+    if (head < H) {
+        dst = q_out + (size_t)t * H * D + (size_t)head * D;
+    } else {
+        const long long slot = slots[t];
+        if (slot < 0) return;  // a row that is not to be stored (padding)
+        if (slot >= num_slots) {
+            if (lane == 0) oxr_report(status, OXR_BAD_SLOT, t);
+            return;
+        }
+        const bool is_k = head < H + KV;
+        const int kvh = is_k ? head - H : head - H - KV;
+        dst = (is_k ? k_cache : v_cache) + (size_t)slot * KV * D + (size_t)kvh * D;
+        if (!is_k) {  // v: copied unchanged
+            for (int j = lane; j < D; j += 32) dst[j] = src[j];
+            return;
+        }
+    }
+
+    const bool is_q = head < H;
+    const bool do_norm = is_q ? norm_q : norm_k;
+    const float* w = is_q ? q_weight : k_weight;
+
+    float x1[MAX_PAIRS_PER_LANE], x2[MAX_PAIRS_PER_LANE];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAX_PAIRS_PER_LANE; ++i) {
+        const int j = lane + 32 * i;
+        x1[i] = x2[i] = 0.f;
+        if (j < half) {
+            x1[i] = Num<T>::to_f32(src[j]);
+            x2[i] = Num<T>::to_f32(src[j + half]);
+            ss += x1[i] * x1[i] + x2[i] * x2[i];
+        }
+    }
+    float inv = 1.f;
+    if (do_norm) {
+        ss = warp_sum(ss);
+        inv = rsqrtf(ss / (float)D + eps);
+    }
+    int pos = 0;
+    if (rotate) {
+        pos = positions[t];
+        if (pos < 0 || pos >= max_positions) {
+            if (lane == 0) oxr_report(status, OXR_BAD_POSITION, t);
+            pos = 0;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < MAX_PAIRS_PER_LANE; ++i) {
+        const int j = lane + 32 * i;
+        if (j < half) {
+            float y1 = x1[i], y2 = x2[i];
+            if (do_norm) {
+                y1 = y1 * inv * w[j];
+                y2 = y2 * inv * w[j + half];
+            }
+            if (rotate) {
+                const float c = cos_table[(size_t)pos * half + j], s = sin_table[(size_t)pos * half + j];
+                const float r1 = y1 * c - y2 * s, r2 = y1 * s + y2 * c;
+                y1 = r1;
+                y2 = r2;
+            }
+            dst[j] = Num<T>::from_f32(y1);
+            dst[j + half] = Num<T>::from_f32(y2);
+        }
+    }
+}
+
+// dtype: 0 = float32, 1 = bfloat16 (qkv, q_out and the cache). head_dim: even, at most 512.
+// k_cache / v_cache: one layer's pool viewed as [num_slots, KV, D]. slots[t] < 0 skips the store.
+OXR_API int oxr_qk_norm_rope_store(void* q_out, void* k_cache, void* v_cache, const void* qkv, const float* q_weight,
+                                   const float* k_weight, const float* cos_table, const float* sin_table,
+                                   const int* positions, const int* slots, int n_tokens, int H, int KV, int D, float eps,
+                                   int max_positions, long long num_slots, int norm_q, int norm_k, int rotate, int dtype,
+                                   int* status, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (D <= 0 || (D & 1) || D > 512) return OXR_BAD_ARGUMENT;
+    const int warps = 4;
+    const long long units = (long long)n_tokens * (H + 2 * KV);
+    const unsigned blocks = (unsigned)((units + warps - 1) / warps);
+    const int pairs = (D / 2 + 31) / 32;  // 1..8
+#define LAUNCH(T, P)                                                                                               \
+    qk_norm_rope_store_kernel<T, P><<<blocks, warps * 32, 0, stream>>>(                                              \
+        (T*)q_out, (T*)k_cache, (T*)v_cache, (const T*)qkv, q_weight, k_weight, cos_table, sin_table, positions, slots, \
+        n_tokens, H, KV, D, eps, max_positions, num_slots, norm_q, norm_k, rotate, status)
+#define DISPATCH(T)                                   \
+    if (pairs <= 1) LAUNCH(T, 1);                     \
+    else if (pairs <= 2) LAUNCH(T, 2);                \
+    else if (pairs <= 4) LAUNCH(T, 4);                \
+    else LAUNCH(T, 8)
+    if (dtype == 0) { DISPATCH(float); }
+    else if (dtype == 1) { DISPATCH(__nv_bfloat16); }
+    else return OXR_BAD_ARGUMENT;
+#undef DISPATCH
+#undef LAUNCH
+    return oxr_launch_status();
+}

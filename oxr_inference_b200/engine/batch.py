@@ -1,0 +1,217 @@
+"""Turns a step's host-side description into the device tensors the model reads: one staging block, one copy.
+
+A step is a list of entries (request's cache, its next tokens, which of them want logits). All index arrays the
+kernels need (token ids, positions, request boundaries, context lengths, block tables and store slots per cache
+group, attention tile lists, rows whose logits are wanted, sampling parameters) are laid out in ONE pinned int32
+block and reach the device with ONE asynchronous copy issued before the step's first kernel, as the reference
+takes care to do (oxr_runtime/engine.py:523-539, oxr_runtime/decode_graph.py:102-115). With a fixed ``Layout``
+(CUDA-graph replay) the device block and every view into it keep their addresses from step to step; rows
+beyond the real requests are padding that writes and reads the scratch page (oxr_runtime/decode_graph.py:104-110).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from oxr_inference_b200.cache.manager import CacheManager, RequestCache
+from oxr_inference_b200.parts.base import StepContext
+
+
+@dataclass
+class StepEntry:
+    cache: RequestCache
+    tokens: list[int]
+    """The request's next tokens, at positions cache.length .. cache.length + len(tokens) - 1."""
+    want: list[int]
+    """Indices into ``tokens`` whose logits are wanted, in the order wanted."""
+    temperature: float = 0.0
+    seed: int = 0
+    counter: int = 0
+    """Index of the output token that will be sampled from this entry's (last) wanted row."""
+
+
+def _align(n: int) -> int:
+    return (n + 3) // 4 * 4
+
+
+class Layout:
+    """Offsets (in int32 words) of every array inside the staging block, for given capacities."""
+
+    def __init__(self, tokens: int, requests: int, rows: int, widths: list[int], tile_caps: dict[int, int]):
+        self.tokens, self.requests, self.rows, self.widths, self.tile_caps = tokens, requests, rows, list(widths), dict(tile_caps)
+        self.offsets: dict[str, tuple[int, int]] = {}
+        at = 0
+
+        def put(name: str, size: int) -> None:
+            nonlocal at
+            self.offsets[name] = (at, size)
+            at += _align(max(size, 1))
+
+        for name in ("token_ids", "positions", "req_of_token", "no_store"):
+            put(name, tokens)
+        put("cu_q", requests + 1)
+        put("ctx_lens", requests)
+        put("state_slots", requests)
+        for name in ("logit_rows", "temperature", "seed_lo", "seed_hi", "counter", "row_slot"):
+            put(name, rows)
+        for g, w in enumerate(widths):
+            put(f"slots{g}", tokens)
+            put(f"table{g}", requests * w)
+        for tpt, cap in tile_caps.items():
+            put(f"tile_req{tpt}", cap)
+            put(f"tile_tok0{tpt}", cap)
+        self.total = at
+
+
+class BatchBuilder:
+    def __init__(self, manager: CacheManager, tile_sizes: list[int], device: torch.device, status: torch.Tensor):
+        self.manager, self.tile_sizes, self.device, self.status = manager, list(tile_sizes), device, status
+        self._pinned: torch.Tensor | None = None
+        self._copied: torch.cuda.Event | None = None
+
+    # ---- host memory
+    def _staging(self, words: int) -> np.ndarray:
+        if self._copied is not None:
+            self._copied.synchronize()  # the previous step's copy has left the block
+            self._copied = None
+        if self._pinned is None or self._pinned.numel() < words:
+            self._pinned = torch.empty(max(words, 4096), dtype=torch.int32).pin_memory()
+        return self._pinned.numpy()
+
+    def eager_layout(self, entries: list[StepEntry]) -> Layout:
+        m = self.manager
+        tokens = sum(len(e.tokens) for e in entries)
+        rows = sum(len(e.want) for e in entries)
+        widths = [m.table_width([e.cache for e in entries], g) for g in range(len(m.pools))]
+        caps = {t: sum((len(e.tokens) + t - 1) // t for e in entries) for t in self.tile_sizes}
+        return Layout(tokens, len(entries), rows, widths, caps)
+
+    def decode_layout(self, bucket: int, max_positions: int) -> Layout:
+        """Fixed layout of a decode-only step of ``bucket`` rows with the widest possible block tables."""
+        m = self.manager
+        width = (max_positions + m.page_size - 1) // m.page_size
+        return Layout(bucket, bucket, bucket, [width] * len(m.pools), {t: bucket for t in self.tile_sizes})
+
+    # ---- the build
+    def build(self, entries: list[StepEntry], layout: Layout | None = None,
+              device_block: torch.Tensor | None = None) -> StepContext:
+        """Fill the staging block for ``entries`` and copy it. With ``layout``/``device_block`` (graph replay) the
+        entries must be single tokens and at most ``layout.requests``; the remaining rows are padding."""
+        m = self.manager
+        fixed = layout is not None
+        if not fixed:
+            layout = self.eager_layout(entries)
+        n_real = len(entries)
+        if fixed and (n_real > layout.requests or any(len(e.tokens) != 1 or e.want != [0] for e in entries)):
+            raise ValueError("a fixed layout takes single-token entries that want their logits, up to its size")
+        host = self._staging(layout.total)
+        P = m.page_size
+
+        def seg(name: str) -> np.ndarray:
+            at, size = layout.offsets[name]
+            return host[at:at + size]
+
+        n, T = layout.requests, layout.tokens
+        q_lens = [len(e.tokens) for e in entries] + [1] * (n - n_real)
+        starts = [e.cache.length for e in entries] + [0] * (n - n_real)
+        cu = np.zeros(n + 1, dtype=np.int64)
+        np.cumsum(q_lens, out=cu[1:])
+        if int(cu[-1]) != T:
+            raise ValueError(f"layout holds {T} tokens, the entries bring {int(cu[-1])}")
+
+        ids, pos, req = seg("token_ids"), seg("positions"), seg("req_of_token")
+        ids[:] = 0
+        pos[:] = 0
+        for i, e in enumerate(entries):
+            a, b = int(cu[i]), int(cu[i + 1])
+            ids[a:b] = e.tokens
+            pos[a:b] = np.arange(starts[i], starts[i] + q_lens[i])
+        req[:] = np.repeat(np.arange(n, dtype=np.int32), q_lens)
+        seg("no_store")[:] = -1
+        seg("cu_q")[:] = cu
+        seg("ctx_lens")[:] = [s + q for s, q in zip(starts, q_lens)]
+        seg("state_slots")[:] = [e.cache.state_slot for e in entries] + [m.scratch_slot] * (n - n_real)
+
+        rows, temp, slo, shi, cnt, rslot = (seg(k) for k in ("logit_rows", "temperature", "seed_lo", "seed_hi", "counter", "row_slot"))
+        temp_f = temp.view(np.float32)
+        r = 0
+        for i, e in enumerate(entries):
+            for w in e.want:
+                if not 0 <= w < q_lens[i]:
+                    raise ValueError(f"wanted index {w} is outside the entry's {q_lens[i]} tokens")
+                rows[r] = int(cu[i]) + w
+                temp_f[r] = e.temperature
+                slo[r] = _as_i32(e.seed & 0xFFFFFFFF)
+                shi[r] = _as_i32((e.seed >> 32) & 0xFFFFFFFF)
+                cnt[r] = e.counter
+                rslot[r] = e.cache.state_slot
+                r += 1
+        for i in range(n_real, n):  # padding rows: greedy on their own token
+            rows[r] = int(cu[i])
+            temp_f[r] = 0.0
+            slo[r] = shi[r] = cnt[r] = 0
+            rslot[r] = m.scratch_slot
+            r += 1
+        if r != layout.rows:
+            raise ValueError(f"layout holds {layout.rows} logit rows, the entries want {r}")
+
+        for g in range(len(m.pools)):
+            w = layout.widths[g]
+            slots, table = seg(f"slots{g}"), seg(f"table{g}").reshape(n, w)
+            fill = m.scratch_pages[g] if m.scratch_pages else 0
+            table[:] = fill
+            for i, e in enumerate(entries):
+                t = e.cache.tables[g]
+                if len(t) > w:
+                    raise ValueError(f"a block table of {len(t)} pages does not fit the layout's width {w}")
+                table[i, :len(t)] = t
+                slots[int(cu[i]):int(cu[i + 1])] = m.slots(e.cache, g, starts[i], starts[i] + q_lens[i])
+            for i in range(n_real, n):
+                slots[int(cu[i])] = fill * P
+
+        tiles_n: dict[int, int] = {}
+        for tpt in self.tile_sizes:
+            treq, ttok = seg(f"tile_req{tpt}"), seg(f"tile_tok0{tpt}")
+            k = 0
+            for i, q in enumerate(q_lens):
+                cnt_i = (q + tpt - 1) // tpt
+                treq[k:k + cnt_i] = i
+                ttok[k:k + cnt_i] = np.arange(cnt_i) * tpt
+                k += cnt_i
+            tiles_n[tpt] = k
+
+        if device_block is None:
+            device_block = torch.empty(layout.total, dtype=torch.int32, device=self.device)
+        device_block[:layout.total].copy_(self._pinned[:layout.total], non_blocking=True)
+        self._copied = torch.cuda.Event()
+        self._copied.record()
+        return self.views(layout, device_block, tiles_n, q_lens, [s + q for s, q in zip(starts, q_lens)])
+
+    def views(self, layout: Layout, block: torch.Tensor, tiles_n: dict[int, int], q_lens: list[int],
+              ctx_lens: list[int]) -> StepContext:
+        m = self.manager
+
+        def dev(name: str) -> torch.Tensor:
+            at, size = layout.offsets[name]
+            return block[at:at + size]
+
+        groups = [m.group_view(g, dev(f"table{g}").view(layout.requests, layout.widths[g]), dev(f"slots{g}"))
+                  for g in range(len(m.pools))]
+        ctx = StepContext(
+            n_tokens=layout.tokens, n_requests=layout.requests, token_ids=dev("token_ids"), positions=dev("positions"),
+            req_of_token=dev("req_of_token"), cu_q=dev("cu_q"), ctx_lens=dev("ctx_lens"), state_slots=dev("state_slots"),
+            logit_rows=dev("logit_rows"), no_store_slots=dev("no_store"), groups=groups,
+            tiles={t: (dev(f"tile_req{t}"), dev(f"tile_tok0{t}"), tiles_n[t]) for t in self.tile_sizes},
+            q_lens=q_lens, ctx_lens_host=ctx_lens, status=self.status,
+        )
+        ctx.sampling = {"temperature": dev("temperature").view(torch.float32), "seed_lo": dev("seed_lo"),
+                        "seed_hi": dev("seed_hi"), "counter": dev("counter"), "row_slot": dev("row_slot")}
+        return ctx
+
+
+def _as_i32(u: int) -> int:
+    """Reinterpret an unsigned 32-bit value as the int32 with the same bits."""
+    return u - (1 << 32) if u >= (1 << 31) else u

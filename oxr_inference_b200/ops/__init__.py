@@ -1,0 +1,346 @@
+"""Python entry points of the hand-written sm_100a kernels (``csrc/``), one function per kernel.
+
+Every function launches on torch's current CUDA stream, takes and returns torch tensors (used as storage
+only) and raises :class:`KernelError` when a launcher refuses its arguments. There is no CPU path and no
+fallback: tensors that are not on a CUDA device are an error, and a missing compiler or failed build raises
+``BuildError`` at the first call.
+
+Matrix products: the 32-bit path and the decode-sized bf16 products (at most ``SKINNY_MAX_ROWS`` rows) run on
+this package's own kernels; larger bf16 products go to cuBLAS through ``torch.mm``, as the reference's do
+through ``nn.Linear`` (oxr_runtime/language.py:223-244).
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_size_t, c_void_p
+
+import torch
+
+from oxr_inference_b200.ops import build
+from oxr_inference_b200.ops.build import BuildError  # noqa: F401
+
+SKINNY_MAX_ROWS = 64
+STATUS_NAMES = {
+    1: "token id outside the vocabulary", 2: "cache slot outside the pool", 3: "position outside the rotary table",
+    4: "block table names a page outside the pool", 5: "a bounded wait inside a kernel ran out",
+}
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+
+launch_count = 0
+"""Kernels of this package launched so far in this process (cuBLAS calls are not counted)."""
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise KernelError(f"dtype {t.dtype} is not supported; kernels take float32 and bfloat16") from None
+
+
+def _need(t: torch.Tensor, name: str, dtype: torch.dtype | None = None) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} is on {t.device}; the kernels run on a CUDA device only (there is no CPU path)")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _done(code: int, what: str) -> None:
+    global launch_count
+    if code != 0:
+        if code >= 1000:
+            raise KernelError(f"{what}: CUDA error {code - 1000} at launch")
+        raise KernelError(f"{what}: launcher refused its arguments (code {code})")
+    launch_count += 1
+
+
+_core = None
+
+
+def _lib():
+    global _core
+    if _core is None:
+        lib = build.core_library()
+        p, i, f = c_void_p, c_int, c_float
+        lib.oxr_embedding.argtypes = [p, p, p, i, i, i, i, i, p, p]
+        lib.oxr_add_rms_norm.argtypes = [p, p, p, p, p, p, i, i, f, i, p]
+        lib.oxr_silu_mul.argtypes = [p, p, i, i, i, p]
+        lib.oxr_cast.argtypes = [p, p, c_size_t, i, i, p]
+        lib.oxr_qk_norm_rope_store.argtypes = [p, p, p, p, p, p, p, p, p, p, i, i, i, i, f, i, c_longlong, i, i, i, i, p, p]
+        lib.oxr_gemm_f32_nt.argtypes = [p, p, p, i, i, i, p]
+        lib.oxr_gemm_skinny_bf16.argtypes = [p, p, p, i, i, i, i, p]
+        lib.oxr_sample.argtypes = [p, p, i, i, p, p, p, p, p]
+        lib.oxr_repetition_penalty.argtypes = [p, p, p, p, i, i, p]
+        lib.oxr_mark_seen.argtypes = [p, p, p, i, i, p]
+        for name in ("oxr_embedding", "oxr_add_rms_norm", "oxr_silu_mul", "oxr_cast", "oxr_qk_norm_rope_store",
+                     "oxr_gemm_f32_nt", "oxr_gemm_skinny_bf16", "oxr_sample", "oxr_repetition_penalty", "oxr_mark_seen"):
+            getattr(lib, name).restype = c_int
+        _core = lib
+    return _core
+
+
+_attn: dict[int, ctypes.CDLL] = {}
+
+
+def _attn_lib(head_dim: int):
+    lib = _attn.get(head_dim)
+    if lib is None:
+        lib = build.attention_library(head_dim)
+        p, i, f = c_void_p, c_int, c_float
+        lib.oxr_paged_attention.argtypes = [p, p, p, p, p, p, i, p, p, p, i, i, i, i, i, f, i, i, p, p]
+        lib.oxr_paged_attention.restype = c_int
+        lib.oxr_attn_tile_rows.restype = c_int
+        lib.oxr_attn_head_dim.restype = c_int
+        if lib.oxr_attn_head_dim() != head_dim:
+            raise BuildError(f"attention library for head size {head_dim} reports {lib.oxr_attn_head_dim()}")
+        _attn[head_dim] = lib
+    return lib
+
+
+def warm_up(head_dims: tuple[int, ...] = ()) -> None:
+    """Build and load what a model needs, before the first step."""
+    _lib()
+    for d in head_dims:
+        _attn_lib(d)
+
+
+def new_status(device: torch.device | str = "cuda") -> torch.Tensor:
+    """The device status word: [code, detail, 0, 0]; kernels write the first error they meet."""
+    return torch.zeros(4, dtype=torch.int32, device=device)
+
+
+def check_status(status: torch.Tensor) -> None:
+    """Read the status word (synchronises) and raise if a kernel reported an error; clears it."""
+    code, detail = status[:2].tolist()
+    if code != 0:
+        status.zero_()
+        raise KernelError(f"a kernel reported: {STATUS_NAMES.get(code, code)} (at index {detail})")
+
+
+# --------------------------------------------------------------------------------------------------- ops
+def embedding(ids: torch.Tensor, table: torch.Tensor, out_dtype: torch.dtype, status: torch.Tensor) -> torch.Tensor:
+    """``out[t] = table[ids[t]]`` (oxr_runtime/decode_graph.py:75); an id outside the table sets the status word."""
+    _need(ids, "ids", torch.int32)
+    _need(table, "table")
+    n, (vocab, hidden) = ids.numel(), table.shape
+    out = torch.empty((n, hidden), dtype=out_dtype, device=table.device)
+    code = _lib().oxr_embedding(out.data_ptr(), table.data_ptr(), ids.data_ptr(), n, hidden, vocab, _dtype_code(table),
+                                _DT[out_dtype], status.data_ptr(), _stream())
+    _done(code, "embedding")
+    return out
+
+
+def add_rms_norm(x: torch.Tensor, residual: torch.Tensor | None, weight: torch.Tensor, eps: float, *,
+                 rows: torch.Tensor | None = None, keep_residual: bool = True):
+    """RMSNorm with the residual add fused in (oxr_runtime/language.py:69-72,94-99).
+
+    ``sum = x + residual`` (fp32; just ``x`` when ``residual`` is None), ``out = sum * rsqrt(mean(sum^2) + eps) *
+    weight`` rounded to ``x.dtype``. The fp32 residual stream is updated in place (created when None) and returned
+    unless ``keep_residual`` is False. With ``rows`` (int32 indices) only those rows are normalised, output row i
+    coming from input row ``rows[i]``; the residual is then left untouched.
+    """
+    _need(x, "x")
+    _need(weight, "weight", torch.float32)
+    n, hidden = x.shape
+    if weight.numel() != hidden:
+        raise KernelError(f"norm weight has {weight.numel()} entries for rows of {hidden}")
+    if residual is not None:
+        _need(residual, "residual", torch.float32)
+        if residual.shape != x.shape:
+            raise KernelError(f"residual {tuple(residual.shape)} does not match x {tuple(x.shape)}")
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+        n_out, res_out = rows.numel(), None
+    else:
+        n_out = n
+        res_out = None if not keep_residual else (residual if residual is not None else
+                                                  torch.empty((n, hidden), dtype=torch.float32, device=x.device))
+    out = torch.empty((n_out, hidden), dtype=x.dtype, device=x.device)
+    code = _lib().oxr_add_rms_norm(out.data_ptr(), _ptr(res_out), x.data_ptr(), _ptr(residual), weight.data_ptr(),
+                                   _ptr(rows), n_out, hidden, float(eps), _dtype_code(x), _stream())
+    _done(code, "add_rms_norm")
+    return out, res_out
+
+
+def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
+    """``silu(gate) * up`` for ``gate_up = [gate | up]`` along the last axis (oxr_runtime/language.py:102-104)."""
+    _need(gate_up, "gate_up")
+    n, two_i = gate_up.shape
+    if two_i % 2:
+        raise KernelError("gate_up must have an even number of columns")
+    out = torch.empty((n, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
+    code = _lib().oxr_silu_mul(out.data_ptr(), gate_up.data_ptr(), n, two_i // 2, _dtype_code(gate_up), _stream())
+    _done(code, "silu_mul")
+    return out
+
+
+def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    if x.dtype == dtype:
+        return x
+    _need(x, "x")
+    out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    code = _lib().oxr_cast(out.data_ptr(), x.data_ptr(), x.numel(), _dtype_code(x), _DT[dtype], _stream())
+    _done(code, "cast")
+    return out
+
+
+def qk_norm_rope_store(qkv: torch.Tensor, q_weight: torch.Tensor | None, k_weight: torch.Tensor | None,
+                       cos: torch.Tensor | None, sin: torch.Tensor | None, positions: torch.Tensor,
+                       slots: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, num_heads: int,
+                       num_kv_heads: int, head_dim: int, eps: float, status: torch.Tensor) -> torch.Tensor:
+    """Per-head RMSNorm of q and k, rotary encoding of both, K and V stored at ``slots`` of one layer's pool;
+    returns q ``[n, H, D]`` (oxr_runtime/kernels.py:66-99). A None weight skips that norm, None tables skip the
+    rotation, a negative slot skips that token's store."""
+    _need(qkv, "qkv")
+    _need(positions, "positions", torch.int32)
+    _need(slots, "slots", torch.int32)
+    _need(k_cache, "k_cache", qkv.dtype)
+    _need(v_cache, "v_cache", qkv.dtype)
+    n = qkv.shape[0]
+    width = (num_heads + 2 * num_kv_heads) * head_dim
+    if qkv.shape[1] != width:
+        raise KernelError(f"qkv has {qkv.shape[1]} columns, expected (H + 2 KV) * D = {width}")
+    for w, nm in ((q_weight, "q_weight"), (k_weight, "k_weight")):
+        if w is not None:
+            _need(w, nm, torch.float32)
+            if w.numel() != head_dim:
+                raise KernelError(f"{nm} has {w.numel()} entries for head size {head_dim}")
+    rotate = cos is not None
+    max_positions = 0
+    if rotate:
+        _need(cos, "cos", torch.float32)
+        _need(sin, "sin", torch.float32)
+        if cos.shape[1] != head_dim // 2 or sin.shape != cos.shape:
+            raise KernelError("rotary tables must be [max_positions, head_dim / 2]")
+        max_positions = cos.shape[0]
+    num_slots = k_cache.numel() // (num_kv_heads * head_dim)
+    q = torch.empty((n, num_heads, head_dim), dtype=qkv.dtype, device=qkv.device)
+    code = _lib().oxr_qk_norm_rope_store(
+        q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), qkv.data_ptr(), _ptr(q_weight), _ptr(k_weight), _ptr(cos),
+        _ptr(sin), positions.data_ptr(), slots.data_ptr(), n, num_heads, num_kv_heads, head_dim, float(eps),
+        max_positions, num_slots, int(q_weight is not None), int(k_weight is not None), int(rotate), _dtype_code(qkv),
+        status.data_ptr(), _stream())
+    _done(code, "qk_norm_rope_store")
+    return q
+
+
+def attention_tile_tokens(num_heads: int, num_kv_heads: int, head_dim: int) -> int:
+    """Tokens of one request that one attention tile covers; the host cuts the step's requests into such tiles."""
+    build.check_head_dim(head_dim)
+    rows = 16
+    group = num_heads // num_kv_heads
+    return rows // min(group, rows)
+
+
+def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, *, tile_req: torch.Tensor,
+                    tile_tok0: torch.Tensor, num_tiles: int, cu_q: torch.Tensor, ctx_lens: torch.Tensor,
+                    block_table: torch.Tensor, page_size: int, scale: float, window: int,
+                    status: torch.Tensor) -> torch.Tensor:
+    """Causal grouped-query attention of the step's new tokens over the paged cache
+    (oxr_runtime/attention.py:47-109). ``q`` is ``[tokens, H, D]``; ``k_cache`` / ``v_cache`` are one layer's pool
+    ``[pages, page_size, KV, D]``; ``window`` > 0 limits a query to its last ``window`` keys."""
+    _need(q, "q")
+    _need(k_cache, "k_cache", q.dtype)
+    _need(v_cache, "v_cache", q.dtype)
+    for t, nm in ((tile_req, "tile_req"), (tile_tok0, "tile_tok0"), (cu_q, "cu_q"), (ctx_lens, "ctx_lens"),
+                  (block_table, "block_table")):
+        _need(t, nm, torch.int32)
+    _, num_heads, head_dim = q.shape
+    num_pages, page, num_kv_heads, d2 = k_cache.shape
+    if page != page_size or d2 != head_dim or v_cache.shape != k_cache.shape:
+        raise KernelError(f"cache pool {tuple(k_cache.shape)} does not fit page size {page_size} / head size {head_dim}")
+    lib = _attn_lib(head_dim)
+    out = torch.empty_like(q)
+    code = lib.oxr_paged_attention(
+        out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), tile_req.data_ptr(), tile_tok0.data_ptr(),
+        num_tiles, cu_q.data_ptr(), ctx_lens.data_ptr(), block_table.data_ptr(), block_table.shape[-1], page_size,
+        num_pages, num_heads, num_kv_heads, float(scale), int(window), _dtype_code(q), status.data_ptr(), _stream())
+    _done(code, "paged_attention")
+    return out
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """``x @ weight.T`` for ``weight [out, in]``, no bias (oxr_runtime/language.py:223-231), fp32 accumulation.
+
+    float32 x float32 runs the fp32 CUDA-core kernel (no TF32). bfloat16 x bfloat16 runs the skinny kernel up to
+    ``SKINNY_MAX_ROWS`` rows and cuBLAS beyond. A weight kept in float32 under bfloat16 activations is multiplied
+    in fp32 and the result rounded once.
+    """
+    _need(x, "x")
+    _need(weight, "weight")
+    m, k = x.shape
+    n, k2 = weight.shape
+    if k != k2:
+        raise KernelError(f"linear: x has {k} columns, weight has {k2}")
+    out_dtype = out_dtype or x.dtype
+    lib = _lib()
+    if weight.dtype == torch.float32:
+        x32 = cast(x, torch.float32)
+        out = torch.empty((m, n), dtype=torch.float32, device=x.device)
+        _done(lib.oxr_gemm_f32_nt(out.data_ptr(), x32.data_ptr(), weight.data_ptr(), m, n, k, _stream()), "gemm_f32")
+        return cast(out, out_dtype)
+    if x.dtype != torch.bfloat16:
+        raise KernelError(f"linear: activations {x.dtype} with weight {weight.dtype} is not a supported pair")
+    if m <= SKINNY_MAX_ROWS and k % 8 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0:
+        out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+        _done(lib.oxr_gemm_skinny_bf16(out.data_ptr(), x.data_ptr(), weight.data_ptr(), m, n, k, _DT[out_dtype], _stream()),
+              "gemm_skinny")
+        return out
+    if out_dtype == torch.float32:
+        return torch.mm(x, weight.t(), out_dtype=torch.float32)
+    return torch.mm(x, weight.t())
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor | None = None, seed_lo: torch.Tensor | None = None,
+           seed_hi: torch.Tensor | None = None, counter: torch.Tensor | None = None) -> torch.Tensor:
+    """One token per row of fp32 ``logits``: the first maximum where ``temperature`` <= 0 (or None), else a draw
+    from softmax(logits / temperature) decided by (seed, counter) alone."""
+    _need(logits, "logits", torch.float32)
+    rows, vocab = logits.shape
+    if temperature is not None:
+        _need(temperature, "temperature", torch.float32)
+        for t, nm in ((seed_lo, "seed_lo"), (seed_hi, "seed_hi"), (counter, "counter")):
+            if t is None:
+                raise KernelError(f"sample: {nm} is required with a temperature")
+            _need(t, nm, torch.int32)
+    out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    code = _lib().oxr_sample(out.data_ptr(), logits.data_ptr(), rows, vocab, _ptr(temperature), _ptr(seed_lo),
+                             _ptr(seed_hi), _ptr(counter), _stream())
+    _done(code, "sample")
+    return out
+
+
+def repetition_penalty(logits: torch.Tensor, seen: torch.Tensor, row_slot: torch.Tensor, penalty: torch.Tensor) -> None:
+    """In place: for tokens marked in ``seen[row_slot[r]]`` a positive logit is divided by ``penalty[r]``, any other
+    multiplied (oxr_runtime/engine.py:632-639)."""
+    _need(logits, "logits", torch.float32)
+    _need(seen, "seen", torch.uint8)
+    _need(row_slot, "row_slot", torch.int32)
+    _need(penalty, "penalty", torch.float32)
+    rows, vocab = logits.shape
+    code = _lib().oxr_repetition_penalty(logits.data_ptr(), seen.data_ptr(), row_slot.data_ptr(), penalty.data_ptr(), rows,
+                                         vocab, _stream())
+    _done(code, "repetition_penalty")
+
+
+def mark_seen(seen: torch.Tensor, slots: torch.Tensor, tokens: torch.Tensor) -> None:
+    """``seen[slots[i], tokens[i]] = 1``."""
+    _need(seen, "seen", torch.uint8)
+    _need(slots, "slots", torch.int32)
+    _need(tokens, "tokens", torch.int32)
+    code = _lib().oxr_mark_seen(seen.data_ptr(), slots.data_ptr(), tokens.data_ptr(), tokens.numel(), seen.shape[1], _stream())
+    _done(code, "mark_seen")

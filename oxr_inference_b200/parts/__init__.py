@@ -1,0 +1,14 @@
+"""Parts a decoder is assembled from; importing the package registers the built-in ones."""
+
+from oxr_inference_b200.parts import attention, block, mlp, norm, rope  # noqa: F401  (register themselves)
+from oxr_inference_b200.parts.base import (ARRANGEMENTS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, FeedForward,
+                                           GroupView, LayerCache, Mixer, Norm, PagedKVNeed, ParamInfo, Part,
+                                           PositionEncoding, Runtime, StateNeed, StepContext)
+from oxr_inference_b200.parts.decoder import DecoderModel
+from oxr_inference_b200.parts.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+
+__all__ = [
+    "ARRANGEMENTS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITION_ENCODINGS", "DecoderModel", "FeedForward", "GroupView",
+    "LayerCache", "LayerSpec", "Mixer", "ModelSpec", "Norm", "PagedKVNeed", "ParamInfo", "Part", "PartSpec",
+    "PositionEncoding", "Runtime", "ScheduleEntry", "StateNeed", "StepContext",
+]

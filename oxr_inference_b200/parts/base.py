@@ -1,0 +1,185 @@
+"""Interfaces of the parts a decoder is assembled from, their registries, and what a step hands to them.
+
+Families and what each must provide:
+
+* **Norm** – ``forward(x, residual) -> (normed, residual)``; the add of the not-yet-added block output into the
+  fp32 residual stream is part of the norm (oxr_runtime/language.py:94-99).
+* **PositionEncoding** – ``tables()``: whatever its mixers consume (rotary: fp32 cos and sin by position).
+* **Mixer** – ``forward(h, ctx, cache) -> y`` over the step's packed tokens; ``cache_need()`` says what it keeps
+  between steps: paged keys/values (:class:`PagedKVNeed`), fixed-size per-request state (:class:`StateNeed`),
+  or nothing. ``tile_tokens()`` (optional) asks the batch builder for a tile list.
+* **FeedForward** – ``forward(h) -> y``.
+* **Block arrangement** – puts a mixer and a feed-forward behind their norms.
+
+Every part lists its tensors with :meth:`Part.parameters` (local names; the spec's prefix makes them checkpoint
+names) and receives them one by one through :meth:`Part.assign`. No part knows which model it is in.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Callable
+
+import torch
+
+from oxr_inference_b200.cache.needs import PagedKVNeed, StateNeed  # noqa: F401  (part of this interface)
+
+
+# ------------------------------------------------------------------------------------------- parameters
+@dataclass(frozen=True)
+class ParamInfo:
+    shape: tuple[int, ...]
+    init: str = "normal"
+    """Random-weights mode: ``normal`` = N(0, std); ``around_one`` = 1 + N(0, norm_std)."""
+    role: str = "matrix"
+    """``matrix``: multiplied on the tensor cores, kept in the compute dtype (a tensor stored in 32-bit stays
+    32-bit); ``vector``: small, used in fp32 math, always kept in fp32."""
+
+
+@dataclass
+class Runtime:
+    """Where and how the parts run."""
+
+    device: torch.device
+    dtype: torch.dtype
+    """Activation dtype: torch.bfloat16 (serving) or torch.float32 (everything in true 32-bit)."""
+    max_positions: int
+    status: torch.Tensor
+    """Device status word that kernels write their first error to (see ``ops.check_status``)."""
+
+    def store_dtype(self, info: ParamInfo, stored: torch.dtype) -> torch.dtype:
+        if info.role == "vector" or self.dtype == torch.float32:
+            return torch.float32
+        if stored == torch.float32:
+            return torch.float32  # stored in 32-bit: stays so
+        return torch.bfloat16
+
+
+class Part:
+    """Base of all parts: a bag of named tensors."""
+
+    def parameters(self) -> dict[str, ParamInfo]:
+        return {}
+
+    def assign(self, name: str, tensor: torch.Tensor) -> None:
+        """Take the tensor stored under local name ``name`` (host or device, dtype as stored)."""
+        raise KeyError(name)
+
+    def finish_loading(self) -> None:
+        """Called once after all tensors were assigned."""
+
+
+# ------------------------------------------------------------------------------------------- step context
+@dataclass
+class GroupView:
+    """What one cache group looks like to a mixer during one step."""
+
+    page_size: int
+    k_pool: torch.Tensor | None
+    """[layers of the group, pages, page_size, KV, D]"""
+    v_pool: torch.Tensor | None
+    block_table: torch.Tensor
+    """int32 [requests, width]"""
+    slots: torch.Tensor
+    """int32 [tokens]: where each new token's K and V go (page * page_size + offset)."""
+
+
+@dataclass
+class LayerCache:
+    """The cache of one schedule entry for this step."""
+
+    group: GroupView | None = None
+    layer_in_group: int = 0
+    store: bool = True
+    """False when this run reads a cache that another run fills."""
+    state: torch.Tensor | None = None
+    """[slots, *shape] for a mixer with :class:`StateNeed`; index with ``ctx.state_slots``."""
+
+
+@dataclass
+class StepContext:
+    """One step's batch on the device: the new tokens of all requests packed along one axis."""
+
+    n_tokens: int
+    n_requests: int
+    token_ids: torch.Tensor      # int32 [tokens]
+    positions: torch.Tensor      # int32 [tokens] absolute position of each token in its request
+    req_of_token: torch.Tensor   # int32 [tokens]
+    cu_q: torch.Tensor           # int32 [requests + 1]
+    ctx_lens: torch.Tensor       # int32 [requests] tokens in the cache after this step
+    state_slots: torch.Tensor    # int32 [requests]
+    logit_rows: torch.Tensor     # int32 [wanted] indices into the token axis
+    no_store_slots: torch.Tensor  # int32 [tokens], all -1
+    groups: list[GroupView]
+    tiles: dict[int, tuple[torch.Tensor, torch.Tensor, int]] = field(default_factory=dict)
+    """tokens-per-tile -> (tile_req, tile_tok0, number of tiles)"""
+    q_lens: list[int] = field(default_factory=list)       # host copies, for parts that plan on the host
+    ctx_lens_host: list[int] = field(default_factory=list)
+    status: torch.Tensor | None = None
+    sampling: dict[str, torch.Tensor] = field(default_factory=dict)
+    """Per logit row: temperature (fp32), seed_lo, seed_hi, counter, row_slot (the row's state slot)."""
+
+
+# ------------------------------------------------------------------------------------------- families
+class Norm(Part):
+    def forward(self, x: torch.Tensor, residual: torch.Tensor | None):
+        raise NotImplementedError
+
+    def forward_rows(self, x: torch.Tensor, residual: torch.Tensor | None, rows: torch.Tensor) -> torch.Tensor:
+        """Normalise only the given rows of ``x + residual`` (the rows whose logits are wanted)."""
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def tables(self) -> Any:
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    def cache_need(self) -> PagedKVNeed | StateNeed | None:
+        return None
+
+    def tile_tokens(self) -> int | None:
+        return None
+
+    def forward(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+
+# ------------------------------------------------------------------------------------------- registries
+class Registry:
+    def __init__(self, family: str):
+        self.family = family
+        self._items: dict[str, Callable[..., Any]] = {}
+
+    def register(self, kind: str, factory: Callable[..., Any] | None = None, *, replace: bool = False):
+        def put(f):
+            if kind in self._items and not replace:
+                raise ValueError(f"{self.family} {kind!r} is already registered")
+            self._items[kind] = f
+            return f
+
+        return put if factory is None else put(factory)
+
+    def build(self, kind: str, *args, **kwargs):
+        if kind not in self._items:
+            raise KeyError(f"no {self.family} named {kind!r}; registered: {sorted(self._items)}")
+        return self._items[kind](*args, **kwargs)
+
+    def __contains__(self, kind: str) -> bool:
+        return kind in self._items
+
+    def kinds(self) -> list[str]:
+        return sorted(self._items)
+
+
+NORMS = Registry("norm")
+POSITION_ENCODINGS = Registry("position encoding")
+MIXERS = Registry("mixer")
+FEED_FORWARDS = Registry("feed-forward")
+ARRANGEMENTS = Registry("block arrangement")

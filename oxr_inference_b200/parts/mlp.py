@@ -1,0 +1,34 @@
+"""Dense SiLU-gated feed-forward."""
+
+from __future__ import annotations
+
+import torch
+
+from oxr_inference_b200 import ops
+from oxr_inference_b200.parts.base import FEED_FORWARDS, FeedForward, ParamInfo, Runtime
+from oxr_inference_b200.parts.linear import StackedLinear
+
+
+@FEED_FORWARDS.register("swiglu")
+class SwiGLU(FeedForward):
+    """``down( silu(h W_gate^T) * (h W_up^T) )`` with gate and up as one product (oxr_runtime/language.py:266-269,
+    102-104). No biases (language.py:229-231)."""
+
+    def __init__(self, runtime: Runtime, *, hidden_size: int, intermediate_size: int):
+        self.hidden, self.inter = int(hidden_size), int(intermediate_size)
+        self.gate_up = StackedLinear(runtime, self.hidden, {"gate_proj.weight": self.inter, "up_proj.weight": self.inter})
+        self.down = StackedLinear(runtime, self.inter, {"down_proj.weight": self.hidden})
+
+    def parameters(self) -> dict[str, ParamInfo]:
+        return {**self.gate_up.parameters(), **self.down.parameters()}
+
+    def assign(self, name: str, tensor: torch.Tensor) -> None:
+        if name in self.gate_up.outs:
+            self.gate_up.assign(name, tensor)
+        elif name in self.down.outs:
+            self.down.assign(name, tensor)
+        else:
+            raise KeyError(name)
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        return self.down(ops.silu_mul(self.gate_up(h)))
