@@ -4,7 +4,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
-from oxr_inference_b200.cache.needs import PagedKVNeed, StateNeed
+from oxr_inference_b200.parts.base import PagedKVNeed, StateNeed
 
 
 @dataclass(frozen=True)

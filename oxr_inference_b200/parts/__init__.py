@@ -4,8 +4,18 @@ from oxr_inference_b200.parts import attention, block, mlp, norm, rope  # noqa: 
 from oxr_inference_b200.parts.base import (ARRANGEMENTS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, FeedForward,
                                            GroupView, LayerCache, Mixer, Norm, PagedKVNeed, ParamInfo, Part,
                                            PositionEncoding, Runtime, StateNeed, StepContext)
-from oxr_inference_b200.parts.decoder import DecoderModel
 from oxr_inference_b200.parts.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+
+
+
+def __getattr__(name: str):
+    # The decoder needs the cache's plan, and the cache needs this package's interfaces: import it on demand.
+    if name == "DecoderModel":
+        from oxr_inference_b200.parts.decoder import DecoderModel
+
+        return DecoderModel
+    raise AttributeError(name)
+
 
 __all__ = [
     "ARRANGEMENTS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITION_ENCODINGS", "DecoderModel", "FeedForward", "GroupView",

@@ -22,8 +22,6 @@ from typing import Any, Callable
 
 import torch
 
-from oxr_inference_b200.cache.needs import PagedKVNeed, StateNeed  # noqa: F401  (part of this interface)
-
 
 # ------------------------------------------------------------------------------------------- parameters
 @dataclass(frozen=True)
@@ -67,6 +65,25 @@ class Part:
 
     def finish_loading(self) -> None:
         """Called once after all tensors were assigned."""
+
+
+# ------------------------------------------------------------------------------------------- cache needs
+@dataclass(frozen=True)
+class PagedKVNeed:
+    """Keys and values of every token (or of the last ``window`` tokens) in pages."""
+
+    num_kv_heads: int
+    head_dim: int
+    window: int = 0
+    """0: all keys are kept; > 0: a query sees its last ``window`` keys, pages wholly behind that are released."""
+
+
+@dataclass(frozen=True)
+class StateNeed:
+    """A fixed-size tensor per request (shape without the request axis), zeroed when a request starts."""
+
+    shape: tuple[int, ...]
+    dtype: torch.dtype = torch.float32
 
 
 # ------------------------------------------------------------------------------------------- step context

@@ -1,0 +1,3 @@
+from oxr_inference_b200.sampling.params import Completion, SamplingParams
+
+__all__ = ["Completion", "SamplingParams"]

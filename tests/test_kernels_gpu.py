@@ -1,0 +1,359 @@
+"""Each CUDA kernel alone against its plain PyTorch statement (tests/plain/kernels_plain.py), at sizes other than
+the engine's: odd widths, head sizes in steps of 16, group sizes that do not divide the tile, several page sizes."""
+
+import math
+
+import pytest
+import torch
+
+from plain import kernels_plain as KP
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from oxr_inference_b200 import ops as _ops
+
+    torch.backends.cuda.matmul.allow_tf32 = False
+    return _ops
+
+
+def _tol(dtype):
+    return dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hidden", [64, 100, 4096])
+def test_embedding(ops, dtype, hidden):
+    g = torch.Generator(device=DEV).manual_seed(0)
+    table = torch.randn(301, hidden, device=DEV, generator=g).to(dtype)
+    ids = torch.tensor([0, 300, 5, 5, 17], dtype=torch.int32, device=DEV)
+    status = ops.new_status(DEV)
+    out = ops.embedding(ids, table, dtype, status)
+    assert torch.equal(out, table[ids.long()])
+    ops.check_status(status)
+    bad = torch.tensor([3, 301], dtype=torch.int32, device=DEV)
+    out = ops.embedding(bad, table, dtype, status)
+    assert torch.equal(out[0], table[3]) and not out[1].any()
+    with pytest.raises(ops.KernelError, match="vocabulary"):
+        ops.check_status(status)
+
+
+def test_embedding_widens_and_narrows(ops):
+    table = torch.randn(50, 72, device=DEV)
+    ids = torch.arange(50, dtype=torch.int32, device=DEV)
+    status = ops.new_status(DEV)
+    assert torch.equal(ops.embedding(ids, table, torch.bfloat16, status), table.bfloat16())
+    assert torch.equal(ops.embedding(ids, table.bfloat16(), torch.float32, status), table.bfloat16().float())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hidden", [96, 2560, 10300])
+def test_add_rms_norm(ops, dtype, hidden):
+    g = torch.Generator(device=DEV).manual_seed(1)
+    n = 37
+    x = torch.randn(n, hidden, device=DEV, generator=g).to(dtype)
+    res = torch.randn(n, hidden, device=DEV, generator=g) * 3
+    w = 1 + 0.1 * torch.randn(hidden, device=DEV, generator=g)
+    eps = 1e-5
+    # first layer: no residual yet
+    out, r0 = ops.add_rms_norm(x, None, w, eps)
+    want, want_r = KP.add_rms_norm(x, None, w, eps)
+    torch.testing.assert_close(out.float(), want, **_tol(dtype))
+    assert torch.equal(r0, want_r)
+    # later layers: residual updated in place
+    res_in = res.clone()
+    out, r1 = ops.add_rms_norm(x, res_in, w, eps)
+    want, want_r = KP.add_rms_norm(x, res, w, eps)
+    assert r1.data_ptr() == res_in.data_ptr()
+    torch.testing.assert_close(r1, want_r, atol=0, rtol=0)
+    torch.testing.assert_close(out.float(), want, **_tol(dtype))
+    # chosen rows only, residual untouched
+    rows = torch.tensor([36, 0, 5], dtype=torch.int32, device=DEV)
+    before = res.clone()
+    out, none = ops.add_rms_norm(x, res, w, eps, rows=rows)
+    assert none is None and torch.equal(res, before)
+    torch.testing.assert_close(out.float(), want[rows.long()], **_tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("inter", [160, 77, 12288])
+def test_silu_mul(ops, dtype, inter):
+    g = torch.Generator(device=DEV).manual_seed(2)
+    gu = (torch.randn(9, 2 * inter, device=DEV, generator=g) * 3).to(dtype)
+    torch.testing.assert_close(ops.silu_mul(gu).float(), KP.silu_mul(gu), **_tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,KV,D", [(4, 2, 16), (6, 2, 32), (5, 5, 48), (32, 8, 128), (3, 1, 256)])
+def test_qk_norm_rope_store(ops, dtype, H, KV, D):
+    g = torch.Generator(device=DEV).manual_seed(3)
+    n, pages, P, maxpos, eps = 23, 7, 8, 300, 1e-5
+    qkv = torch.randn(n, (H + 2 * KV) * D, device=DEV, generator=g).to(dtype)
+    qw = 1 + 0.2 * torch.randn(D, device=DEV, generator=g)
+    kw = 1 + 0.2 * torch.randn(D, device=DEV, generator=g)
+    inv = 1.0 / (1e4 ** (torch.arange(0, D, 2, dtype=torch.float) / D))
+    fr = torch.outer(torch.arange(maxpos, dtype=torch.float), inv)
+    cos, sin = fr.cos().to(DEV), fr.sin().to(DEV)
+    positions = torch.randint(0, maxpos, (n,), device=DEV, generator=g, dtype=torch.int32)
+    slots = torch.randperm(pages * P, device=DEV, generator=g)[:n].int()
+    slots[4] = -1  # not stored
+    k_cache = torch.full((pages, P, KV, D), 9.0, device=DEV, dtype=dtype)
+    v_cache = torch.full((pages, P, KV, D), 9.0, device=DEV, dtype=dtype)
+    status = ops.new_status(DEV)
+    q = ops.qk_norm_rope_store(qkv, qw, kw, cos, sin, positions, slots, k_cache, v_cache, H, KV, D, eps, status)
+    ops.check_status(status)
+    wq, wk, wv = KP.qk_norm_rope(qkv, qw, kw, cos, sin, positions, H, KV, D, eps)
+    torch.testing.assert_close(q.float(), wq, **_tol(dtype))
+    kc, vc = k_cache.view(-1, KV, D).float(), v_cache.view(-1, KV, D).float()
+    stored = slots >= 0
+    torch.testing.assert_close(kc[slots[stored].long()], wk[stored], **_tol(dtype))
+    assert torch.equal(vc[slots[stored].long()], wv[stored])
+    untouched = torch.ones(pages * P, dtype=torch.bool, device=DEV)
+    untouched[slots[stored].long()] = False
+    assert (kc[untouched] == 9.0).all() and (vc[untouched] == 9.0).all(), "a slot outside the step's was written"
+    # a slot beyond the pool is reported, not written
+    slots2 = slots.clone()
+    slots2[0] = pages * P
+    ops.qk_norm_rope_store(qkv, qw, kw, cos, sin, positions, slots2, k_cache, v_cache, H, KV, D, eps, status)
+    with pytest.raises(ops.KernelError, match="slot"):
+        ops.check_status(status)
+
+
+def test_qk_norm_rope_parts_can_be_switched_off(ops):
+    g = torch.Generator(device=DEV).manual_seed(4)
+    H, KV, D, n = 2, 1, 32, 5
+    qkv = torch.randn(n, (H + 2 * KV) * D, device=DEV, generator=g)
+    k_cache = torch.zeros(2, 4, KV, D, device=DEV)
+    v_cache = torch.zeros(2, 4, KV, D, device=DEV)
+    pos = torch.arange(n, dtype=torch.int32, device=DEV)
+    slots = torch.arange(n, dtype=torch.int32, device=DEV)
+    status = ops.new_status(DEV)
+    q = ops.qk_norm_rope_store(qkv, None, None, None, None, pos, slots, k_cache, v_cache, H, KV, D, 1e-6, status)
+    assert torch.equal(q.view(n, -1), qkv[:, :H * D])
+    assert torch.equal(k_cache.view(-1, D)[:n], qkv[:, H * D:(H + KV) * D])
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 64, 64), (7, 509, 96), (16, 160, 96), (17, 192, 160), (150, 333, 77), (64, 4096, 1030)])
+def test_gemm_f32(ops, M, N, K):
+    g = torch.Generator(device=DEV).manual_seed(5)
+    x = torch.randn(M, K, device=DEV, generator=g)
+    w = torch.randn(N, K, device=DEV, generator=g)
+    got = ops.linear(x, w)
+    want = (x.double() @ w.double().T).float()
+    torch.testing.assert_close(got, want, atol=1e-4 * math.sqrt(K), rtol=1e-5)
+    # a row's result does not depend on how many rows there are: bit-identical alone and in the batch
+    for r in (0, M - 1):
+        assert torch.equal(ops.linear(x[r:r + 1].contiguous(), w)[0], got[r])
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 33, 64])
+@pytest.mark.parametrize("N,K", [(509, 96), (192, 160), (4096, 4096), (1000, 12288)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_skinny_bf16(ops, M, N, K, out_dtype):
+    g = torch.Generator(device=DEV).manual_seed(6)
+    x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=DEV, generator=g) * 0.05).bfloat16()
+    got = ops.linear(x, w, out_dtype)
+    assert got.dtype == out_dtype
+    want = x.float() @ w.float().T
+    if out_dtype == torch.float32:
+        torch.testing.assert_close(got, want, atol=2e-4 * math.sqrt(K) * 0.05, rtol=1e-4)
+    else:
+        torch.testing.assert_close(got.float(), want, atol=1e-2, rtol=1e-2)
+
+
+def test_linear_large_bf16_uses_library_product_and_fp32_output(ops):
+    g = torch.Generator(device=DEV).manual_seed(7)
+    x = torch.randn(200, 256, device=DEV, generator=g).bfloat16()
+    w = (torch.randn(300, 256, device=DEV, generator=g) * 0.05).bfloat16()
+    want = x.float() @ w.float().T
+    torch.testing.assert_close(ops.linear(x, w, torch.float32), want, atol=1e-3, rtol=1e-3)
+    torch.testing.assert_close(ops.linear(x, w).float(), want, atol=2e-2, rtol=2e-2)
+
+
+def test_linear_keeps_a_32bit_weight_32bit(ops):
+    g = torch.Generator(device=DEV).manual_seed(8)
+    x = torch.randn(5, 96, device=DEV, generator=g).bfloat16()
+    w = torch.randn(40, 96, device=DEV, generator=g)
+    got = ops.linear(x, w)
+    assert got.dtype == torch.bfloat16
+    torch.testing.assert_close(got.float(), (x.float() @ w.T), atol=1e-1, rtol=1e-2)
+
+
+# ------------------------------------------------------------------------------------------------ attention
+def _paged_case(g, q_lens, ctx_lens, H, KV, D, P, dtype, extra_pages=3):
+    """Random q, a cache whose pages are handed out in shuffled order, block tables, tile lists."""
+    n = len(q_lens)
+    need = [-(-c // P) for c in ctx_lens]
+    total = sum(need) + extra_pages
+    order = torch.randperm(total, generator=torch.Generator().manual_seed(11)).tolist()
+    width = max(need) + 1
+    table = torch.full((n, width), -7, dtype=torch.int32)  # unused entries hold rubbish on purpose
+    at = 0
+    for r in range(n):
+        table[r, :need[r]] = torch.tensor(order[at:at + need[r]], dtype=torch.int32)
+        at += need[r]
+    k_cache = torch.randn(total, P, KV, D, device=DEV, generator=g).to(dtype)
+    v_cache = torch.randn(total, P, KV, D, device=DEV, generator=g).to(dtype)
+    T = sum(q_lens)
+    q = torch.randn(T, H, D, device=DEV, generator=g).to(dtype)
+    cu = [0]
+    for x in q_lens:
+        cu.append(cu[-1] + x)
+    return q, k_cache, v_cache, table.to(DEV), cu
+
+
+def _tiles(ops, q_lens, H, KV, D):
+    tpt = ops.attention_tile_tokens(H, KV, D)
+    req, tok = [], []
+    for r, ql in enumerate(q_lens):
+        for t0 in range(0, ql, tpt):
+            req.append(r)
+            tok.append(t0)
+    return (torch.tensor(req, dtype=torch.int32, device=DEV), torch.tensor(tok, dtype=torch.int32, device=DEV), len(req))
+
+
+def _run_attn(ops, q, k_cache, v_cache, table, cu, q_lens, ctx_lens, scale, window):
+    H, D, KV, P = q.shape[1], q.shape[2], k_cache.shape[2], k_cache.shape[1]
+    treq, ttok, nt = _tiles(ops, q_lens, H, KV, D)
+    status = ops.new_status(DEV)
+    out = ops.paged_attention(q, k_cache, v_cache, tile_req=treq, tile_tok0=ttok, num_tiles=nt,
+                              cu_q=torch.tensor(cu, dtype=torch.int32, device=DEV),
+                              ctx_lens=torch.tensor(ctx_lens, dtype=torch.int32, device=DEV), block_table=table,
+                              page_size=P, scale=scale, window=window, status=status)
+    ops.check_status(status)
+    return out
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,KV,D,P", [(4, 2, 16, 16), (6, 2, 32, 8), (8, 1, 64, 16), (5, 5, 48, 4), (20, 1, 16, 16),
+                                      (32, 8, 128, 16), (2, 2, 256, 64), (3, 1, 80, 16)])
+@pytest.mark.parametrize("window", [0, 13])
+def test_paged_attention_mixed_batch(ops, dtype, H, KV, D, P, window):
+    g = torch.Generator(device=DEV).manual_seed(20 + D)
+    q_lens = [1, 37, 2, 1, 70]      # decode tokens beside prompt portions
+    ctx_lens = [1, 37, 130, 200, 75]  # position 0 alone; a whole prompt; portions deep into a context
+    q, k_cache, v_cache, table, cu = _paged_case(g, q_lens, ctx_lens, H, KV, D, P, dtype)
+    scale = D ** -0.5
+    got = _run_attn(ops, q, k_cache, v_cache, table, cu, q_lens, ctx_lens, scale, window)
+    want = KP.paged_attention(q, k_cache, v_cache, cu, ctx_lens, table, scale, window)
+    tol = dict(atol=2e-5, rtol=2e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(got.float(), want, **tol)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_finds_one_far_key_and_respects_the_window_edge(ops, dtype):
+    """One key among hundreds is made to match the query so strongly that it takes all the weight: if the kernel
+    skipped it (a page's edge, the first or last key, the key just inside the window) the output would be far off.
+    The key just outside the window is made as strong and must be ignored."""
+    H, KV, D, P = 4, 2, 32, 8
+    ctx = 389
+    g = torch.Generator(device=DEV).manual_seed(30)
+    for far in (0, 7, 8, 255, 256, 388 - 20, 388):
+        for window in (0, 21):
+            q, k_cache, v_cache, table, cu = _paged_case(g, [1], [ctx], H, KV, D, P, dtype)
+            k_cache.mul_(0.05)
+            qpos = ctx - 1
+            target = far if window == 0 else max(far, qpos - window + 1)   # a key inside the window
+            pages = table[0].tolist()
+
+            def key(pos):
+                return k_cache[pages[pos // P], pos % P]
+            for kvh in range(KV):
+                key(target)[kvh] = q[0, kvh * (H // KV)].float().mul(3.0).to(dtype)
+                if window and qpos - window >= 0:
+                    key(qpos - window)[kvh] = q[0, kvh * (H // KV)].float().mul(6.0).to(dtype)   # just outside
+            got = _run_attn(ops, q, k_cache, v_cache, table, cu, [1], [ctx], 1.0, window)
+            want = KP.paged_attention(q, k_cache, v_cache, cu, [ctx], table, 1.0, window)
+            tol = dict(atol=1e-4, rtol=1e-4) if dtype == torch.float32 else dict(atol=3e-2, rtol=3e-2)
+            torch.testing.assert_close(got.float(), want, **tol)
+            # the first head of each group must have picked exactly the target's value
+            v_t = v_cache[pages[target // P], target % P].float()
+            for kvh in range(KV):
+                torch.testing.assert_close(got[0, kvh * (H // KV)].float(), v_t[kvh], atol=5e-2, rtol=5e-2)
+
+
+def test_attention_fp32_is_bit_identical_however_the_queries_are_cut(ops):
+    H, KV, D, P = 6, 2, 32, 8
+    g = torch.Generator(device=DEV).manual_seed(31)
+    ctx = 150
+    q, k_cache, v_cache, table, cu = _paged_case(g, [ctx], [ctx], H, KV, D, P, torch.float32)
+    whole = _run_attn(ops, q, k_cache, v_cache, table, cu, [ctx], [ctx], D ** -0.5, 0)
+    pos = 0
+    for c in (7, 2, 13, 1, 50, 3, 74):
+        part = _run_attn(ops, q[pos:pos + c].contiguous(), k_cache, v_cache, table, [0, c], [c], [pos + c], D ** -0.5, 0)
+        assert torch.equal(part, whole[pos:pos + c]), f"portion at {pos} of {c} differs from the whole run"
+        pos += c
+
+
+def test_attention_reports_a_page_outside_the_pool(ops):
+    H, KV, D, P = 2, 1, 16, 8
+    g = torch.Generator(device=DEV).manual_seed(32)
+    q, k_cache, v_cache, table, cu = _paged_case(g, [1], [20], H, KV, D, P, torch.float32)
+    table[0, 1] = k_cache.shape[0] + 5
+    with pytest.raises(ops.KernelError, match="page"):
+        _run_attn(ops, q, k_cache, v_cache, table, cu, [1], [20], 1.0, 0)
+
+
+def test_attention_refuses_a_head_size_it_cannot_do(ops):
+    with pytest.raises(ValueError, match="multiples of 16"):
+        ops.attention_tile_tokens(4, 2, 24)
+
+
+# ------------------------------------------------------------------------------------------------ sampling
+def test_greedy_takes_the_first_maximum(ops):
+    logits = torch.randn(6, 1000, device=DEV)
+    logits[0, 500] = logits[0, 700] = 50.0
+    logits[1, 999] = 60.0
+    logits[2, 0] = 60.0
+    logits[3] = 1.0
+    got = ops.sample(logits).tolist()
+    assert got[0] == 500 and got[1] == 999 and got[2] == 0 and got[3] == 0
+    assert got[4:] == logits[4:].argmax(-1).tolist()
+
+
+@pytest.mark.parametrize("vocab", [509, 151936])
+def test_temperature_sampling_follows_the_cdf_and_its_seed(ops, vocab):
+    g = torch.Generator(device=DEV).manual_seed(40)
+    rows = 16
+    logits = torch.randn(rows, vocab, device=DEV, generator=g) * 2
+    temp = torch.full((rows,), 0.7, device=DEV)
+    temp[3] = 0.0  # greedy among the sampled
+    seeds = [123456789012345 + 17 * r for r in range(rows)]
+    lo = torch.tensor([(s & 0xFFFFFFFF) - (1 << 32) if (s & 0xFFFFFFFF) >= (1 << 31) else (s & 0xFFFFFFFF) for s in seeds], dtype=torch.int32, device=DEV)
+    hi = torch.tensor([s >> 32 for s in seeds], dtype=torch.int32, device=DEV)
+    counter = torch.arange(rows, dtype=torch.int32, device=DEV)
+    got = ops.sample(logits, temp, lo, hi, counter).tolist()
+    assert got[3] == int(logits[3].argmax())
+    for r in range(rows):
+        if r == 3:
+            continue
+        cdf, target = KP.sample_interval(logits[r].cpu(), 0.7, seeds[r], r)
+        i = got[r]
+        below = float(cdf[i - 1]) if i > 0 else 0.0
+        slack = 1e-5 * float(cdf[-1])
+        assert below - slack <= target <= float(cdf[i]) + slack, f"row {r}: index {i} does not hold the target"
+    # the same row gives the same token whatever else is in the batch and wherever it sits
+    alone = ops.sample(logits[5:6].contiguous(), temp[5:6].contiguous(), lo[5:6].contiguous(), hi[5:6].contiguous(),
+                       counter[5:6].contiguous()).tolist()
+    assert alone == [got[5]]
+    # different counters give different draws somewhere
+    again = ops.sample(logits, temp, lo, hi, counter + 100).tolist()
+    assert again != got
+
+
+def test_repetition_penalty(ops):
+    logits = torch.tensor([[2.0, -2.0, 3.0, -1.0], [2.0, -2.0, 3.0, -1.0]], device=DEV)
+    seen = torch.zeros(3, 4, dtype=torch.uint8, device=DEV)
+    ops.mark_seen(seen, torch.tensor([2, 2, 0], dtype=torch.int32, device=DEV), torch.tensor([0, 1, 3], dtype=torch.int32, device=DEV))
+    assert seen.tolist() == [[0, 0, 0, 1], [0, 0, 0, 0], [1, 1, 0, 0]]
+    ops.repetition_penalty(logits, seen, torch.tensor([2, 0], dtype=torch.int32, device=DEV), torch.tensor([2.0, 1.0], device=DEV))
+    assert logits.tolist() == [[1.0, -4.0, 3.0, -1.0], [2.0, -2.0, 3.0, -1.0]]
+
+
+def test_no_cpu_path(ops):
+    with pytest.raises(ops.KernelError, match="CUDA device only"):
+        ops.silu_mul(torch.zeros(2, 4))

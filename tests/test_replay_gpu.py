@@ -1,0 +1,133 @@
+"""Trace replay on the GPU against the plain implementation: every way of cutting the same requests.
+
+Each (configuration, dtype) pair gets one ``bin/trace_run`` process; the tests feed it steps and compare the
+logits files with whole-sequence logits of ``tests/plain/qwen3_plain.py``.
+"""
+
+import pytest
+
+import util
+from util import Replay, compare, make_folder, plain_logits, token_ids
+
+pytestmark = pytest.mark.gpu
+
+CASES = [("A", "float32"), ("A", "bfloat16"), ("B", "float32"), ("B", "bfloat16")]
+LENGTHS = {"A": [5, 17, 33, 100], "B": [1, 12, 40, 64, 131]}
+
+
+@pytest.fixture(scope="module", params=CASES, ids=lambda c: f"{c[0]}-{c[1]}")
+def replay(request, tmp_path_factory):
+    name, dtype = request.param
+    tmp = tmp_path_factory.mktemp(f"replay_{name}_{dtype}")
+    folder = make_folder(tmp, name, seed=3)
+    # 448 tokens of cache: the mixed test below cannot run without pages being handed out again
+    r = Replay(folder, dtype, tmp / "out", max_tokens=448, page_size=util.PAGE[name])
+    yield name, dtype, folder, r
+    assert r.close() == 0
+
+
+def test_each_request_alone_and_whole(replay):
+    name, dtype, folder, r = replay
+    for n in LENGTHS[name]:
+        ids = token_ids(name, n, seed=1)
+        got = r.step([{"id": f"w{n}", "tokens": ids, "want": list(range(n))}], end=[f"w{n}"])
+        compare(got, plain_logits(folder, ids), dtype, f"whole request of {n}")
+
+
+def test_most_in_one_step_then_32_one_by_one(replay):
+    name, dtype, folder, r = replay
+    for n in (40, 131):
+        ids = token_ids(name, n, seed=2)
+        want = plain_logits(folder, ids)
+        head = n - 32
+        got = r.step([{"id": "d", "tokens": ids[:head], "want": [head - 1]}])
+        compare(got, want[head - 1:head], dtype, f"last row of the first {head}")
+        for p in range(head, n):
+            got = r.step([{"id": "d", "tokens": [ids[p]], "want": [0]}], end=["d"] if p == n - 1 else [])
+            compare(got, want[p:p + 1], dtype, f"decoded position {p} of {n}")
+
+
+def test_portions_of_changing_size(replay):
+    name, dtype, folder, r = replay
+    n = 150
+    ids = token_ids(name, n, seed=3)
+    want = plain_logits(folder, ids)
+    cuts = [7, 2, 13, 3, 2, 31, 1, 16, 2, 17, 8, 40, 2, 6]
+    assert sum(cuts) == n
+    pos = 0
+    for i, c in enumerate(cuts):
+        got = r.step([{"id": "p", "tokens": ids[pos:pos + c], "want": list(range(c))}], end=["p"] if i == len(cuts) - 1 else [])
+        compare(got, want[pos:pos + c], dtype, f"portion {i} of {c} tokens at {pos}")
+        pos += c
+
+
+def test_first_tokens_of_a_sequence(replay):
+    name, dtype, folder, r = replay
+    ids = token_ids(name, 3, seed=4)
+    want = plain_logits(folder, ids)
+    got = r.step([{"id": "f", "tokens": ids[:1], "want": [0]}])
+    compare(got, want[:1], dtype, "position 0 alone")
+    got = r.step([{"id": "f", "tokens": ids[1:3], "want": [0, 1]}], end=["f"])
+    compare(got, want[1:3], dtype, "positions 1-2")
+
+
+def test_long_decoding(replay):
+    name, dtype, folder, r = replay
+    n = 200
+    ids = token_ids(name, n, seed=5)
+    want = plain_logits(folder, ids)
+    got = r.step([{"id": "l", "tokens": ids[:3], "want": [2]}])
+    compare(got, want[2:3], dtype, "prompt of 3")
+    for p in range(3, n):
+        got = r.step([{"id": "l", "tokens": [ids[p]], "want": [0]}], end=["l"] if p == n - 1 else [])
+        compare(got, want[p:p + 1], dtype, f"decoded position {p}")
+
+
+def test_mixed_requests_with_pages_used_again(replay):
+    """Up to four live requests; portions of some beside decoded tokens of others; requests end and new ones
+    start on the pages just given back (448 tokens of cache, far less than the sum of all requests)."""
+    name, dtype, folder, r = replay
+    lengths = [90, 61, 120, 33, 75, 110, 48, 100]
+    seqs = {f"m{i}": token_ids(name, n, seed=10 + i) for i, n in enumerate(lengths)}
+    want = {k: plain_logits(folder, v) for k, v in seqs.items()}
+    pos = {k: 0 for k in seqs}
+    waiting = list(seqs)
+    live: list[str] = []
+    portion = {"m0": 50, "m1": 7, "m2": 64, "m3": 2, "m4": 30, "m5": 41, "m6": 9, "m7": 16}
+    step_no = 0
+    while waiting or live:
+        # admit while there is room for the request's whole length rounded up to 64
+        def held(k):
+            return -(-len(seqs[k]) // 64) * 64
+        while waiting and len(live) < 4 and sum(held(k) for k in live) + held(waiting[0]) <= 448:
+            live.append(waiting.pop(0))
+        entries, checks, ended = [], [], []
+        for j, k in enumerate(live):
+            if (step_no + j) % 5 == 4:
+                continue  # this request sits the step out
+            left = len(seqs[k]) - pos[k]
+            prompt_part = len(seqs[k]) - 32
+            if pos[k] < prompt_part:
+                c = min(portion[k], prompt_part - pos[k])
+                wanted = [c - 1] if c > 1 else [0]
+                if c > 2:
+                    wanted = [0, c - 1]
+            else:
+                c, wanted = 1, [0]
+            entries.append({"id": k, "tokens": seqs[k][pos[k]:pos[k] + c], "want": wanted})
+            checks.append((k, [pos[k] + w for w in wanted]))
+            pos[k] += c
+            if c == left:
+                ended.append(k)
+        if entries:
+            got = r.step(entries, end=ended)
+            row = 0
+            for k, places in checks:
+                for p in places:
+                    compare(got[row:row + 1], want[k][p:p + 1], dtype, f"step {step_no}: request {k} position {p}")
+                    row += 1
+            assert row == got.shape[0]
+        for k in ended:
+            live.remove(k)
+        step_no += 1
+        assert step_no < 2000
