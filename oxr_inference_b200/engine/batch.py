@@ -31,6 +31,8 @@ class StepEntry:
     seed: int = 0
     counter: int = 0
     """Index of the output token that will be sampled from this entry's (last) wanted row."""
+    penalty: float = 1.0
+    """Repetition penalty of the request."""
 
 
 def _align(n: int) -> int:
@@ -55,7 +57,7 @@ class Layout:
         put("cu_q", requests + 1)
         put("ctx_lens", requests)
         put("state_slots", requests)
-        for name in ("logit_rows", "temperature", "seed_lo", "seed_hi", "counter", "row_slot"):
+        for name in ("logit_rows", "temperature", "seed_lo", "seed_hi", "counter", "row_slot", "penalty"):
             put(name, rows)
         for g, w in enumerate(widths):
             put(f"slots{g}", tokens)
@@ -136,7 +138,7 @@ class BatchBuilder:
         seg("state_slots")[:] = [e.cache.state_slot for e in entries] + [m.scratch_slot] * (n - n_real)
 
         rows, temp, slo, shi, cnt, rslot = (seg(k) for k in ("logit_rows", "temperature", "seed_lo", "seed_hi", "counter", "row_slot"))
-        temp_f = temp.view(np.float32)
+        temp_f, pen_f = temp.view(np.float32), seg("penalty").view(np.float32)
         r = 0
         for i, e in enumerate(entries):
             for w in e.want:
@@ -148,12 +150,14 @@ class BatchBuilder:
                 shi[r] = _as_i32((e.seed >> 32) & 0xFFFFFFFF)
                 cnt[r] = e.counter
                 rslot[r] = e.cache.state_slot
+                pen_f[r] = e.penalty
                 r += 1
         for i in range(n_real, n):  # padding rows: greedy on their own token
             rows[r] = int(cu[i])
             temp_f[r] = 0.0
             slo[r] = shi[r] = cnt[r] = 0
             rslot[r] = m.scratch_slot
+            pen_f[r] = 1.0
             r += 1
         if r != layout.rows:
             raise ValueError(f"layout holds {layout.rows} logit rows, the entries want {r}")
@@ -208,7 +212,8 @@ class BatchBuilder:
             q_lens=q_lens, ctx_lens_host=ctx_lens, status=self.status,
         )
         ctx.sampling = {"temperature": dev("temperature").view(torch.float32), "seed_lo": dev("seed_lo"),
-                        "seed_hi": dev("seed_hi"), "counter": dev("counter"), "row_slot": dev("row_slot")}
+                        "seed_hi": dev("seed_hi"), "counter": dev("counter"), "row_slot": dev("row_slot"),
+                        "penalty": dev("penalty").view(torch.float32)}
         return ctx
 
 

@@ -1,0 +1,84 @@
+"""Decode-only steps replayed from CUDA graphs.
+
+As in the reference (oxr_runtime/decode_graph.py:33-119): batch sizes are rounded up to buckets, the inputs live
+in fixed device memory filled from pinned host memory before each replay, rows beyond the real requests point at
+a scratch page, and the graph holds the whole step: embedding, every layer, output head and the choice of the
+next token. Differences: graphs are captured at first use instead of all at start-up, and a graph is keyed by
+(batch bucket, block-table width bucket) so that short contexts do not pay for the widest possible table.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from oxr_inference_b200 import ops
+from oxr_inference_b200.engine.batch import Layout, StepEntry
+from oxr_inference_b200.engine.runtime import ModelRunner
+
+BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 192, 256, 384, 512, 768, 1024)  # oxr_runtime/decode_graph.py:30
+
+
+class DecodeGraphs:
+    def __init__(self, runner: ModelRunner, *, max_batch: int, max_positions: int):
+        self.runner = runner
+        self.buckets = [b for b in BUCKETS if b < max_batch] + [max_batch]
+        self.max_width = (max_positions + runner.cache.page_size - 1) // runner.cache.page_size
+        self._graphs: dict[tuple[int, int], tuple] = {}
+        self._pool = None
+        self.kernels_per_replay: dict[tuple[int, int], int] = {}
+        self.replays = 0
+
+    def _width_bucket(self, entries: list[StepEntry]) -> int:
+        need = max(len(t) for e in entries for t in e.cache.tables)
+        w = 16
+        while w < need:
+            w *= 2
+        return min(w, max(self.max_width, need))
+
+    def run(self, entries: list[StepEntry]) -> torch.Tensor | None:
+        """Replay the step for single-token entries; returns the chosen tokens (int32, one per entry; the view
+        is overwritten by the next replay) or None when the batch is larger than the largest bucket."""
+        n = len(entries)
+        bucket = next((b for b in self.buckets if b >= n), None)
+        if bucket is None:
+            return None
+        key = (bucket, self._width_bucket(entries))
+        if key not in self._graphs:
+            self._capture(key, entries)
+        graph, layout, block, tokens, tiles_n = self._graphs[key]
+        self.runner.builder.build(entries, layout=layout, device_block=block)
+        graph.replay()
+        self.replays += 1
+        ops.launch_count += self.kernels_per_replay[key]
+        return tokens[:n]
+
+    def _forward(self, ctx) -> torch.Tensor:
+        logits = self.runner.model.step(ctx, self.runner.cache)
+        s = ctx.sampling
+        return ops.sample(logits, s["temperature"], s["seed_lo"], s["seed_hi"], s["counter"])
+
+    @torch.inference_mode()
+    def _capture(self, key: tuple[int, int], entries: list[StepEntry]) -> None:
+        bucket, width = key
+        b = self.runner.builder
+        m = self.runner.cache
+        layout = Layout(bucket, bucket, bucket, [width] * len(m.pools), {t: bucket for t in b.tile_sizes})
+        block = torch.zeros(layout.total, dtype=torch.int32, device=b.device)
+        # Warm-up with the real entries: what they write into the cache is what the replay writes again.
+        ctx = b.build(entries, layout=layout, device_block=block)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                self._forward(ctx)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        if self._pool is None:
+            self._pool = torch.cuda.graph_pool_handle()
+        before = ops.launch_count
+        with torch.cuda.graph(graph, pool=self._pool):
+            tokens = self._forward(ctx)
+        self.kernels_per_replay[key] = ops.launch_count - before
+        ops.launch_count = before  # capturing launches nothing
+        self._graphs[key] = (graph, layout, block, tokens, ctx.tiles)
