@@ -1,0 +1,247 @@
+#!/usr/bin/env python3
+"""Measures the engine on one B200: Qwen3-8B layer sizes, bf16, random weights, synthetic token ids.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line. ``value`` is decoded tokens per second at batch 8 with 2,048 tokens of context per request,
+timed on the device over K replays of the decode step; ``e2e`` is the same through ``Engine.step`` (host token ids
+in through pinned memory, sampled token ids out, every step). ``prefill`` is one 2,048-token prompt in one step;
+``points`` holds decode at batch 1 and 64; ``roofline`` divides the bytes a decode step has to read (every weight
+once, plus the cache of the live requests) by its time. A step's inputs (15 GB of weights) are far larger than L2,
+so nothing is cached between timed iterations.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+QWEN3_8B = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "hidden_size": 4096, "intermediate_size": 12288,
+    "num_hidden_layers": 36, "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "rms_norm_eps": 1e-6,
+    "rope_theta": 1000000.0, "vocab_size": 151936, "tie_word_embeddings": False, "max_position_embeddings": 4096,
+}
+CONTEXT = 2048
+PREFILL_TOKENS = 2048
+METRIC = "Qwen3-8B bf16 decode tok/s at batch 8 (context 2048)"
+
+
+def peaks() -> tuple[float, float, str]:
+    """(HBM GB/s, bf16 TFLOP/s, 'measured' | 'fallback')"""
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.is_file():
+        try:
+            p = json.loads(path.read_text())
+            return float(p["hbm_gbs"]), float(p["bf16_tflops"]), "measured"
+        except (KeyError, ValueError):
+            pass
+    return 6650.0, 1590.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock and throttle-reason samples while a timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self) -> None:
+        self.rows: list[list[str]] = []
+        self.proc = None
+        self.thread = None
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self) -> None:
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        self.proc.wait(timeout=10)
+        self.thread.join(timeout=5)
+        sm = [int(r[0]) for r in self.rows if len(r) >= 6 and r[0].isdigit()]
+        mx = [int(r[1]) for r in self.rows if len(r) >= 6 and r[1].isdigit()]
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": int(statistics.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def reference_arm() -> int:
+    print(json.dumps({"impl": "reference", "unavailable":
+                      "the reference cannot be installed: pip reports that /root/reference has neither setup.py nor "
+                      "pyproject.toml, and its engine only loads its own vision+language model folder"}))
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    ap.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"], help="fewer layers than the model has (named in config)")
+    ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64 (quick runs)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm()
+    if args.gpus != 1:
+        print(f"this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    K, W = args.steps, max(args.warmup, 3)
+
+    import torch
+
+    from oxr_inference_b200 import ops
+    from oxr_inference_b200.config import EngineSettings
+    from oxr_inference_b200.engine.api import Engine
+    from oxr_inference_b200.engine.batch import StepEntry
+    from oxr_inference_b200.sampling import SamplingParams
+
+    cfg = dict(QWEN3_8B, num_hidden_layers=args.layers)
+    page = 16
+    pages = 64 * ((CONTEXT + 2 * (K + W) + 64) // page + 2) + 64
+    engine = Engine(random_config=cfg, seed=0, settings=EngineSettings(
+        dtype="bfloat16", page_size=page, num_pages=pages, max_running=64, max_step_tokens=8192, prefill_chunk=2048,
+        max_positions=4096, cuda_graphs=True))
+    model = engine.runner.model
+    gen = torch.Generator().manual_seed(0)
+    hbm_gbs, bf16_tflops, peak_kind = peaks()
+
+    L, h, I, V = cfg["num_hidden_layers"], cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    H, KV, D = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    layer_params = (H + 2 * KV) * D * h + H * D * h + 2 * I * h + I * h
+    weight_bytes = 2 * (L * layer_params + V * h) + 4 * (L * (2 * h + 2 * D) + h)
+    kv_bytes_per_token = 2 * L * KV * D * 2
+
+    def prompts(n: int) -> list[list[int]]:
+        return [torch.randint(0, V, (CONTEXT,), generator=gen).tolist() for _ in range(n)]
+
+    def fill(batch: int, budget: int) -> None:
+        """`batch` requests, each with CONTEXT tokens in the cache and one token left to decode."""
+        for r in list(engine.scheduler.running) + list(engine.scheduler.waiting):
+            r.cancelled = True
+        engine.step()
+        for p in prompts(batch):
+            engine.add_request(p, SamplingParams(max_tokens=budget, ignore_eos=True))
+        while engine.scheduler.waiting or any(r.pending > 1 for r in engine.scheduler.running):
+            engine.step()
+        assert len(engine.scheduler.running) == batch
+
+    def decode_device(batch: int) -> tuple[float, int, int]:
+        """ms per decode step on the device (K replays after W), kernels per step, context length."""
+        fill(batch, 2 * (K + W) + 8)
+        plan = engine.scheduler.schedule()
+        assert plan.decode_only and len(plan.entries) == batch
+        entries = [StepEntry(p.request.cache, p.request.tokens[p.start:p.start + 1], [0], counter=len(p.request.output))
+                   for p in plan.entries]
+        tokens = engine.graphs.run(entries)  # captures at first use, fills the static inputs
+        key = next(k for k in engine.graphs._graphs if k[0] >= batch)
+        key = min((k for k in engine.graphs._graphs if k[0] >= batch), key=lambda k: k)
+        graph = engine.graphs._graphs[key][0]
+        for _ in range(W):
+            graph.replay()
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(K):
+            graph.replay()
+        end.record()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(end) / K
+        ctx = plan.entries[0].start + 1
+        engine.scheduler.commit(plan, {p.request.id: t for p, t in zip(plan.entries, tokens.tolist())})
+        return ms, engine.graphs.kernels_per_replay[key], ctx
+
+    sampler = ClockSampler()
+    sampler.start()
+
+    # ---- headline: batch 8, device-timed
+    ms8, kernels_per_step, ctx8 = decode_device(8)
+    value = 8 * 1000.0 / ms8
+    step_bytes = weight_bytes + 8 * ctx8 * kv_bytes_per_token + 8 * h * 2
+    achieved = step_bytes / (ms8 * 1e-3) / 1e9
+
+    # ---- the same through the entry point: host tokens in, sampled tokens out, every step
+    for _ in range(W):
+        engine.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(K):
+        engine.step()
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    e2e = 8 * K / e2e_s
+    layout_words = next(v[1].total for k, v in engine.graphs._graphs.items() if k[0] == 8)
+
+    points = {}
+    if not args.skip_points:
+        for b in (1, 64):
+            ms, _, _ = decode_device(b)
+            points[f"decode_b{b}"] = round(b * 1000.0 / ms, 1)
+
+    # ---- prefill: one prompt of 2,048 tokens in one step
+    for r in list(engine.scheduler.running):
+        r.cancelled = True
+    engine.step()
+    ids = torch.randint(0, V, (PREFILL_TOKENS,), generator=gen).tolist()
+    times = []
+    for i in range(W + 5):
+        rc = engine.runner.cache.open("prefill")
+        assert engine.runner.cache.reserve(rc, PREFILL_TOKENS)
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        engine.runner.step([StepEntry(rc, ids, [PREFILL_TOKENS - 1])])
+        end.record()
+        torch.cuda.synchronize()
+        if i >= W:
+            times.append(start.elapsed_time(end))
+        engine.runner.cache.close(rc)
+    engine.runner.check()
+    prefill_ms = statistics.median(times)
+    T = PREFILL_TOKENS
+    flops = 2 * T * L * layer_params + 2 * V * h + L * 2 * H * D * T * (T + 1)
+    prefill_frac = flops / (prefill_ms * 1e-3) / (bf16_tflops * 1e12)
+
+    clocks = sampler.stop()
+    out = {
+        "metric": METRIC, "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
+        "ms_per_step": round(ms8, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic uniform token ids, random weights N(0, 0.02)", "impl": "ours",
+        "config": {"model": "Qwen3-8B shape", "layers": L, "layers_of_model": QWEN3_8B["num_hidden_layers"], "hidden": h,
+                   "heads": H, "kv_heads": KV, "head_dim": D, "intermediate": I, "vocab": V, "global_batch": 8,
+                   "seq_len": CONTEXT, "page_size": page, "tied": False, "parallelism": "single GPU",
+                   "l2": "step inputs (15 GB of weights) exceed L2", "peaks": peak_kind},
+        "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": layout_words * 4, "d2h_bytes_per_step": (8 + 2) * 4},
+        "gpu_launches": kernels_per_step * K,
+        "prefill": {"value": round(T / (prefill_ms * 1e-3), 1), "tokens": T, "ms": round(prefill_ms, 3), "frac": round(prefill_frac, 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_gbs, "unit": "GB/s", "frac": round(achieved / hbm_gbs, 4)},
+        "points": points,
+        "clocks": clocks,
+    }
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,181 @@
+"""Generation through the Python entry point on the GPU: greedy against the plain implementation, CUDA-graph
+replay against eager steps, temperature sampling that does not depend on batching or preemption, repetition
+penalty, and the command line."""
+
+import json
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import util
+from plain import qwen3_plain as QP
+from util import make_folder, plain_logits, token_ids
+
+pytestmark = pytest.mark.gpu
+
+
+def _engine(folder, name, dtype, **kw):
+    from oxr_inference_b200.config import EngineSettings
+    from oxr_inference_b200.engine.api import Engine
+
+    kw.setdefault("num_pages", 64)
+    kw.setdefault("max_running", 4)
+    return Engine(folder, EngineSettings(dtype=dtype, page_size=util.PAGE[name], **kw))
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    tmp = tmp_path_factory.mktemp("engine")
+    return {name: make_folder(tmp, name, seed=11) for name in ("A", "B")}
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("graphs", [False, True])
+def test_greedy_generation_float32_is_the_plain_implementations(folders, name, graphs):
+    from oxr_inference_b200.sampling import SamplingParams
+
+    folder = folders[name]
+    cfg, w = QP.read_model(folder)
+    prompts = [token_ids(name, n, seed=21) for n in ((5, 17, 33) if name == "A" else (1, 12, 40, 64))]
+    steps = 8 if name == "A" else 12
+    want = [QP.greedy(cfg, w, p, steps) for p in prompts]
+    engine = _engine(folder, name, "float32", cuda_graphs=graphs)
+    got = engine.generate(prompts, SamplingParams(max_tokens=steps, ignore_eos=True))
+    assert [c.token_ids for c in got] == want
+    assert all(c.finish_reason == "length" and c.prompt_tokens == len(p) for c, p in zip(got, prompts))
+    assert (engine.counters["graph_steps"] > 0) == graphs
+    engine.runner.cache.check()
+    assert engine.runner.cache.free_pages == engine.runner.cache.usable_pages
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_bfloat16_picks_near_maxima_of_the_plain_logits(folders, name):
+    """bfloat16 may break a near-tie the other way; every token it picks must still be within the bfloat16 error
+    bound of the plain implementation's maximum, given the engine's own earlier tokens."""
+    from oxr_inference_b200.sampling import SamplingParams
+
+    folder = folders[name]
+    prompts = [token_ids(name, n, seed=22) for n in (7, 30, 61)]
+    engine = _engine(folder, name, "bfloat16")
+    got = engine.generate(prompts, SamplingParams(max_tokens=10, ignore_eos=True))
+    for prompt, c in zip(prompts, got):
+        seq = prompt + c.token_ids
+        logits = plain_logits(folder, seq[:-1])
+        scale = logits.abs().max().item()
+        for i, tok in enumerate(c.token_ids):
+            row = logits[len(prompt) - 1 + i]
+            assert row[tok] >= row.max() - 2 * 8e-2 * scale, f"token {i} = {tok} is not near the plain maximum"
+
+
+def test_cuda_graph_replay_equals_eager_steps(folders):
+    from oxr_inference_b200.sampling import SamplingParams
+
+    folder = folders["B"]
+    prompts = [token_ids("B", n, seed=23) for n in (3, 20, 50)]
+    runs = []
+    for graphs in (False, True):
+        engine = _engine(folder, "B", "bfloat16", cuda_graphs=graphs)
+        runs.append([c.token_ids for c in engine.generate(prompts, SamplingParams(max_tokens=40, ignore_eos=True))])
+    assert runs[0] == runs[1]
+
+
+def test_temperature_sampling_does_not_depend_on_batching_or_preemption(folders):
+    from oxr_inference_b200.sampling import SamplingParams
+
+    folder = folders["B"]
+    prompts = [token_ids("B", n, seed=24) for n in (1, 12, 40, 64)]
+    params = [SamplingParams(max_tokens=12, temperature=0.7, seed=1000 + i, ignore_eos=True) for i in range(4)]
+    together = _engine(folder, "B", "float32").generate(prompts, params)
+    alone = [_engine(folder, "B", "float32", cuda_graphs=False).generate([p], [q])[0] for p, q in zip(prompts, params)]
+    assert [c.token_ids for c in together] == [c.token_ids for c in alone]
+    greedy = _engine(folder, "B", "float32").generate(prompts, SamplingParams(max_tokens=12, ignore_eos=True))
+    assert [c.token_ids for c in greedy] != [c.token_ids for c in together], "temperature 0.7 should not equal greedy everywhere"
+    # so few pages that requests are pushed out and recomputed: the draws must come out the same
+    squeezed = _engine(folder, "B", "float32", num_pages=15, max_step_tokens=24, prefill_chunk=9)
+    again = squeezed.generate(prompts, params)
+    assert squeezed.preemptions > 0, "this cache is too small to run the four requests without preemption"
+    assert [c.token_ids for c in again] == [c.token_ids for c in together]
+    # another seed, other tokens
+    other = _engine(folder, "B", "float32").generate(prompts[3:], [SamplingParams(max_tokens=12, temperature=0.7, seed=5, ignore_eos=True)])
+    assert other[0].token_ids != together[3].token_ids
+
+
+def test_chunked_prefill_under_a_small_token_budget_gives_the_same_tokens(folders):
+    from oxr_inference_b200.sampling import SamplingParams
+
+    folder = folders["A"]
+    cfg, w = QP.read_model(folder)
+    prompts = [token_ids("A", n, seed=25) for n in (5, 17, 33, 90)]
+    want = [QP.greedy(cfg, w, p, 8) for p in prompts]
+    engine = _engine(folder, "A", "float32", max_step_tokens=11, prefill_chunk=7, num_pages=20)
+    got = engine.generate(prompts, SamplingParams(max_tokens=8, ignore_eos=True))
+    assert [c.token_ids for c in got] == want
+
+
+def test_eos_stops_generation(folders):
+    from oxr_inference_b200.sampling import SamplingParams
+
+    folder = folders["A"]
+    cfg, w = QP.read_model(folder)
+    prompt = token_ids("A", 9, seed=26)
+    free_run = QP.greedy(cfg, w, prompt, 6)
+    cut = max(i for i in range(6) if free_run[i] not in free_run[:i])  # the last token that is new when it appears
+    engine = _engine(folder, "A", "float32")
+    stopped = engine.generate([prompt], SamplingParams(max_tokens=6, stop_token_ids=(free_run[cut],)))[0]
+    assert stopped.token_ids == free_run[:cut] and stopped.finish_reason == "stop"
+
+
+def test_repetition_penalty_follows_the_reference_rule(folders):
+    """Greedy with a penalty: recompute with the plain implementation, dividing positive and multiplying other
+    logits of every token seen so far, prompt included (oxr_runtime/engine.py:632-639)."""
+    from oxr_inference_b200.sampling import SamplingParams
+
+    folder = folders["A"]
+    cfg, w = QP.read_model(folder)
+    prompt = token_ids("A", 12, seed=27)
+    seq, want = list(prompt), []
+    for _ in range(8):
+        row = QP.logits(cfg, w, seq)[-1].clone()
+        seen = torch.tensor(sorted(set(seq)))
+        row[seen] = torch.where(row[seen] > 0, row[seen] / 1.8, row[seen] * 1.8)
+        want.append(int(row.argmax()))
+        seq.append(want[-1])
+    engine = _engine(folder, "A", "float32")
+    got = engine.generate([prompt], SamplingParams(max_tokens=8, repetition_penalty=1.8, ignore_eos=True))[0]
+    assert got.token_ids == want
+    plain_greedy = QP.greedy(cfg, w, prompt, 8)
+    assert want != plain_greedy or True  # the penalty usually changes the tokens; equality is not an error
+
+
+def test_step_failure_is_loud_and_pages_come_back(folders):
+    from oxr_inference_b200.sampling import SamplingParams
+    from oxr_inference_b200 import ops
+
+    engine = _engine(folders["A"], "A", "float32", cuda_graphs=False)
+    engine.add_request([5, 999999], SamplingParams(max_tokens=2))  # a token id outside the vocabulary
+    with pytest.raises(ops.KernelError, match="vocabulary"):
+        engine.step()
+    assert not engine.has_work() and engine.runner.cache.free_pages == engine.runner.cache.usable_pages
+    ok = engine.generate([[1, 2, 3]], SamplingParams(max_tokens=2, ignore_eos=True))
+    assert len(ok[0].token_ids) == 2, "the engine stays usable after a failed step"
+
+
+def test_command_line(folders, tmp_path):
+    folder = folders["A"]
+    cfg, w = QP.read_model(folder)
+    out = tmp_path / "result.json"
+    cmd = [sys.executable, "-m", "oxr_inference_b200", "--model", str(folder), "--prompt-ids", "5,17,3", "--prompt-ids", "9 8 7 6",
+           "--max-tokens", "5", "--dtype", "float32", "--num-pages", "32", "--max-running", "4", "--ignore-eos", "--out", str(out)]
+    res = subprocess.run(cmd, capture_output=True, text=True, cwd=str(util.ROOT), timeout=600)
+    assert res.returncode == 0, res.stderr
+    rows = [json.loads(line) for line in res.stdout.strip().splitlines()]
+    assert [r["token_ids"] for r in rows] == [QP.greedy(cfg, w, [5, 17, 3], 5), QP.greedy(cfg, w, [9, 8, 7, 6], 5)]
+    assert json.loads(out.read_text())["results"][0]["finish_reason"] == "length"
+
+
+def test_smoke_entry():
+    import __graft_entry__
+
+    __graft_entry__.smoke()

@@ -1,0 +1,296 @@
+"""Each part alone on the GPU against the plain implementation's function for it, and a toy architecture made of
+the built-in parts plus a mixer with state of its own that is defined and registered here, in the test."""
+
+import pytest
+import torch
+
+from plain import qwen3_plain as QP
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _runtime(dtype=torch.float32, max_positions=128):
+    from oxr_inference_b200 import ops
+    from oxr_inference_b200.parts.base import Runtime
+
+    dev = torch.device("cuda", torch.cuda.current_device())
+    return Runtime(device=dev, dtype=dtype, max_positions=max_positions, status=ops.new_status(dev))
+
+
+def _fill(part, seed=0, scale=0.3):
+    """Random tensors for every parameter of a part; returns them by local name (fp32, on the host)."""
+    g = torch.Generator().manual_seed(seed)
+    out = {}
+    for name, info in part.parameters().items():
+        t = torch.randn(info.shape, generator=g)
+        t = 1 + 0.1 * t if info.init == "around_one" else scale * t
+        out[name] = t
+        part.assign(name, t)
+    part.finish_loading()
+    return out
+
+
+def test_rms_norm_part():
+    from oxr_inference_b200.parts import NORMS
+
+    rt = _runtime()
+    norm = NORMS.build("rms_norm", rt, size=96, eps=1e-5)
+    w = _fill(norm)["weight"].to(DEV)
+    x, res = torch.randn(7, 96, device=DEV), torch.randn(7, 96, device=DEV)
+    out, new_res = norm.forward(x, None)
+    torch.testing.assert_close(out, QP.rms_norm(x, w, 1e-5), atol=1e-5, rtol=1e-5)
+    assert torch.equal(new_res, x)
+    out, new_res = norm.forward(x, res.clone())
+    torch.testing.assert_close(new_res, x + res)
+    torch.testing.assert_close(out, QP.rms_norm(x + res, w, 1e-5), atol=1e-5, rtol=1e-5)
+    rows = torch.tensor([6, 2], dtype=torch.int32, device=DEV)
+    torch.testing.assert_close(norm.forward_rows(x, res, rows), QP.rms_norm(x + res, w, 1e-5)[rows.long()], atol=1e-5, rtol=1e-5)
+
+
+def test_rotary_table_part_is_the_reference_formula():
+    from oxr_inference_b200.parts import POSITION_ENCODINGS
+
+    rope = POSITION_ENCODINGS.build("rope_neox", _runtime(max_positions=300), dim=48, theta=1e6)
+    cos, sin = rope.tables()
+    want_cos, want_sin = QP.rope_tables(48, 1e6, 300, torch.float32)
+    assert cos.dtype == torch.float32 and torch.equal(cos.cpu(), want_cos) and torch.equal(sin.cpu(), want_sin)
+
+
+def test_swiglu_part():
+    from oxr_inference_b200.parts import FEED_FORWARDS
+
+    for dtype in (torch.float32, torch.bfloat16):
+        ff = FEED_FORWARDS.build("swiglu", _runtime(dtype), hidden_size=96, intermediate_size=160)
+        w = {k: v.to(DEV) for k, v in _fill(ff, scale=0.1).items()}
+        if dtype == torch.bfloat16:
+            w = {k: v.bfloat16().float() for k, v in w.items()}
+        h = torch.randn(9, 96, device=DEV).to(dtype)
+        want = QP.swiglu(h.float(), w["gate_proj.weight"], w["up_proj.weight"], w["down_proj.weight"])
+        tol = dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=3e-2, rtol=3e-2)
+        torch.testing.assert_close(ff.forward(h).float(), want, **tol)
+
+
+def _one_layer_context(mixer, rt, q_lens, starts, page_size=8):
+    """A cache for one mixer and a step context in which request i brings q_lens[i] tokens at position starts[i]."""
+    from oxr_inference_b200.cache import CacheManager, make_cache_plan
+    from oxr_inference_b200.engine.batch import BatchBuilder, StepEntry
+
+    plan = make_cache_plan([mixer.cache_need()], [None])
+    manager = CacheManager(plan, page_size=page_size, num_pages=64, max_requests=4, device=rt.device, dtype=rt.dtype)
+    builder = BatchBuilder(manager, [mixer.tile_tokens()], rt.device, rt.status)
+    return manager, builder, StepEntry
+
+
+@pytest.mark.parametrize("window", [0, 9])
+def test_attention_part_in_portions_equals_the_plain_whole_sequence(window):
+    from oxr_inference_b200 import ops
+    from oxr_inference_b200.parts import MIXERS, POSITION_ENCODINGS
+
+    rt = _runtime()
+    cfg = {"num_attention_heads": 6, "num_key_value_heads": 2, "head_dim": 32, "rms_norm_eps": 1e-5}
+    rope = POSITION_ENCODINGS.build("rope_neox", rt, dim=32, theta=1e4)
+    attn = MIXERS.build("gqa_attention", rt, rope, hidden_size=96, num_heads=6, num_kv_heads=2, head_dim=32, scale=32 ** -0.5,
+                        qk_norm=True, eps=1e-5, window=window)
+    w = {"p." + k: v.to(DEV) for k, v in _fill(attn, scale=0.15).items()}
+    n = 45
+    h = torch.randn(n, 96, device=DEV)
+    cos, sin = QP.rope_tables(32, 1e4, n, torch.float32)
+    want = QP.attention_block(h, w, "p.", cfg, cos.to(DEV), sin.to(DEV), window)
+    manager, builder, StepEntry = _one_layer_context(attn, rt, None, None)
+    rc = manager.open("r")
+    pos, outs = 0, []
+    for c in (7, 2, 20, 1, 15):
+        assert manager.reserve(rc, pos + c)
+        ctx = builder.build([StepEntry(rc, [0] * c, [])])
+        outs.append(attn.forward(h[pos:pos + c].contiguous(), ctx, manager.layer_cache(0, ctx)))
+        manager.advance(rc, pos + c)
+        pos += c
+    ops.check_status(rt.status)
+    torch.testing.assert_close(torch.cat(outs), want, atol=2e-5, rtol=2e-5)
+
+
+def test_block_part_carries_the_residual_like_the_plain_layer():
+    from oxr_inference_b200.parts import ARRANGEMENTS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS
+
+    rt = _runtime()
+    cfg = {"num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 16, "rms_norm_eps": 1e-6, "hidden_size": 64,
+           "num_hidden_layers": 1}
+    rope = POSITION_ENCODINGS.build("rope_neox", rt, dim=16, theta=1e4)
+    attn = MIXERS.build("gqa_attention", rt, rope, hidden_size=64, num_heads=4, num_kv_heads=2, head_dim=16, scale=0.25, eps=1e-6)
+    n1, n2 = NORMS.build("rms_norm", rt, size=64, eps=1e-6), NORMS.build("rms_norm", rt, size=64, eps=1e-6)
+    ff = FEED_FORWARDS.build("swiglu", rt, hidden_size=64, intermediate_size=128)
+    block = ARRANGEMENTS.build("pre_norm", attn, n1, ff, n2)
+    w = {}
+    for prefix, part, seed in (("model.layers.0.self_attn.", attn, 1), ("model.layers.0.input_layernorm.", n1, 2),
+                               ("model.layers.0.mlp.", ff, 3), ("model.layers.0.post_attention_layernorm.", n2, 4)):
+        w.update({prefix + k: v.to(DEV) for k, v in _fill(part, seed, 0.15).items()})
+    n = 21
+    x = torch.randn(n, 64, device=DEV)
+    cos, sin = QP.rope_tables(16, 1e4, n, torch.float32)
+    want = QP.decoder_layer(x, w, 0, cfg, cos.to(DEV), sin.to(DEV))
+    manager, builder, StepEntry = _one_layer_context(attn, rt, None, None)
+    rc = manager.open("r")
+    assert manager.reserve(rc, n)
+    ctx = builder.build([StepEntry(rc, [0] * n, [])])
+    out, residual = block.forward(x, None, ctx, manager.layer_cache(0, ctx))
+    torch.testing.assert_close(out + residual, want, atol=2e-5, rtol=2e-5)
+
+
+def test_embedding_and_head_parts_tied_and_untied():
+    from oxr_inference_b200.parts.decoder import OutputHead, TokenEmbedding
+
+    rt = _runtime()
+    emb = TokenEmbedding(rt, vocab_size=50, hidden_size=24)
+    table = _fill(emb)["weight"].to(DEV)
+    ids = torch.tensor([0, 49, 7], dtype=torch.int32, device=DEV)
+    assert torch.equal(emb.forward(ids), table[ids.long()])
+    h = torch.randn(3, 24, device=DEV)
+    tied = OutputHead(rt, emb, vocab_size=50, hidden_size=24, tied=True)
+    assert tied.parameters() == {}
+    torch.testing.assert_close(tied.forward(h), h @ table.T, atol=1e-5, rtol=1e-5)
+    own = OutputHead(rt, emb, vocab_size=50, hidden_size=24, tied=False)
+    w = _fill(own, seed=5)["weight"].to(DEV)
+    torch.testing.assert_close(own.forward(h), h @ w.T, atol=1e-5, rtol=1e-5)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# A toy architecture, defined here: layer 0 is the built-in attention + feed-forward; layer 1 has a mixer that keeps
+# a running sum of its inputs as per-request state; the schedule runs layer 0, layer 1, and layer 0 AGAIN, the
+# second run reading the keys and values the first run stored. Nothing under oxr_inference_b200/ knows about it.
+# ---------------------------------------------------------------------------------------------------------------
+TOY = {"architectures": ["ToyScheduleForTests"], "hidden_size": 32, "intermediate_size": 48, "vocab_size": 50, "heads": 4,
+       "kv_heads": 2, "head_dim": 16, "eps": 1e-5, "theta": 1e4, "max_positions": 128}
+
+
+def _register_toy():
+    from oxr_inference_b200.config.registry import ARCHITECTURES, Architecture, register_architecture
+    from oxr_inference_b200.parts import MIXERS, LayerSpec, Mixer, ModelSpec, ParamInfo, PartSpec, ScheduleEntry, StateNeed
+
+    if "toy_running_mean" not in MIXERS:
+        @MIXERS.register("toy_running_mean")
+        class RunningMean(Mixer):
+            """y[t] = gain * mean of the inputs at positions 0..t of the same request. State: the sum so far."""
+
+            def __init__(self, runtime, position, *, hidden_size):
+                self.runtime, self.hidden, self.gain = runtime, hidden_size, None
+
+            def parameters(self):
+                return {"gain": ParamInfo((self.hidden,), init="around_one", role="vector")}
+
+            def assign(self, name, tensor):
+                assert name == "gain"
+                self.gain = tensor.to(self.runtime.device, torch.float32)
+
+            def cache_need(self):
+                return StateNeed((self.hidden,), torch.float32)
+
+            def forward(self, h, ctx, cache):
+                out = torch.empty_like(h)
+                cu = ctx.cu_q.tolist()
+                for r in range(ctx.n_requests):
+                    a, b = cu[r], cu[r + 1]
+                    slot = int(ctx.state_slots[r])
+                    run = cache.state[slot] + torch.cumsum(h[a:b].float(), 0)
+                    cache.state[slot] = run[-1]
+                    out[a:b] = (run / (ctx.positions[a:b].float() + 1)[:, None] * self.gain).to(h.dtype)
+                return out
+
+    if "ToyScheduleForTests" not in ARCHITECTURES:
+        def spec(c):
+            norm = lambda p: PartSpec("rms_norm", {"size": c["hidden_size"], "eps": c["eps"]}, prefix=p)  # noqa: E731
+            ff = lambda p: PartSpec("swiglu", {"hidden_size": c["hidden_size"], "intermediate_size": c["intermediate_size"]}, prefix=p)  # noqa: E731
+            rope = PartSpec("rope_neox", {"dim": c["head_dim"], "theta": c["theta"]})
+            attn = PartSpec("gqa_attention", {"hidden_size": c["hidden_size"], "num_heads": c["heads"], "num_kv_heads": c["kv_heads"],
+                                              "head_dim": c["head_dim"], "scale": c["head_dim"] ** -0.5, "eps": c["eps"]},
+                            prefix="model.layers.0.self_attn.")
+            toy = PartSpec("toy_running_mean", {"hidden_size": c["hidden_size"]}, prefix="model.layers.1.mixer.")
+            layers = (
+                LayerSpec(attn, norm("model.layers.0.input_layernorm."), ff("model.layers.0.mlp."),
+                          norm("model.layers.0.post_attention_layernorm."), position=rope),
+                LayerSpec(toy, norm("model.layers.1.input_layernorm."), ff("model.layers.1.mlp."),
+                          norm("model.layers.1.post_attention_layernorm.")),
+            )
+            return ModelSpec(
+                architecture="ToyScheduleForTests", hidden_size=c["hidden_size"], vocab_size=c["vocab_size"],
+                embedding=PartSpec("token_embedding", {"vocab_size": c["vocab_size"], "hidden_size": c["hidden_size"]}, prefix="model.embed_tokens."),
+                layers=layers, schedule=(ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0, cache_of=0)),
+                final_norm=norm("model.norm."),
+                head=PartSpec("linear_head", {"vocab_size": c["vocab_size"], "hidden_size": c["hidden_size"], "tied": True}, prefix="lm_head."),
+                max_positions=c["max_positions"])
+
+        register_architecture(Architecture("ToyScheduleForTests", lambda raw, gen: dict(raw), spec))
+
+
+def _toy_plain(w, ids):
+    """The toy model on a whole sequence, written out with the plain implementation's functions."""
+    c = {"num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 16, "rms_norm_eps": 1e-5}
+    n, eps = len(ids), 1e-5
+    x = w["model.embed_tokens.weight"][torch.tensor(ids)]
+    cos, sin = QP.rope_tables(16, 1e4, n, torch.float32)
+    p = "model.layers.0."
+
+    def qkv(h):
+        q = (h @ w[p + "self_attn.q_proj.weight"].T).view(n, 4, 16)
+        k = (h @ w[p + "self_attn.k_proj.weight"].T).view(n, 2, 16)
+        v = (h @ w[p + "self_attn.v_proj.weight"].T).view(n, 2, 16)
+        q = QP.rotate_half_split(QP.rms_norm(q, w[p + "self_attn.q_norm.weight"], eps), cos, sin)
+        k = QP.rotate_half_split(QP.rms_norm(k, w[p + "self_attn.k_norm.weight"], eps), cos, sin)
+        return q, k, v
+
+    def mlp(x, q):
+        h = QP.rms_norm(x, w[q + "post_attention_layernorm.weight"], eps)
+        return x + QP.swiglu(h, w[q + "mlp.gate_proj.weight"], w[q + "mlp.up_proj.weight"], w[q + "mlp.down_proj.weight"])
+
+    # run 1 of layer 0
+    q, k0, v0 = qkv(QP.rms_norm(x, w[p + "input_layernorm.weight"], eps))
+    x = mlp(x + QP.causal_attention(q, k0, v0, 0.25).reshape(n, 64) @ w[p + "self_attn.o_proj.weight"].T, p)
+    # layer 1: running mean
+    h = QP.rms_norm(x, w["model.layers.1.input_layernorm.weight"], eps)
+    mean = torch.cumsum(h, 0) / torch.arange(1, n + 1)[:, None]
+    x = mlp(x + mean * w["model.layers.1.mixer.gain"], "model.layers.1.")
+    # run 2 of layer 0: its own queries, the keys and values of run 1
+    q, _, _ = qkv(QP.rms_norm(x, w[p + "input_layernorm.weight"], eps))
+    x = mlp(x + QP.causal_attention(q, k0, v0, 0.25).reshape(n, 64) @ w[p + "self_attn.o_proj.weight"].T, p)
+    return QP.rms_norm(x, w["model.norm.weight"], eps) @ w["model.embed_tokens.weight"].T
+
+
+def test_a_toy_architecture_with_a_stateful_mixer_registers_builds_and_steps(tmp_path):
+    from safetensors.torch import load_file
+
+    from oxr_inference_b200.engine.batch import StepEntry
+    from oxr_inference_b200.engine.runtime import ModelRunner
+    from oxr_inference_b200.weights import write_random_model
+
+    _register_toy()
+    folder = write_random_model(TOY, tmp_path / "toy", seed=3, dtype="float32", std=0.15)
+    w = load_file(str(folder / "model.safetensors"))
+    assert "model.layers.1.mixer.gain" in w and "model.layers.1.self_attn.q_proj.weight" not in w
+    runner = ModelRunner.from_folder(folder, dtype="float32", page_size=8, num_pages=32, max_requests=3)
+    plan = runner.model.cache_plan
+    assert len(plan.groups) == 1 and plan.groups[0].num_layers == 1, "the second run of layer 0 has no cache of its own"
+    assert len(plan.states) == 1 and plan.entries[2].store is False and plan.entries[1].state == 0
+
+    g = torch.Generator().manual_seed(5)
+    seqs = {k: torch.randint(0, 50, (n,), generator=g).tolist() for k, n in (("a", 37), ("b", 20))}
+    want = {k: _toy_plain(w, v) for k, v in seqs.items()}
+    # request a in portions, request b beside it: a portion, then decoded tokens
+    a, b = runner.cache.open("a"), runner.cache.open("b")
+    got = {"a": [], "b": []}
+    plan_a, plan_b = [5, 2, 11, 1, 18], [12, 1, 1, 1, 5]
+    pa = pb = 0
+    for ca, cb in zip(plan_a, plan_b):
+        assert runner.cache.reserve(a, pa + ca) and runner.cache.reserve(b, pb + cb)
+        logits = runner.step([StepEntry(a, seqs["a"][pa:pa + ca], list(range(ca))), StepEntry(b, seqs["b"][pb:pb + cb], list(range(cb)))])
+        got["a"].append(logits[:ca])
+        got["b"].append(logits[ca:])
+        pa, pb = pa + ca, pb + cb
+    runner.check()
+    for k in seqs:
+        torch.testing.assert_close(torch.cat(got[k]).cpu(), want[k], atol=1e-4, rtol=1e-4)
+    # a new request on a used slot starts from zeroed state
+    runner.cache.close(a)
+    c = runner.cache.open("c")
+    assert c.state_slot == a.state_slot and runner.cache.reserve(c, 37)
+    again = runner.step([StepEntry(c, seqs["a"], list(range(37)))])
+    torch.testing.assert_close(again.cpu(), want["a"], atol=1e-4, rtol=1e-4)
