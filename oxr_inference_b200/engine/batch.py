@@ -98,6 +98,7 @@ class BatchBuilder:
         return Layout(bucket, bucket, bucket, [width] * len(m.pools), {t: bucket for t in self.tile_sizes})
 
     # ---- the build
+    @torch.inference_mode()
     def build(self, entries: list[StepEntry], layout: Layout | None = None,
               device_block: torch.Tensor | None = None) -> StepContext:
         """Fill the staging block for ``entries`` and copy it. With ``layout``/``device_block`` (graph replay) the

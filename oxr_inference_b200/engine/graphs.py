@@ -35,6 +35,7 @@ class DecodeGraphs:
             w *= 2
         return min(w, max(self.max_width, need))
 
+    @torch.inference_mode()
     def run(self, entries: list[StepEntry]) -> torch.Tensor | None:
         """Replay the step for single-token entries; returns the chosen tokens (int32, one per entry; the view
         is overwritten by the next replay) or None when the batch is larger than the largest bucket."""

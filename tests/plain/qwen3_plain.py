@@ -70,8 +70,8 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: f
     rep = H // k.shape[1]
     k, v = k.repeat_interleave(rep, dim=1), v.repeat_interleave(rep, dim=1)
     scores = torch.einsum("nhd,mhd->hnm", q, k) * scale
-    i = torch.arange(n)[:, None]
-    j = torch.arange(n)[None, :]
+    i = torch.arange(n, device=q.device)[:, None]
+    j = torch.arange(n, device=q.device)[None, :]
     hidden = j > i
     if window > 0:
         hidden = hidden | (j <= i - window)
