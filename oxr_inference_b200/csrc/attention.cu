@@ -229,8 +229,495 @@ int launch_simt(void* out, const void* q, const void* k_cache, const void* v_cac
 }
 }  // namespace
 
+
+// =====================================================================================================================
+// bfloat16 on the tensor cores (mma.sync m16n8k16, fp32 accumulation): the same attention, two kernels.
+//
+//  * attn_mma_prefill_kernel: a tile is 64 rows; warp w owns rows 16w..16w+15 and visits every key block.
+//  * attn_mma_decode_kernel: a tile is 16 rows (one decoded token's whole group of q heads, or a few tokens of a
+//    short portion); the four warps share the rows and each takes a quarter of every 64-key block; the key range
+//    is further split over gridDim.z blocks whose partial (max, sum, output) are merged by attn_combine_kernel.
+//
+// K and V blocks are gathered page by page with cp.async (16 bytes per request, zero-filled outside the visible
+// range) into padded shared-memory rows, two stages deep; fragments are read with ldmatrix.
+// =====================================================================================================================
+namespace {
+typedef __nv_bfloat16 bf16;
+constexpr int PADE = 8;                        // 16 bytes of padding per row: ldmatrix rows fall on different banks
+constexpr int LDS = D + PADE;                  // shared-memory row stride in elements
+constexpr int MMA_BN = 64;                     // keys per block
+constexpr int MMA_THREADS = 128;
+constexpr int KSTEPS = D / 16;                 // k16 steps over the head dimension
+constexpr int DT8 = D / 8;                     // n8 tiles over the head dimension
+constexpr bool Q_IN_REGS = D <= 128;
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
+    const int bytes = valid ? 16 : 0;   // 0: the 16 bytes are zero-filled and gmem is not read
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem)), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Gather keys [k0, k0 + MMA_BN) of one request into Ks / Vs (rows of LDS elements); keys outside [k_lo, k_end)
+// become zeros. All MMA_THREADS threads take part.
+__device__ __forceinline__ void load_kv_block(bf16* Ks, bf16* Vs, const bf16* __restrict__ k_cache,
+                                              const bf16* __restrict__ v_cache, const int* __restrict__ table_row,
+                                              const AttnArgs& a, int kvh, int k0, int k_lo, int k_end, int req) {
+    constexpr int CPR = D / 8;   // 16-byte chunks per row
+    for (int idx = threadIdx.x; idx < MMA_BN * CPR; idx += MMA_THREADS) {
+        const int j = idx / CPR, c = idx % CPR;
+        const int kp = k0 + j;
+        bool ok = kp >= k_lo && kp < k_end;
+        size_t base = 0;
+        if (ok) {
+            const int page = table_row[kp / a.page_size];
+            if (page < 0 || page >= a.num_pages) {
+                if (c == 0) oxr_report(a.status, OXR_BAD_PAGE, req);
+                ok = false;
+            } else {
+                base = (((size_t)page * a.page_size + kp % a.page_size) * a.KV + kvh) * D + c * 8;
+            }
+        }
+        cp_async_16(Ks + j * LDS + c * 8, k_cache + base, ok);
+        cp_async_16(Vs + j * LDS + c * 8, v_cache + base, ok);
+    }
+}
+
+// One warp: S = Q K^T for its 16 rows and NK keys starting at Kw, masked online softmax, O += P V.
+// qf: Q fragments when Q_IN_REGS, else read from Qw (this warp's 16 rows in shared memory).
+template <int NK>
+__device__ __forceinline__ void warp_block(const uint32_t (&qf)[Q_IN_REGS ? KSTEPS : 1][4], const bf16* Qw, const bf16* Kw,
+                                           const bf16* Vw, int key0, const int (&row_pos)[2], const bool (&row_ok)[2],
+                                           int window, float scale_log2, float (&m)[2], float (&l)[2], float (&o)[DT8][4]) {
+    constexpr int NT = NK / 8;
+    const int lane = threadIdx.x & 31, t = lane & 3;
+    float s[NT][4];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; ++kk) {
+        uint32_t aq[4];
+        if constexpr (Q_IN_REGS) {
+            aq[0] = qf[kk][0]; aq[1] = qf[kk][1]; aq[2] = qf[kk][2]; aq[3] = qf[kk][3];
+        } else {
+            ldsm_x4(aq, Qw + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + kk * 16 + 8 * (lane >> 4));
+        }
+#pragma unroll
+        for (int np = 0; np < NK / 16; ++np) {
+            uint32_t bk[4];
+            ldsm_x4(bk, Kw + (np * 16 + (lane & 7) + 8 * (lane >> 4)) * LDS + kk * 16 + 8 * ((lane >> 3) & 1));
+            mma16816(s[2 * np], aq, bk[0], bk[1]);
+            mma16816(s[2 * np + 1], aq, bk[2], bk[3]);
+        }
+    }
+    // ---- mask, running maximum
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int i = 0; i < NT; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int r = e >> 1;
+            const int kp = key0 + i * 8 + 2 * t + (e & 1);
+            const bool seen = row_ok[r] && kp <= row_pos[r] && (window <= 0 || kp > row_pos[r] - window);
+            s[i][e] = seen ? s[i][e] * scale_log2 : -INFINITY;
+            mx[r] = fmaxf(mx[r], s[i][e]);
+        }
+    float alpha[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        const float m_new = fmaxf(m[r], mx[r]);
+        alpha[r] = (m_new == -INFINITY) ? 1.f : exp2f(m[r] - m_new);
+        m[r] = m_new;
+    }
+    float psum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < NT; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int r = e >> 1;
+            const float p = (m[r] == -INFINITY) ? 0.f : exp2f(s[i][e] - m[r]);
+            s[i][e] = p;
+            psum[r] += p;
+        }
+    l[0] = l[0] * alpha[0] + psum[0];
+    l[1] = l[1] * alpha[1] + psum[1];
+#pragma unroll
+    for (int i = 0; i < DT8; ++i) {
+        o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
+        o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+    }
+    // ---- O += P V
+#pragma unroll
+    for (int kk = 0; kk < NK / 16; ++kk) {
+        uint32_t ap[4];
+        ap[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        ap[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        ap[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        ap[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+        for (int dp = 0; dp < D / 16; ++dp) {
+            uint32_t bv[4];
+            ldsm_x4_trans(bv, Vw + (kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + dp * 16 + 8 * (lane >> 4));
+            mma16816(o[2 * dp], ap, bv[0], bv[1]);
+            mma16816(o[2 * dp + 1], ap, bv[2], bv[3]);
+        }
+    }
+}
+
+// Row r of a tile of `rows` rows -> (token offset inside the request's new tokens, q head inside the group).
+struct TileGeometry {
+    int req, tok0, kvh, hg, G, q_begin, q_len, pos0, tok_end, heads_per_tile, rows_used;
+    __device__ __forceinline__ bool row(int r, int& tok, int& gh) const {
+        tok = tok0 + r / heads_per_tile;
+        gh = hg * heads_per_tile + r % heads_per_tile;
+        return r < rows_used && tok < tok_end && gh < G;
+    }
+};
+__device__ __forceinline__ TileGeometry tile_geometry(const AttnArgs& a, int rows) {
+    TileGeometry g;
+    g.G = a.H / a.KV;
+    g.heads_per_tile = g.G < rows ? g.G : rows;
+    const int tokens_per_tile = rows / g.heads_per_tile;
+    const int head_groups = (g.G + g.heads_per_tile - 1) / g.heads_per_tile;
+    g.kvh = blockIdx.y / head_groups;
+    g.hg = blockIdx.y % head_groups;
+    g.req = a.tile_req[blockIdx.x];
+    g.tok0 = a.tile_tok0[blockIdx.x];
+    g.q_begin = a.cu_q[g.req];
+    g.q_len = a.cu_q[g.req + 1] - g.q_begin;
+    g.pos0 = a.ctx_lens[g.req] - g.q_len;
+    g.tok_end = min(g.tok0 + tokens_per_tile, g.q_len);
+    g.rows_used = tokens_per_tile * g.heads_per_tile;
+    return g;
+}
+
+// Q rows [row0, row0 + nrows) of the tile -> shared memory (zeros for rows without a token/head).
+__device__ __forceinline__ void load_q_rows(bf16* Qs, const bf16* __restrict__ q, const AttnArgs& a, const TileGeometry& g,
+                                            int nrows) {
+    constexpr int CPR = D / 8;
+    for (int idx = threadIdx.x; idx < nrows * CPR; idx += MMA_THREADS) {
+        const int r = idx / CPR, c = idx % CPR;
+        int tok, gh;
+        const bool ok = g.row(r, tok, gh);
+        const size_t src = ok ? ((size_t)(g.q_begin + tok) * a.H + (size_t)g.kvh * g.G + gh) * D + c * 8 : 0;
+        cp_async_16(Qs + r * LDS + c * 8, q + src, ok);
+    }
+}
+
+constexpr int PREFILL_ROWS = 64;
+constexpr size_t PREFILL_SMEM = (size_t)(PREFILL_ROWS + 4 * MMA_BN) * LDS * sizeof(bf16);
+
+__global__ void __launch_bounds__(MMA_THREADS)
+attn_mma_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, const bf16* __restrict__ k_cache,
+                        const bf16* __restrict__ v_cache, const AttnArgs a) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* Qs = reinterpret_cast<bf16*>(smem_raw);
+    bf16* Ks = Qs + PREFILL_ROWS * LDS;          // 2 stages
+    bf16* Vs = Ks + 2 * MMA_BN * LDS;            // 2 stages
+    const TileGeometry g = tile_geometry(a, PREFILL_ROWS);
+    if (g.tok0 >= g.tok_end) return;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int* table_row = a.block_table + (size_t)g.req * a.table_width;
+
+    const int k_end = g.pos0 + g.tok_end;
+    const int k_lo = a.window > 0 ? max(0, g.pos0 + g.tok0 - a.window + 1) : 0;
+    const int k_first = (k_lo / MMA_BN) * MMA_BN;
+    const int n_blocks = (k_end - k_first + MMA_BN - 1) / MMA_BN;
+
+    load_q_rows(Qs, q, a, g, PREFILL_ROWS);
+    load_kv_block(Ks, Vs, k_cache, v_cache, table_row, a, g.kvh, k_first, k_lo, k_end, g.req);
+    cp_async_commit();
+
+    int row_pos[2];
+    bool row_ok[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        int tok, gh;
+        row_ok[r] = g.row(warp * 16 + (lane >> 2) + 8 * r, tok, gh);
+        row_pos[r] = g.pos0 + tok;
+    }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[DT8][4];
+#pragma unroll
+    for (int i = 0; i < DT8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    uint32_t qf[Q_IN_REGS ? KSTEPS : 1][4];
+    const bf16* Qw = Qs + warp * 16 * LDS;
+    const float scale_log2 = a.scale * LOG2E;
+    // the last key this warp's rows can see: blocks beyond it are skipped by this warp
+    int warp_last_pos = -1;
+    {
+        int tok, gh;
+        for (int r = 15; r >= 0; --r)
+            if (g.row(warp * 16 + r, tok, gh)) { warp_last_pos = g.pos0 + tok; break; }
+    }
+
+    for (int b = 0; b < n_blocks; ++b) {
+        const int stage = b & 1;
+        if (b + 1 < n_blocks)
+            load_kv_block(Ks + (stage ^ 1) * MMA_BN * LDS, Vs + (stage ^ 1) * MMA_BN * LDS, k_cache, v_cache, table_row, a, g.kvh,
+                          k_first + (b + 1) * MMA_BN, k_lo, k_end, g.req);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        if (b == 0) {
+            if constexpr (Q_IN_REGS) {
+#pragma unroll
+                for (int kk = 0; kk < KSTEPS; ++kk)
+                    ldsm_x4(qf[kk], Qw + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + kk * 16 + 8 * (lane >> 4));
+            }
+        }
+        const int key0 = k_first + b * MMA_BN;
+        if (key0 <= warp_last_pos)
+            warp_block<MMA_BN>(qf, Qw, Ks + stage * MMA_BN * LDS, Vs + stage * MMA_BN * LDS, key0, row_pos, row_ok, a.window,
+                               scale_log2, m, l, o);
+        __syncthreads();   // everyone is done with this stage before the next prefetch overwrites it
+    }
+
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        int tok, gh;
+        if (!g.row(warp * 16 + (lane >> 2) + 8 * r, tok, gh)) continue;
+        const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
+        bf16* dst = out + ((size_t)(g.q_begin + tok) * a.H + (size_t)g.kvh * g.G + gh) * D + 2 * (lane & 3);
+#pragma unroll
+        for (int i = 0; i < DT8; ++i)
+            *reinterpret_cast<__nv_bfloat162*>(dst + i * 8) = __floats2bfloat162_rn(o[i][2 * r] * inv, o[i][2 * r + 1] * inv);
+    }
+}
+
+constexpr int DECODE_ROWS = 16;
+constexpr size_t DECODE_STAGE_SMEM = (size_t)(DECODE_ROWS + 4 * MMA_BN) * LDS * sizeof(bf16);
+constexpr size_t DECODE_MERGE_SMEM = (size_t)4 * DECODE_ROWS * (D + 2) * sizeof(float);
+constexpr size_t DECODE_SMEM = DECODE_STAGE_SMEM > DECODE_MERGE_SMEM ? DECODE_STAGE_SMEM : DECODE_MERGE_SMEM;
+
+// part_o: [tiles, KV * head_groups, splits, 16, D] fp32 (unnormalised, relative to the partial maximum);
+// part_ml: [tiles, KV * head_groups, splits, 16, 2] = (maximum in log2 units, sum). With one split the result goes
+// straight to `out`.
+__global__ void __launch_bounds__(MMA_THREADS)
+attn_mma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
+                       const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
+                       const AttnArgs a) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* Qs = reinterpret_cast<bf16*>(smem_raw);
+    bf16* Ks = Qs + DECODE_ROWS * LDS;
+    bf16* Vs = Ks + 2 * MMA_BN * LDS;
+    const TileGeometry g = tile_geometry(a, DECODE_ROWS);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int splits = gridDim.z, split = blockIdx.z;
+    const size_t unit = ((size_t)blockIdx.x * gridDim.y + blockIdx.y) * splits + split;
+    float* my_ml = part_ml + unit * DECODE_ROWS * 2;
+    float* my_o = part_o + unit * DECODE_ROWS * D;
+
+    int first = 0, count = 0, k_lo = 0, k_end = 0, k_first = 0;
+    const bool live = g.tok0 < g.tok_end;
+    if (live) {
+        k_end = g.pos0 + g.tok_end;
+        k_lo = a.window > 0 ? max(0, g.pos0 + g.tok0 - a.window + 1) : 0;
+        k_first = (k_lo / MMA_BN) * MMA_BN;
+        const int n_blocks = (k_end - k_first + MMA_BN - 1) / MMA_BN;
+        const int per = (n_blocks + splits - 1) / splits;
+        first = split * per;
+        count = max(0, min(per, n_blocks - first));
+    }
+    if (count == 0) {   // nothing for this split (or a tile without rows): an empty partial
+        if (splits > 1)
+            for (int i = threadIdx.x; i < DECODE_ROWS; i += MMA_THREADS) { my_ml[2 * i] = -INFINITY; my_ml[2 * i + 1] = 0.f; }
+        return;
+    }
+    const int* table_row = a.block_table + (size_t)g.req * a.table_width;
+    load_q_rows(Qs, q, a, g, DECODE_ROWS);
+    load_kv_block(Ks, Vs, k_cache, v_cache, table_row, a, g.kvh, k_first + first * MMA_BN, k_lo, k_end, g.req);
+    cp_async_commit();
+
+    int row_pos[2];
+    bool row_ok[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        int tok, gh;
+        row_ok[r] = g.row((lane >> 2) + 8 * r, tok, gh);
+        row_pos[r] = g.pos0 + tok;
+    }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[DT8][4];
+#pragma unroll
+    for (int i = 0; i < DT8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    uint32_t qf[Q_IN_REGS ? KSTEPS : 1][4];
+    const float scale_log2 = a.scale * LOG2E;
+
+    for (int b = 0; b < count; ++b) {
+        const int stage = b & 1;
+        if (b + 1 < count)
+            load_kv_block(Ks + (stage ^ 1) * MMA_BN * LDS, Vs + (stage ^ 1) * MMA_BN * LDS, k_cache, v_cache, table_row, a, g.kvh,
+                          k_first + (first + b + 1) * MMA_BN, k_lo, k_end, g.req);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        if (b == 0) {
+            if constexpr (Q_IN_REGS) {
+#pragma unroll
+                for (int kk = 0; kk < KSTEPS; ++kk)
+                    ldsm_x4(qf[kk], Qs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + kk * 16 + 8 * (lane >> 4));
+            }
+        }
+        const int key0 = k_first + (first + b) * MMA_BN + warp * 16;   // this warp's quarter of the block
+        warp_block<16>(qf, Qs, Ks + (stage * MMA_BN + warp * 16) * LDS, Vs + (stage * MMA_BN + warp * 16) * LDS, key0, row_pos,
+                       row_ok, a.window, scale_log2, m, l, o);
+        __syncthreads();
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    }
+    // ---- merge the four warps (the K/V stages are free now: the loop ended with a barrier)
+    float* mo = reinterpret_cast<float*>(smem_raw);   // [4 warps][16 rows][D + 2]: O then (m, l)
+    constexpr int MS = D + 2;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        float* dst = mo + ((size_t)warp * DECODE_ROWS + (lane >> 2) + 8 * r) * MS;
+#pragma unroll
+        for (int i = 0; i < DT8; ++i) {
+            dst[i * 8 + 2 * (lane & 3)] = o[i][2 * r];
+            dst[i * 8 + 2 * (lane & 3) + 1] = o[i][2 * r + 1];
+        }
+        if ((lane & 3) == 0) { dst[D] = m[r]; dst[D + 1] = l[r]; }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < DECODE_ROWS * D; idx += MMA_THREADS) {
+        const int r = idx / D, d = idx % D;
+        int tok, gh;
+        if (!g.row(r, tok, gh)) continue;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, mo[((size_t)w * DECODE_ROWS + r) * MS + D]);
+        float L = 0.f, O = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float* src = mo + ((size_t)w * DECODE_ROWS + r) * MS;
+            const float f = (src[D] == -INFINITY) ? 0.f : exp2f(src[D] - M);
+            L += src[D + 1] * f;
+            O += src[d] * f;
+        }
+        if (splits == 1) {
+            out[((size_t)(g.q_begin + tok) * a.H + (size_t)g.kvh * g.G + gh) * D + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+        } else {
+            my_o[r * D + d] = O;
+            if (d == 0) { my_ml[2 * r] = M; my_ml[2 * r + 1] = L; }
+        }
+    }
+}
+
+// Merge the splits of every (tile, kv head group, row): one block per (tile, blockIdx.y of the decode grid).
+__global__ void __launch_bounds__(MMA_THREADS)
+attn_combine_kernel(bf16* __restrict__ out, const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                    const AttnArgs a, int splits) {
+    const TileGeometry g = tile_geometry(a, DECODE_ROWS);
+    if (g.tok0 >= g.tok_end) return;
+    const size_t unit0 = ((size_t)blockIdx.x * gridDim.y + blockIdx.y) * splits;
+    for (int idx = threadIdx.x; idx < DECODE_ROWS * D; idx += MMA_THREADS) {
+        const int r = idx / D, d = idx % D;
+        int tok, gh;
+        if (!g.row(r, tok, gh)) continue;
+        float M = -INFINITY;
+        for (int s = 0; s < splits; ++s) M = fmaxf(M, part_ml[((unit0 + s) * DECODE_ROWS + r) * 2]);
+        float L = 0.f, O = 0.f;
+        for (int s = 0; s < splits; ++s) {
+            const float ms = part_ml[((unit0 + s) * DECODE_ROWS + r) * 2];
+            if (ms == -INFINITY) continue;   // an empty split wrote no output rows
+            const float f = exp2f(ms - M);
+            L += part_ml[((unit0 + s) * DECODE_ROWS + r) * 2 + 1] * f;
+            O += part_o[((unit0 + s) * DECODE_ROWS + r) * D + d] * f;
+        }
+        out[((size_t)(g.q_begin + tok) * a.H + (size_t)g.kvh * g.G + gh) * D + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+    }
+}
+}  // namespace
+
 OXR_API int oxr_attn_head_dim() { return D; }
 OXR_API int oxr_attn_tile_rows() { return BM; }
+OXR_API int oxr_attn_prefill_rows() { return PREFILL_ROWS; }
+OXR_API int oxr_attn_decode_rows() { return DECODE_ROWS; }
+
+// bfloat16 on the tensor cores. Two tile lists made by the host: `short` tiles (16 rows each; decoded tokens and
+// portions of a few tokens) go to the split-KV kernel, `long` tiles (64 rows each) to the prefill kernel. With
+// splits > 1 the caller provides scratch: part_o [n_short * KV * groups16 * splits * 16 * D] floats and part_ml
+// [n_short * KV * groups16 * splits * 16 * 2] floats, groups16 = ceil(G / min(G, 16)).
+OXR_API int oxr_paged_attention_bf16(void* out, const void* q, const void* k_cache, const void* v_cache,
+                                     const int* short_req, const int* short_tok0, int n_short, const int* long_req,
+                                     const int* long_tok0, int n_long, const int* cu_q, const int* ctx_lens,
+                                     const int* block_table, int table_width, int page_size, int num_pages, int H, int KV,
+                                     float scale, int window, int splits, float* part_o, float* part_ml, int* status,
+                                     cudaStream_t stream) {
+    if (n_short <= 0 && n_long <= 0) return 0;
+    if (H <= 0 || KV <= 0 || H % KV != 0 || page_size <= 0 || table_width <= 0 || window < 0 || splits < 1) return OXR_BAD_ARGUMENT;
+    if (splits > 1 && (part_o == nullptr || part_ml == nullptr)) return OXR_BAD_ARGUMENT;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_mma_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PREFILL_SMEM);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(attn_mma_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DECODE_SMEM);
+        if (e != cudaSuccess) return 1000 + (int)e;
+        configured = true;
+    }
+    const int G = H / KV;
+    AttnArgs a;
+    a.cu_q = cu_q; a.ctx_lens = ctx_lens; a.block_table = block_table;
+    a.table_width = table_width; a.page_size = page_size; a.num_pages = num_pages; a.H = H; a.KV = KV;
+    a.heads_per_tile = a.tokens_per_tile = a.head_groups = 0;   // the tensor-core kernels derive these from their row count
+    a.scale = scale; a.window = window; a.status = status;
+    if (n_long > 0) {
+        const int hpt = G < PREFILL_ROWS ? G : PREFILL_ROWS;
+        const int groups = (G + hpt - 1) / hpt;
+        if ((size_t)KV * groups > 65535) return OXR_BAD_ARGUMENT;
+        a.tile_req = long_req; a.tile_tok0 = long_tok0;
+        attn_mma_prefill_kernel<<<dim3(n_long, KV * groups), MMA_THREADS, PREFILL_SMEM, stream>>>(
+            (bf16*)out, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, a);
+        int rc = oxr_launch_status();
+        if (rc) return rc;
+    }
+    if (n_short > 0) {
+        const int hpt = G < DECODE_ROWS ? G : DECODE_ROWS;
+        const int groups = (G + hpt - 1) / hpt;
+        if ((size_t)KV * groups > 65535 || splits > 65535) return OXR_BAD_ARGUMENT;
+        a.tile_req = short_req; a.tile_tok0 = short_tok0;
+        attn_mma_decode_kernel<<<dim3(n_short, KV * groups, splits), MMA_THREADS, DECODE_SMEM, stream>>>(
+            (bf16*)out, part_o, part_ml, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, a);
+        int rc = oxr_launch_status();
+        if (rc) return rc;
+        if (splits > 1) {
+            attn_combine_kernel<<<dim3(n_short, KV * groups), MMA_THREADS, 0, stream>>>((bf16*)out, part_o, part_ml, a, splits);
+            rc = oxr_launch_status();
+            if (rc) return rc;
+        }
+    }
+    return 0;
+}
 
 // dtype: 0 = float32, 1 = bfloat16 (q, out and the cache). q, out: [tokens, H, D]. k_cache, v_cache: one layer's
 // pool [num_pages, page_size, KV, D]. The tile list is made by the host with tokens_per_tile =

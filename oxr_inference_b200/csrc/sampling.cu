@@ -20,82 +20,138 @@ __device__ __forceinline__ float uniform_from(unsigned long long seed, unsigned 
     return (float)(z >> 40) * (1.0f / 16777216.0f);
 }
 
-// first index of the row maximum (NaN counts as -inf); every thread returns it
-__device__ int block_argmax(const float* __restrict__ row, int vocab, float* best_val, int* smem_idx, float* smem_val) {
-    constexpr int EMPTY = 0x7fffffff;
-    float bv = -INFINITY;
-    int bi = EMPTY;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {   // ascending i: a strict '>' keeps the first index
-        float v = row[i];
-        if (!(v == v)) v = -INFINITY;
-        if (bi == EMPTY || v > bv) { bv = v; bi = i; }
-    }
-    smem_val[threadIdx.x] = bv;
-    smem_idx[threadIdx.x] = bi;
+constexpr int SAMPLE_CHUNK = 2048;   // vocabulary entries per first-pass block
+
+__device__ __forceinline__ float clean(float v) { return (v == v) ? v : -INFINITY; }   // NaN counts as -inf
+
+// (value, index) maximum with the smaller index winning ties, over the block; result in every thread.
+__device__ __forceinline__ void block_argmax(float& v, int& i, float* sval, int* sidx) {
+    sval[threadIdx.x] = v;
+    sidx[threadIdx.x] = i;
     __syncthreads();
     for (int s = blockDim.x >> 1; s > 0; s >>= 1) {
         if (threadIdx.x < s) {
-            const float ov = smem_val[threadIdx.x + s], mv = smem_val[threadIdx.x];
-            const int oi = smem_idx[threadIdx.x + s], mi = smem_idx[threadIdx.x];
-            if (ov > mv || (ov == mv && oi < mi)) {
-                smem_val[threadIdx.x] = ov;
-                smem_idx[threadIdx.x] = oi;
-            }
+            const float ov = sval[threadIdx.x + s], mv = sval[threadIdx.x];
+            const int oi = sidx[threadIdx.x + s], mi = sidx[threadIdx.x];
+            if (ov > mv || (ov == mv && oi < mi)) { sval[threadIdx.x] = ov; sidx[threadIdx.x] = oi; }
         }
         __syncthreads();
     }
-    const int idx = smem_idx[0];
-    *best_val = smem_val[0];
+    v = sval[0];
+    i = sidx[0];
     __syncthreads();
-    return idx == EMPTY ? 0 : idx;
 }
 
-// One block per row. temperature[r] <= 0 -> greedy.
+// Pass 1, grid (chunks, rows): maximum, its first index and sum of exp((x - max) / T) of one chunk of one row.
 __global__ void __launch_bounds__(SAMPLE_THREADS)
-sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
-              const int* __restrict__ seed_lo, const int* __restrict__ seed_hi, const int* __restrict__ counter) {
+sample_partial_kernel(float* __restrict__ part_max, int* __restrict__ part_idx, float* __restrict__ part_sum,
+                      const float* __restrict__ logits, int vocab, const float* __restrict__ temperature) {
     __shared__ float sval[SAMPLE_THREADS];
     __shared__ int sidx[SAMPLE_THREADS];
-    __shared__ int chosen;
-    const int r = blockIdx.x;
+    const int r = blockIdx.y, chunks = gridDim.x, c = blockIdx.x;
     const float* row = logits + (size_t)r * vocab;
-    float vmax;
-    const int greedy = block_argmax(row, vocab, &vmax, sidx, sval);
+    const int lo = c * SAMPLE_CHUNK, hi = min(vocab, lo + SAMPLE_CHUNK);
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = lo + threadIdx.x; i < hi; i += SAMPLE_THREADS) {
+        const float v = clean(row[i]);
+        if (bi == 0x7fffffff || v > bv) { bv = v; bi = i; }
+    }
+    block_argmax(bv, bi, sval, sidx);
     const float temp = temperature ? temperature[r] : 0.f;
-    if (!(temp > 0.f)) {
+    float sum = 0.f;
+    if (temp > 0.f && bv != -INFINITY) {
+        const float inv_t = 1.f / temp;
+        float part = 0.f;
+        for (int i = lo + threadIdx.x; i < hi; i += SAMPLE_THREADS) part += expf((clean(row[i]) - bv) * inv_t);
+        sum = block_sum(part, sval);
+    }
+    if (threadIdx.x == 0) {
+        part_max[(size_t)r * chunks + c] = bv;
+        part_idx[(size_t)r * chunks + c] = bi;
+        part_sum[(size_t)r * chunks + c] = sum;
+    }
+}
+
+// Pass 2, one block per row: the row's first maximum; with a temperature, the chunk and then the entry in which
+// the cumulative probability (taken in index order) passes uniform(seed, counter) * total.
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_final_kernel(int* __restrict__ out, const float* __restrict__ part_max, const int* __restrict__ part_idx,
+                    const float* __restrict__ part_sum, int chunks, const float* __restrict__ logits, int vocab,
+                    const float* __restrict__ temperature, const int* __restrict__ seed_lo, const int* __restrict__ seed_hi,
+                    const int* __restrict__ counter) {
+    __shared__ float sval[SAMPLE_THREADS];
+    __shared__ int sidx[SAMPLE_THREADS];
+    __shared__ float s_target;
+    __shared__ int s_chunk;
+    const int r = blockIdx.x;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int c = threadIdx.x; c < chunks; c += SAMPLE_THREADS) {   // ascending chunks: ascending indices
+        const float v = part_max[(size_t)r * chunks + c];
+        const int i = part_idx[(size_t)r * chunks + c];
+        if (bi == 0x7fffffff || v > bv) { bv = v; bi = i; }
+    }
+    block_argmax(bv, bi, sval, sidx);
+    const int greedy = bi == 0x7fffffff ? 0 : bi;
+    const float temp = temperature ? temperature[r] : 0.f;
+    if (!(temp > 0.f) || bv == -INFINITY) {
         if (threadIdx.x == 0) out[r] = greedy;
         return;
     }
-    const float inv_t = 1.f / temp;
-    // contiguous segment per thread so that the cumulative sum runs in index order
-    const int seg = (vocab + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
-    const int lo = min(vocab, (int)threadIdx.x * seg), hi = min(vocab, lo + seg);
-    float part = 0.f;
-    for (int i = lo; i < hi; ++i) part += expf((row[i] - vmax) * inv_t);
-    sval[threadIdx.x] = part;
-    __syncthreads();
+    const float inv_t = 1.f / temp, M = bv;
     if (threadIdx.x == 0) {
         float total = 0.f;
-        for (int k = 0; k < SAMPLE_THREADS; ++k) total += sval[k];
+        for (int c = 0; c < chunks; ++c) {
+            const float cm = part_max[(size_t)r * chunks + c];
+            if (cm != -INFINITY) total += part_sum[(size_t)r * chunks + c] * expf((cm - M) * inv_t);
+        }
         const unsigned long long seed = ((unsigned long long)(unsigned int)seed_hi[r] << 32) | (unsigned int)seed_lo[r];
         const float target = uniform_from(seed, (unsigned int)counter[r]) * total;
         float run = 0.f;
-        int k = 0;
-        for (; k < SAMPLE_THREADS - 1; ++k) {
-            if (run + sval[k] > target) break;
-            run += sval[k];
+        int pick = chunks - 1;
+        for (int c = 0; c < chunks; ++c) {
+            const float cm = part_max[(size_t)r * chunks + c];
+            const float w = cm != -INFINITY ? part_sum[(size_t)r * chunks + c] * expf((cm - M) * inv_t) : 0.f;
+            if (run + w > target) { pick = c; break; }
+            run += w;
         }
-        const int a = min(vocab, k * seg), b = min(vocab, a + seg);
+        s_chunk = pick;
+        s_target = target - run;   // what is left to pass inside the chosen chunk
+    }
+    __syncthreads();
+    const float* row = logits + (size_t)r * vocab;
+    const int lo = s_chunk * SAMPLE_CHUNK, hi = min(vocab, lo + SAMPLE_CHUNK);
+    constexpr int PER = SAMPLE_CHUNK / SAMPLE_THREADS;   // contiguous entries per thread
+    const int a = min(hi, lo + (int)threadIdx.x * PER), b = min(hi, a + PER);
+    float mine = 0.f;
+    for (int i = a; i < b; ++i) mine += expf((clean(row[i]) - M) * inv_t);
+    sval[threadIdx.x] = mine;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float run = 0.f;
+        int owner = -1;
+        for (int t = 0; t < SAMPLE_THREADS; ++t) {
+            if (run + sval[t] > s_target) { owner = t; break; }
+            run += sval[t];
+        }
         int pick = -1, last_pos = -1;
-        for (int i = a; i < b; ++i) {
-            const float p = expf((row[i] - vmax) * inv_t);
-            if (p > 0.f) last_pos = i;
-            run += p;
-            if (run > target) { pick = i; break; }
+        if (owner >= 0) {
+            const int oa = min(hi, lo + owner * PER), ob = min(hi, oa + PER);
+            for (int i = oa; i < ob; ++i) {
+                const float p = expf((clean(row[i]) - M) * inv_t);
+                if (p > 0.f) last_pos = i;
+                run += p;
+                if (run > s_target) { pick = i; break; }
+            }
         }
-        if (pick < 0) pick = last_pos >= 0 ? last_pos : greedy;   // rounding left the target just beyond the segment
-        chosen = pick;
-        out[r] = chosen;
+        if (pick < 0) {   // rounding left the target just beyond the sums: the last entry with any probability
+            if (last_pos < 0)
+                for (int i = hi - 1; i >= lo; --i)
+                    if (expf((clean(row[i]) - M) * inv_t) > 0.f) { last_pos = i; break; }
+            pick = last_pos >= 0 ? last_pos : greedy;
+        }
+        out[r] = pick;
     }
 }
 
@@ -124,12 +180,23 @@ __global__ void mark_seen_kernel(unsigned char* __restrict__ seen, const int* __
 }
 }  // namespace
 
-// logits: fp32 [rows, vocab]. temperature / seed_lo / seed_hi / counter: per row; temperature may be null (all greedy).
+OXR_API int oxr_sample_chunks(int vocab) { return (vocab + SAMPLE_CHUNK - 1) / SAMPLE_CHUNK; }
+
+// logits: fp32 [rows, vocab]. temperature / seed_lo / seed_hi / counter: per row; temperature may be null (all
+// greedy). scratch: 3 * rows * oxr_sample_chunks(vocab) 4-byte words, overwritten.
 OXR_API int oxr_sample(int* out, const float* logits, int rows, int vocab, const float* temperature, const int* seed_lo,
-                       const int* seed_hi, const int* counter, cudaStream_t stream) {
+                       const int* seed_hi, const int* counter, void* scratch, cudaStream_t stream) {
     if (rows <= 0) return 0;
-    if (vocab <= 0) return OXR_BAD_ARGUMENT;
-    sample_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(out, logits, vocab, temperature, seed_lo, seed_hi, counter);
+    if (vocab <= 0 || scratch == nullptr || rows > 65535) return OXR_BAD_ARGUMENT;
+    const int chunks = (vocab + SAMPLE_CHUNK - 1) / SAMPLE_CHUNK;
+    float* part_max = (float*)scratch;
+    int* part_idx = (int*)scratch + (size_t)rows * chunks;
+    float* part_sum = (float*)scratch + 2 * (size_t)rows * chunks;
+    sample_partial_kernel<<<dim3(chunks, rows), SAMPLE_THREADS, 0, stream>>>(part_max, part_idx, part_sum, logits, vocab, temperature);
+    int rc = oxr_launch_status();
+    if (rc) return rc;
+    sample_final_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(out, part_max, part_idx, part_sum, chunks, logits, vocab, temperature,
+                                                            seed_lo, seed_hi, counter);
     return oxr_launch_status();
 }
 

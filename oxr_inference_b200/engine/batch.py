@@ -42,7 +42,7 @@ def _align(n: int) -> int:
 class Layout:
     """Offsets (in int32 words) of every array inside the staging block, for given capacities."""
 
-    def __init__(self, tokens: int, requests: int, rows: int, widths: list[int], tile_caps: dict[int, int]):
+    def __init__(self, tokens: int, requests: int, rows: int, widths: list[int], tile_caps: dict[tuple[int, int, int], int]):
         self.tokens, self.requests, self.rows, self.widths, self.tile_caps = tokens, requests, rows, list(widths), dict(tile_caps)
         self.offsets: dict[str, tuple[int, int]] = {}
         at = 0
@@ -62,15 +62,15 @@ class Layout:
         for g, w in enumerate(widths):
             put(f"slots{g}", tokens)
             put(f"table{g}", requests * w)
-        for tpt, cap in tile_caps.items():
-            put(f"tile_req{tpt}", cap)
-            put(f"tile_tok0{tpt}", cap)
+        for spec, cap in tile_caps.items():
+            put(f"tile_req{spec}", cap)
+            put(f"tile_tok0{spec}", cap)
         self.total = at
 
 
 class BatchBuilder:
-    def __init__(self, manager: CacheManager, tile_sizes: list[int], device: torch.device, status: torch.Tensor):
-        self.manager, self.tile_sizes, self.device, self.status = manager, list(tile_sizes), device, status
+    def __init__(self, manager: CacheManager, tile_specs: list[tuple[int, int, int]], device: torch.device, status: torch.Tensor):
+        self.manager, self.tile_specs, self.device, self.status = manager, list(tile_specs), device, status
         self._pinned: torch.Tensor | None = None
         self._copied: torch.cuda.Event | None = None
 
@@ -88,14 +88,19 @@ class BatchBuilder:
         tokens = sum(len(e.tokens) for e in entries)
         rows = sum(len(e.want) for e in entries)
         widths = [m.table_width([e.cache for e in entries], g) for g in range(len(m.pools))]
-        caps = {t: sum((len(e.tokens) + t - 1) // t for e in entries) for t in self.tile_sizes}
+        caps = {spec: sum((len(e.tokens) + spec[0] - 1) // spec[0] for e in entries if spec[1] <= len(e.tokens) <= spec[2])
+                for spec in self.tile_specs}
         return Layout(tokens, len(entries), rows, widths, caps)
 
     def decode_layout(self, bucket: int, max_positions: int) -> Layout:
         """Fixed layout of a decode-only step of ``bucket`` rows with the widest possible block tables."""
         m = self.manager
         width = (max_positions + m.page_size - 1) // m.page_size
-        return Layout(bucket, bucket, bucket, [width] * len(m.pools), {t: bucket for t in self.tile_sizes})
+        return Layout(bucket, bucket, bucket, [width] * len(m.pools), self.decode_tile_caps(bucket))
+
+    def decode_tile_caps(self, bucket: int) -> dict[tuple[int, int, int], int]:
+        """Single-token requests make one tile each in every list that covers them, none in the others."""
+        return {spec: (bucket if spec[1] <= 1 else 0) for spec in self.tile_specs}
 
     # ---- the build
     @torch.inference_mode()
@@ -177,26 +182,31 @@ class BatchBuilder:
             for i in range(n_real, n):
                 slots[int(cu[i])] = fill * P
 
-        tiles_n: dict[int, int] = {}
-        for tpt in self.tile_sizes:
-            treq, ttok = seg(f"tile_req{tpt}"), seg(f"tile_tok0{tpt}")
+        tiles_n: dict[tuple[int, int, int], int] = {}
+        for spec in self.tile_specs:
+            tpt, fewest, most = spec
+            treq, ttok = seg(f"tile_req{spec}"), seg(f"tile_tok0{spec}")
             k = 0
             for i, q in enumerate(q_lens):
+                if not fewest <= q <= most:
+                    continue
                 cnt_i = (q + tpt - 1) // tpt
                 treq[k:k + cnt_i] = i
                 ttok[k:k + cnt_i] = np.arange(cnt_i) * tpt
                 k += cnt_i
-            tiles_n[tpt] = k
+            tiles_n[spec] = k
 
         if device_block is None:
             device_block = torch.empty(layout.total, dtype=torch.int32, device=self.device)
         device_block[:layout.total].copy_(self._pinned[:layout.total], non_blocking=True)
         self._copied = torch.cuda.Event()
         self._copied.record()
-        return self.views(layout, device_block, tiles_n, q_lens, [s + q for s, q in zip(starts, q_lens)])
+        ctx_lens = [s + q for s, q in zip(starts, q_lens)]
+        bound = max(layout.widths) * P if fixed else max(ctx_lens)
+        return self.views(layout, device_block, tiles_n, q_lens, ctx_lens, bound)
 
-    def views(self, layout: Layout, block: torch.Tensor, tiles_n: dict[int, int], q_lens: list[int],
-              ctx_lens: list[int]) -> StepContext:
+    def views(self, layout: Layout, block: torch.Tensor, tiles_n: dict, q_lens: list[int], ctx_lens: list[int],
+              kv_len_bound: int) -> StepContext:
         m = self.manager
 
         def dev(name: str) -> torch.Tensor:
@@ -209,8 +219,8 @@ class BatchBuilder:
             n_tokens=layout.tokens, n_requests=layout.requests, token_ids=dev("token_ids"), positions=dev("positions"),
             req_of_token=dev("req_of_token"), cu_q=dev("cu_q"), ctx_lens=dev("ctx_lens"), state_slots=dev("state_slots"),
             logit_rows=dev("logit_rows"), no_store_slots=dev("no_store"), groups=groups,
-            tiles={t: (dev(f"tile_req{t}"), dev(f"tile_tok0{t}"), tiles_n[t]) for t in self.tile_sizes},
-            q_lens=q_lens, ctx_lens_host=ctx_lens, status=self.status,
+            tiles={t: (dev(f"tile_req{t}"), dev(f"tile_tok0{t}"), tiles_n[t]) for t in self.tile_specs},
+            kv_len_bound=kv_len_bound, q_lens=q_lens, ctx_lens_host=ctx_lens, status=self.status,
         )
         ctx.sampling = {"temperature": dev("temperature").view(torch.float32), "seed_lo": dev("seed_lo"),
                         "seed_hi": dev("seed_hi"), "counter": dev("counter"), "row_slot": dev("row_slot"),

@@ -63,7 +63,7 @@ class DecodeGraphs:
         bucket, width = key
         b = self.runner.builder
         m = self.runner.cache
-        layout = Layout(bucket, bucket, bucket, [width] * len(m.pools), {t: bucket for t in b.tile_sizes})
+        layout = Layout(bucket, bucket, bucket, [width] * len(m.pools), b.decode_tile_caps(bucket))
         block = torch.zeros(layout.total, dtype=torch.int32, device=b.device)
         # Warm-up with the real entries: what they write into the cache is what the replay writes again.
         ctx = b.build(entries, layout=layout, device_block=block)

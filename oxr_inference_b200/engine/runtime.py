@@ -42,7 +42,7 @@ class ModelRunner:
         ops.warm_up(model.head_dims())
         self.cache = CacheManager(model.cache_plan, page_size=page_size, num_pages=num_pages, max_requests=max_requests,
                                   device=rt.device, dtype=rt.dtype)
-        self.builder = BatchBuilder(self.cache, model.tile_sizes, rt.device, rt.status)
+        self.builder = BatchBuilder(self.cache, model.tile_specs, rt.device, rt.status)
         self.steps = 0
 
     # ---- construction

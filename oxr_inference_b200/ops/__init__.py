@@ -83,7 +83,9 @@ def _lib():
         lib.oxr_qk_norm_rope_store.argtypes = [p, p, p, p, p, p, p, p, p, p, i, i, i, i, f, i, c_longlong, i, i, i, i, p, p]
         lib.oxr_gemm_f32_nt.argtypes = [p, p, p, i, i, i, p]
         lib.oxr_gemm_skinny_bf16.argtypes = [p, p, p, i, i, i, i, p]
-        lib.oxr_sample.argtypes = [p, p, i, i, p, p, p, p, p]
+        lib.oxr_sample.argtypes = [p, p, i, i, p, p, p, p, p, p]
+        lib.oxr_sample_chunks.argtypes = [i]
+        lib.oxr_sample_chunks.restype = c_int
         lib.oxr_repetition_penalty.argtypes = [p, p, p, p, i, i, p]
         lib.oxr_mark_seen.argtypes = [p, p, p, i, i, p]
         for name in ("oxr_embedding", "oxr_add_rms_norm", "oxr_silu_mul", "oxr_cast", "oxr_qk_norm_rope_store",
@@ -103,6 +105,8 @@ def _attn_lib(head_dim: int):
         p, i, f = c_void_p, c_int, c_float
         lib.oxr_paged_attention.argtypes = [p, p, p, p, p, p, i, p, p, p, i, i, i, i, i, f, i, i, p, p]
         lib.oxr_paged_attention.restype = c_int
+        lib.oxr_paged_attention_bf16.argtypes = [p, p, p, p, p, p, i, p, p, i, p, p, p, i, i, i, i, i, f, i, i, p, p, p, p]
+        lib.oxr_paged_attention_bf16.restype = c_int
         lib.oxr_attn_tile_rows.restype = c_int
         lib.oxr_attn_head_dim.restype = c_int
         if lib.oxr_attn_head_dim() != head_dim:
@@ -238,26 +242,50 @@ def qk_norm_rope_store(qkv: torch.Tensor, q_weight: torch.Tensor | None, k_weigh
     return q
 
 
-def attention_tile_tokens(num_heads: int, num_kv_heads: int, head_dim: int) -> int:
-    """Tokens of one request that one attention tile covers; the host cuts the step's requests into such tiles."""
+GENERIC_ROWS, DECODE_ROWS, PREFILL_ROWS = 16, 16, 64
+SHORT_MAX_TOKENS = 8
+"""Requests that bring at most this many tokens go to the split-KV kernel, longer portions to the prefill kernel."""
+MAX_SPLITS = 32
+NUM_SMS = 148
+
+
+def _tokens_per_tile(num_heads: int, num_kv_heads: int, rows: int) -> int:
+    return rows // min(num_heads // num_kv_heads, rows)
+
+
+def attention_tile_specs(num_heads: int, num_kv_heads: int, head_dim: int, dtype: torch.dtype) -> list[tuple[int, int, int]]:
+    """The tile lists the attention kernels of this dtype read: (tokens per tile, fewest, most new tokens of the
+    requests the list covers). The host cuts each request's new tokens into such tiles."""
     build.check_head_dim(head_dim)
-    rows = 16
+    big = 1 << 30
+    if dtype == torch.bfloat16:
+        return [(_tokens_per_tile(num_heads, num_kv_heads, DECODE_ROWS), 1, SHORT_MAX_TOKENS),
+                (_tokens_per_tile(num_heads, num_kv_heads, PREFILL_ROWS), SHORT_MAX_TOKENS + 1, big)]
+    return [(_tokens_per_tile(num_heads, num_kv_heads, GENERIC_ROWS), 1, big)]
+
+
+def attention_splits(n_short_tiles: int, num_heads: int, num_kv_heads: int, kv_len_bound: int) -> int:
+    """Into how many pieces the split-KV kernel cuts each request's keys: enough blocks to fill the GPU twice, no
+    piece shorter than 128 keys. Depends only on sizes the host knows before the step (fixed inside a CUDA graph)."""
     group = num_heads // num_kv_heads
-    return rows // min(group, rows)
+    blocks = max(1, n_short_tiles * num_kv_heads * -(-group // min(group, DECODE_ROWS)))
+    want = -(-2 * NUM_SMS // blocks)
+    return max(1, min(want, max(1, kv_len_bound // 128), MAX_SPLITS))
 
 
-def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, *, tile_req: torch.Tensor,
-                    tile_tok0: torch.Tensor, num_tiles: int, cu_q: torch.Tensor, ctx_lens: torch.Tensor,
-                    block_table: torch.Tensor, page_size: int, scale: float, window: int,
-                    status: torch.Tensor) -> torch.Tensor:
+def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, *, tiles: dict, cu_q: torch.Tensor,
+                    ctx_lens: torch.Tensor, block_table: torch.Tensor, page_size: int, scale: float, window: int,
+                    kv_len_bound: int, status: torch.Tensor, generic: bool = False) -> torch.Tensor:
     """Causal grouped-query attention of the step's new tokens over the paged cache
     (oxr_runtime/attention.py:47-109). ``q`` is ``[tokens, H, D]``; ``k_cache`` / ``v_cache`` are one layer's pool
-    ``[pages, page_size, KV, D]``; ``window`` > 0 limits a query to its last ``window`` keys."""
+    ``[pages, page_size, KV, D]``; ``window`` > 0 limits a query to its last ``window`` keys; ``tiles`` maps each
+    spec of :func:`attention_tile_specs` to ``(tile_req, tile_tok0, count)``; ``kv_len_bound`` is an upper bound of
+    the context lengths. float32 runs the fp32 CUDA-core kernel, bfloat16 the tensor-core kernels (``generic``
+    forces the CUDA-core kernel, which then needs the float32 tile spec)."""
     _need(q, "q")
     _need(k_cache, "k_cache", q.dtype)
     _need(v_cache, "v_cache", q.dtype)
-    for t, nm in ((tile_req, "tile_req"), (tile_tok0, "tile_tok0"), (cu_q, "cu_q"), (ctx_lens, "ctx_lens"),
-                  (block_table, "block_table")):
+    for t, nm in ((cu_q, "cu_q"), (ctx_lens, "ctx_lens"), (block_table, "block_table")):
         _need(t, nm, torch.int32)
     _, num_heads, head_dim = q.shape
     num_pages, page, num_kv_heads, d2 = k_cache.shape
@@ -265,11 +293,31 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         raise KernelError(f"cache pool {tuple(k_cache.shape)} does not fit page size {page_size} / head size {head_dim}")
     lib = _attn_lib(head_dim)
     out = torch.empty_like(q)
-    code = lib.oxr_paged_attention(
-        out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), tile_req.data_ptr(), tile_tok0.data_ptr(),
-        num_tiles, cu_q.data_ptr(), ctx_lens.data_ptr(), block_table.data_ptr(), block_table.shape[-1], page_size,
-        num_pages, num_heads, num_kv_heads, float(scale), int(window), _dtype_code(q), status.data_ptr(), _stream())
-    _done(code, "paged_attention")
+    common = (cu_q.data_ptr(), ctx_lens.data_ptr(), block_table.data_ptr(), block_table.shape[-1], page_size, num_pages,
+              num_heads, num_kv_heads, float(scale), int(window))
+    if q.dtype == torch.float32 or generic:
+        (spec,) = attention_tile_specs(num_heads, num_kv_heads, head_dim, torch.float32)
+        tile_req, tile_tok0, n = tiles[spec]
+        code = lib.oxr_paged_attention(out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), tile_req.data_ptr(),
+                                       tile_tok0.data_ptr(), n, *common, _dtype_code(q), status.data_ptr(), _stream())
+        _done(code, "paged_attention")
+        return out
+    short, long_ = attention_tile_specs(num_heads, num_kv_heads, head_dim, torch.bfloat16)
+    s_req, s_tok, n_short = tiles[short]
+    l_req, l_tok, n_long = tiles[long_]
+    splits = attention_splits(n_short, num_heads, num_kv_heads, kv_len_bound) if n_short else 1
+    part_o = part_ml = None
+    if splits > 1:
+        group = num_heads // num_kv_heads
+        units = n_short * num_kv_heads * -(-group // min(group, DECODE_ROWS)) * splits
+        part_o = torch.empty(units * DECODE_ROWS * head_dim, dtype=torch.float32, device=q.device)
+        part_ml = torch.empty(units * DECODE_ROWS * 2, dtype=torch.float32, device=q.device)
+    code = lib.oxr_paged_attention_bf16(out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), s_req.data_ptr(),
+                                        s_tok.data_ptr(), n_short, l_req.data_ptr(), l_tok.data_ptr(), n_long, *common, splits,
+                                        _ptr(part_o), _ptr(part_ml), status.data_ptr(), _stream())
+    global launch_count
+    _done(code, "paged_attention_bf16")
+    launch_count += (1 if n_long and n_short else 0) + (1 if n_short and splits > 1 else 0)
     return out
 
 
@@ -318,9 +366,14 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor | None = None, seed_l
                 raise KernelError(f"sample: {nm} is required with a temperature")
             _need(t, nm, torch.int32)
     out = torch.empty(rows, dtype=torch.int32, device=logits.device)
-    code = _lib().oxr_sample(out.data_ptr(), logits.data_ptr(), rows, vocab, _ptr(temperature), _ptr(seed_lo),
-                             _ptr(seed_hi), _ptr(counter), _stream())
+    lib = _lib()
+    # per row and vocabulary chunk: maximum, its index, sum of exponentials
+    scratch = torch.empty(3 * rows * lib.oxr_sample_chunks(vocab), dtype=torch.int32, device=logits.device)
+    code = lib.oxr_sample(out.data_ptr(), logits.data_ptr(), rows, vocab, _ptr(temperature), _ptr(seed_lo),
+                          _ptr(seed_hi), _ptr(counter), scratch.data_ptr(), _stream())
     _done(code, "sample")
+    global launch_count
+    launch_count += 1  # two kernels
     return out
 
 

@@ -56,8 +56,8 @@ class GroupedQueryAttention(Mixer):
     def cache_need(self) -> PagedKVNeed:
         return PagedKVNeed(self.KV, self.D, self.window)
 
-    def tile_tokens(self) -> int:
-        return ops.attention_tile_tokens(self.H, self.KV, self.D)
+    def tile_specs(self) -> list[tuple[int, int, int]]:
+        return ops.attention_tile_specs(self.H, self.KV, self.D, self.runtime.dtype)
 
     def forward(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
         group = cache.group
@@ -69,8 +69,7 @@ class GroupedQueryAttention(Mixer):
         q = ops.qk_norm_rope_store(qkv, self.q_norm, self.k_norm, cos, sin, ctx.positions,
                                    group.slots if cache.store else ctx.no_store_slots, k_pool, v_pool,
                                    self.H, self.KV, self.D, self.eps, ctx.status)
-        tile_req, tile_tok0, num_tiles = ctx.tiles[self.tile_tokens()]
-        o = ops.paged_attention(q, k_pool, v_pool, tile_req=tile_req, tile_tok0=tile_tok0, num_tiles=num_tiles,
-                                cu_q=ctx.cu_q, ctx_lens=ctx.ctx_lens, block_table=group.block_table,
-                                page_size=group.page_size, scale=self.scale, window=self.window, status=ctx.status)
+        o = ops.paged_attention(q, k_pool, v_pool, tiles=ctx.tiles, cu_q=ctx.cu_q, ctx_lens=ctx.ctx_lens,
+                                block_table=group.block_table, page_size=group.page_size, scale=self.scale,
+                                window=self.window, kv_len_bound=ctx.kv_len_bound, status=ctx.status)
         return self.o_proj(o.view(ctx.n_tokens, self.H * self.D))

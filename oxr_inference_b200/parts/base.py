@@ -7,7 +7,7 @@ Families and what each must provide:
 * **PositionEncoding** – ``tables()``: whatever its mixers consume (rotary: fp32 cos and sin by position).
 * **Mixer** – ``forward(h, ctx, cache) -> y`` over the step's packed tokens; ``cache_need()`` says what it keeps
   between steps: paged keys/values (:class:`PagedKVNeed`), fixed-size per-request state (:class:`StateNeed`),
-  or nothing. ``tile_tokens()`` (optional) asks the batch builder for a tile list.
+  or nothing. ``tile_specs()`` (optional) asks the batch builder for tile lists.
 * **FeedForward** – ``forward(h) -> y``.
 * **Block arrangement** – puts a mixer and a feed-forward behind their norms.
 
@@ -128,8 +128,10 @@ class StepContext:
     logit_rows: torch.Tensor     # int32 [wanted] indices into the token axis
     no_store_slots: torch.Tensor  # int32 [tokens], all -1
     groups: list[GroupView]
-    tiles: dict[int, tuple[torch.Tensor, torch.Tensor, int]] = field(default_factory=dict)
-    """tokens-per-tile -> (tile_req, tile_tok0, number of tiles)"""
+    tiles: dict[tuple[int, int, int], tuple[torch.Tensor, torch.Tensor, int]] = field(default_factory=dict)
+    """(tokens per tile, fewest, most new tokens of the requests covered) -> (tile_req, tile_tok0, number of tiles)"""
+    kv_len_bound: int = 0
+    """No request's context is longer than this; fixed for a CUDA graph, else the step's longest context."""
     q_lens: list[int] = field(default_factory=list)       # host copies, for parts that plan on the host
     ctx_lens_host: list[int] = field(default_factory=list)
     status: torch.Tensor | None = None
@@ -156,8 +158,10 @@ class Mixer(Part):
     def cache_need(self) -> PagedKVNeed | StateNeed | None:
         return None
 
-    def tile_tokens(self) -> int | None:
-        return None
+    def tile_specs(self) -> list[tuple[int, int, int]]:
+        """Tile lists this mixer's kernels want from the batch builder: (tokens per tile, fewest, most new tokens of
+        the requests the list covers)."""
+        return []
 
     def forward(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
         raise NotImplementedError

@@ -88,7 +88,7 @@ class DecoderModel:
         self.schedule = spec.schedule
         self.cache_plan: CachePlan = make_cache_plan(
             [self.blocks[e.layer].mixer.cache_need() for e in self.schedule], [e.cache_of for e in self.schedule])
-        self.tile_sizes = sorted({t for b in self.blocks if (t := b.mixer.tile_tokens()) is not None})
+        self.tile_specs = sorted({spec for b in self.blocks for spec in b.mixer.tile_specs()})
 
     # ---- construction helpers
     def _position(self, spec: PartSpec | None):

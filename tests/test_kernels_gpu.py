@@ -206,46 +206,54 @@ def _paged_case(g, q_lens, ctx_lens, H, KV, D, P, dtype, extra_pages=3):
     return q, k_cache, v_cache, table.to(DEV), cu
 
 
-def _tiles(ops, q_lens, H, KV, D):
-    tpt = ops.attention_tile_tokens(H, KV, D)
-    req, tok = [], []
-    for r, ql in enumerate(q_lens):
-        for t0 in range(0, ql, tpt):
-            req.append(r)
-            tok.append(t0)
-    return (torch.tensor(req, dtype=torch.int32, device=DEV), torch.tensor(tok, dtype=torch.int32, device=DEV), len(req))
+def _tiles(ops, q_lens, H, KV, D, dtype):
+    """The tile lists the kernels of this dtype want: each request's new tokens cut into tiles."""
+    out = {}
+    for spec in ops.attention_tile_specs(H, KV, D, dtype):
+        tpt, fewest, most = spec
+        req, tok = [], []
+        for r, ql in enumerate(q_lens):
+            if fewest <= ql <= most:
+                for t0 in range(0, ql, tpt):
+                    req.append(r)
+                    tok.append(t0)
+        out[spec] = (torch.tensor(req + [0], dtype=torch.int32, device=DEV), torch.tensor(tok + [0], dtype=torch.int32, device=DEV), len(req))
+    return out
 
 
-def _run_attn(ops, q, k_cache, v_cache, table, cu, q_lens, ctx_lens, scale, window):
+def _run_attn(ops, q, k_cache, v_cache, table, cu, q_lens, ctx_lens, scale, window, generic=False):
     H, D, KV, P = q.shape[1], q.shape[2], k_cache.shape[2], k_cache.shape[1]
-    treq, ttok, nt = _tiles(ops, q_lens, H, KV, D)
+    tiles = _tiles(ops, q_lens, H, KV, D, torch.float32 if generic else q.dtype)
     status = ops.new_status(DEV)
-    out = ops.paged_attention(q, k_cache, v_cache, tile_req=treq, tile_tok0=ttok, num_tiles=nt,
-                              cu_q=torch.tensor(cu, dtype=torch.int32, device=DEV),
+    out = ops.paged_attention(q, k_cache, v_cache, tiles=tiles, cu_q=torch.tensor(cu, dtype=torch.int32, device=DEV),
                               ctx_lens=torch.tensor(ctx_lens, dtype=torch.int32, device=DEV), block_table=table,
-                              page_size=P, scale=scale, window=window, status=status)
+                              page_size=P, scale=scale, window=window, kv_len_bound=max(ctx_lens), status=status, generic=generic)
     ops.check_status(status)
     return out
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+KINDS = [(torch.float32, False), (torch.bfloat16, False), (torch.bfloat16, True)]
+KIND_IDS = ["float32", "bfloat16-tensorcore", "bfloat16-generic"]
+
+
+@pytest.mark.parametrize("dtype,generic", KINDS, ids=KIND_IDS)
 @pytest.mark.parametrize("H,KV,D,P", [(4, 2, 16, 16), (6, 2, 32, 8), (8, 1, 64, 16), (5, 5, 48, 4), (20, 1, 16, 16),
-                                      (32, 8, 128, 16), (2, 2, 256, 64), (3, 1, 80, 16)])
+                                      (32, 8, 128, 16), (2, 2, 256, 64), (3, 1, 80, 16), (80, 1, 32, 16)])
 @pytest.mark.parametrize("window", [0, 13])
-def test_paged_attention_mixed_batch(ops, dtype, H, KV, D, P, window):
+def test_paged_attention_mixed_batch(ops, dtype, generic, H, KV, D, P, window):
     g = torch.Generator(device=DEV).manual_seed(20 + D)
-    q_lens = [1, 37, 2, 1, 70]      # decode tokens beside prompt portions
-    ctx_lens = [1, 37, 130, 200, 75]  # position 0 alone; a whole prompt; portions deep into a context
+    q_lens = [1, 37, 2, 1, 70, 8, 9]      # decode tokens beside prompt portions, around the short/long boundary
+    ctx_lens = [1, 37, 130, 200, 75, 8, 140]  # position 0 alone; a whole prompt; portions deep into a context
     q, k_cache, v_cache, table, cu = _paged_case(g, q_lens, ctx_lens, H, KV, D, P, dtype)
     scale = D ** -0.5
-    got = _run_attn(ops, q, k_cache, v_cache, table, cu, q_lens, ctx_lens, scale, window)
+    got = _run_attn(ops, q, k_cache, v_cache, table, cu, q_lens, ctx_lens, scale, window, generic)
     want = KP.paged_attention(q, k_cache, v_cache, cu, ctx_lens, table, scale, window)
     tol = dict(atol=2e-5, rtol=2e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
     torch.testing.assert_close(got.float(), want, **tol)
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_attention_finds_one_far_key_and_respects_the_window_edge(ops, dtype):
+@pytest.mark.parametrize("dtype,generic", KINDS, ids=KIND_IDS)
+def test_attention_finds_one_far_key_and_respects_the_window_edge(ops, dtype, generic):
     """One key among hundreds is made to match the query so strongly that it takes all the weight: if the kernel
     skipped it (a page's edge, the first or last key, the key just inside the window) the output would be far off.
     The key just outside the window is made as strong and must be ignored."""
@@ -266,7 +274,7 @@ def test_attention_finds_one_far_key_and_respects_the_window_edge(ops, dtype):
                 key(target)[kvh] = q[0, kvh * (H // KV)].float().mul(3.0).to(dtype)
                 if window and qpos - window >= 0:
                     key(qpos - window)[kvh] = q[0, kvh * (H // KV)].float().mul(6.0).to(dtype)   # just outside
-            got = _run_attn(ops, q, k_cache, v_cache, table, cu, [1], [ctx], 1.0, window)
+            got = _run_attn(ops, q, k_cache, v_cache, table, cu, [1], [ctx], 1.0, window, generic)
             want = KP.paged_attention(q, k_cache, v_cache, cu, [ctx], table, 1.0, window)
             tol = dict(atol=1e-4, rtol=1e-4) if dtype == torch.float32 else dict(atol=3e-2, rtol=3e-2)
             torch.testing.assert_close(got.float(), want, **tol)
@@ -300,7 +308,35 @@ def test_attention_reports_a_page_outside_the_pool(ops):
 
 def test_attention_refuses_a_head_size_it_cannot_do(ops):
     with pytest.raises(ValueError, match="multiples of 16"):
-        ops.attention_tile_tokens(4, 2, 24)
+        ops.attention_tile_specs(4, 2, 24, torch.bfloat16)
+
+
+@pytest.mark.parametrize("H,KV,D,P", [(32, 8, 128, 16), (6, 2, 32, 8), (16, 1, 64, 16), (2, 2, 256, 32)])
+@pytest.mark.parametrize("window", [0, 300])
+def test_split_kv_decode_on_long_contexts(ops, H, KV, D, P, window):
+    """Few decoded tokens over long contexts: the keys of each request are cut over several blocks whose partial
+    results are merged. One request has a single key (most of its pieces are empty), one a few new tokens."""
+    g = torch.Generator(device=DEV).manual_seed(50 + D)
+    q_lens = [1, 1, 1, 5]
+    ctx_lens = [1500, 333, 1, 1029]
+    assert ops.attention_splits(4 if H // KV <= 16 else 8, H, KV, max(ctx_lens)) > 1
+    q, k_cache, v_cache, table, cu = _paged_case(g, q_lens, ctx_lens, H, KV, D, P, torch.bfloat16)
+    got = _run_attn(ops, q, k_cache, v_cache, table, cu, q_lens, ctx_lens, D ** -0.5, window)
+    want = KP.paged_attention(q, k_cache, v_cache, cu, ctx_lens, table, D ** -0.5, window)
+    torch.testing.assert_close(got.float(), want, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("H,KV,D,P", [(32, 8, 128, 16), (6, 2, 32, 8), (3, 3, 64, 16)])
+def test_prefill_kernel_on_long_portions(ops, H, KV, D, P):
+    """Portions of hundreds of tokens, from position 0 and deep inside a context, several key blocks each."""
+    g = torch.Generator(device=DEV).manual_seed(60 + D)
+    q_lens = [300, 130, 64]
+    ctx_lens = [300, 517, 1000]
+    q, k_cache, v_cache, table, cu = _paged_case(g, q_lens, ctx_lens, H, KV, D, P, torch.bfloat16)
+    for window in (0, 77):
+        got = _run_attn(ops, q, k_cache, v_cache, table, cu, q_lens, ctx_lens, D ** -0.5, window)
+        want = KP.paged_attention(q, k_cache, v_cache, cu, ctx_lens, table, D ** -0.5, window)
+        torch.testing.assert_close(got.float(), want, atol=2e-2, rtol=2e-2)
 
 
 # ------------------------------------------------------------------------------------------------ sampling

@@ -78,7 +78,7 @@ def _one_layer_context(mixer, rt, q_lens, starts, page_size=8):
 
     plan = make_cache_plan([mixer.cache_need()], [None])
     manager = CacheManager(plan, page_size=page_size, num_pages=64, max_requests=4, device=rt.device, dtype=rt.dtype)
-    builder = BatchBuilder(manager, [mixer.tile_tokens()], rt.device, rt.status)
+    builder = BatchBuilder(manager, mixer.tile_specs(), rt.device, rt.status)
     return manager, builder, StepEntry
 
 
