@@ -213,3 +213,80 @@ OXR_API int oxr_mark_seen(unsigned char* seen, const int* slots, const int* toke
     mark_seen_kernel<<<(n + 255) / 256, 256, 0, stream>>>(seen, slots, tokens, n, vocab);
     return oxr_launch_status();
 }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// oxr_sample_static: the same two passes with the scratch in a static device array (see sampling_static.h).
+// ---------------------------------------------------------------------------------------------------------------------
+#include <stdio.h>
+
+#include "sampling_static.h"
+
+static_assert(OXR_SAMPLE_STATIC_CHUNK == SAMPLE_CHUNK, "the header states the chunk size of the first pass");
+
+// Partial results of the first pass: [rows * chunks] maxima, then indices, then sums. Device memory of this
+// library image; in host code the name is only a handle for cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) unsigned int oxr_sample_static_scratch[OXR_SAMPLE_STATIC_WORDS];
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+void* g_static_scratch[MAX_DEVICES];   // device address of the array on each device, looked up at first use
+
+int fail(int code, char* msg, int cap, const char* text) {
+    if (msg != nullptr && cap > 0) snprintf(msg, (size_t)cap, "%s", text);
+    return code;
+}
+}  // namespace
+
+int oxr_sample_static(int* out_tokens, const float* logits, int rows, int vocab, const float* temperature, const int* seed_lo,
+                      const int* seed_hi, const int* counter, cudaStream_t stream, char* error_message, int error_capacity) {
+    char text[256];
+    if (out_tokens == nullptr || logits == nullptr || rows <= 0 || vocab <= 0 || rows > 65535)
+        return fail(OXR_SAMPLE_STATIC_BAD_ARGUMENT, error_message, error_capacity,
+                    "oxr_sample_static: out_tokens and logits must be device pointers, 1 <= rows <= 65535, vocab >= 1");
+    if (temperature != nullptr && (seed_lo == nullptr || seed_hi == nullptr || counter == nullptr))
+        return fail(OXR_SAMPLE_STATIC_BAD_ARGUMENT, error_message, error_capacity,
+                    "oxr_sample_static: seed_lo, seed_hi and counter are required when a temperature is given");
+    const long long chunks = ((long long)vocab + SAMPLE_CHUNK - 1) / SAMPLE_CHUNK;
+    const long long words = 3LL * rows * chunks;
+    if (words > OXR_SAMPLE_STATIC_WORDS) {
+        snprintf(text, sizeof(text),
+                 "oxr_sample_static: %d rows x %lld chunks of %d entries need %lld words of scratch, the static array holds %d "
+                 "(rows * ceil(vocab / %d) must not exceed %d); use oxr_sample with caller-provided scratch",
+                 rows, chunks, SAMPLE_CHUNK, words, OXR_SAMPLE_STATIC_WORDS, SAMPLE_CHUNK, OXR_SAMPLE_STATIC_WORDS / 3);
+        return fail(OXR_SAMPLE_STATIC_TOO_LARGE, error_message, error_capacity, text);
+    }
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess || device < 0 || device >= MAX_DEVICES) {
+        snprintf(text, sizeof(text), "oxr_sample_static: cudaGetDevice gave device %d (%s)", device, cudaGetErrorString(e));
+        return fail(OXR_SAMPLE_STATIC_SETUP_FAILED, error_message, error_capacity, text);
+    }
+    if (g_static_scratch[device] == nullptr) {
+        // once per device, with that device current: the array's address there
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, oxr_sample_static_scratch);
+        if (e != cudaSuccess || ptr == nullptr) {
+            snprintf(text, sizeof(text), "oxr_sample_static: cudaGetSymbolAddress failed on device %d: %s", device,
+                     cudaGetErrorString(e));
+            return fail(OXR_SAMPLE_STATIC_SETUP_FAILED, error_message, error_capacity, text);
+        }
+        g_static_scratch[device] = ptr;
+    }
+    void* scratch = g_static_scratch[device];
+    float* part_max = (float*)scratch;
+    int* part_idx = (int*)scratch + (size_t)rows * chunks;
+    float* part_sum = (float*)scratch + 2 * (size_t)rows * chunks;
+    sample_partial_kernel<<<dim3((unsigned)chunks, rows), SAMPLE_THREADS, 0, stream>>>(part_max, part_idx, part_sum, logits, vocab,
+                                                                                        temperature);
+    e = cudaGetLastError();
+    if (e == cudaSuccess) {
+        sample_final_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(out_tokens, part_max, part_idx, part_sum, (int)chunks, logits, vocab,
+                                                                temperature, seed_lo, seed_hi, counter);
+        e = cudaGetLastError();
+    }
+    if (e != cudaSuccess) {
+        snprintf(text, sizeof(text), "oxr_sample_static: kernel launch failed: %s", cudaGetErrorString(e));
+        return fail(1000 + (int)e, error_message, error_capacity, text);
+    }
+    return 0;
+}
