@@ -236,7 +236,7 @@ int launch_simt(void* out, const void* q, const void* k_cache, const void* v_cac
 //  * attn_mma_prefill_kernel: a tile is 64 rows; warp w owns rows 16w..16w+15 and visits every key block.
 //  * attn_mma_decode_kernel: a tile is 16 rows (one decoded token's whole group of q heads, or a few tokens of a
 //    short portion); the four warps share the rows and each takes a quarter of every 64-key block; the key range
-//    is further split over gridDim.z blocks whose partial (max, sum, output) are merged by attn_combine_kernel.
+//    is further split over gridDim.z blocks; the block that finishes last merges the partial (max, sum, output).
 //
 // K and V blocks are gathered page by page with cp.async (16 bytes per request, zero-filled outside the visible
 // range) into padded shared-memory rows, two stages deep; fragments are read with ldmatrix.
@@ -512,31 +512,37 @@ attn_mma_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
 }
 
 constexpr int DECODE_ROWS = 16;
-constexpr size_t DECODE_STAGE_SMEM = (size_t)(DECODE_ROWS + 4 * MMA_BN) * LDS * sizeof(bf16);
+constexpr int DECODE_STAGES = 3;
+constexpr size_t DECODE_STAGE_SMEM = (size_t)(DECODE_ROWS + DECODE_STAGES * 2 * MMA_BN) * LDS * sizeof(bf16);
 constexpr size_t DECODE_MERGE_SMEM = (size_t)4 * DECODE_ROWS * (D + 2) * sizeof(float);
 constexpr size_t DECODE_SMEM = DECODE_STAGE_SMEM > DECODE_MERGE_SMEM ? DECODE_STAGE_SMEM : DECODE_MERGE_SMEM;
 
-// part_o: [tiles, KV * head_groups, splits, 16, D] fp32 (unnormalised, relative to the partial maximum);
-// part_ml: [tiles, KV * head_groups, splits, 16, 2] = (maximum in log2 units, sum). With one split the result goes
-// straight to `out`.
+// Split-KV attention for tiles of 16 rows. Grid (tiles, KV * head groups, splits). Each block handles one piece
+// of the key range; its four warps each take a quarter of every 64-key block and are merged through shared
+// memory. With one split the result goes straight to `out`. With several, each block writes its partial
+//   part_o  [unit, split, 16, D] fp32 (unnormalised, relative to the partial maximum)
+//   part_ml [unit, split, 16, 2] = (maximum in log2 units, sum)
+// and takes a ticket from counters[unit]; the block that draws the last ticket merges all pieces and resets the
+// counter to zero for the next launch. Nobody waits for anybody.
 __global__ void __launch_bounds__(MMA_THREADS)
 attn_mma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
-                       const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
-                       const AttnArgs a) {
+                       int* __restrict__ counters, const bf16* __restrict__ q, const bf16* __restrict__ k_cache,
+                       const bf16* __restrict__ v_cache, const AttnArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
+    __shared__ int s_ticket;
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);
-    bf16* Ks = Qs + DECODE_ROWS * LDS;
-    bf16* Vs = Ks + 2 * MMA_BN * LDS;
+    bf16* Ks = Qs + DECODE_ROWS * LDS;                      // DECODE_STAGES stages
+    bf16* Vs = Ks + DECODE_STAGES * MMA_BN * LDS;           // DECODE_STAGES stages
     const TileGeometry g = tile_geometry(a, DECODE_ROWS);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int splits = gridDim.z, split = blockIdx.z;
-    const size_t unit = ((size_t)blockIdx.x * gridDim.y + blockIdx.y) * splits + split;
-    float* my_ml = part_ml + unit * DECODE_ROWS * 2;
-    float* my_o = part_o + unit * DECODE_ROWS * D;
+    const size_t unit = (size_t)blockIdx.x * gridDim.y + blockIdx.y;
+    float* my_ml = part_ml + (unit * splits + split) * DECODE_ROWS * 2;
+    float* my_o = part_o + (unit * splits + split) * DECODE_ROWS * D;
+    const int rows_live = g.tok0 < g.tok_end ? (g.tok_end - g.tok0) * g.heads_per_tile : 0;   // rows 0..rows_live-1 may hold a (token, head)
 
     int first = 0, count = 0, k_lo = 0, k_end = 0, k_first = 0;
-    const bool live = g.tok0 < g.tok_end;
-    if (live) {
+    if (rows_live > 0) {
         k_end = g.pos0 + g.tok_end;
         k_lo = a.window > 0 ? max(0, g.pos0 + g.tok0 - a.window + 1) : 0;
         k_first = (k_lo / MMA_BN) * MMA_BN;
@@ -545,114 +551,125 @@ attn_mma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
         first = split * per;
         count = max(0, min(per, n_blocks - first));
     }
-    if (count == 0) {   // nothing for this split (or a tile without rows): an empty partial
-        if (splits > 1)
-            for (int i = threadIdx.x; i < DECODE_ROWS; i += MMA_THREADS) { my_ml[2 * i] = -INFINITY; my_ml[2 * i + 1] = 0.f; }
-        return;
-    }
-    const int* table_row = a.block_table + (size_t)g.req * a.table_width;
-    load_q_rows(Qs, q, a, g, DECODE_ROWS);
-    load_kv_block(Ks, Vs, k_cache, v_cache, table_row, a, g.kvh, k_first + first * MMA_BN, k_lo, k_end, g.req);
-    cp_async_commit();
+    if (rows_live == 0) return;   // every split of this unit returns here: no tickets are drawn
 
-    int row_pos[2];
-    bool row_ok[2];
+    if (count > 0) {
+        const int* table_row = a.block_table + (size_t)g.req * a.table_width;
+        load_q_rows(Qs, q, a, g, DECODE_ROWS);
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        int tok, gh;
-        row_ok[r] = g.row((lane >> 2) + 8 * r, tok, gh);
-        row_pos[r] = g.pos0 + tok;
-    }
-    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-    float o[DT8][4];
+        for (int st = 0; st < DECODE_STAGES - 1; ++st) {
+            if (st < count)
+                load_kv_block(Ks + st * MMA_BN * LDS, Vs + st * MMA_BN * LDS, k_cache, v_cache, table_row, a, g.kvh,
+                              k_first + (first + st) * MMA_BN, k_lo, k_end, g.req);
+            cp_async_commit();
+        }
+        int row_pos[2];
+        bool row_ok[2];
 #pragma unroll
-    for (int i = 0; i < DT8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-    uint32_t qf[Q_IN_REGS ? KSTEPS : 1][4];
-    const float scale_log2 = a.scale * LOG2E;
+        for (int r = 0; r < 2; ++r) {
+            int tok, gh;
+            row_ok[r] = g.row((lane >> 2) + 8 * r, tok, gh);
+            row_pos[r] = g.pos0 + tok;
+        }
+        float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+        float o[DT8][4];
+#pragma unroll
+        for (int i = 0; i < DT8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+        uint32_t qf[Q_IN_REGS ? KSTEPS : 1][4];
+        const float scale_log2 = a.scale * LOG2E;
 
-    for (int b = 0; b < count; ++b) {
-        const int stage = b & 1;
-        if (b + 1 < count)
-            load_kv_block(Ks + (stage ^ 1) * MMA_BN * LDS, Vs + (stage ^ 1) * MMA_BN * LDS, k_cache, v_cache, table_row, a, g.kvh,
-                          k_first + (first + b + 1) * MMA_BN, k_lo, k_end, g.req);
-        cp_async_commit();
-        cp_async_wait<1>();
+        for (int b = 0; b < count; ++b) {
+            const int stage = b % DECODE_STAGES;
+            // block b + STAGES - 1 goes into the stage that block b - 1 used; the barrier at the end of the previous
+            // iteration made it free
+            const int nb = b + DECODE_STAGES - 1;
+            if (nb < count)
+                load_kv_block(Ks + (nb % DECODE_STAGES) * MMA_BN * LDS, Vs + (nb % DECODE_STAGES) * MMA_BN * LDS, k_cache, v_cache,
+                              table_row, a, g.kvh, k_first + (first + nb) * MMA_BN, k_lo, k_end, g.req);
+            cp_async_commit();
+            cp_async_wait<DECODE_STAGES - 1>();
+            __syncthreads();
+            if (b == 0) {
+                if constexpr (Q_IN_REGS) {
+#pragma unroll
+                    for (int kk = 0; kk < KSTEPS; ++kk)
+                        ldsm_x4(qf[kk], Qs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + kk * 16 + 8 * (lane >> 4));
+                }
+            }
+            const int key0 = k_first + (first + b) * MMA_BN + warp * 16;   // this warp's quarter of the block
+            warp_block<16>(qf, Qs, Ks + (stage * MMA_BN + warp * 16) * LDS, Vs + (stage * MMA_BN + warp * 16) * LDS, key0, row_pos,
+                           row_ok, a.window, scale_log2, m, l, o);
+            __syncthreads();
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+            l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+        }
+        // ---- merge the four warps (the K/V stages are free now: the loop ended with a barrier)
+        float* mo = reinterpret_cast<float*>(smem_raw);   // [4 warps][16 rows][D + 2]: O then (m, l)
+        constexpr int MS = D + 2;
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            float* dst = mo + ((size_t)warp * DECODE_ROWS + (lane >> 2) + 8 * r) * MS;
+#pragma unroll
+            for (int i = 0; i < DT8; ++i) {
+                dst[i * 8 + 2 * (lane & 3)] = o[i][2 * r];
+                dst[i * 8 + 2 * (lane & 3) + 1] = o[i][2 * r + 1];
+            }
+            if ((lane & 3) == 0) { dst[D] = m[r]; dst[D + 1] = l[r]; }
+        }
         __syncthreads();
-        if (b == 0) {
-            if constexpr (Q_IN_REGS) {
+        for (int idx = threadIdx.x; idx < rows_live * D; idx += MMA_THREADS) {
+            const int r = idx / D, d = idx % D;
+            int tok, gh;
+            if (!g.row(r, tok, gh)) continue;
+            float M = -INFINITY;
 #pragma unroll
-                for (int kk = 0; kk < KSTEPS; ++kk)
-                    ldsm_x4(qf[kk], Qs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + kk * 16 + 8 * (lane >> 4));
+            for (int w = 0; w < 4; ++w) M = fmaxf(M, mo[((size_t)w * DECODE_ROWS + r) * MS + D]);
+            float L = 0.f, O = 0.f;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float* src = mo + ((size_t)w * DECODE_ROWS + r) * MS;
+                const float f = (src[D] == -INFINITY) ? 0.f : exp2f(src[D] - M);
+                L += src[D + 1] * f;
+                O += src[d] * f;
+            }
+            if (splits == 1) {
+                out[((size_t)(g.q_begin + tok) * a.H + (size_t)g.kvh * g.G + gh) * D + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+            } else {
+                my_o[r * D + d] = O;
+                if (d == 0) { my_ml[2 * r] = M; my_ml[2 * r + 1] = L; }
             }
         }
-        const int key0 = k_first + (first + b) * MMA_BN + warp * 16;   // this warp's quarter of the block
-        warp_block<16>(qf, Qs, Ks + (stage * MMA_BN + warp * 16) * LDS, Vs + (stage * MMA_BN + warp * 16) * LDS, key0, row_pos,
-                       row_ok, a.window, scale_log2, m, l, o);
-        __syncthreads();
+    } else if (splits > 1) {   // nothing for this piece: an empty partial
+        for (int i = threadIdx.x; i < rows_live; i += MMA_THREADS) { my_ml[2 * i] = -INFINITY; my_ml[2 * i + 1] = 0.f; }
     }
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
-        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
-    }
-    // ---- merge the four warps (the K/V stages are free now: the loop ended with a barrier)
-    float* mo = reinterpret_cast<float*>(smem_raw);   // [4 warps][16 rows][D + 2]: O then (m, l)
-    constexpr int MS = D + 2;
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        float* dst = mo + ((size_t)warp * DECODE_ROWS + (lane >> 2) + 8 * r) * MS;
-#pragma unroll
-        for (int i = 0; i < DT8; ++i) {
-            dst[i * 8 + 2 * (lane & 3)] = o[i][2 * r];
-            dst[i * 8 + 2 * (lane & 3) + 1] = o[i][2 * r + 1];
-        }
-        if ((lane & 3) == 0) { dst[D] = m[r]; dst[D + 1] = l[r]; }
-    }
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < DECODE_ROWS * D; idx += MMA_THREADS) {
-        const int r = idx / D, d = idx % D;
-        int tok, gh;
-        if (!g.row(r, tok, gh)) continue;
-        float M = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) M = fmaxf(M, mo[((size_t)w * DECODE_ROWS + r) * MS + D]);
-        float L = 0.f, O = 0.f;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            const float* src = mo + ((size_t)w * DECODE_ROWS + r) * MS;
-            const float f = (src[D] == -INFINITY) ? 0.f : exp2f(src[D] - M);
-            L += src[D + 1] * f;
-            O += src[d] * f;
-        }
-        if (splits == 1) {
-            out[((size_t)(g.q_begin + tok) * a.H + (size_t)g.kvh * g.G + gh) * D + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
-        } else {
-            my_o[r * D + d] = O;
-            if (d == 0) { my_ml[2 * r] = M; my_ml[2 * r + 1] = L; }
-        }
-    }
-}
+    if (splits == 1) return;
 
-// Merge the splits of every (tile, kv head group, row): one block per (tile, blockIdx.y of the decode grid).
-__global__ void __launch_bounds__(MMA_THREADS)
-attn_combine_kernel(bf16* __restrict__ out, const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                    const AttnArgs a, int splits) {
-    const TileGeometry g = tile_geometry(a, DECODE_ROWS);
-    if (g.tok0 >= g.tok_end) return;
-    const size_t unit0 = ((size_t)blockIdx.x * gridDim.y + blockIdx.y) * splits;
-    for (int idx = threadIdx.x; idx < DECODE_ROWS * D; idx += MMA_THREADS) {
+    // ---- ticket: the last piece to finish merges them all
+    __threadfence();          // this block's partial is visible device-wide before its ticket is
+    __syncthreads();
+    if (threadIdx.x == 0) s_ticket = atomicAdd(&counters[unit], 1);
+    __syncthreads();
+    if (s_ticket != splits - 1) return;
+    __threadfence();          // order the reads below after the tickets of the other pieces
+    if (threadIdx.x == 0) counters[unit] = 0;   // ready for the next launch (nobody else touches it any more)
+    const float* all_ml = part_ml + unit * splits * DECODE_ROWS * 2;
+    const float* all_o = part_o + unit * splits * DECODE_ROWS * D;
+    for (int idx = threadIdx.x; idx < rows_live * D; idx += MMA_THREADS) {
         const int r = idx / D, d = idx % D;
         int tok, gh;
         if (!g.row(r, tok, gh)) continue;
         float M = -INFINITY;
-        for (int s = 0; s < splits; ++s) M = fmaxf(M, part_ml[((unit0 + s) * DECODE_ROWS + r) * 2]);
+        for (int s2 = 0; s2 < splits; ++s2) M = fmaxf(M, __ldcg(all_ml + ((size_t)s2 * DECODE_ROWS + r) * 2));
         float L = 0.f, O = 0.f;
-        for (int s = 0; s < splits; ++s) {
-            const float ms = part_ml[((unit0 + s) * DECODE_ROWS + r) * 2];
-            if (ms == -INFINITY) continue;   // an empty split wrote no output rows
+        for (int s2 = 0; s2 < splits; ++s2) {
+            const float ms = __ldcg(all_ml + ((size_t)s2 * DECODE_ROWS + r) * 2);
+            if (ms == -INFINITY) continue;   // an empty piece wrote no output rows
             const float f = exp2f(ms - M);
-            L += part_ml[((unit0 + s) * DECODE_ROWS + r) * 2 + 1] * f;
-            O += part_o[((unit0 + s) * DECODE_ROWS + r) * D + d] * f;
+            L += __ldcg(all_ml + ((size_t)s2 * DECODE_ROWS + r) * 2 + 1) * f;
+            O += __ldcg(all_o + ((size_t)s2 * DECODE_ROWS + r) * D + d) * f;
         }
         out[((size_t)(g.q_begin + tok) * a.H + (size_t)g.kvh * g.G + gh) * D + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
     }
@@ -666,17 +683,18 @@ OXR_API int oxr_attn_decode_rows() { return DECODE_ROWS; }
 
 // bfloat16 on the tensor cores. Two tile lists made by the host: `short` tiles (16 rows each; decoded tokens and
 // portions of a few tokens) go to the split-KV kernel, `long` tiles (64 rows each) to the prefill kernel. With
-// splits > 1 the caller provides scratch: part_o [n_short * KV * groups16 * splits * 16 * D] floats and part_ml
-// [n_short * KV * groups16 * splits * 16 * 2] floats, groups16 = ceil(G / min(G, 16)).
+// splits > 1 the caller provides scratch: part_o [n_short * KV * groups16 * splits * 16 * D] floats, part_ml
+// [n_short * KV * groups16 * splits * 16 * 2] floats and counters [n_short * KV * groups16] ints that are zero
+// before the first launch (the kernel leaves them zero), groups16 = ceil(G / min(G, 16)).
 OXR_API int oxr_paged_attention_bf16(void* out, const void* q, const void* k_cache, const void* v_cache,
                                      const int* short_req, const int* short_tok0, int n_short, const int* long_req,
                                      const int* long_tok0, int n_long, const int* cu_q, const int* ctx_lens,
                                      const int* block_table, int table_width, int page_size, int num_pages, int H, int KV,
-                                     float scale, int window, int splits, float* part_o, float* part_ml, int* status,
-                                     cudaStream_t stream) {
+                                     float scale, int window, int splits, float* part_o, float* part_ml, int* counters,
+                                     int* status, cudaStream_t stream) {
     if (n_short <= 0 && n_long <= 0) return 0;
     if (H <= 0 || KV <= 0 || H % KV != 0 || page_size <= 0 || table_width <= 0 || window < 0 || splits < 1) return OXR_BAD_ARGUMENT;
-    if (splits > 1 && (part_o == nullptr || part_ml == nullptr)) return OXR_BAD_ARGUMENT;
+    if (splits > 1 && (part_o == nullptr || part_ml == nullptr || counters == nullptr)) return OXR_BAD_ARGUMENT;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_mma_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PREFILL_SMEM);
@@ -707,14 +725,9 @@ OXR_API int oxr_paged_attention_bf16(void* out, const void* q, const void* k_cac
         if ((size_t)KV * groups > 65535 || splits > 65535) return OXR_BAD_ARGUMENT;
         a.tile_req = short_req; a.tile_tok0 = short_tok0;
         attn_mma_decode_kernel<<<dim3(n_short, KV * groups, splits), MMA_THREADS, DECODE_SMEM, stream>>>(
-            (bf16*)out, part_o, part_ml, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, a);
+            (bf16*)out, part_o, part_ml, counters, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, a);
         int rc = oxr_launch_status();
         if (rc) return rc;
-        if (splits > 1) {
-            attn_combine_kernel<<<dim3(n_short, KV * groups), MMA_THREADS, 0, stream>>>((bf16*)out, part_o, part_ml, a, splits);
-            rc = oxr_launch_status();
-            if (rc) return rc;
-        }
     }
     return 0;
 }

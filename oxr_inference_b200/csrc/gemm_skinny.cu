@@ -30,11 +30,10 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint3
 }
 
 constexpr int SKINNY_WARPS = 8;
-constexpr int SKINNY_UNROLL = 4;
 
 // TILES = number of 8-row groups of X (M <= 8 * TILES). TO = output type.
 template <int TILES, typename TO>
-__global__ void __launch_bounds__(SKINNY_WARPS * 32)
+__global__ void __launch_bounds__(SKINNY_WARPS * 32, TILES <= 2 ? 2 : 1)
 gemm_skinny_kernel(TO* __restrict__ C, const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W, int M,
                    int N, int K) {
     __shared__ float partial[SKINNY_WARPS][16][8 * TILES + 1];
@@ -52,6 +51,7 @@ gemm_skinny_kernel(TO* __restrict__ C, const __nv_bfloat16* __restrict__ X, cons
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
 
+    constexpr int SKINNY_UNROLL = TILES <= 2 ? 8 : 4;   // 16-byte weight loads in flight per lane and row
     const int chunks = (K + 31) / 32;
     const uint4 zero = make_uint4(0, 0, 0, 0);
     for (int c0 = warp; c0 < chunks; c0 += SKINNY_WARPS * SKINNY_UNROLL) {

@@ -105,7 +105,7 @@ def _attn_lib(head_dim: int):
         p, i, f = c_void_p, c_int, c_float
         lib.oxr_paged_attention.argtypes = [p, p, p, p, p, p, i, p, p, p, i, i, i, i, i, f, i, i, p, p]
         lib.oxr_paged_attention.restype = c_int
-        lib.oxr_paged_attention_bf16.argtypes = [p, p, p, p, p, p, i, p, p, i, p, p, p, i, i, i, i, i, f, i, i, p, p, p, p]
+        lib.oxr_paged_attention_bf16.argtypes = [p, p, p, p, p, p, i, p, p, i, p, p, p, i, i, i, i, i, f, i, i, p, p, p, p, p]
         lib.oxr_paged_attention_bf16.restype = c_int
         lib.oxr_attn_tile_rows.restype = c_int
         lib.oxr_attn_head_dim.restype = c_int
@@ -306,19 +306,33 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     s_req, s_tok, n_short = tiles[short]
     l_req, l_tok, n_long = tiles[long_]
     splits = attention_splits(n_short, num_heads, num_kv_heads, kv_len_bound) if n_short else 1
-    part_o = part_ml = None
+    part_o = part_ml = counters = None
     if splits > 1:
         group = num_heads // num_kv_heads
-        units = n_short * num_kv_heads * -(-group // min(group, DECODE_ROWS)) * splits
-        part_o = torch.empty(units * DECODE_ROWS * head_dim, dtype=torch.float32, device=q.device)
-        part_ml = torch.empty(units * DECODE_ROWS * 2, dtype=torch.float32, device=q.device)
+        units = n_short * num_kv_heads * -(-group // min(group, DECODE_ROWS))
+        part_o = torch.empty(units * splits * DECODE_ROWS * head_dim, dtype=torch.float32, device=q.device)
+        part_ml = torch.empty(units * splits * DECODE_ROWS * 2, dtype=torch.float32, device=q.device)
+        counters = _ticket_counters(q.device, units)
     code = lib.oxr_paged_attention_bf16(out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), s_req.data_ptr(),
                                         s_tok.data_ptr(), n_short, l_req.data_ptr(), l_tok.data_ptr(), n_long, *common, splits,
-                                        _ptr(part_o), _ptr(part_ml), status.data_ptr(), _stream())
+                                        _ptr(part_o), _ptr(part_ml), _ptr(counters), status.data_ptr(), _stream())
     global launch_count
     _done(code, "paged_attention_bf16")
-    launch_count += (1 if n_long and n_short else 0) + (1 if n_short and splits > 1 else 0)
+    launch_count += 1 if n_long and n_short else 0
     return out
+
+
+_counters: dict[torch.device, torch.Tensor] = {}
+
+
+def _ticket_counters(device: torch.device, units: int) -> torch.Tensor:
+    """Zeroed ticket counters of the split-KV kernel, one per (tile, KV head group). The kernel leaves them zero, so
+    one array serves every launch on a stream."""
+    t = _counters.get(device)
+    if t is None or t.numel() < units:
+        t = torch.zeros(max(units, 1 << 16), dtype=torch.int32, device=device)
+        _counters[device] = t
+    return t
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
