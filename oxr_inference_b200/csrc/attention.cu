@@ -36,6 +36,7 @@ struct AttnArgs {
     const int* block_table;  // [n, table_width] page ids; entries of released pages may hold anything
     int table_width;
     int page_size;
+    int page_shift;          // log2(page_size) when it is a power of two, else -1
     int num_pages;
     int H, KV;
     int heads_per_tile;      // q heads of one KV head handled by one tile: min(G, BM)
@@ -278,27 +279,42 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 // Gather keys [k0, k0 + MMA_BN) of one request into Ks / Vs (rows of LDS elements); keys outside [k_lo, k_end)
-// become zeros. All MMA_THREADS threads take part.
+// become zeros. All MMA_THREADS threads take part: a thread keeps its 16-byte column and walks down the rows, so
+// that per row it needs one block-table lookup, one multiply and two cp.async. page_shift >= 0 when the page size
+// is a power of two.
 __device__ __forceinline__ void load_kv_block(bf16* Ks, bf16* Vs, const bf16* __restrict__ k_cache,
                                               const bf16* __restrict__ v_cache, const int* __restrict__ table_row,
                                               const AttnArgs& a, int kvh, int k0, int k_lo, int k_end, int req) {
-    constexpr int CPR = D / 8;   // 16-byte chunks per row
-    for (int idx = threadIdx.x; idx < MMA_BN * CPR; idx += MMA_THREADS) {
-        const int j = idx / CPR, c = idx % CPR;
+    constexpr int CPR = D / 8;                                    // 16-byte chunks per row
+    constexpr int ROW_STEP = MMA_THREADS / CPR > 0 ? MMA_THREADS / CPR : 1;
+    static_assert(CPR <= MMA_THREADS, "a row has at most as many 16-byte chunks as the block has threads");
+    if (threadIdx.x >= ROW_STEP * CPR) return;                   // head sizes whose chunk count does not divide the block
+    const int c = threadIdx.x % CPR;
+    const size_t row_elems = (size_t)a.KV * D;
+    const size_t col = (size_t)kvh * D + c * 8;
+    const int smem_col = c * 8;
+    for (int j = threadIdx.x / CPR; j < MMA_BN; j += ROW_STEP) {
         const int kp = k0 + j;
         bool ok = kp >= k_lo && kp < k_end;
         size_t base = 0;
         if (ok) {
-            const int page = table_row[kp / a.page_size];
+            int page, slot;
+            if (a.page_shift >= 0) {
+                page = table_row[kp >> a.page_shift];
+                slot = (page << a.page_shift) + (kp & (a.page_size - 1));
+            } else {
+                page = table_row[kp / a.page_size];
+                slot = page * a.page_size + kp % a.page_size;
+            }
             if (page < 0 || page >= a.num_pages) {
                 if (c == 0) oxr_report(a.status, OXR_BAD_PAGE, req);
                 ok = false;
             } else {
-                base = (((size_t)page * a.page_size + kp % a.page_size) * a.KV + kvh) * D + c * 8;
+                base = (size_t)slot * row_elems + col;
             }
         }
-        cp_async_16(Ks + j * LDS + c * 8, k_cache + base, ok);
-        cp_async_16(Vs + j * LDS + c * 8, v_cache + base, ok);
+        cp_async_16(Ks + j * LDS + smem_col, k_cache + base, ok);
+        cp_async_16(Vs + j * LDS + smem_col, v_cache + base, ok);
     }
 }
 
@@ -707,6 +723,8 @@ OXR_API int oxr_paged_attention_bf16(void* out, const void* q, const void* k_cac
     AttnArgs a;
     a.cu_q = cu_q; a.ctx_lens = ctx_lens; a.block_table = block_table;
     a.table_width = table_width; a.page_size = page_size; a.num_pages = num_pages; a.H = H; a.KV = KV;
+    a.page_shift = -1;
+    for (int sh = 0; sh < 30; ++sh) if ((1 << sh) == page_size) a.page_shift = sh;
     a.heads_per_tile = a.tokens_per_tile = a.head_groups = 0;   // the tensor-core kernels derive these from their row count
     a.scale = scale; a.window = window; a.status = status;
     if (n_long > 0) {
@@ -745,6 +763,8 @@ OXR_API int oxr_paged_attention(void* out, const void* q, const void* k_cache, c
     AttnArgs a;
     a.tile_req = tile_req; a.tile_tok0 = tile_tok0; a.cu_q = cu_q; a.ctx_lens = ctx_lens; a.block_table = block_table;
     a.table_width = table_width; a.page_size = page_size; a.num_pages = num_pages; a.H = H; a.KV = KV;
+    a.page_shift = -1;
+    for (int sh = 0; sh < 30; ++sh) if ((1 << sh) == page_size) a.page_shift = sh;
     a.heads_per_tile = G < BM ? G : BM;
     a.tokens_per_tile = BM / a.heads_per_tile;
     a.head_groups = (G + a.heads_per_tile - 1) / a.heads_per_tile;

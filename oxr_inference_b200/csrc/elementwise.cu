@@ -110,6 +110,65 @@ __global__ void add_rms_norm_kernel(T* __restrict__ out, float* __restrict__ res
     }
 }
 
+// Fast path for bf16 rows that are a whole number of 16-byte words: a thread takes up to VEC_PER_THREAD words of 8
+// elements, loads everything it needs up front (x as one 16-byte load, the residual as two), and writes from
+// registers, so the row is read once and no load waits behind a store.
+template <int VEC_PER_THREAD>
+__global__ void add_rms_norm_bf16x8_kernel(__nv_bfloat16* __restrict__ out, float* residual_out, const __nv_bfloat16* __restrict__ x,
+                                           const float* residual_in, const float* __restrict__ weight,
+                                           const int* __restrict__ rows, int hidden, float eps) {
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    const size_t src = (size_t)(rows ? rows[r] : r) * hidden;
+    const size_t dst = (size_t)r * hidden;
+    const int words = hidden >> 3;
+    float v[VEC_PER_THREAD][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VEC_PER_THREAD; ++i) {
+        const int w = threadIdx.x + i * blockDim.x;
+        if (w < words) {
+            const uint4 xv = *reinterpret_cast<const uint4*>(x + src + (size_t)w * 8);
+            const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float2 f = __bfloat1622float2(xp[k]);
+                v[i][2 * k] = f.x;
+                v[i][2 * k + 1] = f.y;
+            }
+            if (residual_in) {
+                const float4 r0 = *reinterpret_cast<const float4*>(residual_in + src + (size_t)w * 8);
+                const float4 r1 = *reinterpret_cast<const float4*>(residual_in + src + (size_t)w * 8 + 4);
+                v[i][0] += r0.x; v[i][1] += r0.y; v[i][2] += r0.z; v[i][3] += r0.w;
+                v[i][4] += r1.x; v[i][5] += r1.y; v[i][6] += r1.z; v[i][7] += r1.w;
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) ss += v[i][k] * v[i][k];
+        }
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)hidden + eps);
+#pragma unroll
+    for (int i = 0; i < VEC_PER_THREAD; ++i) {
+        const int w = threadIdx.x + i * blockDim.x;
+        if (w < words) {
+            if (residual_out) {
+                *reinterpret_cast<float4*>(residual_out + dst + (size_t)w * 8) = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
+                *reinterpret_cast<float4*>(residual_out + dst + (size_t)w * 8 + 4) = make_float4(v[i][4], v[i][5], v[i][6], v[i][7]);
+            }
+            const float4 w0 = *reinterpret_cast<const float4*>(weight + (size_t)w * 8);
+            const float4 w1 = *reinterpret_cast<const float4*>(weight + (size_t)w * 8 + 4);
+            uint4 o;
+            __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
+            op[0] = __floats2bfloat162_rn(v[i][0] * inv * w0.x, v[i][1] * inv * w0.y);
+            op[1] = __floats2bfloat162_rn(v[i][2] * inv * w0.z, v[i][3] * inv * w0.w);
+            op[2] = __floats2bfloat162_rn(v[i][4] * inv * w1.x, v[i][5] * inv * w1.y);
+            op[3] = __floats2bfloat162_rn(v[i][6] * inv * w1.z, v[i][7] * inv * w1.w);
+            *reinterpret_cast<uint4*>(out + dst + (size_t)w * 8) = o;
+        }
+    }
+}
+
 // dtype: 0 = float32, 1 = bfloat16 (of x and out). residual_in / residual_out / rows may be null.
 // residual_out may alias residual_in only when rows is null (each element is read before it is written by
 // the same thread).
@@ -118,6 +177,19 @@ OXR_API int oxr_add_rms_norm(void* out, float* residual_out, const void* x, cons
                              cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (rows != nullptr && residual_out != nullptr && residual_out == residual_in) return OXR_BAD_ARGUMENT;
+    if (dtype == 1 && hidden % 8 == 0 && hidden <= 8 * 4 * 512 && (uintptr_t)out % 16 == 0 && (uintptr_t)x % 16 == 0 &&
+        (uintptr_t)weight % 16 == 0 && (residual_in == nullptr || (uintptr_t)residual_in % 16 == 0) &&
+        (residual_out == nullptr || (uintptr_t)residual_out % 16 == 0)) {
+        const int words = hidden / 8;
+        const int vt = words <= 128 ? 128 : (words <= 256 ? 256 : 512);
+        const int per = (words + vt - 1) / vt;
+#define NORM_VEC(P) add_rms_norm_bf16x8_kernel<P><<<n_rows, vt, 0, stream>>>((__nv_bfloat16*)out, residual_out, (const __nv_bfloat16*)x, residual_in, weight, rows, hidden, eps)
+        if (per <= 1) NORM_VEC(1);
+        else if (per <= 2) NORM_VEC(2);
+        else NORM_VEC(4);
+#undef NORM_VEC
+        return oxr_launch_status();
+    }
     int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
     const int cache_floats = hidden <= 10240 ? hidden : 0;   // 40 KB of row cache at most
     const size_t smem = (32 + cache_floats) * sizeof(float);

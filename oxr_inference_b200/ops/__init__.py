@@ -264,12 +264,17 @@ def attention_tile_specs(num_heads: int, num_kv_heads: int, head_dim: int, dtype
     return [(_tokens_per_tile(num_heads, num_kv_heads, GENERIC_ROWS), 1, big)]
 
 
+DECODE_BLOCKS_PER_SM = 2
+"""Blocks of the split-KV kernel that fit on one SM (its shared memory is the limit)."""
+
+
 def attention_splits(n_short_tiles: int, num_heads: int, num_kv_heads: int, kv_len_bound: int) -> int:
-    """Into how many pieces the split-KV kernel cuts each request's keys: enough blocks to fill the GPU twice, no
-    piece shorter than 128 keys. Depends only on sizes the host knows before the step (fixed inside a CUDA graph)."""
+    """Into how many pieces the split-KV kernel cuts each request's keys: as many as still run all at once (one wave
+    of blocks), no piece shorter than 128 keys. Depends only on sizes the host knows before the step (fixed inside a
+    CUDA graph)."""
     group = num_heads // num_kv_heads
     blocks = max(1, n_short_tiles * num_kv_heads * -(-group // min(group, DECODE_ROWS)))
-    want = -(-2 * NUM_SMS // blocks)
+    want = (NUM_SMS * DECODE_BLOCKS_PER_SM) // blocks
     return max(1, min(want, max(1, kv_len_bound // 128), MAX_SPLITS))
 
 

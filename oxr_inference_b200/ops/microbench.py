@@ -1,0 +1,136 @@
+"""Times one kernel of this package alone at given sizes (CUDA events around a CUDA graph of repeated calls, after
+warm-up, inputs rotated so that every call reads memory that is not in L2), and prints one JSON line. Also the
+command to put under ``ncu``.
+
+    python -m oxr_inference_b200.ops.microbench gemm --m 8 --n 24576 --k 4096
+    python -m oxr_inference_b200.ops.microbench attention --batch 8 --q-len 1 --context 2048
+    python -m oxr_inference_b200.ops.microbench attention --batch 1 --q-len 2048 --context 2048
+    python -m oxr_inference_b200.ops.microbench norm --rows 8 --hidden 4096
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+
+import torch
+
+from oxr_inference_b200 import ops
+
+
+def _time(fn, reps: int, warmup: int = 3) -> float:
+    """Microseconds per call on the device: `reps` calls are captured into one CUDA graph (as a decode step's kernels
+    are) and the graph's replay is timed, so host launch overhead is not part of the number."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for i in range(warmup):
+            fn(i)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(reps):
+            fn(i)
+    times = []
+    for _ in range(5):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b) * 1e3 / reps)
+    return statistics.median(times)
+
+
+def gemm(args) -> dict:
+    m, n, k = args.m, args.n, args.k
+    copies = max(2, int(300e6 // (n * k * 2)) + 1)  # rotate over > 2 x L2 of weights
+    ws = [torch.randn(n, k, device="cuda").mul_(0.02).bfloat16() for _ in range(copies)]
+    x = torch.randn(m, k, device="cuda").bfloat16()
+    out_dtype = torch.float32 if args.fp32_out else torch.bfloat16
+    us = _time(lambda i: ops.linear(x, ws[i % copies], out_dtype), args.reps)
+    bytes_ = n * k * 2 + m * k * 2 + m * n * (4 if args.fp32_out else 2)
+    return {"kernel": "linear", "m": m, "n": n, "k": k, "us": round(us, 2), "GB/s": round(bytes_ / us / 1e3, 1),
+            "TFLOP/s": round(2 * m * n * k / us / 1e6, 2)}
+
+
+def attention(args) -> dict:
+    H, KV, D, P = args.heads, args.kv_heads, args.head_dim, args.page_size
+    B, q_len, ctx = args.batch, args.q_len, args.context
+    pages_per = -(-ctx // P)
+    layers = max(2, int(300e6 // (B * pages_per * P * KV * D * 2 * 2)) + 1)
+    n_pages = B * pages_per
+    pools = [(torch.randn(n_pages, P, KV, D, device="cuda").bfloat16(), torch.randn(n_pages, P, KV, D, device="cuda").bfloat16())
+             for _ in range(layers)]
+    table = torch.randperm(n_pages, device="cuda").int().view(B, pages_per).contiguous()
+    q = torch.randn(B * q_len, H, D, device="cuda").bfloat16()
+    cu = torch.arange(0, (B + 1) * q_len, q_len, dtype=torch.int32, device="cuda")
+    ctx_lens = torch.full((B,), ctx, dtype=torch.int32, device="cuda")
+    tiles = {}
+    for spec in ops.attention_tile_specs(H, KV, D, torch.bfloat16):
+        tpt, lo, hi = spec
+        req, tok = [], []
+        if lo <= q_len <= hi:
+            for r in range(B):
+                for t0 in range(0, q_len, tpt):
+                    req.append(r)
+                    tok.append(t0)
+        tiles[spec] = (torch.tensor(req + [0], dtype=torch.int32, device="cuda"), torch.tensor(tok + [0], dtype=torch.int32, device="cuda"), len(req))
+    status = ops.new_status("cuda")
+
+    def run(i):
+        k, v = pools[i % layers]
+        ops.paged_attention(q, k, v, tiles=tiles, cu_q=cu, ctx_lens=ctx_lens, block_table=table, page_size=P, scale=D ** -0.5,
+                            window=0, kv_len_bound=ctx, status=status)
+    us = _time(run, args.reps)
+    ops.check_status(status)
+    kv_bytes = B * ctx * KV * D * 2 * 2
+    flops = sum(4 * H * D * (ctx - q_len + i + 1) for i in range(q_len)) * B
+    return {"kernel": "paged_attention", "batch": B, "q_len": q_len, "context": ctx, "heads": H, "kv_heads": KV, "head_dim": D,
+            "us": round(us, 2), "KV GB/s": round(kv_bytes / us / 1e3, 1), "TFLOP/s": round(flops / us / 1e6, 2)}
+
+
+def norm(args) -> dict:
+    rows, hidden = args.rows, args.hidden
+    copies = max(2, int(300e6 // (rows * hidden * 12)) + 1) if rows * hidden * 12 > 1e6 else 4
+    xs = [torch.randn(rows, hidden, device="cuda").bfloat16() for _ in range(copies)]
+    rs = [torch.randn(rows, hidden, device="cuda") for _ in range(copies)]
+    w = torch.ones(hidden, device="cuda")
+    us = _time(lambda i: ops.add_rms_norm(xs[i % copies], rs[i % copies], w, 1e-6), args.reps)
+    return {"kernel": "add_rms_norm", "rows": rows, "hidden": hidden, "us": round(us, 2),
+            "GB/s": round(rows * hidden * (2 + 4 + 4 + 2) / us / 1e3, 1)}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    sub = ap.add_subparsers(dest="what", required=True)
+    g = sub.add_parser("gemm")
+    g.add_argument("--m", type=int, default=8)
+    g.add_argument("--n", type=int, default=4096)
+    g.add_argument("--k", type=int, default=4096)
+    g.add_argument("--fp32-out", action="store_true")
+    g.set_defaults(run=gemm)
+    a = sub.add_parser("attention")
+    a.add_argument("--batch", type=int, default=8)
+    a.add_argument("--q-len", type=int, default=1)
+    a.add_argument("--context", type=int, default=2048)
+    a.add_argument("--heads", type=int, default=32)
+    a.add_argument("--kv-heads", type=int, default=8)
+    a.add_argument("--head-dim", type=int, default=128)
+    a.add_argument("--page-size", type=int, default=16)
+    a.set_defaults(run=attention)
+    n = sub.add_parser("norm")
+    n.add_argument("--rows", type=int, default=8)
+    n.add_argument("--hidden", type=int, default=4096)
+    n.set_defaults(run=norm)
+    for p in (g, a, n):
+        p.add_argument("--reps", type=int, default=20)
+    args = ap.parse_args()
+    torch.backends.cuda.matmul.allow_tf32 = False
+    print(json.dumps(args.run(args)))
+
+
+if __name__ == "__main__":
+    main()
