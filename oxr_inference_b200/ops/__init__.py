@@ -5,9 +5,9 @@ only) and raises :class:`KernelError` when a launcher refuses its arguments. The
 fallback: tensors that are not on a CUDA device are an error, and a missing compiler or failed build raises
 ``BuildError`` at the first call.
 
-Matrix products: the 32-bit path and the decode-sized bf16 products (at most ``SKINNY_MAX_ROWS`` rows) run on
-this package's own kernels; larger bf16 products go to cuBLAS through ``torch.mm``, as the reference's do
-through ``nn.Linear`` (oxr_runtime/language.py:223-244).
+Matrix products (the reference's go to cuBLAS through ``nn.Linear``, oxr_runtime/language.py:223-244): the 32-bit
+path, the decode-sized bf16 products (at most ``SKINNY_MAX_ROWS`` rows) and the larger bf16 products all run on
+this package's own kernels; ``torch.mm`` is kept only for bf16 matrices whose rows TMA cannot fetch.
 """
 
 from __future__ import annotations
@@ -83,13 +83,14 @@ def _lib():
         lib.oxr_qk_norm_rope_store.argtypes = [p, p, p, p, p, p, p, p, p, p, i, i, i, i, f, i, c_longlong, i, i, i, i, p, p]
         lib.oxr_gemm_f32_nt.argtypes = [p, p, p, i, i, i, p]
         lib.oxr_gemm_skinny_bf16.argtypes = [p, p, p, i, i, i, i, p]
+        lib.oxr_gemm_tcgen05_bf16.argtypes = [p, p, p, i, i, i, i, i, p, p]
         lib.oxr_sample.argtypes = [p, p, i, i, p, p, p, p, p, p]
         lib.oxr_sample_chunks.argtypes = [i]
         lib.oxr_sample_chunks.restype = c_int
         lib.oxr_repetition_penalty.argtypes = [p, p, p, p, i, i, p]
         lib.oxr_mark_seen.argtypes = [p, p, p, i, i, p]
         for name in ("oxr_embedding", "oxr_add_rms_norm", "oxr_silu_mul", "oxr_cast", "oxr_qk_norm_rope_store",
-                     "oxr_gemm_f32_nt", "oxr_gemm_skinny_bf16", "oxr_sample", "oxr_repetition_penalty", "oxr_mark_seen"):
+                     "oxr_gemm_f32_nt", "oxr_gemm_skinny_bf16", "oxr_gemm_tcgen05_bf16", "oxr_sample", "oxr_repetition_penalty", "oxr_mark_seen"):
             getattr(lib, name).restype = c_int
         _core = lib
     return _core
@@ -122,9 +123,18 @@ def warm_up(head_dims: tuple[int, ...] = ()) -> None:
         _attn_lib(d)
 
 
+_status: dict[torch.device, torch.Tensor] = {}
+
+
 def new_status(device: torch.device | str = "cuda") -> torch.Tensor:
-    """The device status word: [code, detail, 0, 0]; kernels write the first error they meet."""
-    return torch.zeros(4, dtype=torch.int32, device=device)
+    """The device's status word: [code, detail, 0, 0]; kernels write the first error they meet. One per device, shared
+    by everything that runs there."""
+    device = torch.device(device)
+    if device.type == "cuda" and device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    if device not in _status:
+        _status[device] = torch.zeros(4, dtype=torch.int32, device=device)
+    return _status[device]
 
 
 def check_status(status: torch.Tensor) -> None:
@@ -344,8 +354,9 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
     """``x @ weight.T`` for ``weight [out, in]``, no bias (oxr_runtime/language.py:223-231), fp32 accumulation.
 
     float32 x float32 runs the fp32 CUDA-core kernel (no TF32). bfloat16 x bfloat16 runs the skinny kernel up to
-    ``SKINNY_MAX_ROWS`` rows and cuBLAS beyond. A weight kept in float32 under bfloat16 activations is multiplied
-    in fp32 and the result rounded once.
+    ``SKINNY_MAX_ROWS`` rows and the TMA + tcgen05 kernel beyond (cuBLAS only when a row is not a whole number of
+    16-byte words). A weight kept in float32 under bfloat16 activations is multiplied in fp32 and the result
+    rounded once.
     """
     _need(x, "x")
     _need(weight, "weight")
@@ -367,6 +378,15 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
         _done(lib.oxr_gemm_skinny_bf16(out.data_ptr(), x.data_ptr(), weight.data_ptr(), m, n, k, _DT[out_dtype], _stream()),
               "gemm_skinny")
         return out
+    if k % 8 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0:
+        out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+        # 128 x 256 tiles when they fill the GPU at least once, else 128 x 128 tiles for more blocks
+        tile_n = 256 if -(-m // 128) * -(-n // 256) >= NUM_SMS else 128
+        code = lib.oxr_gemm_tcgen05_bf16(out.data_ptr(), x.data_ptr(), weight.data_ptr(), m, n, k, _DT[out_dtype],
+                                         tile_n, new_status(x.device).data_ptr(), _stream())
+        _done(code, "gemm_tcgen05")
+        return out
+    # rows that are not whole 16-byte words cannot be fetched by TMA: the library product takes them
     if out_dtype == torch.float32:
         return torch.mm(x, weight.t(), out_dtype=torch.float32)
     return torch.mm(x, weight.t())

@@ -165,10 +165,30 @@ def test_gemm_skinny_bf16(ops, M, N, K, out_dtype):
         torch.testing.assert_close(got.float(), want, atol=1e-2, rtol=1e-2)
 
 
-def test_linear_large_bf16_uses_library_product_and_fp32_output(ops):
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (65, 509, 96), (200, 300, 256), (129, 128, 1000), (300, 160, 4096),
+                                   (2048, 4096, 4096), (1000, 12288, 160), (77, 64, 64)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_tcgen05_bf16(ops, M, N, K, out_dtype):
+    """The TMA + tcgen05 kernel that takes every bf16 product of more than 64 rows: whole tiles, ragged edges in
+    M, N and K, both tile widths, both output types."""
+    g = torch.Generator(device=DEV).manual_seed(9)
+    x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=DEV, generator=g) * 0.05).bfloat16()
+    status = ops.new_status(DEV)
+    got = ops.linear(x, w, out_dtype)
+    ops.check_status(status)
+    assert got.dtype == out_dtype and got.shape == (M, N)
+    want = x.float() @ w.float().T
+    if out_dtype == torch.float32:
+        torch.testing.assert_close(got, want, atol=2e-4 * math.sqrt(K) * 0.05, rtol=1e-4)
+    else:
+        torch.testing.assert_close(got.float(), want, atol=1e-2, rtol=1e-2)
+
+
+def test_linear_large_bf16_with_rows_that_are_not_16_byte_words_falls_to_the_library(ops):
     g = torch.Generator(device=DEV).manual_seed(7)
-    x = torch.randn(200, 256, device=DEV, generator=g).bfloat16()
-    w = (torch.randn(300, 256, device=DEV, generator=g) * 0.05).bfloat16()
+    x = torch.randn(200, 250, device=DEV, generator=g).bfloat16()
+    w = (torch.randn(300, 250, device=DEV, generator=g) * 0.05).bfloat16()
     want = x.float() @ w.float().T
     torch.testing.assert_close(ops.linear(x, w, torch.float32), want, atol=1e-3, rtol=1e-3)
     torch.testing.assert_close(ops.linear(x, w).float(), want, atol=2e-2, rtol=2e-2)
