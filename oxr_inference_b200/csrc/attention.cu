@@ -323,7 +323,8 @@ __device__ __forceinline__ void load_kv_block(bf16* Ks, bf16* Vs, const bf16* __
 template <int NK>
 __device__ __forceinline__ void warp_block(const uint32_t (&qf)[Q_IN_REGS ? KSTEPS : 1][4], const bf16* Qw, const bf16* Kw,
                                            const bf16* Vw, int key0, const int (&row_pos)[2], const bool (&row_ok)[2],
-                                           int window, float scale_log2, float (&m)[2], float (&l)[2], float (&o)[DT8][4]) {
+                                           int window, bool full_block, float scale_log2, float (&m)[2], float (&l)[2],
+                                           float (&o)[DT8][4]) {
     constexpr int NT = NK / 8;
     const int lane = threadIdx.x & 31, t = lane & 3;
     float s[NT][4];
@@ -345,18 +346,29 @@ __device__ __forceinline__ void warp_block(const uint32_t (&qf)[Q_IN_REGS ? KSTE
             mma16816(s[2 * np + 1], aq, bk[2], bk[3]);
         }
     }
-    // ---- mask, running maximum
+    // ---- mask, running maximum. A block that every row of the warp sees in full (no causal or window edge inside)
+    // needs no per-element test.
     float mx[2] = {-INFINITY, -INFINITY};
+    if (full_block) {
 #pragma unroll
-    for (int i = 0; i < NT; ++i)
+        for (int i = 0; i < NT; ++i)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const int r = e >> 1;
-            const int kp = key0 + i * 8 + 2 * t + (e & 1);
-            const bool seen = row_ok[r] && kp <= row_pos[r] && (window <= 0 || kp > row_pos[r] - window);
-            s[i][e] = seen ? s[i][e] * scale_log2 : -INFINITY;
-            mx[r] = fmaxf(mx[r], s[i][e]);
-        }
+            for (int e = 0; e < 4; ++e) {
+                s[i][e] *= scale_log2;
+                mx[e >> 1] = fmaxf(mx[e >> 1], s[i][e]);
+            }
+    } else {
+#pragma unroll
+        for (int i = 0; i < NT; ++i)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int r = e >> 1;
+                const int kp = key0 + i * 8 + 2 * t + (e & 1);
+                const bool seen = row_ok[r] && kp <= row_pos[r] && (window <= 0 || kp > row_pos[r] - window);
+                s[i][e] = seen ? s[i][e] * scale_log2 : -INFINITY;
+                mx[r] = fmaxf(mx[r], s[i][e]);
+            }
+    }
     float alpha[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
@@ -378,10 +390,13 @@ __device__ __forceinline__ void warp_block(const uint32_t (&qf)[Q_IN_REGS ? KSTE
         }
     l[0] = l[0] * alpha[0] + psum[0];
     l[1] = l[1] * alpha[1] + psum[1];
+    // the accumulator is rescaled only when some row's maximum moved (after the first blocks it rarely does)
+    if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
 #pragma unroll
-    for (int i = 0; i < DT8; ++i) {
-        o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
-        o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+        for (int i = 0; i < DT8; ++i) {
+            o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
+            o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+        }
     }
     // ---- O += P V
 #pragma unroll
@@ -481,11 +496,18 @@ attn_mma_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
     const bf16* Qw = Qs + warp * 16 * LDS;
     const float scale_log2 = a.scale * LOG2E;
     // the last key this warp's rows can see: blocks beyond it are skipped by this warp
-    int warp_last_pos = -1;
+    int warp_last_pos = -1, warp_first_pos = 0x7fffffff;
+    bool warp_all_rows = true;
     {
         int tok, gh;
-        for (int r = 15; r >= 0; --r)
-            if (g.row(warp * 16 + r, tok, gh)) { warp_last_pos = g.pos0 + tok; break; }
+        for (int r = 15; r >= 0; --r) {
+            if (g.row(warp * 16 + r, tok, gh)) {
+                warp_last_pos = max(warp_last_pos, g.pos0 + tok);
+                warp_first_pos = min(warp_first_pos, g.pos0 + tok);
+            } else {
+                warp_all_rows = false;
+            }
+        }
     }
 
     for (int b = 0; b < n_blocks; ++b) {
@@ -504,9 +526,14 @@ attn_mma_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
             }
         }
         const int key0 = k_first + b * MMA_BN;
-        if (key0 <= warp_last_pos)
+        if (key0 <= warp_last_pos) {
+            // every row of the warp holds a (token, head), the block ends at or before the earliest row's position and
+            // starts inside the latest row's window
+            const bool full_block = warp_all_rows && key0 + MMA_BN - 1 <= warp_first_pos &&
+                                    (a.window <= 0 || key0 > warp_last_pos - a.window);
             warp_block<MMA_BN>(qf, Qw, Ks + stage * MMA_BN * LDS, Vs + stage * MMA_BN * LDS, key0, row_pos, row_ok, a.window,
-                               scale_log2, m, l, o);
+                               full_block, scale_log2, m, l, o);
+        }
         __syncthreads();   // everyone is done with this stage before the next prefetch overwrites it
     }
 
@@ -593,6 +620,7 @@ attn_mma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
         for (int i = 0; i < DT8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
         uint32_t qf[Q_IN_REGS ? KSTEPS : 1][4];
         const float scale_log2 = a.scale * LOG2E;
+        const int tile_first_pos = g.pos0 + g.tok0, tile_last_pos = g.pos0 + g.tok_end - 1;
 
         for (int b = 0; b < count; ++b) {
             const int stage = b % DECODE_STAGES;
@@ -613,8 +641,11 @@ attn_mma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
                 }
             }
             const int key0 = k_first + (first + b) * MMA_BN + warp * 16;   // this warp's quarter of the block
+            // rows without a (token, head) have zero queries: unmasked they give finite numbers that are never stored,
+            // so the block counts as fully visible when the rows that do exist see all of it
+            const bool full_block = key0 + 15 <= tile_first_pos && key0 >= k_lo && (a.window <= 0 || key0 > tile_last_pos - a.window);
             warp_block<16>(qf, Qs, Ks + (stage * MMA_BN + warp * 16) * LDS, Vs + (stage * MMA_BN + warp * 16) * LDS, key0, row_pos,
-                           row_ok, a.window, scale_log2, m, l, o);
+                           row_ok, a.window, full_block, scale_log2, m, l, o);
             __syncthreads();
         }
 #pragma unroll
