@@ -115,7 +115,7 @@ def hidden_states(cfg: dict, w: dict, ids: list[int]) -> torch.Tensor:
     """Final-norm hidden state of every position of one whole sequence (oxr_runtime/language.py:177-187)."""
     dtype = w["model.embed_tokens.weight"].dtype
     x = w["model.embed_tokens.weight"][torch.tensor(ids, dtype=torch.long)]
-    cos, sin = rope_tables(head_dim_of(cfg), cfg["rope_theta"], len(ids), dtype)
+    cos, sin = (t.to(x.device) for t in rope_tables(head_dim_of(cfg), cfg["rope_theta"], len(ids), dtype))
     for layer in range(cfg["num_hidden_layers"]):
         x = decoder_layer(x, w, layer, cfg, cos, sin)
     return rms_norm(x, w["model.norm.weight"], cfg["rms_norm_eps"])

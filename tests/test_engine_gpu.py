@@ -179,3 +179,36 @@ def test_smoke_entry():
     import __graft_entry__
 
     __graft_entry__.smoke()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_two_layers_at_qwen3_8b_sizes_match_the_plain_implementation(dtype):
+    """The serving sizes (hidden 4096, 32 query and 8 KV heads of 128, feed-forward 12288, vocabulary 151936, untied)
+    with two layers and random weights drawn on the device: logits of a prompt cut into a long portion (the prefill
+    kernels), a short one and single tokens (the decode kernels) against the plain implementation run in fp32 on the
+    same device with the same weights."""
+    from oxr_inference_b200.engine.batch import StepEntry
+    from oxr_inference_b200.engine.runtime import ModelRunner
+    from oxr_inference_b200.weights import random_tensor
+
+    cfg = {"architectures": ["Qwen3ForCausalLM"], "hidden_size": 4096, "intermediate_size": 12288, "num_hidden_layers": 2,
+           "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0,
+           "vocab_size": 151936, "tie_word_embeddings": False, "max_position_embeddings": 4096}
+    torch.backends.cuda.matmul.allow_tf32 = False
+    runner = ModelRunner.from_config(cfg, seed=5, dtype=dtype, page_size=16, num_pages=40, max_requests=2)
+    # the same weights for the plain implementation: same seed, same names, same device -> the same draws (bf16-rounded)
+    w = {name: random_tensor(name, info, 5, std=0.02, norm_std=0.1, device="cuda", dtype=torch.bfloat16).float()
+         for name, (_, _, info) in runner.model.named_parameters().items()}
+    g = torch.Generator().manual_seed(8)
+    ids = torch.randint(0, cfg["vocab_size"], (300,), generator=g).tolist()
+    want = QP.logits(cfg, w, ids)
+    del w
+    rc = runner.cache.open("r")
+    got, pos = [], 0
+    for c in (270, 6, 1, 1, 22):
+        assert runner.cache.reserve(rc, pos + c)
+        got.append(runner.step([StepEntry(rc, ids[pos:pos + c], [0, c - 1] if c > 1 else [0])]))
+        rows = [pos, pos + c - 1] if c > 1 else [pos]
+        util.compare(got[-1], want[rows], dtype, f"portion of {c} at {pos}")
+        pos += c
+    runner.check()
