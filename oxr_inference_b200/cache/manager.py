@@ -73,6 +73,11 @@ class CacheManager:
                 self.v_pools.append(torch.zeros(shape, dtype=dtype, device=device))
             for s in plan.states:
                 self.states.append(torch.zeros((max_requests + 1, *s.shape), dtype=s.dtype, device=device))
+        self.kv_maps: list = [None] * len(self.k_pools)
+        if device is not None and torch.device(device).type == "cuda":
+            from oxr_inference_b200 import ops
+
+            self.kv_maps = [ops.make_kv_maps(k, v, page_size) for k, v in zip(self.k_pools, self.v_pools)]
 
     # ---- sizes
     @staticmethod
@@ -210,4 +215,5 @@ class CacheManager:
 
     def group_view(self, group: int, block_table: torch.Tensor, slots: torch.Tensor) -> GroupView:
         return GroupView(self.page_size, self.k_pools[group] if self.k_pools else None,
-                         self.v_pools[group] if self.v_pools else None, block_table, slots)
+                         self.v_pools[group] if self.v_pools else None, block_table, slots,
+                         self.kv_maps[group] if self.k_pools else None)

@@ -12,7 +12,7 @@
 // packed next to each other so that K and V are read once for the whole group. Keys are visited in blocks of
 // BN = 32 that start at absolute positions 0, 32, 64, ...; because the blocks do not depend on where a portion
 // starts or on the rest of the batch, a row's result is bit-identical however the work was cut.
-#include "common.cuh"
+#include "tma.cuh"
 
 #ifndef HEAD_DIM
 #error "compile with -DHEAD_DIM=<head size>"
@@ -318,9 +318,21 @@ __device__ __forceinline__ void load_kv_block(bf16* Ks, bf16* Vs, const bf16* __
     }
 }
 
+// Where element (row, d) of a K or V block lives in shared memory. Padded layout (cp.async gathers): rows of LDS
+// elements. Swizzled layout (TMA gathers): panels of 64 keys x 64 d, 128 bytes per row, the 16-byte chunks of a row
+// XOR-ed with the row number modulo 8 (the TMA 128-byte swizzle), 8 KB per panel.
+template <bool SWZ>
+__device__ __forceinline__ const bf16* kv_elem(const bf16* base, int row, int d) {
+    if constexpr (SWZ) {
+        return base + (d >> 6) * (MMA_BN * 64) + row * 64 + ((((d & 63) >> 3) ^ (row & 7)) << 3);
+    } else {
+        return base + row * LDS + d;
+    }
+}
+
 // One warp: S = Q K^T for its 16 rows and NK keys starting at Kw, masked online softmax, O += P V.
 // qf: Q fragments when Q_IN_REGS, else read from Qw (this warp's 16 rows in shared memory).
-template <int NK>
+template <int NK, bool SWZ = false>
 __device__ __forceinline__ void warp_block(const uint32_t (&qf)[Q_IN_REGS ? KSTEPS : 1][4], const bf16* Qw, const bf16* Kw,
                                            const bf16* Vw, int key0, const int (&row_pos)[2], const bool (&row_ok)[2],
                                            int window, bool full_block, float scale_log2, float (&m)[2], float (&l)[2],
@@ -341,7 +353,7 @@ __device__ __forceinline__ void warp_block(const uint32_t (&qf)[Q_IN_REGS ? KSTE
 #pragma unroll
         for (int np = 0; np < NK / 16; ++np) {
             uint32_t bk[4];
-            ldsm_x4(bk, Kw + (np * 16 + (lane & 7) + 8 * (lane >> 4)) * LDS + kk * 16 + 8 * ((lane >> 3) & 1));
+            ldsm_x4(bk, kv_elem<SWZ>(Kw, np * 16 + (lane & 7) + 8 * (lane >> 4), kk * 16 + 8 * ((lane >> 3) & 1)));
             mma16816(s[2 * np], aq, bk[0], bk[1]);
             mma16816(s[2 * np + 1], aq, bk[2], bk[3]);
         }
@@ -409,7 +421,7 @@ __device__ __forceinline__ void warp_block(const uint32_t (&qf)[Q_IN_REGS ? KSTE
 #pragma unroll
         for (int dp = 0; dp < D / 16; ++dp) {
             uint32_t bv[4];
-            ldsm_x4_trans(bv, Vw + (kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + dp * 16 + 8 * (lane >> 4));
+            ldsm_x4_trans(bv, kv_elem<SWZ>(Vw, kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), dp * 16 + 8 * (lane >> 4)));
             mma16816(o[2 * dp], ap, bv[0], bv[1]);
             mma16816(o[2 * dp + 1], ap, bv[2], bv[3]);
         }
@@ -721,6 +733,231 @@ attn_mma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
         out[((size_t)(g.q_begin + tok) * a.H + (size_t)g.kvh * g.G + gh) * D + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
     }
 }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// The same split-KV kernel with the K/V blocks fetched by TMA instead of per-thread cp.async: a fifth warp is the
+// producer; for every 64-key block each of its lanes issues one cp.async.bulk.tensor per (page piece, 64-wide panel
+// of K or V), the hardware writes them 128-byte-swizzled, and an mbarrier per stage counts the bytes. The four
+// consumer warps wait on that barrier, compute as before (ldmatrix with the swizzled addressing) and hand the stage
+// back through a second mbarrier. Needs head sizes that are multiples of 64 and pages of 8 x 2^k tokens.
+// The tensor maps cover a whole group's pool: rows = layers * pages * page_size, columns = KV * D.
+// ---------------------------------------------------------------------------------------------------------------------
+constexpr bool TMA_OK = (D % 64 == 0);
+constexpr int PANELS = D / 64 > 0 ? D / 64 : 1;             // 64-wide panels of one head
+constexpr int PANEL_BYTES = MMA_BN * 128;                    // 64 keys x 128 bytes
+constexpr int KV_STAGE_BYTES = 2 * PANELS * PANEL_BYTES;     // K panels then V panels
+constexpr int TMA_STAGES = 3;
+constexpr int TMA_THREADS = 160;                             // 4 consumer warps + 1 producer warp
+constexpr size_t TMA_DECODE_TILES = (size_t)TMA_STAGES * KV_STAGE_BYTES;
+constexpr size_t TMA_DECODE_SMEM = 1024 + (TMA_DECODE_TILES > DECODE_MERGE_SMEM ? TMA_DECODE_TILES : DECODE_MERGE_SMEM) +
+                                   (size_t)DECODE_ROWS * LDS * sizeof(bf16) + 128;
+
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+__global__ void __launch_bounds__(TMA_THREADS)
+attn_tma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters,
+                       const bf16* __restrict__ q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                       int pool_row0, int box_rows, const AttnArgs a) {
+    extern __shared__ unsigned char smem_dyn[];
+    __shared__ int s_ticket;
+    __shared__ int s_gave_up;
+    unsigned char* stages = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+    constexpr size_t TILE_REGION = TMA_DECODE_TILES > DECODE_MERGE_SMEM ? TMA_DECODE_TILES : DECODE_MERGE_SMEM;
+    bf16* Qs = reinterpret_cast<bf16*>(stages + TILE_REGION);
+    uint64_t* full = reinterpret_cast<uint64_t*>(stages + TILE_REGION + (size_t)DECODE_ROWS * LDS * sizeof(bf16));
+    uint64_t* empty = full + TMA_STAGES;
+
+    const TileGeometry g = tile_geometry(a, DECODE_ROWS);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int splits = gridDim.z, split = blockIdx.z;
+    const size_t unit = (size_t)blockIdx.x * gridDim.y + blockIdx.y;
+    float* my_ml = part_ml + (unit * splits + split) * DECODE_ROWS * 2;
+    float* my_o = part_o + (unit * splits + split) * DECODE_ROWS * D;
+    const int rows_live = g.tok0 < g.tok_end ? (g.tok_end - g.tok0) * g.heads_per_tile : 0;
+    if (rows_live == 0) return;   // every piece of this unit returns here: no tickets are drawn
+
+    const int k_end = g.pos0 + g.tok_end;
+    const int k_lo = a.window > 0 ? max(0, g.pos0 + g.tok0 - a.window + 1) : 0;
+    const int k_first = (k_lo / MMA_BN) * MMA_BN;
+    const int n_blocks = (k_end - k_first + MMA_BN - 1) / MMA_BN;
+    const int per = (n_blocks + splits - 1) / splits;
+    const int first = split * per;
+    const int count = max(0, min(per, n_blocks - first));
+
+    if (count > 0) {
+        if (threadIdx.x == 0) {
+            for (int s2 = 0; s2 < TMA_STAGES; ++s2) { mbar_init(full + s2, 1); mbar_init(empty + s2, 4); }
+            s_gave_up = 0;
+            mbar_fence_init();
+        }
+        // Pages that lie wholly outside the visible range are not fetched; what they would have covered keeps what the
+        // stage held before, which must be finite numbers (it is multiplied by a probability of exactly zero): clear
+        // the stages once.
+        for (int i = threadIdx.x; i < (int)(TMA_DECODE_TILES / 16); i += TMA_THREADS) reinterpret_cast<uint4*>(stages)[i] = make_uint4(0, 0, 0, 0);
+        fence_proxy_async();
+        __syncthreads();
+
+        if (warp == 4) {
+            // ------------------------------------------------------------------ producer
+            const int* table_row = a.block_table + (size_t)g.req * a.table_width;
+            const int boxes = MMA_BN / box_rows;              // page pieces per block
+            const int loads = boxes * 2 * PANELS;             // TMA instructions per block
+            for (int b = 0; b < count; ++b) {
+                const int st = b % TMA_STAGES;
+                if (!mbar_wait(empty + st, ((b / TMA_STAGES) & 1) ^ 1)) {
+                    if (lane == 0) { atomicExch(&s_gave_up, 1); oxr_report(a.status, OXR_WAIT_EXPIRED, 10); }
+                    break;
+                }
+                const int k0 = k_first + (first + b) * MMA_BN;
+                unsigned char* dst = stages + (size_t)st * KV_STAGE_BYTES;
+                // which of this lane's loads are wanted, and where they come from
+                int my_bytes = 0;
+                for (int i = lane; i < loads; i += 32) {
+                    const int kp = k0 + (i / (2 * PANELS)) * box_rows;
+                    if (kp < k_end && kp + box_rows > k_lo) {
+                        const int page = table_row[a.page_shift >= 0 ? (kp >> a.page_shift) : (kp / a.page_size)];
+                        if (page >= 0 && page < a.num_pages) my_bytes += box_rows * 128;
+                        else oxr_report(a.status, OXR_BAD_PAGE, g.req);
+                    }
+                }
+                const int total = __reduce_add_sync(0xffffffffu, my_bytes);
+                if (lane == 0) {
+                    if (total > 0) mbar_expect_tx(full + st, (uint32_t)total);
+                    else mbar_arrive(full + st);
+                }
+                __syncwarp();
+                for (int i = lane; i < loads; i += 32) {
+                    const int box = i / (2 * PANELS), which = i % (2 * PANELS);     // which: K panels, then V panels
+                    const int kp = k0 + box * box_rows;
+                    if (kp < k_end && kp + box_rows > k_lo) {
+                        const int page = table_row[a.page_shift >= 0 ? (kp >> a.page_shift) : (kp / a.page_size)];
+                        if (page >= 0 && page < a.num_pages) {
+                            const int panel = which % PANELS;
+                            const int row = pool_row0 + page * a.page_size + (a.page_shift >= 0 ? (kp & (a.page_size - 1)) : (kp % a.page_size));
+                            unsigned char* d2 = dst + (size_t)which * PANEL_BYTES + (size_t)box * box_rows * 128;
+                            tma_load_2d(d2, which < PANELS ? &map_k : &map_v, g.kvh * D + panel * 64, row, full + st);
+                        }
+                    }
+                }
+            }
+            return;   // the producer takes no part in the merge
+        }
+
+        // ---------------------------------------------------------------------- consumers (warps 0..3)
+        load_q_rows(Qs, q, a, g, DECODE_ROWS);   // strided over MMA_THREADS = the 128 consumer threads
+        cp_async_commit();
+        int row_pos[2];
+        bool row_ok[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            int tok, gh;
+            row_ok[r] = g.row((lane >> 2) + 8 * r, tok, gh);
+            row_pos[r] = g.pos0 + tok;
+        }
+        float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+        float o[DT8][4];
+#pragma unroll
+        for (int i = 0; i < DT8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+        uint32_t qf[Q_IN_REGS ? KSTEPS : 1][4];
+        const float scale_log2 = a.scale * LOG2E;
+        const int tile_first_pos = g.pos0 + g.tok0, tile_last_pos = g.pos0 + g.tok_end - 1;
+        cp_async_wait<0>();
+        consumer_sync();
+        if constexpr (Q_IN_REGS) {
+#pragma unroll
+            for (int kk = 0; kk < KSTEPS; ++kk)
+                ldsm_x4(qf[kk], Qs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + kk * 16 + 8 * (lane >> 4));
+        }
+        for (int b = 0; b < count; ++b) {
+            const int st = b % TMA_STAGES;
+            if (!mbar_wait(full + st, (b / TMA_STAGES) & 1)) {
+                if (lane == 0) { atomicExch(&s_gave_up, 1); oxr_report(a.status, OXR_WAIT_EXPIRED, 11); }
+                break;
+            }
+            const bf16* Kst = reinterpret_cast<const bf16*>(stages + (size_t)st * KV_STAGE_BYTES);
+            const bf16* Vst = Kst + PANELS * (PANEL_BYTES / 2);
+            const int key0 = k_first + (first + b) * MMA_BN + warp * 16;
+            const bool full_block = key0 + 15 <= tile_first_pos && key0 >= k_lo && (a.window <= 0 || key0 > tile_last_pos - a.window);
+            warp_block<16, true>(qf, Qs, Kst + warp * 16 * 64, Vst + warp * 16 * 64, key0, row_pos, row_ok, a.window, full_block,
+                                 scale_log2, m, l, o);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty + st);   // this warp is done with the stage
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+            l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+        }
+        consumer_sync();   // every consumer has left the loop: all fetched stages were read, the region is free
+        float* mo = reinterpret_cast<float*>(stages);   // [4 warps][16 rows][D + 2]: O then (m, l)
+        constexpr int MS = D + 2;
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            float* dst = mo + ((size_t)warp * DECODE_ROWS + (lane >> 2) + 8 * r) * MS;
+#pragma unroll
+            for (int i = 0; i < DT8; ++i) {
+                dst[i * 8 + 2 * (lane & 3)] = o[i][2 * r];
+                dst[i * 8 + 2 * (lane & 3) + 1] = o[i][2 * r + 1];
+            }
+            if ((lane & 3) == 0) { dst[D] = m[r]; dst[D + 1] = l[r]; }
+        }
+        consumer_sync();
+        for (int idx = threadIdx.x; idx < rows_live * D; idx += MMA_THREADS) {
+            const int r = idx / D, d = idx % D;
+            int tok, gh;
+            if (!g.row(r, tok, gh)) continue;
+            float M = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) M = fmaxf(M, mo[((size_t)w * DECODE_ROWS + r) * MS + D]);
+            float L = 0.f, O = 0.f;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float* src = mo + ((size_t)w * DECODE_ROWS + r) * MS;
+                const float f = (src[D] == -INFINITY) ? 0.f : exp2f(src[D] - M);
+                L += src[D + 1] * f;
+                O += src[d] * f;
+            }
+            if (splits == 1) {
+                out[((size_t)(g.q_begin + tok) * a.H + (size_t)g.kvh * g.G + gh) * D + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+            } else {
+                my_o[r * D + d] = O;
+                if (d == 0) { my_ml[2 * r] = M; my_ml[2 * r + 1] = L; }
+            }
+        }
+    } else {
+        if (warp == 4) return;
+        if (splits > 1)   // nothing for this piece: an empty partial
+            for (int i = threadIdx.x; i < rows_live; i += MMA_THREADS) { my_ml[2 * i] = -INFINITY; my_ml[2 * i + 1] = 0.f; }
+    }
+    if (splits == 1) return;
+
+    // ---- ticket (consumer warps only): the last piece to finish merges them all
+    __threadfence();
+    consumer_sync();
+    if (threadIdx.x == 0) s_ticket = atomicAdd(&counters[unit], 1);
+    consumer_sync();
+    if (s_ticket != splits - 1) return;
+    __threadfence();
+    if (threadIdx.x == 0) counters[unit] = 0;
+    const float* all_ml = part_ml + unit * splits * DECODE_ROWS * 2;
+    const float* all_o = part_o + unit * splits * DECODE_ROWS * D;
+    for (int idx = threadIdx.x; idx < rows_live * D; idx += MMA_THREADS) {
+        const int r = idx / D, d = idx % D;
+        int tok, gh;
+        if (!g.row(r, tok, gh)) continue;
+        float M = -INFINITY;
+        for (int s2 = 0; s2 < splits; ++s2) M = fmaxf(M, __ldcg(all_ml + ((size_t)s2 * DECODE_ROWS + r) * 2));
+        float L = 0.f, O = 0.f;
+        for (int s2 = 0; s2 < splits; ++s2) {
+            const float ms = __ldcg(all_ml + ((size_t)s2 * DECODE_ROWS + r) * 2);
+            if (ms == -INFINITY) continue;
+            const float f = exp2f(ms - M);
+            L += __ldcg(all_ml + ((size_t)s2 * DECODE_ROWS + r) * 2 + 1) * f;
+            O += __ldcg(all_o + ((size_t)s2 * DECODE_ROWS + r) * D + d) * f;
+        }
+        out[((size_t)(g.q_begin + tok) * a.H + (size_t)g.kvh * g.G + gh) * D + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+    }
+}
 }  // namespace
 
 OXR_API int oxr_attn_head_dim() { return D; }
@@ -733,12 +970,14 @@ OXR_API int oxr_attn_decode_rows() { return DECODE_ROWS; }
 // splits > 1 the caller provides scratch: part_o [n_short * KV * groups16 * splits * 16 * D] floats, part_ml
 // [n_short * KV * groups16 * splits * 16 * 2] floats and counters [n_short * KV * groups16] ints that are zero
 // before the first launch (the kernel leaves them zero), groups16 = ceil(G / min(G, 16)).
+// kv_maps (optional): the two tensor maps of oxr_attn_make_kv_maps for the pool that k_cache / v_cache are a layer
+// of, with pool_row0 = layer * num_pages * page_size; the split-KV kernel then fetches K and V by TMA.
 OXR_API int oxr_paged_attention_bf16(void* out, const void* q, const void* k_cache, const void* v_cache,
                                      const int* short_req, const int* short_tok0, int n_short, const int* long_req,
                                      const int* long_tok0, int n_long, const int* cu_q, const int* ctx_lens,
                                      const int* block_table, int table_width, int page_size, int num_pages, int H, int KV,
                                      float scale, int window, int splits, float* part_o, float* part_ml, int* counters,
-                                     int* status, cudaStream_t stream) {
+                                     const void* kv_maps, int pool_row0, int* status, cudaStream_t stream) {
     if (n_short <= 0 && n_long <= 0) return 0;
     if (H <= 0 || KV <= 0 || H % KV != 0 || page_size <= 0 || table_width <= 0 || window < 0 || splits < 1) return OXR_BAD_ARGUMENT;
     if (splits > 1 && (part_o == nullptr || part_ml == nullptr || counters == nullptr)) return OXR_BAD_ARGUMENT;
@@ -773,6 +1012,20 @@ OXR_API int oxr_paged_attention_bf16(void* out, const void* q, const void* k_cac
         const int groups = (G + hpt - 1) / hpt;
         if ((size_t)KV * groups > 65535 || splits > 65535) return OXR_BAD_ARGUMENT;
         a.tile_req = short_req; a.tile_tok0 = short_tok0;
+        if (TMA_OK && kv_maps != nullptr && a.page_shift >= 3) {
+            // K/V blocks by TMA: kv_maps holds the group's two tensor maps (K, V) made by oxr_attn_make_kv_maps
+            static bool tma_configured = false;
+            if (!tma_configured) {
+                cudaError_t e = cudaFuncSetAttribute(attn_tma_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TMA_DECODE_SMEM);
+                if (e != cudaSuccess) return 1000 + (int)e;
+                tma_configured = true;
+            }
+            const CUtensorMap* maps = reinterpret_cast<const CUtensorMap*>(kv_maps);
+            const int box_rows = page_size < MMA_BN ? page_size : MMA_BN;
+            attn_tma_decode_kernel<<<dim3(n_short, KV * groups, splits), TMA_THREADS, TMA_DECODE_SMEM, stream>>>(
+                (bf16*)out, part_o, part_ml, counters, (const bf16*)q, maps[0], maps[1], pool_row0, box_rows, a);
+            return oxr_launch_status();
+        }
         attn_mma_decode_kernel<<<dim3(n_short, KV * groups, splits), MMA_THREADS, DECODE_SMEM, stream>>>(
             (bf16*)out, part_o, part_ml, counters, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, a);
         int rc = oxr_launch_status();
@@ -804,4 +1057,20 @@ OXR_API int oxr_paged_attention(void* out, const void* q, const void* k_cache, c
     if (dtype == 0) return launch_simt<float>(out, q, k_cache, v_cache, a, num_tiles, stream);
     if (dtype == 1) return launch_simt<__nv_bfloat16>(out, q, k_cache, v_cache, a, num_tiles, stream);
     return OXR_BAD_ARGUMENT;
+}
+
+// Two CUtensorMap (K then V, 128 bytes each, written to 64-byte aligned host memory at `out_maps`) over a whole
+// group's pool [layers * pages * page_size rows, KV * D columns] bf16, in boxes of min(page_size, 64) rows x 64
+// columns with the 128-byte swizzle. Returns 0, or OXR_BAD_ARGUMENT when the sizes do not allow TMA gathers (head size
+// not a multiple of 64, page size not 8 * 2^k, misaligned pool).
+OXR_API int oxr_attn_make_kv_maps(void* out_maps, const void* k_pool, const void* v_pool, unsigned long long total_rows, int row_elems,
+                                  int page_size) {
+    if (!TMA_OK || out_maps == nullptr || (uintptr_t)out_maps % 64 != 0 || row_elems % 8 != 0 || total_rows == 0) return OXR_BAD_ARGUMENT;
+    if (page_size < 8 || (page_size & (page_size - 1)) != 0) return OXR_BAD_ARGUMENT;
+    if ((uintptr_t)k_pool % 16 != 0 || (uintptr_t)v_pool % 16 != 0) return OXR_BAD_ARGUMENT;
+    CUtensorMap* maps = reinterpret_cast<CUtensorMap*>(out_maps);
+    const int box_rows = page_size < MMA_BN ? page_size : MMA_BN;
+    if (!oxr_make_map_bf16(&maps[0], k_pool, total_rows, (unsigned long long)row_elems, box_rows)) return OXR_BAD_ARGUMENT;
+    if (!oxr_make_map_bf16(&maps[1], v_pool, total_rows, (unsigned long long)row_elems, box_rows)) return OXR_BAD_ARGUMENT;
+    return 0;
 }

@@ -13,16 +13,13 @@
 // epilogue of one tile overlaps the MMAs of the next. Rows and columns beyond M, N and K are zero-filled by TMA on
 // the way in and masked on the way out. Every wait on an mbarrier is bounded: if one runs out, the block records
 // OXR_WAIT_EXPIRED in the status word, stops waiting, frees its tensor memory and returns.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tma.cuh"
 
 namespace {
 constexpr int BM = 128;           // rows of X per tile = TMEM lanes
 constexpr int BK = 64;            // k per stage: 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int TC_THREADS = 192;   // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2..5: epilogue
-constexpr uint32_t WAIT_LIMIT = 1u << 22;   // polls of an mbarrier before giving up (seconds at most)
 
 template <int BN> struct Cfg {
     static constexpr int STAGES = BN >= 256 ? 4 : 6;
@@ -32,33 +29,6 @@ template <int BN> struct Cfg {
     static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
 };
 
-__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
-}
-// Poll until the phase with the given parity has completed. False if the limit of polls ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    const uint32_t addr = smem_addr(bar);
-    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
-        uint32_t done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-        if (done) return true;
-    }
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(smem_addr(dst)), "l"(map), "r"(smem_addr(bar)), "r"(c0), "r"(c1) : "memory");
-}
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte swizzle: rows 128 B apart,
 // groups of 8 rows 1024 B apart (stride byte offset), leading byte offset 1 (unused for swizzled K-major),
 // descriptor version 1, layout type 2 (SWIZZLE_128B).
@@ -107,10 +77,6 @@ __device__ __forceinline__ bool elect_one() {
     return pred != 0;
 }
 
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
-}
-
 // Tile order: blocks that run at the same time share few W tiles and GROUP_M consecutive X tiles, so that W is
 // streamed from HBM once and the X tiles of a group stay in L2 (W can be far larger than L2, X of a group is not).
 template <int BN>
@@ -149,7 +115,7 @@ gemm_tcgen05_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap map_
         for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
         for (int i = 0; i < 2; ++i) { mbar_init(accum_full + i, 1); mbar_init(accum_empty + i, 4); }
         *gave_up = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_fence_init();
     }
     if (warp == 1) {   // the whole warp allocates the tensor memory and gives up the permit to allocate more
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(TMEM_COLS) : "memory");
@@ -270,33 +236,6 @@ gemm_tcgen05_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap map_
 }
 
 // ---------------------------------------------------------------------------------------------------- host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled() {
-    static EncodeTiledFn fn = nullptr;
-    if (fn == nullptr) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    }
-    return fn;
-}
-
-// A [rows, K] bf16 row-major matrix seen as tiles of box_rows x 64, 128-byte swizzle; out-of-range elements read as zero.
-bool make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
-    EncodeTiledFn fn = encode_tiled();
-    if (fn == nullptr) return false;
-    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-    const cuuint32_t elem[2] = {1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
-              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 template <int BN, typename TO>
 int launch(void* C, const void* X, const void* W, int M, int N, int K, int* status, cudaStream_t stream) {
     static bool configured = false;
@@ -306,7 +245,7 @@ int launch(void* C, const void* X, const void* W, int M, int N, int K, int* stat
         configured = true;
     }
     CUtensorMap map_x, map_w;
-    if (!make_map(&map_x, X, M, K, BM) || !make_map(&map_w, W, N, K, BN)) return OXR_BAD_ARGUMENT;
+    if (!oxr_make_map_bf16(&map_x, X, M, K, BM) || !oxr_make_map_bf16(&map_w, W, N, K, BN)) return OXR_BAD_ARGUMENT;
     const long long tiles = (long long)((N + BN - 1) / BN) * ((M + BM - 1) / BM);
     if (tiles > 0x7fffffffLL) return OXR_BAD_ARGUMENT;
     static int num_sms = 0;

@@ -106,7 +106,9 @@ def _attn_lib(head_dim: int):
         p, i, f = c_void_p, c_int, c_float
         lib.oxr_paged_attention.argtypes = [p, p, p, p, p, p, i, p, p, p, i, i, i, i, i, f, i, i, p, p]
         lib.oxr_paged_attention.restype = c_int
-        lib.oxr_paged_attention_bf16.argtypes = [p, p, p, p, p, p, i, p, p, i, p, p, p, i, i, i, i, i, f, i, i, p, p, p, p, p]
+        lib.oxr_paged_attention_bf16.argtypes = [p, p, p, p, p, p, i, p, p, i, p, p, p, i, i, i, i, i, f, i, i, p, p, p, p, i, p, p]
+        lib.oxr_attn_make_kv_maps.argtypes = [p, p, p, ctypes.c_ulonglong, i, i]
+        lib.oxr_attn_make_kv_maps.restype = c_int
         lib.oxr_paged_attention_bf16.restype = c_int
         lib.oxr_attn_tile_rows.restype = c_int
         lib.oxr_attn_head_dim.restype = c_int
@@ -288,15 +290,40 @@ def attention_splits(n_short_tiles: int, num_heads: int, num_kv_heads: int, kv_l
     return max(1, min(want, max(1, kv_len_bound // 128), MAX_SPLITS))
 
 
+class KVMaps:
+    """The two TMA tensor maps (K, V) of one cache group's pool, in 64-byte aligned host memory."""
+
+    def __init__(self, raw: ctypes.Array, address: int, pool_ptrs: tuple[int, int], rows_per_layer: int):
+        self.raw, self.address, self.pool_ptrs, self.rows_per_layer = raw, address, pool_ptrs, rows_per_layer
+
+
+def make_kv_maps(k_pool: torch.Tensor, v_pool: torch.Tensor, page_size: int) -> KVMaps | None:
+    """Tensor maps over a group's whole pool ``[layers, pages, page_size, KV, D]`` so that the split-KV kernel can
+    fetch K and V by TMA; None when the sizes do not allow it (the kernel then gathers with cp.async)."""
+    if k_pool.dtype != torch.bfloat16 or not k_pool.is_cuda:
+        return None
+    layers, pages, page, kv, d = k_pool.shape
+    if d % 64 != 0 or page_size < 8 or page_size & (page_size - 1):
+        return None
+    raw = ctypes.create_string_buffer(2 * 128 + 64)
+    address = (ctypes.addressof(raw) + 63) & ~63
+    code = _attn_lib(d).oxr_attn_make_kv_maps(address, k_pool.data_ptr(), v_pool.data_ptr(), layers * pages * page, kv * d, page_size)
+    if code != 0:
+        return None
+    return KVMaps(raw, address, (k_pool.data_ptr(), v_pool.data_ptr()), pages * page)
+
+
 def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, *, tiles: dict, cu_q: torch.Tensor,
                     ctx_lens: torch.Tensor, block_table: torch.Tensor, page_size: int, scale: float, window: int,
-                    kv_len_bound: int, status: torch.Tensor, generic: bool = False) -> torch.Tensor:
+                    kv_len_bound: int, status: torch.Tensor, generic: bool = False, kv_maps: KVMaps | None = None,
+                    layer_in_pool: int = 0) -> torch.Tensor:
     """Causal grouped-query attention of the step's new tokens over the paged cache
     (oxr_runtime/attention.py:47-109). ``q`` is ``[tokens, H, D]``; ``k_cache`` / ``v_cache`` are one layer's pool
     ``[pages, page_size, KV, D]``; ``window`` > 0 limits a query to its last ``window`` keys; ``tiles`` maps each
     spec of :func:`attention_tile_specs` to ``(tile_req, tile_tok0, count)``; ``kv_len_bound`` is an upper bound of
     the context lengths. float32 runs the fp32 CUDA-core kernel, bfloat16 the tensor-core kernels (``generic``
-    forces the CUDA-core kernel, which then needs the float32 tile spec)."""
+    forces the CUDA-core kernel, which then needs the float32 tile spec). With ``kv_maps`` (of the pool that
+    ``k_cache`` / ``v_cache`` are layer ``layer_in_pool`` of) the split-KV kernel fetches K and V by TMA."""
     _need(q, "q")
     _need(k_cache, "k_cache", q.dtype)
     _need(v_cache, "v_cache", q.dtype)
@@ -330,7 +357,10 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         counters = _ticket_counters(q.device, units)
     code = lib.oxr_paged_attention_bf16(out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), s_req.data_ptr(),
                                         s_tok.data_ptr(), n_short, l_req.data_ptr(), l_tok.data_ptr(), n_long, *common, splits,
-                                        _ptr(part_o), _ptr(part_ml), _ptr(counters), status.data_ptr(), _stream())
+                                        _ptr(part_o), _ptr(part_ml), _ptr(counters),
+                                        kv_maps.address if kv_maps is not None else None,
+                                        layer_in_pool * kv_maps.rows_per_layer if kv_maps is not None else 0,
+                                        status.data_ptr(), _stream())
     global launch_count
     _done(code, "paged_attention_bf16")
     launch_count += 1 if n_long and n_short else 0

@@ -29,7 +29,7 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompil
 
 CORE_SOURCES = ["elementwise.cu", "qk_norm_rope.cu", "gemm_f32.cu", "gemm_skinny.cu", "gemm_tcgen05.cu", "sampling.cu"]
 ATTENTION_SOURCES = ["attention.cu"]
-HEADERS = ["common.cuh", "sampling_static.h"]
+HEADERS = ["common.cuh", "tma.cuh", "sampling_static.h"]
 
 
 class BuildError(RuntimeError):

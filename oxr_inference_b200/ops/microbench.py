@@ -82,11 +82,15 @@ def attention(args) -> dict:
                     tok.append(t0)
         tiles[spec] = (torch.tensor(req + [0], dtype=torch.int32, device="cuda"), torch.tensor(tok + [0], dtype=torch.int32, device="cuda"), len(req))
     status = ops.new_status("cuda")
+    k_pool = torch.stack([p[0] for p in pools])
+    v_pool = torch.stack([p[1] for p in pools])
+    del pools
+    maps = None if args.no_tma else ops.make_kv_maps(k_pool, v_pool, P)
 
     def run(i):
-        k, v = pools[i % layers]
-        ops.paged_attention(q, k, v, tiles=tiles, cu_q=cu, ctx_lens=ctx_lens, block_table=table, page_size=P, scale=D ** -0.5,
-                            window=0, kv_len_bound=ctx, status=status)
+        layer = i % layers
+        ops.paged_attention(q, k_pool[layer], v_pool[layer], tiles=tiles, cu_q=cu, ctx_lens=ctx_lens, block_table=table, page_size=P,
+                            scale=D ** -0.5, window=0, kv_len_bound=ctx, status=status, kv_maps=maps, layer_in_pool=layer)
     us = _time(run, args.reps)
     ops.check_status(status)
     kv_bytes = B * ctx * KV * D * 2 * 2
@@ -124,6 +128,7 @@ def main() -> None:
     a.add_argument("--kv-heads", type=int, default=8)
     a.add_argument("--head-dim", type=int, default=128)
     a.add_argument("--page-size", type=int, default=16)
+    a.add_argument("--no-tma", action="store_true", help="gather K and V with cp.async instead of TMA")
     a.set_defaults(run=attention)
     n = sub.add_parser("norm")
     n.add_argument("--rows", type=int, default=8)

@@ -99,6 +99,8 @@ class GroupView:
     """int32 [requests, width]"""
     slots: torch.Tensor
     """int32 [tokens]: where each new token's K and V go (page * page_size + offset)."""
+    kv_maps: object | None = None
+    """TMA tensor maps over the pools (``ops.make_kv_maps``), when the sizes allow them."""
 
 
 @dataclass

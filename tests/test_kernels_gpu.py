@@ -413,3 +413,38 @@ def test_repetition_penalty(ops):
 def test_no_cpu_path(ops):
     with pytest.raises(ops.KernelError, match="CUDA device only"):
         ops.silu_mul(torch.zeros(2, 4))
+
+
+@pytest.mark.parametrize("H,KV,D,P", [(32, 8, 128, 16), (8, 2, 64, 8), (4, 4, 128, 64), (16, 1, 64, 256), (2, 2, 256, 32)])
+@pytest.mark.parametrize("window", [0, 300])
+def test_split_kv_decode_with_tma_gathers(ops, H, KV, D, P, window):
+    """The split-KV kernel fetching K and V by TMA from a pool of several layers (the layer is chosen by a row offset
+    into the pool's tensor map): against the plain statement, and against the cp.async version of the same kernel."""
+    g = torch.Generator(device=DEV).manual_seed(70 + D)
+    q_lens = [1, 1, 1, 5, 2]
+    ctx_lens = [1500, 333, 1, 1029, 64]
+    layers, layer = 3, 1
+    q, k_cache, v_cache, table, cu = _paged_case(g, q_lens, ctx_lens, H, KV, D, P, torch.bfloat16)
+    k_pool = torch.randn(layers, *k_cache.shape, device=DEV, generator=g).bfloat16()
+    v_pool = torch.randn(layers, *v_cache.shape, device=DEV, generator=g).bfloat16()
+    k_pool[layer], v_pool[layer] = k_cache, v_cache
+    maps = ops.make_kv_maps(k_pool, v_pool, P)
+    assert maps is not None
+    tiles = _tiles(ops, q_lens, H, KV, D, torch.bfloat16)
+    status = ops.new_status(DEV)
+    common = dict(tiles=tiles, cu_q=torch.tensor(cu, dtype=torch.int32, device=DEV), ctx_lens=torch.tensor(ctx_lens, dtype=torch.int32, device=DEV),
+                  block_table=table, page_size=P, scale=D ** -0.5, window=window, kv_len_bound=max(ctx_lens), status=status)
+    got = ops.paged_attention(q, k_pool[layer], v_pool[layer], kv_maps=maps, layer_in_pool=layer, **common)
+    plain_gather = ops.paged_attention(q, k_pool[layer], v_pool[layer], **common)
+    ops.check_status(status)
+    want = KP.paged_attention(q, k_cache, v_cache, cu, ctx_lens, table, D ** -0.5, window)
+    torch.testing.assert_close(got.float(), want, atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(got.float(), plain_gather.float(), atol=4e-3, rtol=4e-3)
+
+
+def test_tma_gathers_are_refused_for_sizes_they_cannot_do(ops):
+    pool = torch.zeros(1, 4, 4, 2, 128, device=DEV, dtype=torch.bfloat16)
+    assert ops.make_kv_maps(pool, pool, 4) is None          # pages of 4 tokens
+    pool = torch.zeros(1, 4, 16, 2, 48, device=DEV, dtype=torch.bfloat16)
+    assert ops.make_kv_maps(pool, pool, 16) is None         # head size 48
+    assert ops.make_kv_maps(pool.float(), pool.float(), 16) is None
