@@ -33,6 +33,8 @@ class RequestCache:
     tables: list[list[int]] = field(default_factory=list)
     """Per group: page id of each page-sized stretch of positions; RELEASED behind a window."""
     closed: bool = False
+    version: int = 0
+    """Changes whenever ``tables`` changes (pages added or released), so that a copy of a table row can be reused."""
 
 
 def pages_for(tokens: int, page_size: int) -> int:
@@ -127,11 +129,15 @@ class CacheManager:
             raise ValueError("the request was closed")
         if new_length < rc.length:
             raise ValueError(f"a request cannot shrink ({rc.length} -> {new_length})")
-        needed = self.pages_needed(rc, new_length)
+        want = pages_for(new_length, self.page_size)
+        if all(want <= len(table) for table in rc.tables):
+            return True   # the pages are there already (the common case while decoding)
+        needed = [max(0, want - len(table)) for table in rc.tables]
         if any(n > pool.free for n, pool in zip(needed, self.pools)):
             return False
         for table, pool, n in zip(rc.tables, self.pools, needed):
             table.extend(pool.allocate(n))
+        rc.version += 1
         return True
 
     def advance(self, rc: RequestCache, new_length: int) -> None:
@@ -149,6 +155,7 @@ class CacheManager:
                 pool.release(gone)
                 for i in range(min(keep_from, len(table))):
                     table[i] = RELEASED
+                rc.version += 1
 
     def close(self, rc: RequestCache) -> None:
         """Give back every page and the state slot (finish, cancel, preemption, error:
@@ -160,6 +167,7 @@ class CacheManager:
             table.clear()
         self._free_slots.append(rc.state_slot)
         rc.closed = True
+        rc.version += 1
         rc.length = 0
         del self._open[id(rc)]
 
@@ -200,6 +208,13 @@ class CacheManager:
         if (pages < 0).any():
             raise ValueError("a position to be written lies on a released page")
         return (pages * self.page_size + pos % self.page_size).astype(np.int32)
+
+    def slot(self, rc: RequestCache, group: int, position: int) -> int:
+        """Cache slot of one position (the single-token case of :meth:`slots`, without numpy)."""
+        page = rc.tables[group][position // self.page_size]
+        if page < 0:
+            raise ValueError("a position to be written lies on a released page")
+        return page * self.page_size + position % self.page_size
 
     def table_width(self, rcs: list[RequestCache], group: int) -> int:
         return max([len(rc.tables[group]) for rc in rcs] + [1])

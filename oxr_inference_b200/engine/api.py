@@ -63,6 +63,7 @@ class Engine:
         self.graphs = DecodeGraphs(self.runner, max_batch=s.max_running, max_positions=self.max_positions) if s.cuda_graphs else None
         self._seen: torch.Tensor | None = None  # [slots + 1, vocab] uint8, made when a request first asks for a penalty
         self._done: dict[int, Completion] = {}
+        self._readback: torch.Tensor | None = None  # pinned: sampled tokens + status word of a step
         self.tokenizer = None
         if model_dir is not None and (Path(model_dir) / "tokenizer.json").is_file():
             from tokenizers import Tokenizer
@@ -147,8 +148,14 @@ class Engine:
             tokens = ops.sample(logits, s["temperature"], s["seed_lo"], s["seed_hi"], s["counter"]) if sampled else ops.sample(logits)
             if penalised:
                 ops.mark_seen(self._seen, s["row_slot"], tokens)
-        # one device-to-host read per step: the tokens and the kernels' status word together
-        host = torch.cat((tokens, rt.status[:2])).tolist()
+        # one synchronisation per step: the tokens and the kernels' status word land in pinned memory together
+        n = tokens.numel()
+        if self._readback is None or self._readback.numel() < n + 2:
+            self._readback = torch.empty(max(n + 2, 1026), dtype=torch.int32).pin_memory()
+        self._readback[:n].copy_(tokens, non_blocking=True)
+        self._readback[n:n + 2].copy_(rt.status[:2], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        host = self._readback[:n + 2].tolist()
         if host[-2] != 0:
             ops.check_status(rt.status)
         return host[:-2]

@@ -73,15 +73,27 @@ class BatchBuilder:
         self.manager, self.tile_specs, self.device, self.status = manager, list(tile_specs), device, status
         self._pinned: torch.Tensor | None = None
         self._copied: torch.cuda.Event | None = None
+        self._fixed_pinned: dict[int, torch.Tensor] = {}
+        self._fixed_views: dict[int, StepContext] = {}
+        self._rows: dict[int, list] = {}
+        """Per fixed device block: which (request, table version) each block-table row was last filled from, so that
+        rows that did not change are not written again."""
 
     # ---- host memory
-    def _staging(self, words: int) -> np.ndarray:
+    def _staging(self, words: int, fixed_block: torch.Tensor | None) -> torch.Tensor:
+        """Pinned host memory for one step's arrays. A fixed layout has a staging block of its own, which therefore
+        still holds what the layout's previous step wrote."""
         if self._copied is not None:
-            self._copied.synchronize()  # the previous step's copy has left the block
+            self._copied.synchronize()  # the previous step's copy has left its block
             self._copied = None
+        if fixed_block is not None:
+            key = id(fixed_block)
+            if key not in self._fixed_pinned:
+                self._fixed_pinned[key] = torch.zeros(words, dtype=torch.int32).pin_memory()
+            return self._fixed_pinned[key]
         if self._pinned is None or self._pinned.numel() < words:
             self._pinned = torch.empty(max(words, 4096), dtype=torch.int32).pin_memory()
-        return self._pinned.numpy()
+        return self._pinned
 
     def eager_layout(self, entries: list[StepEntry]) -> Layout:
         m = self.manager
@@ -115,7 +127,8 @@ class BatchBuilder:
         n_real = len(entries)
         if fixed and (n_real > layout.requests or any(len(e.tokens) != 1 or e.want != [0] for e in entries)):
             raise ValueError("a fixed layout takes single-token entries that want their logits, up to its size")
-        host = self._staging(layout.total)
+        pinned = self._staging(layout.total, device_block if fixed else None)
+        host = pinned.numpy()
         P = m.page_size
 
         def seg(name: str) -> np.ndarray:
@@ -131,13 +144,21 @@ class BatchBuilder:
             raise ValueError(f"layout holds {T} tokens, the entries bring {int(cu[-1])}")
 
         ids, pos, req = seg("token_ids"), seg("positions"), seg("req_of_token")
-        ids[:] = 0
-        pos[:] = 0
-        for i, e in enumerate(entries):
-            a, b = int(cu[i]), int(cu[i + 1])
-            ids[a:b] = e.tokens
-            pos[a:b] = np.arange(starts[i], starts[i] + q_lens[i])
-        req[:] = np.repeat(np.arange(n, dtype=np.int32), q_lens)
+        single = all(q == 1 for q in q_lens)
+        if single:   # decode-only step: one assignment per array
+            ids[:n_real] = [e.tokens[0] for e in entries]
+            ids[n_real:] = 0
+            pos[:n_real] = starts[:n_real]
+            pos[n_real:] = 0
+            req[:] = np.arange(n, dtype=np.int32)
+        else:
+            ids[:] = 0
+            pos[:] = 0
+            for i, e in enumerate(entries):
+                a, b = int(cu[i]), int(cu[i + 1])
+                ids[a:b] = e.tokens
+                pos[a:b] = np.arange(starts[i], starts[i] + q_lens[i])
+            req[:] = np.repeat(np.arange(n, dtype=np.int32), q_lens)
         seg("no_store")[:] = -1
         seg("cu_q")[:] = cu
         seg("ctx_lens")[:] = [s + q for s, q in zip(starts, q_lens)]
@@ -145,41 +166,74 @@ class BatchBuilder:
 
         rows, temp, slo, shi, cnt, rslot = (seg(k) for k in ("logit_rows", "temperature", "seed_lo", "seed_hi", "counter", "row_slot"))
         temp_f, pen_f = temp.view(np.float32), seg("penalty").view(np.float32)
-        r = 0
-        for i, e in enumerate(entries):
-            for w in e.want:
-                if not 0 <= w < q_lens[i]:
-                    raise ValueError(f"wanted index {w} is outside the entry's {q_lens[i]} tokens")
-                rows[r] = int(cu[i]) + w
-                temp_f[r] = e.temperature
-                slo[r] = _as_i32(e.seed & 0xFFFFFFFF)
-                shi[r] = _as_i32((e.seed >> 32) & 0xFFFFFFFF)
-                cnt[r] = e.counter
-                rslot[r] = e.cache.state_slot
-                pen_f[r] = e.penalty
+        if single and all(e.want == [0] for e in entries):
+            if layout.rows != n:
+                raise ValueError(f"layout holds {layout.rows} logit rows, the entries want {n}")
+            rows[:] = np.arange(n, dtype=np.int32)
+            temp_f[:n_real] = [e.temperature for e in entries]
+            slo[:n_real] = [_as_i32(e.seed & 0xFFFFFFFF) for e in entries]
+            shi[:n_real] = [_as_i32((e.seed >> 32) & 0xFFFFFFFF) for e in entries]
+            cnt[:n_real] = [e.counter for e in entries]
+            rslot[:n_real] = [e.cache.state_slot for e in entries]
+            pen_f[:n_real] = [e.penalty for e in entries]
+            temp_f[n_real:] = 0.0
+            slo[n_real:] = 0
+            shi[n_real:] = 0
+            cnt[n_real:] = 0
+            rslot[n_real:] = m.scratch_slot
+            pen_f[n_real:] = 1.0
+        else:
+            r = 0
+            for i, e in enumerate(entries):
+                for w in e.want:
+                    if not 0 <= w < q_lens[i]:
+                        raise ValueError(f"wanted index {w} is outside the entry's {q_lens[i]} tokens")
+                    rows[r] = int(cu[i]) + w
+                    temp_f[r] = e.temperature
+                    slo[r] = _as_i32(e.seed & 0xFFFFFFFF)
+                    shi[r] = _as_i32((e.seed >> 32) & 0xFFFFFFFF)
+                    cnt[r] = e.counter
+                    rslot[r] = e.cache.state_slot
+                    pen_f[r] = e.penalty
+                    r += 1
+            for i in range(n_real, n):  # padding rows: greedy on their own token
+                rows[r] = int(cu[i])
+                temp_f[r] = 0.0
+                slo[r] = shi[r] = cnt[r] = 0
+                rslot[r] = m.scratch_slot
+                pen_f[r] = 1.0
                 r += 1
-        for i in range(n_real, n):  # padding rows: greedy on their own token
-            rows[r] = int(cu[i])
-            temp_f[r] = 0.0
-            slo[r] = shi[r] = cnt[r] = 0
-            rslot[r] = m.scratch_slot
-            pen_f[r] = 1.0
-            r += 1
-        if r != layout.rows:
-            raise ValueError(f"layout holds {layout.rows} logit rows, the entries want {r}")
+            if r != layout.rows:
+                raise ValueError(f"layout holds {layout.rows} logit rows, the entries want {r}")
 
+        # Block tables: the staging block of a fixed layout keeps last step's rows, so a row whose request and table
+        # did not change is left as it is.
+        remembered = self._rows.setdefault(id(device_block), [None] * (n * len(m.pools))) if fixed else None
+        if remembered is not None and len(remembered) != n * len(m.pools):
+            remembered = self._rows[id(device_block)] = [None] * (n * len(m.pools))
         for g in range(len(m.pools)):
             w = layout.widths[g]
             slots, table = seg(f"slots{g}"), seg(f"table{g}").reshape(n, w)
             fill = m.scratch_pages[g] if m.scratch_pages else 0
-            table[:] = fill
             for i, e in enumerate(entries):
-                t = e.cache.tables[g]
-                if len(t) > w:
-                    raise ValueError(f"a block table of {len(t)} pages does not fit the layout's width {w}")
-                table[i, :len(t)] = t
-                slots[int(cu[i]):int(cu[i + 1])] = m.slots(e.cache, g, starts[i], starts[i] + q_lens[i])
+                key = (id(e.cache), e.cache.version)
+                if remembered is None or remembered[g * n + i] != key:
+                    t = e.cache.tables[g]
+                    if len(t) > w:
+                        raise ValueError(f"a block table of {len(t)} pages does not fit the layout's width {w}")
+                    table[i, :len(t)] = t
+                    table[i, len(t):] = fill
+                    if remembered is not None:
+                        remembered[g * n + i] = key
+                if q_lens[i] == 1:
+                    slots[int(cu[i])] = m.slot(e.cache, g, starts[i])
+                else:
+                    slots[int(cu[i]):int(cu[i + 1])] = m.slots(e.cache, g, starts[i], starts[i] + q_lens[i])
             for i in range(n_real, n):
+                if remembered is None or remembered[g * n + i] != "pad":
+                    table[i, :] = fill
+                    if remembered is not None:
+                        remembered[g * n + i] = "pad"
                 slots[int(cu[i])] = fill * P
 
         tiles_n: dict[tuple[int, int, int], int] = {}
@@ -198,12 +252,17 @@ class BatchBuilder:
 
         if device_block is None:
             device_block = torch.empty(layout.total, dtype=torch.int32, device=self.device)
-        device_block[:layout.total].copy_(self._pinned[:layout.total], non_blocking=True)
+        device_block[:layout.total].copy_(pinned[:layout.total], non_blocking=True)
         self._copied = torch.cuda.Event()
         self._copied.record()
         ctx_lens = [s + q for s, q in zip(starts, q_lens)]
-        bound = max(layout.widths) * P if fixed else max(ctx_lens)
-        return self.views(layout, device_block, tiles_n, q_lens, ctx_lens, bound)
+        if fixed:   # the views into a fixed block never change: make them once
+            ctx = self._fixed_views.get(id(device_block))
+            if ctx is None:
+                ctx = self._fixed_views[id(device_block)] = self.views(layout, device_block, tiles_n, q_lens, ctx_lens, max(layout.widths) * P)
+            ctx.q_lens, ctx.ctx_lens_host = q_lens, ctx_lens
+            return ctx
+        return self.views(layout, device_block, tiles_n, q_lens, ctx_lens, max(ctx_lens))
 
     def views(self, layout: Layout, block: torch.Tensor, tiles_n: dict, q_lens: list[int], ctx_lens: list[int],
               kv_len_bound: int) -> StepContext:
