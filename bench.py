@@ -31,6 +31,16 @@ QWEN3_8B = {
     "num_hidden_layers": 36, "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "rms_norm_eps": 1e-6,
     "rope_theta": 1000000.0, "vocab_size": 151936, "tie_word_embeddings": False, "max_position_embeddings": 4096,
 }
+QWEN3_4B = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "hidden_size": 2560, "intermediate_size": 9728,
+    "num_hidden_layers": 36, "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "rms_norm_eps": 1e-6,
+    "rope_theta": 1000000.0, "vocab_size": 151936, "tie_word_embeddings": True, "max_position_embeddings": 4096,
+}
+QWEN3_32B = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "hidden_size": 5120, "intermediate_size": 25600,
+    "num_hidden_layers": 64, "num_attention_heads": 64, "num_key_value_heads": 8, "head_dim": 128, "rms_norm_eps": 1e-6,
+    "rope_theta": 1000000.0, "vocab_size": 151936, "tie_word_embeddings": False, "max_position_embeddings": 8192,
+}
 CONTEXT = 2048
 PREFILL_TOKENS = 2048
 METRIC = "Qwen3-8B bf16 decode tok/s at batch 8 (context 2048)"
@@ -93,6 +103,54 @@ def reference_arm() -> int:
     return 0
 
 
+def serving_workload(which: str) -> int:
+    """The two serving workloads beside the headline: many requests through ``Engine.generate`` (wall clock, host in the
+    loop). ``continuous``: Qwen3-4B sizes (tied head), 256 requests, prompts of 64..2048 and outputs of 32..512 tokens,
+    greedy. ``chunked``: Qwen3-32B sizes, 32 requests of 4,096 prompt tokens cut into 2,048-token portions mixed with
+    decoding, 256 output tokens each."""
+    import random
+
+    import torch
+
+    from oxr_inference_b200 import ops
+    from oxr_inference_b200.config import EngineSettings
+    from oxr_inference_b200.engine.api import Engine
+    from oxr_inference_b200.sampling import SamplingParams
+
+    rng = random.Random(0)
+    if which == "continuous":
+        cfg, kv_gb, max_running, budget = QWEN3_4B, 40.0, 256, 8192
+        work = [(rng.randint(64, 2048), rng.randint(32, 512)) for _ in range(256)]
+    else:
+        cfg, kv_gb, max_running, budget = QWEN3_32B, 40.0, 32, 2048 + 32
+        work = [(4096, 256)] * 32
+    V = cfg["vocab_size"]
+    engine = Engine(random_config=cfg, seed=0, settings=EngineSettings(
+        dtype="bfloat16", page_size=16, kv_cache_gb=kv_gb, max_running=max_running, max_step_tokens=budget, prefill_chunk=2048,
+        max_positions=cfg["max_position_embeddings"], cuda_graphs=True))
+    prompts = [[rng.randrange(V) for _ in range(p)] for p, _ in work]
+    params = [SamplingParams(max_tokens=o, ignore_eos=True) for _, o in work]
+    engine.generate(prompts[:2], [SamplingParams(max_tokens=4, ignore_eos=True)] * 2)   # warm-up: libraries, first graphs
+    before = dict(engine.counters)
+    launches = ops.launch_count
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    done = engine.generate(prompts, params)
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - t0
+    out_tokens = sum(len(c.token_ids) for c in done)
+    in_tokens = sum(len(p) for p in prompts)
+    assert all(len(c.token_ids) == o for c, (_, o) in zip(done, work))
+    print(json.dumps({
+        "workload": which, "model": "Qwen3-4B shape (tied)" if which == "continuous" else "Qwen3-32B shape", "requests": len(work),
+        "prompt_tokens": in_tokens, "output_tokens": out_tokens, "seconds": round(seconds, 3),
+        "output_tok_s": round(out_tokens / seconds, 1), "total_tok_s": round((in_tokens + out_tokens) / seconds, 1),
+        "steps": engine.counters["steps"] - before["steps"], "graph_steps": engine.counters["graph_steps"] - before["graph_steps"],
+        "preemptions": engine.preemptions, "gpu_launches": ops.launch_count - launches, "dtype": "bf16",
+        "data": "synthetic uniform token ids, random weights N(0, 0.02)"}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -101,12 +159,16 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"], help="fewer layers than the model has (named in config)")
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64 (quick runs)")
+    ap.add_argument("--workload", default="decode", choices=("decode", "continuous", "chunked"),
+                    help="decode: the headline line (default); continuous / chunked: the two serving workloads, one line each")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
     if args.gpus != 1:
         print(f"this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.workload != "decode":
+        return serving_workload(args.workload)
     K, W = args.steps, max(args.warmup, 3)
 
     import torch
