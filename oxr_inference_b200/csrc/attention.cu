@@ -332,8 +332,8 @@ __device__ __forceinline__ const bf16* kv_elem(const bf16* base, int row, int d)
 
 // One warp: S = Q K^T for its 16 rows and NK keys starting at Kw, masked online softmax, O += P V.
 // qf: Q fragments when Q_IN_REGS, else read from Qw (this warp's 16 rows in shared memory).
-template <int NK, bool SWZ = false>
-__device__ __forceinline__ void warp_block(const uint32_t (&qf)[Q_IN_REGS ? KSTEPS : 1][4], const bf16* Qw, const bf16* Kw,
+template <int NK, bool SWZ = false, bool QREG = Q_IN_REGS>
+__device__ __forceinline__ void warp_block(const uint32_t (&qf)[QREG ? KSTEPS : 1][4], const bf16* Qw, const bf16* Kw,
                                            const bf16* Vw, int key0, const int (&row_pos)[2], const bool (&row_ok)[2],
                                            int window, bool full_block, float scale_log2, float (&m)[2], float (&l)[2],
                                            float (&o)[DT8][4]) {
@@ -345,7 +345,7 @@ __device__ __forceinline__ void warp_block(const uint32_t (&qf)[Q_IN_REGS ? KSTE
 #pragma unroll
     for (int kk = 0; kk < KSTEPS; ++kk) {
         uint32_t aq[4];
-        if constexpr (Q_IN_REGS) {
+        if constexpr (QREG) {
             aq[0] = qf[kk][0]; aq[1] = qf[kk][1]; aq[2] = qf[kk][2]; aq[3] = qf[kk][3];
         } else {
             ldsm_x4(aq, Qw + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + kk * 16 + 8 * (lane >> 4));
@@ -958,6 +958,327 @@ attn_tma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
         out[((size_t)(g.q_begin + tok) * a.H + (size_t)g.kvh * g.G + gh) * D + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
     }
 }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Prefill attention on tcgen05: a tile is 128 rows (one TMEM lane each). Per 64-key block
+//   S = Q K^T      tcgen05.mma, Q and K from shared memory (K-major, 128-byte swizzle), S (128 x 64 fp32) in TMEM,
+//                  double-buffered so that the next block's S is computed while this block's softmax runs;
+//   softmax        four warps, ONE THREAD PER ROW: tcgen05.ld its row of S, mask, running maximum and sum without any
+//                  shuffle, P = exp2(S - m) written as bf16 into a swizzled shared-memory tile;
+//   O += P V       tcgen05.mma, P from shared memory, V from the TMA stage as an MN-major operand, O (128 x D fp32) in TMEM.
+// The running maximum is only raised when a row's maximum grows by more than 8 (in log2 units): P then stays below
+// 2^8, which bf16 and the fp32 accumulator take without loss, and the rescale of O (tcgen05.ld, multiply, tcgen05.st)
+// becomes rare. K and V blocks arrive by TMA from a producer warp exactly as in the split-KV kernel.
+// Warp roles: 0 = TMA producer, 1 = MMA issuer and owner of the TMEM allocation, 2..5 = softmax and epilogue.
+// Every mbarrier wait is bounded.
+// ---------------------------------------------------------------------------------------------------------------------
+constexpr int BIG_ROWS = 128;
+constexpr int TC_STAGES = 3;
+constexpr int TC_THREADS = 192;
+constexpr int Q_PANEL_BYTES = BIG_ROWS * 128;                       // 128 rows x 64 d
+constexpr int P_BYTES = BIG_ROWS * 128;                             // 128 rows x 64 keys
+constexpr size_t TC_SMEM = 1024 + (size_t)PANELS * Q_PANEL_BYTES + (size_t)TC_STAGES * KV_STAGE_BYTES + 2 * P_BYTES + 256;
+constexpr uint32_t TC_TMEM_COLS = D <= 128 ? 256 : 512;             // S0 (64) | S1 (64) | O (D)
+constexpr float RESCALE_THRESHOLD = 8.f;
+
+// K-major operand tile with 128-byte rows, 128-byte swizzle (Q, K, P): see gemm_tcgen05.cu
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t saddr) {
+    return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// MN-major operand (V: rows are keys = K, 64 d contiguous per 128-byte row, panels of 64 d 8 KB apart): 8 keys per
+// swizzle atom, the next 8 keys 1024 bytes on (stride byte offset), the next 64 d one panel on (leading byte offset).
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t saddr) {
+    return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)(PANEL_BYTES >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+           ((uint64_t)2 << 61);
+}
+// kind::f16 instruction descriptor: fp32 accumulator, bf16 operands, A K-major, B K-major or MN-major
+__host__ __device__ constexpr uint32_t attn_idesc(int m, int n, bool b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+          "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
+          "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+          "r"(r[30]), "r"(r[31])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ bool elect_one_lane() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__global__ void __launch_bounds__(TC_THREADS, 1)
+attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, const __grid_constant__ CUtensorMap map_k,
+                        const __grid_constant__ CUtensorMap map_v, int pool_row0, int box_rows, const AttnArgs a) {
+    extern __shared__ unsigned char smem_dyn[];
+    unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+    unsigned char* Qs = base;                                              // PANELS panels of [128 rows][128 B], swizzled
+    unsigned char* stages = Qs + (size_t)PANELS * Q_PANEL_BYTES;           // TC_STAGES x (K panels, V panels)
+    unsigned char* Ps = stages + (size_t)TC_STAGES * KV_STAGE_BYTES;       // 2 x [128 rows][128 B], swizzled
+    uint64_t* kv_full = reinterpret_cast<uint64_t*>(Ps + 2 * P_BYTES);
+    uint64_t* kv_empty = kv_full + TC_STAGES;
+    uint64_t* s_full = kv_empty + TC_STAGES;     // [2] S(b) is in TMEM
+    uint64_t* s_empty = s_full + 2;              // [2] the softmax warps have read S(b) (4 arrivals)
+    uint64_t* p_full = s_empty + 2;              // [2] P(b) is in shared memory and O is rescaled (4 arrivals)
+    uint64_t* o_done = p_full + 2;               // [2] O += P(b) V(b) has completed
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 2);
+
+    const TileGeometry g = tile_geometry(a, BIG_ROWS);
+    if (g.tok0 >= g.tok_end) return;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int k_end = g.pos0 + g.tok_end;
+    const int k_lo = a.window > 0 ? max(0, g.pos0 + g.tok0 - a.window + 1) : 0;
+    const int k_first = (k_lo / MMA_BN) * MMA_BN;
+    const int count = (k_end - k_first + MMA_BN - 1) / MMA_BN;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < TC_STAGES; ++i) { mbar_init(kv_full + i, 1); mbar_init(kv_empty + i, 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(s_full + i, 1); mbar_init(s_empty + i, 4); mbar_init(p_full + i, 4); mbar_init(o_done + i, 1); }
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(TC_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    // The stages must hold finite numbers where pages are not fetched (they meet a probability of exactly zero).
+    for (int i = threadIdx.x; i < (int)((size_t)TC_STAGES * KV_STAGE_BYTES / 16); i += TC_THREADS)
+        reinterpret_cast<uint4*>(stages)[i] = make_uint4(0, 0, 0, 0);
+    // Q: every softmax thread copies its own row (D bf16) into the swizzled panels; rows without a (token, head) are zero.
+    if (warp >= 2) {
+        const int r = (warp - 2) * 32 + lane;
+        int tok, gh;
+        const bool ok = g.row(r, tok, gh);
+        const uint4* src = reinterpret_cast<const uint4*>(q + ((size_t)(g.q_begin + (ok ? tok : 0)) * a.H + (size_t)g.kvh * g.G + (ok ? gh : 0)) * D);
+#pragma unroll
+        for (int c = 0; c < D / 8; ++c) {
+            const uint4 v = ok ? __ldg(src + c) : make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(Qs + (size_t)(c >> 3) * Q_PANEL_BYTES + (size_t)r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
+        }
+    }
+    fence_proxy_async();
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_o = tmem_base + 128;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------------- TMA producer (all 32 lanes issue)
+        const int* table_row = a.block_table + (size_t)g.req * a.table_width;
+        const int boxes = MMA_BN / box_rows, loads = boxes * 2 * PANELS;
+        for (int b = 0; b < count; ++b) {
+            const int st = b % TC_STAGES;
+            if (!mbar_wait(kv_empty + st, ((b / TC_STAGES) & 1) ^ 1)) { if (lane == 0) oxr_report(a.status, OXR_WAIT_EXPIRED, 30); break; }
+            const int k0 = k_first + b * MMA_BN;
+            unsigned char* dst = stages + (size_t)st * KV_STAGE_BYTES;
+            int my_bytes = 0;
+            for (int i = lane; i < loads; i += 32) {
+                const int kp = k0 + (i / (2 * PANELS)) * box_rows;
+                if (kp < k_end && kp + box_rows > k_lo) {
+                    const int page = table_row[a.page_shift >= 0 ? (kp >> a.page_shift) : (kp / a.page_size)];
+                    if (page >= 0 && page < a.num_pages) my_bytes += box_rows * 128;
+                    else oxr_report(a.status, OXR_BAD_PAGE, g.req);
+                }
+            }
+            const int total = __reduce_add_sync(0xffffffffu, my_bytes);
+            if (lane == 0) {
+                if (total > 0) mbar_expect_tx(kv_full + st, (uint32_t)total);
+                else mbar_arrive(kv_full + st);
+            }
+            __syncwarp();
+            for (int i = lane; i < loads; i += 32) {
+                const int box = i / (2 * PANELS), which = i % (2 * PANELS);
+                const int kp = k0 + box * box_rows;
+                if (kp < k_end && kp + box_rows > k_lo) {
+                    const int page = table_row[a.page_shift >= 0 ? (kp >> a.page_shift) : (kp / a.page_size)];
+                    if (page >= 0 && page < a.num_pages) {
+                        const int row = pool_row0 + page * a.page_size + (a.page_shift >= 0 ? (kp & (a.page_size - 1)) : (kp % a.page_size));
+                        tma_load_2d(dst + (size_t)which * PANEL_BYTES + (size_t)box * box_rows * 128, which < PANELS ? &map_k : &map_v,
+                                    g.kvh * D + (which % PANELS) * 64, row, kv_full + st);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------------- MMA issuer
+        if (elect_one_lane()) {
+            constexpr uint32_t idesc_s = attn_idesc(BIG_ROWS, MMA_BN, false);
+            constexpr uint32_t idesc_o = attn_idesc(BIG_ROWS, D, true);
+            const uint32_t q_addr = smem_addr(Qs), p_addr = smem_addr(Ps);
+            bool ok = true;
+            // S(b) is issued one block ahead of O(b): S(0); then for each b: S(b + 1), wait P(b), O += P(b) V(b)
+            auto issue_s = [&](int b) -> bool {
+                const int st = b % TC_STAGES;
+                if (!mbar_wait(kv_full + st, (b / TC_STAGES) & 1)) { oxr_report(a.status, OXR_WAIT_EXPIRED, 31); return false; }
+                if (!mbar_wait(s_empty + (b & 1), ((b >> 1) & 1) ^ 1)) { oxr_report(a.status, OXR_WAIT_EXPIRED, 32); return false; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t k_addr = smem_addr(stages + (size_t)st * KV_STAGE_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk)
+                    tc_mma(tmem_base + (uint32_t)((b & 1) * MMA_BN), desc_kmajor(q_addr + (kk >> 2) * Q_PANEL_BYTES + (kk & 3) * 32),
+                           desc_kmajor(k_addr + (kk >> 2) * PANEL_BYTES + (kk & 3) * 32), idesc_s, kk > 0 ? 1u : 0u);
+                tc_commit(s_full + (b & 1));
+                return true;
+            };
+            ok = issue_s(0);
+            for (int b = 0; b < count && ok; ++b) {
+                if (b + 1 < count) ok = issue_s(b + 1);
+                if (!ok) break;
+                if (!mbar_wait(p_full + (b & 1), (b >> 1) & 1)) { oxr_report(a.status, OXR_WAIT_EXPIRED, 33); break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const int st = b % TC_STAGES;
+                const uint32_t v_addr = smem_addr(stages + (size_t)st * KV_STAGE_BYTES + (size_t)PANELS * PANEL_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < MMA_BN / 16; ++kk)
+                    tc_mma(tmem_o, desc_kmajor(p_addr + (b & 1) * P_BYTES + kk * 32), desc_mnmajor(v_addr + kk * 16 * 128), idesc_o,
+                           (b > 0 || kk > 0) ? 1u : 0u);
+                tc_commit(kv_empty + st);       // K and V of this stage have been read by both products
+                tc_commit(o_done + (b & 1));
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------------- softmax and epilogue: one thread per row
+        const int quarter = warp & 3;                        // TMEM lanes 32 * quarter .. + 31 belong to this warp
+        const int r = quarter * 32 + lane;
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        int tok, gh;
+        const bool row_ok = g.row(r, tok, gh);
+        const int row_pos = g.pos0 + tok;
+        const float scale_log2 = a.scale * LOG2E;
+        float m_used = -INFINITY, l = 0.f;                   // the maximum P is taken against, the running sum
+        unsigned char* my_p_row = Ps + (size_t)r * 128;
+        bool alive = true;
+        for (int b = 0; b < count; ++b) {
+            const int key0 = k_first + b * MMA_BN;
+            if (!mbar_wait(s_full + (b & 1), (b >> 1) & 1)) { if (lane == 0) oxr_report(a.status, OXR_WAIT_EXPIRED, 34); alive = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            uint32_t sv[2][32];
+            tc_ld32(tmem_base + lane_base + (uint32_t)((b & 1) * MMA_BN), sv[0]);
+            tc_ld32(tmem_base + lane_base + (uint32_t)((b & 1) * MMA_BN + 32), sv[1]);
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(s_empty + (b & 1));    // S(b) is in registers: the buffer may take S(b + 2)
+            float mx = -INFINITY;
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const int kp = key0 + h * 32 + j;
+                    const bool seen = row_ok && kp <= row_pos && kp >= k_lo && (a.window <= 0 || kp > row_pos - a.window);
+                    const float v = seen ? __uint_as_float(sv[h][j]) * scale_log2 : -INFINITY;
+                    sv[h][j] = __float_as_uint(v);
+                    mx = fmaxf(mx, v);
+                }
+            // raise the maximum only when it grew by more than the threshold (or there was none yet)
+            float alpha = 1.f;
+            bool raise = mx > m_used + RESCALE_THRESHOLD || (m_used == -INFINITY && mx != -INFINITY);
+            if (raise) {
+                alpha = (m_used == -INFINITY) ? 0.f : fast_exp2(m_used - mx);
+                m_used = mx;
+            }
+            // the P buffer was last read by O(b - 2); a raised maximum also needs O(b - 1) finished before O is touched
+            const bool any_raise = __any_sync(0xffffffffu, raise && b > 0);
+            if (b >= 2 && !mbar_wait(o_done + (b & 1), ((b - 2) >> 1) & 1)) { if (lane == 0) oxr_report(a.status, OXR_WAIT_EXPIRED, 35); alive = false; break; }
+            if (any_raise) {
+                if (!mbar_wait(o_done + ((b - 1) & 1), ((b - 1) >> 1) & 1)) { if (lane == 0) oxr_report(a.status, OXR_WAIT_EXPIRED, 36); alive = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+                for (int c = 0; c < D / 32; ++c) {
+                    uint32_t ov[32];
+                    tc_ld32(tmem_o + lane_base + (uint32_t)(c * 32), ov);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) ov[j] = __float_as_uint(__uint_as_float(ov[j]) * alpha);
+                    tc_st32(tmem_o + lane_base + (uint32_t)(c * 32), ov);
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            }
+            float sum = 0.f;
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {         // 8 keys = one 16-byte chunk of the row
+                    uint4 chunk;
+                    __nv_bfloat162* cp = reinterpret_cast<__nv_bfloat162*>(&chunk);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float p0 = (m_used == -INFINITY) ? 0.f : fast_exp2(__uint_as_float(sv[h][c * 8 + 2 * e]) - m_used);
+                        const float p1 = (m_used == -INFINITY) ? 0.f : fast_exp2(__uint_as_float(sv[h][c * 8 + 2 * e + 1]) - m_used);
+                        sum += p0 + p1;
+                        cp[e] = __floats2bfloat162_rn(p0, p1);
+                    }
+                    *reinterpret_cast<uint4*>(my_p_row + (size_t)(b & 1) * P_BYTES + ((((h * 4 + c)) ^ (r & 7)) << 4)) = chunk;
+                }
+            l = l * alpha + sum;
+            fence_proxy_async();                      // P is read by the tensor core through the async proxy
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full + (b & 1));
+        }
+        // ---- epilogue: O / l -> out
+        if (alive && count > 0) {
+            const int last = count - 1;
+            if (!mbar_wait(o_done + (last & 1), (last >> 1) & 1)) { if (lane == 0) oxr_report(a.status, OXR_WAIT_EXPIRED, 37); alive = false; }
+        }
+        alive = __all_sync(0xffffffffu, alive);
+        if (alive) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            bf16* dst = out + ((size_t)(g.q_begin + (row_ok ? tok : 0)) * a.H + (size_t)g.kvh * g.G + (row_ok ? gh : 0)) * D;
+#pragma unroll 1
+            for (int c = 0; c < D / 32; ++c) {
+                uint32_t ov[32];
+                tc_ld32(tmem_o + lane_base + (uint32_t)(c * 32), ov);
+                if (row_ok) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        uint4 o4;
+                        __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            op[e] = __floats2bfloat162_rn(__uint_as_float(ov[8 * j + 2 * e]) * inv, __uint_as_float(ov[8 * j + 2 * e + 1]) * inv);
+                        reinterpret_cast<uint4*>(dst + c * 32)[j] = o4;
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TC_TMEM_COLS) : "memory");
+    }
+}
 }  // namespace
 
 OXR_API int oxr_attn_head_dim() { return D; }
@@ -972,12 +1293,13 @@ OXR_API int oxr_attn_decode_rows() { return DECODE_ROWS; }
 // before the first launch (the kernel leaves them zero), groups16 = ceil(G / min(G, 16)).
 // kv_maps (optional): the two tensor maps of oxr_attn_make_kv_maps for the pool that k_cache / v_cache are a layer
 // of, with pool_row0 = layer * num_pages * page_size; the split-KV kernel then fetches K and V by TMA.
+// long_rows: rows per long tile the host cut the long list for: 64 (cp.async kernel) or 128 (TMA kernel, needs kv_maps).
 OXR_API int oxr_paged_attention_bf16(void* out, const void* q, const void* k_cache, const void* v_cache,
                                      const int* short_req, const int* short_tok0, int n_short, const int* long_req,
                                      const int* long_tok0, int n_long, const int* cu_q, const int* ctx_lens,
                                      const int* block_table, int table_width, int page_size, int num_pages, int H, int KV,
                                      float scale, int window, int splits, float* part_o, float* part_ml, int* counters,
-                                     const void* kv_maps, int pool_row0, int* status, cudaStream_t stream) {
+                                     const void* kv_maps, int pool_row0, int long_rows, int* status, cudaStream_t stream) {
     if (n_short <= 0 && n_long <= 0) return 0;
     if (H <= 0 || KV <= 0 || H % KV != 0 || page_size <= 0 || table_width <= 0 || window < 0 || splits < 1) return OXR_BAD_ARGUMENT;
     if (splits > 1 && (part_o == nullptr || part_ml == nullptr || counters == nullptr)) return OXR_BAD_ARGUMENT;
@@ -997,7 +1319,27 @@ OXR_API int oxr_paged_attention_bf16(void* out, const void* q, const void* k_cac
     for (int sh = 0; sh < 30; ++sh) if ((1 << sh) == page_size) a.page_shift = sh;
     a.heads_per_tile = a.tokens_per_tile = a.head_groups = 0;   // the tensor-core kernels derive these from their row count
     a.scale = scale; a.window = window; a.status = status;
-    if (n_long > 0) {
+    if (n_long > 0 && long_rows == BIG_ROWS) {
+        // long tiles of 128 rows: the tcgen05 kernel (the host made the tile list for 128 rows)
+        if (!TMA_OK || D > 128 || kv_maps == nullptr || a.page_shift < 3) return OXR_BAD_ARGUMENT;
+        static bool big_configured = false;
+        if (!big_configured) {
+            cudaError_t e = cudaFuncSetAttribute(attn_tc5_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM);
+            if (e != cudaSuccess) return 1000 + (int)e;
+            big_configured = true;
+        }
+        const int hpt = G < BIG_ROWS ? G : BIG_ROWS;
+        const int groups = (G + hpt - 1) / hpt;
+        if ((size_t)KV * groups > 65535) return OXR_BAD_ARGUMENT;
+        a.tile_req = long_req; a.tile_tok0 = long_tok0;
+        const CUtensorMap* maps = reinterpret_cast<const CUtensorMap*>(kv_maps);
+        const int box_rows = page_size < MMA_BN ? page_size : MMA_BN;
+        attn_tc5_prefill_kernel<<<dim3(n_long, KV * groups), TC_THREADS, TC_SMEM, stream>>>((bf16*)out, (const bf16*)q, maps[0], maps[1],
+                                                                                             pool_row0, box_rows, a);
+        int rc = oxr_launch_status();
+        if (rc) return rc;
+    } else if (n_long > 0) {
+        if (long_rows != PREFILL_ROWS) return OXR_BAD_ARGUMENT;
         const int hpt = G < PREFILL_ROWS ? G : PREFILL_ROWS;
         const int groups = (G + hpt - 1) / hpt;
         if ((size_t)KV * groups > 65535) return OXR_BAD_ARGUMENT;

@@ -44,7 +44,8 @@ class Engine:
             raw, generation = read_config_json(model_dir)
         else:
             raw, generation = dict(random_config), None
-        model, self.config = ModelRunner.build_model(raw, generation, dtype=s.dtype, device=device, max_positions=s.max_positions)
+        model, self.config = ModelRunner.build_model(raw, generation, dtype=s.dtype, device=device, max_positions=s.max_positions,
+                                                      page_size=s.page_size)
         if model_dir is not None:
             load_weights(model, model_dir)
         else:

@@ -39,6 +39,8 @@ class ModelRunner:
     def __init__(self, model: DecoderModel, config: Any, *, page_size: int, num_pages: int, max_requests: int):
         self.model, self.config = model, config
         rt = model.runtime
+        if rt.page_size != page_size:
+            raise ValueError(f"the model was built for pages of {rt.page_size} tokens, the cache is asked for {page_size}")
         ops.warm_up(model.head_dims())
         self.cache = CacheManager(model.cache_plan, page_size=page_size, num_pages=num_pages, max_requests=max_requests,
                                   device=rt.device, dtype=rt.dtype)
@@ -48,20 +50,20 @@ class ModelRunner:
     # ---- construction
     @staticmethod
     def build_model(raw_config: Mapping[str, Any], generation: Mapping[str, Any] | None, *, dtype: str,
-                    device: str | torch.device = "cuda", max_positions: int | None = None):
+                    device: str | torch.device = "cuda", max_positions: int | None = None, page_size: int = 16):
         dev = require_cuda(device)
         arch = resolve_architecture(raw_config)
         config = arch.config_from_dict(raw_config, generation)
         spec = arch.model_spec(config)
         runtime = Runtime(device=dev, dtype=DTYPES[dtype], max_positions=max_positions or spec.max_positions,
-                          status=ops.new_status(dev))
+                          status=ops.new_status(dev), page_size=page_size)
         return DecoderModel(spec, runtime), config
 
     @classmethod
     def from_folder(cls, model_dir: str | Path, *, dtype: str, page_size: int, num_pages: int, max_requests: int,
                     device: str | torch.device = "cuda", max_positions: int | None = None) -> "ModelRunner":
         raw, generation = read_config_json(model_dir)
-        model, config = cls.build_model(raw, generation, dtype=dtype, device=device, max_positions=max_positions)
+        model, config = cls.build_model(raw, generation, dtype=dtype, device=device, max_positions=max_positions, page_size=page_size)
         load_weights(model, model_dir)
         return cls(model, config, page_size=page_size, num_pages=num_pages, max_requests=max_requests)
 
@@ -70,7 +72,7 @@ class ModelRunner:
                     max_requests: int, device: str | torch.device = "cuda", max_positions: int | None = None,
                     std: float = 0.02, norm_std: float = 0.1) -> "ModelRunner":
         """Random weights drawn on the device (no file)."""
-        model, config = cls.build_model(raw_config, None, dtype=dtype, device=device, max_positions=max_positions)
+        model, config = cls.build_model(raw_config, None, dtype=dtype, device=device, max_positions=max_positions, page_size=page_size)
         fill_random(model, seed, std=std, norm_std=norm_std)
         return cls(model, config, page_size=page_size, num_pages=num_pages, max_requests=max_requests)
 

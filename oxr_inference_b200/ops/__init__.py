@@ -106,7 +106,7 @@ def _attn_lib(head_dim: int):
         p, i, f = c_void_p, c_int, c_float
         lib.oxr_paged_attention.argtypes = [p, p, p, p, p, p, i, p, p, p, i, i, i, i, i, f, i, i, p, p]
         lib.oxr_paged_attention.restype = c_int
-        lib.oxr_paged_attention_bf16.argtypes = [p, p, p, p, p, p, i, p, p, i, p, p, p, i, i, i, i, i, f, i, i, p, p, p, p, i, p, p]
+        lib.oxr_paged_attention_bf16.argtypes = [p, p, p, p, p, p, i, p, p, i, p, p, p, i, i, i, i, i, f, i, i, p, p, p, p, i, i, p, p]
         lib.oxr_attn_make_kv_maps.argtypes = [p, p, p, ctypes.c_ulonglong, i, i]
         lib.oxr_attn_make_kv_maps.restype = c_int
         lib.oxr_paged_attention_bf16.restype = c_int
@@ -254,7 +254,7 @@ def qk_norm_rope_store(qkv: torch.Tensor, q_weight: torch.Tensor | None, k_weigh
     return q
 
 
-GENERIC_ROWS, DECODE_ROWS, PREFILL_ROWS = 16, 16, 64
+GENERIC_ROWS, DECODE_ROWS, PREFILL_ROWS, PREFILL_ROWS_TMA = 16, 16, 64, 128
 SHORT_MAX_TOKENS = 8
 """Requests that bring at most this many tokens go to the split-KV kernel, longer portions to the prefill kernel."""
 MAX_SPLITS = 32
@@ -265,14 +265,26 @@ def _tokens_per_tile(num_heads: int, num_kv_heads: int, rows: int) -> int:
     return rows // min(num_heads // num_kv_heads, rows)
 
 
-def attention_tile_specs(num_heads: int, num_kv_heads: int, head_dim: int, dtype: torch.dtype) -> list[tuple[int, int, int]]:
+def tma_gathers_possible(head_dim: int, page_size: int, dtype: torch.dtype) -> bool:
+    """Whether K and V of such a cache can be fetched by TMA: bf16, head size a multiple of 64, pages of 8 * 2^k tokens."""
+    return dtype == torch.bfloat16 and head_dim % 64 == 0 and page_size >= 8 and page_size & (page_size - 1) == 0
+
+
+def _long_rows(head_dim: int, tma: bool) -> int:
+    return PREFILL_ROWS_TMA if tma and head_dim <= 128 else PREFILL_ROWS
+
+
+def attention_tile_specs(num_heads: int, num_kv_heads: int, head_dim: int, dtype: torch.dtype,
+                         page_size: int | None = None) -> list[tuple[int, int, int]]:
     """The tile lists the attention kernels of this dtype read: (tokens per tile, fewest, most new tokens of the
-    requests the list covers). The host cuts each request's new tokens into such tiles."""
+    requests the list covers). The host cuts each request's new tokens into such tiles. With a ``page_size`` that
+    allows TMA gathers the long tiles are 128 rows (the TMA prefill kernel), else 64."""
     build.check_head_dim(head_dim)
     big = 1 << 30
     if dtype == torch.bfloat16:
+        tma = page_size is not None and tma_gathers_possible(head_dim, page_size, dtype)
         return [(_tokens_per_tile(num_heads, num_kv_heads, DECODE_ROWS), 1, SHORT_MAX_TOKENS),
-                (_tokens_per_tile(num_heads, num_kv_heads, PREFILL_ROWS), SHORT_MAX_TOKENS + 1, big)]
+                (_tokens_per_tile(num_heads, num_kv_heads, _long_rows(head_dim, tma)), SHORT_MAX_TOKENS + 1, big)]
     return [(_tokens_per_tile(num_heads, num_kv_heads, GENERIC_ROWS), 1, big)]
 
 
@@ -344,7 +356,10 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
                                        tile_tok0.data_ptr(), n, *common, _dtype_code(q), status.data_ptr(), _stream())
         _done(code, "paged_attention")
         return out
-    short, long_ = attention_tile_specs(num_heads, num_kv_heads, head_dim, torch.bfloat16)
+    long_rows = _long_rows(head_dim, kv_maps is not None)
+    short, long_ = attention_tile_specs(num_heads, num_kv_heads, head_dim, torch.bfloat16, page_size if kv_maps is not None else None)
+    if long_ not in tiles:
+        raise KernelError(f"no tile list for long tiles of {long_rows} rows: the batch was cut for {sorted(tiles)}")
     s_req, s_tok, n_short = tiles[short]
     l_req, l_tok, n_long = tiles[long_]
     splits = attention_splits(n_short, num_heads, num_kv_heads, kv_len_bound) if n_short else 1
@@ -359,7 +374,7 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
                                         s_tok.data_ptr(), n_short, l_req.data_ptr(), l_tok.data_ptr(), n_long, *common, splits,
                                         _ptr(part_o), _ptr(part_ml), _ptr(counters),
                                         kv_maps.address if kv_maps is not None else None,
-                                        layer_in_pool * kv_maps.rows_per_layer if kv_maps is not None else 0,
+                                        layer_in_pool * kv_maps.rows_per_layer if kv_maps is not None else 0, long_rows,
                                         status.data_ptr(), _stream())
     global launch_count
     _done(code, "paged_attention_bf16")

@@ -72,7 +72,7 @@ def attention(args) -> dict:
     cu = torch.arange(0, (B + 1) * q_len, q_len, dtype=torch.int32, device="cuda")
     ctx_lens = torch.full((B,), ctx, dtype=torch.int32, device="cuda")
     tiles = {}
-    for spec in ops.attention_tile_specs(H, KV, D, torch.bfloat16):
+    for spec in ops.attention_tile_specs(H, KV, D, torch.bfloat16, None if args.no_tma else P):
         tpt, lo, hi = spec
         req, tok = [], []
         if lo <= q_len <= hi:

@@ -57,7 +57,7 @@ class GroupedQueryAttention(Mixer):
         return PagedKVNeed(self.KV, self.D, self.window)
 
     def tile_specs(self) -> list[tuple[int, int, int]]:
-        return ops.attention_tile_specs(self.H, self.KV, self.D, self.runtime.dtype)
+        return ops.attention_tile_specs(self.H, self.KV, self.D, self.runtime.dtype, self.runtime.page_size)
 
     def forward(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
         group = cache.group

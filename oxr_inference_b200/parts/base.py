@@ -44,6 +44,8 @@ class Runtime:
     max_positions: int
     status: torch.Tensor
     """Device status word that kernels write their first error to (see ``ops.check_status``)."""
+    page_size: int = 16
+    """Tokens per cache page (an engine setting): kernels that read the cache may plan their tiles by it."""
 
     def store_dtype(self, info: ParamInfo, stored: torch.dtype) -> torch.dtype:
         if info.role == "vector" or self.dtype == torch.float32:

@@ -226,10 +226,11 @@ def _paged_case(g, q_lens, ctx_lens, H, KV, D, P, dtype, extra_pages=3):
     return q, k_cache, v_cache, table.to(DEV), cu
 
 
-def _tiles(ops, q_lens, H, KV, D, dtype):
-    """The tile lists the kernels of this dtype want: each request's new tokens cut into tiles."""
+def _tiles(ops, q_lens, H, KV, D, dtype, page_size=None):
+    """The tile lists the kernels of this dtype want: each request's new tokens cut into tiles (with a page size: the
+    lists for a cache whose K and V are fetched by TMA)."""
     out = {}
-    for spec in ops.attention_tile_specs(H, KV, D, dtype):
+    for spec in ops.attention_tile_specs(H, KV, D, dtype, page_size):
         tpt, fewest, most = spec
         req, tok = [], []
         for r, ql in enumerate(q_lens):
@@ -431,15 +432,42 @@ def test_split_kv_decode_with_tma_gathers(ops, H, KV, D, P, window):
     maps = ops.make_kv_maps(k_pool, v_pool, P)
     assert maps is not None
     tiles = _tiles(ops, q_lens, H, KV, D, torch.bfloat16)
+    tma_tiles = _tiles(ops, q_lens, H, KV, D, torch.bfloat16, P)
     status = ops.new_status(DEV)
-    common = dict(tiles=tiles, cu_q=torch.tensor(cu, dtype=torch.int32, device=DEV), ctx_lens=torch.tensor(ctx_lens, dtype=torch.int32, device=DEV),
+    common = dict( cu_q=torch.tensor(cu, dtype=torch.int32, device=DEV), ctx_lens=torch.tensor(ctx_lens, dtype=torch.int32, device=DEV),
                   block_table=table, page_size=P, scale=D ** -0.5, window=window, kv_len_bound=max(ctx_lens), status=status)
-    got = ops.paged_attention(q, k_pool[layer], v_pool[layer], kv_maps=maps, layer_in_pool=layer, **common)
-    plain_gather = ops.paged_attention(q, k_pool[layer], v_pool[layer], **common)
+    got = ops.paged_attention(q, k_pool[layer], v_pool[layer], tiles=tma_tiles, kv_maps=maps, layer_in_pool=layer, **common)
+    plain_gather = ops.paged_attention(q, k_pool[layer], v_pool[layer], tiles=tiles, **common)
     ops.check_status(status)
     want = KP.paged_attention(q, k_cache, v_cache, cu, ctx_lens, table, D ** -0.5, window)
     torch.testing.assert_close(got.float(), want, atol=2e-2, rtol=2e-2)
     torch.testing.assert_close(got.float(), plain_gather.float(), atol=4e-3, rtol=4e-3)
+
+
+@pytest.mark.parametrize("H,KV,D,P", [(32, 8, 128, 16), (6, 2, 64, 8), (3, 3, 64, 16), (4, 1, 128, 64), (40, 1, 64, 16)])
+def test_prefill_kernel_with_tma_gathers_on_long_portions(ops, H, KV, D, P):
+    """The 128-row prefill kernel (K and V by TMA): portions of hundreds of tokens from position 0 and deep inside a
+    context, beside short entries that go to the split-KV kernel in the same call."""
+    g = torch.Generator(device=DEV).manual_seed(80 + D)
+    q_lens = [300, 130, 64, 1, 9]
+    ctx_lens = [300, 517, 1000, 77, 9]
+    layers, layer = 2, 1
+    q, k_cache, v_cache, table, cu = _paged_case(g, q_lens, ctx_lens, H, KV, D, P, torch.bfloat16)
+    k_pool = torch.randn(layers, *k_cache.shape, device=DEV, generator=g).bfloat16()
+    v_pool = torch.randn(layers, *v_cache.shape, device=DEV, generator=g).bfloat16()
+    k_pool[layer], v_pool[layer] = k_cache, v_cache
+    maps = ops.make_kv_maps(k_pool, v_pool, P)
+    assert maps is not None
+    tiles = _tiles(ops, q_lens, H, KV, D, torch.bfloat16, P)
+    assert any(spec[0] == max(1, 128 // min(H // KV, 128)) and spec[1] > 1 for spec in tiles), "the long list is cut for 128-row tiles"
+    status = ops.new_status(DEV)
+    for window in (0, 77):
+        got = ops.paged_attention(q, k_pool[layer], v_pool[layer], tiles=tiles, cu_q=torch.tensor(cu, dtype=torch.int32, device=DEV),
+                                  ctx_lens=torch.tensor(ctx_lens, dtype=torch.int32, device=DEV), block_table=table, page_size=P,
+                                  scale=D ** -0.5, window=window, kv_len_bound=max(ctx_lens), status=status, kv_maps=maps, layer_in_pool=layer)
+        ops.check_status(status)
+        want = KP.paged_attention(q, k_cache, v_cache, cu, ctx_lens, table, D ** -0.5, window)
+        torch.testing.assert_close(got.float(), want, atol=2e-2, rtol=2e-2)
 
 
 def test_tma_gathers_are_refused_for_sizes_they_cannot_do(ops):

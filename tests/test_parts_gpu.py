@@ -15,7 +15,7 @@ def _runtime(dtype=torch.float32, max_positions=128):
     from oxr_inference_b200.parts.base import Runtime
 
     dev = torch.device("cuda", torch.cuda.current_device())
-    return Runtime(device=dev, dtype=dtype, max_positions=max_positions, status=ops.new_status(dev))
+    return Runtime(device=dev, dtype=dtype, max_positions=max_positions, status=ops.new_status(dev), page_size=8)
 
 
 def _fill(part, seed=0, scale=0.3):
