@@ -965,6 +965,7 @@ attn_tma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
 //                  double-buffered so that the next block's S is computed while this block's softmax runs;
 //   softmax        four warps, ONE THREAD PER ROW: tcgen05.ld its row of S, mask, running maximum and sum without any
 //                  shuffle, P = exp2(S - m) written as bf16 into a swizzled shared-memory tile;
+//                  (two such blocks run per SM so that one's TMEM loads and barrier round trips hide behind the other's work)
 //   O += P V       tcgen05.mma, P from shared memory, V from the TMA stage as an MN-major operand, O (128 x D fp32) in TMEM.
 // The running maximum is only raised when a row's maximum grows by more than 8 (in log2 units): P then stays below
 // 2^8, which bf16 and the fp32 accumulator take without loss, and the rescale of O (tcgen05.ld, multiply, tcgen05.st)
@@ -973,11 +974,11 @@ attn_tma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
 // Every mbarrier wait is bounded.
 // ---------------------------------------------------------------------------------------------------------------------
 constexpr int BIG_ROWS = 128;
-constexpr int TC_STAGES = 3;
+constexpr int TC_STAGES = 2;
 constexpr int TC_THREADS = 192;
 constexpr int Q_PANEL_BYTES = BIG_ROWS * 128;                       // 128 rows x 64 d
 constexpr int P_BYTES = BIG_ROWS * 128;                             // 128 rows x 64 keys
-constexpr size_t TC_SMEM = 1024 + (size_t)PANELS * Q_PANEL_BYTES + (size_t)TC_STAGES * KV_STAGE_BYTES + 2 * P_BYTES + 256;
+constexpr size_t TC_SMEM = (size_t)PANELS * Q_PANEL_BYTES + (size_t)TC_STAGES * KV_STAGE_BYTES + P_BYTES + 128;   // two blocks fit on an SM
 constexpr uint32_t TC_TMEM_COLS = D <= 128 ? 256 : 512;             // S0 (64) | S1 (64) | O (D)
 constexpr float RESCALE_THRESHOLD = 8.f;
 
@@ -1038,24 +1039,30 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(TC_THREADS, 2)
 attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, int pool_row0, int box_rows, const AttnArgs a) {
-    extern __shared__ unsigned char smem_dyn[];
-    unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+    // The kernel has no static shared memory, so the dynamic part starts at the block's shared-memory origin, which
+    // is 1024-byte aligned as the swizzled tiles need (checked below).
+    extern __shared__ __align__(1024) unsigned char smem_dyn[];
+    unsigned char* base = smem_dyn;
     unsigned char* Qs = base;                                              // PANELS panels of [128 rows][128 B], swizzled
     unsigned char* stages = Qs + (size_t)PANELS * Q_PANEL_BYTES;           // TC_STAGES x (K panels, V panels)
-    unsigned char* Ps = stages + (size_t)TC_STAGES * KV_STAGE_BYTES;       // 2 x [128 rows][128 B], swizzled
-    uint64_t* kv_full = reinterpret_cast<uint64_t*>(Ps + 2 * P_BYTES);
+    unsigned char* Ps = stages + (size_t)TC_STAGES * KV_STAGE_BYTES;       // [128 rows][128 B], swizzled
+    uint64_t* kv_full = reinterpret_cast<uint64_t*>(Ps + P_BYTES);
     uint64_t* kv_empty = kv_full + TC_STAGES;
     uint64_t* s_full = kv_empty + TC_STAGES;     // [2] S(b) is in TMEM
     uint64_t* s_empty = s_full + 2;              // [2] the softmax warps have read S(b) (4 arrivals)
-    uint64_t* p_full = s_empty + 2;              // [2] P(b) is in shared memory and O is rescaled (4 arrivals)
+    uint64_t* p_full = s_empty + 2;              // [2] P(b) is in shared memory and O is rescaled (4 arrivals); one buffer, two phases
     uint64_t* o_done = p_full + 2;               // [2] O += P(b) V(b) has completed
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 2);
 
     const TileGeometry g = tile_geometry(a, BIG_ROWS);
     if (g.tok0 >= g.tok_end) return;
+    if (smem_addr(base) & 1023u) {   // cannot happen without static shared memory; refuse rather than compute rubbish
+        if (threadIdx.x == 0) oxr_report(a.status, OXR_BAD_ARGUMENT, 1024);
+        return;
+    }
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int k_end = g.pos0 + g.tok_end;
     const int k_lo = a.window > 0 ? max(0, g.pos0 + g.tok0 - a.window + 1) : 0;
@@ -1161,7 +1168,7 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
                 const uint32_t v_addr = smem_addr(stages + (size_t)st * KV_STAGE_BYTES + (size_t)PANELS * PANEL_BYTES);
 #pragma unroll
                 for (int kk = 0; kk < MMA_BN / 16; ++kk)
-                    tc_mma(tmem_o, desc_kmajor(p_addr + (b & 1) * P_BYTES + kk * 32), desc_mnmajor(v_addr + kk * 16 * 128), idesc_o,
+                    tc_mma(tmem_o, desc_kmajor(p_addr + kk * 32), desc_mnmajor(v_addr + kk * 16 * 128), idesc_o,
                            (b > 0 || kk > 0) ? 1u : 0u);
                 tc_commit(kv_empty + st);       // K and V of this stage have been read by both products
                 tc_commit(o_done + (b & 1));
@@ -1189,17 +1196,25 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(s_empty + (b & 1));    // S(b) is in registers: the buffer may take S(b + 2)
-            float mx = -INFINITY;
+            // Blocks that this row sees in full need no per-key test; on the others the hidden keys become -inf.
+            const bool whole = row_ok && key0 + MMA_BN - 1 <= row_pos && key0 >= k_lo && (a.window <= 0 || key0 > row_pos - a.window);
+            if (!whole) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int kp = key0 + h * 32 + j;
+                        const bool seen = row_ok && kp <= row_pos && kp >= k_lo && (a.window <= 0 || kp > row_pos - a.window);
+                        if (!seen) sv[h][j] = __float_as_uint(-INFINITY);
+                    }
+            }
+            // maximum of the raw scores over four independent chains; the (positive) scale is applied once
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
             for (int h = 0; h < 2; ++h)
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int kp = key0 + h * 32 + j;
-                    const bool seen = row_ok && kp <= row_pos && kp >= k_lo && (a.window <= 0 || kp > row_pos - a.window);
-                    const float v = seen ? __uint_as_float(sv[h][j]) * scale_log2 : -INFINITY;
-                    sv[h][j] = __float_as_uint(v);
-                    mx = fmaxf(mx, v);
-                }
+                for (int j = 0; j < 32; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(sv[h][j]));
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
             // raise the maximum only when it grew by more than the threshold (or there was none yet)
             float alpha = 1.f;
             bool raise = mx > m_used + RESCALE_THRESHOLD || (m_used == -INFINITY && mx != -INFINITY);
@@ -1207,11 +1222,10 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
                 alpha = (m_used == -INFINITY) ? 0.f : fast_exp2(m_used - mx);
                 m_used = mx;
             }
-            // the P buffer was last read by O(b - 2); a raised maximum also needs O(b - 1) finished before O is touched
+            // the one P buffer was last read by O(b - 1), which must also be finished before a raised maximum rescales O
             const bool any_raise = __any_sync(0xffffffffu, raise && b > 0);
-            if (b >= 2 && !mbar_wait(o_done + (b & 1), ((b - 2) >> 1) & 1)) { if (lane == 0) oxr_report(a.status, OXR_WAIT_EXPIRED, 35); alive = false; break; }
+            if (b >= 1 && !mbar_wait(o_done + ((b - 1) & 1), ((b - 1) >> 1) & 1)) { if (lane == 0) oxr_report(a.status, OXR_WAIT_EXPIRED, 35); alive = false; break; }
             if (any_raise) {
-                if (!mbar_wait(o_done + ((b - 1) & 1), ((b - 1) >> 1) & 1)) { if (lane == 0) oxr_report(a.status, OXR_WAIT_EXPIRED, 36); alive = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
                 for (int c = 0; c < D / 32; ++c) {
@@ -1223,7 +1237,9 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
                 }
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             }
-            float sum = 0.f;
+            // P = exp2(score * scale - m): one FMA and one ex2 per key; a row that has seen no key yet has only -inf scores
+            const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int h = 0; h < 2; ++h)
 #pragma unroll
@@ -1232,13 +1248,14 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
                     __nv_bfloat162* cp = reinterpret_cast<__nv_bfloat162*>(&chunk);
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        const float p0 = (m_used == -INFINITY) ? 0.f : fast_exp2(__uint_as_float(sv[h][c * 8 + 2 * e]) - m_used);
-                        const float p1 = (m_used == -INFINITY) ? 0.f : fast_exp2(__uint_as_float(sv[h][c * 8 + 2 * e + 1]) - m_used);
-                        sum += p0 + p1;
+                        const float p0 = fast_exp2(fmaf(__uint_as_float(sv[h][c * 8 + 2 * e]), scale_log2, neg_m));
+                        const float p1 = fast_exp2(fmaf(__uint_as_float(sv[h][c * 8 + 2 * e + 1]), scale_log2, neg_m));
+                        sum4[e] += p0 + p1;
                         cp[e] = __floats2bfloat162_rn(p0, p1);
                     }
-                    *reinterpret_cast<uint4*>(my_p_row + (size_t)(b & 1) * P_BYTES + ((((h * 4 + c)) ^ (r & 7)) << 4)) = chunk;
+                    *reinterpret_cast<uint4*>(my_p_row + ((((h * 4 + c)) ^ (r & 7)) << 4)) = chunk;
                 }
+            const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             l = l * alpha + sum;
             fence_proxy_async();                      // P is read by the tensor core through the async proxy
             __syncwarp();
@@ -1321,7 +1338,7 @@ OXR_API int oxr_paged_attention_bf16(void* out, const void* q, const void* k_cac
     a.scale = scale; a.window = window; a.status = status;
     if (n_long > 0 && long_rows == BIG_ROWS) {
         // long tiles of 128 rows: the tcgen05 kernel (the host made the tile list for 128 rows)
-        if (!TMA_OK || D > 128 || kv_maps == nullptr || a.page_shift < 3) return OXR_BAD_ARGUMENT;
+        if (!TMA_OK || D > 128 || kv_maps == nullptr || a.page_shift < 3 || !(scale > 0.f)) return OXR_BAD_ARGUMENT;
         static bool big_configured = false;
         if (!big_configured) {
             cudaError_t e = cudaFuncSetAttribute(attn_tc5_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM);
