@@ -437,7 +437,9 @@ struct TileGeometry {
         return r < rows_used && tok < tok_end && gh < G;
     }
 };
-__device__ __forceinline__ TileGeometry tile_geometry(const AttnArgs& a, int rows) {
+// `tile`: index into the tile list (default: the block's x index).
+__device__ __forceinline__ TileGeometry tile_geometry(const AttnArgs& a, int rows, int tile = -1) {
+    if (tile < 0) tile = blockIdx.x;
     TileGeometry g;
     g.G = a.H / a.KV;
     g.heads_per_tile = g.G < rows ? g.G : rows;
@@ -445,8 +447,8 @@ __device__ __forceinline__ TileGeometry tile_geometry(const AttnArgs& a, int row
     const int head_groups = (g.G + g.heads_per_tile - 1) / g.heads_per_tile;
     g.kvh = blockIdx.y / head_groups;
     g.hg = blockIdx.y % head_groups;
-    g.req = a.tile_req[blockIdx.x];
-    g.tok0 = a.tile_tok0[blockIdx.x];
+    g.req = a.tile_req[tile];
+    g.tok0 = a.tile_tok0[tile];
     g.q_begin = a.cu_q[g.req];
     g.q_len = a.cu_q[g.req + 1] - g.q_begin;
     g.pos0 = a.ctx_lens[g.req] - g.q_len;
@@ -478,7 +480,8 @@ attn_mma_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);
     bf16* Ks = Qs + PREFILL_ROWS * LDS;          // 2 stages
     bf16* Vs = Ks + 2 * MMA_BN * LDS;            // 2 stages
-    const TileGeometry g = tile_geometry(a, PREFILL_ROWS);
+    // the list is in token order and later tiles of a prompt see more keys: start the long ones first
+    const TileGeometry g = tile_geometry(a, PREFILL_ROWS, (int)(gridDim.x - 1 - blockIdx.x));
     if (g.tok0 >= g.tok_end) return;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int* table_row = a.block_table + (size_t)g.req * a.table_width;
@@ -1057,7 +1060,8 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
     uint64_t* o_done = p_full + 2;               // [2] O += P(b) V(b) has completed
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 2);
 
-    const TileGeometry g = tile_geometry(a, BIG_ROWS);
+    // the list is in token order and later tiles of a prompt see more keys: start the long ones first
+    const TileGeometry g = tile_geometry(a, BIG_ROWS, (int)(gridDim.x - 1 - blockIdx.x));
     if (g.tok0 >= g.tok_end) return;
     if (smem_addr(base) & 1023u) {   // cannot happen without static shared memory; refuse rather than compute rubbish
         if (threadIdx.x == 0) oxr_report(a.status, OXR_BAD_ARGUMENT, 1024);

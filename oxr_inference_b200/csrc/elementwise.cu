@@ -223,12 +223,14 @@ __global__ void silu_mul_kernel<float>(float* __restrict__ out, const float* __r
     }
 }
 
-// bf16, inter a multiple of 8: 16-byte loads and stores.
-__global__ void silu_mul_bf16x8_kernel(uint4* __restrict__ out, const uint4* __restrict__ gate_up, int inter8, size_t total8) {
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total8; i += (size_t)gridDim.x * blockDim.x) {
-        const size_t row = i / inter8, col = i % inter8;
-        uint4 g = __ldg(gate_up + row * 2 * inter8 + col);
-        uint4 u = __ldg(gate_up + row * 2 * inter8 + inter8 + col);
+// bf16, inter a multiple of 8: 16-byte loads and stores. Grid (column chunks, rows): no division per element.
+__global__ void silu_mul_bf16x8_kernel(uint4* __restrict__ out, const uint4* __restrict__ gate_up, int inter8) {
+    const size_t row = blockIdx.y;
+    const uint4* g_row = gate_up + row * 2 * inter8;
+    uint4* o_row = out + row * inter8;
+    for (int col = blockIdx.x * blockDim.x + threadIdx.x; col < inter8; col += gridDim.x * blockDim.x) {
+        uint4 g = __ldg(g_row + col);
+        uint4 u = __ldg(g_row + inter8 + col);
         const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g);
         const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&u);
         uint4 o;
@@ -241,7 +243,7 @@ __global__ void silu_mul_bf16x8_kernel(uint4* __restrict__ out, const uint4* __r
             r.y = gf.y / (1.f + __expf(-gf.y)) * uf.y;
             op[k] = __float22bfloat162_rn(r);
         }
-        out[i] = o;
+        o_row[col] = o;
     }
 }
 
@@ -250,9 +252,15 @@ OXR_API int oxr_silu_mul(void* out, const void* gate_up, int n_rows, int inter, 
     if (total == 0) return 0;
     const int threads = 256;
     if (dtype == 1 && inter % 8 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)gate_up % 16 == 0) {
-        const size_t total8 = total / 8;
-        const int blocks = (int)((total8 + threads - 1) / threads < 148 * 16 ? (total8 + threads - 1) / threads : 148 * 16);
-        silu_mul_bf16x8_kernel<<<blocks, threads, 0, stream>>>((uint4*)out, (const uint4*)gate_up, inter / 8, total8);
+        const int inter8 = inter / 8;
+        int rows_done = 0;
+        while (rows_done < n_rows) {   // grid.y holds at most 65535 rows per launch
+            const int rows = n_rows - rows_done < 65535 ? n_rows - rows_done : 65535;
+            dim3 grid((inter8 + threads - 1) / threads, rows);
+            silu_mul_bf16x8_kernel<<<grid, threads, 0, stream>>>((uint4*)out + (size_t)rows_done * inter8,
+                                                               (const uint4*)gate_up + (size_t)rows_done * 2 * inter8, inter8);
+            rows_done += rows;
+        }
         return oxr_launch_status();
     }
     const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);

@@ -95,6 +95,115 @@ __global__ void qk_norm_rope_store_kernel(
     }
 }
 
+// bf16 with head sizes that are multiples of 64. One warp takes HPW consecutive heads of a token: lane l holds elements
+// 2l, 2l+1 (+64 per step) of the first half of each head and their partners in the second half (4-byte loads and
+// stores); the loads of all its heads are issued before anything is reduced, so that a warp has several cache lines in
+// flight. v heads are copied with 16-byte words.
+template <int STEPS, int HPW>
+__global__ void qk_norm_rope_store_bf16x2_kernel(
+    __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
+    const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ q_weight, const float* __restrict__ k_weight,
+    const float* __restrict__ cos_table, const float* __restrict__ sin_table, const int* __restrict__ positions,
+    const int* __restrict__ slots, int n_tokens, int H, int KV, int D, float eps, int max_positions, long long num_slots,
+    int norm_q, int norm_k, int rotate, int* status) {
+    const int warps_per_block = blockDim.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const long long unit = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+    const int heads = H + 2 * KV;
+    const int groups = (heads + HPW - 1) / HPW;
+    if (unit >= (long long)n_tokens * groups) return;
+    const int t = (int)(unit / groups), head0 = (int)(unit % groups) * HPW;
+    const int half = D >> 1;
+    const __nv_bfloat16* row = qkv + (size_t)t * heads * D;
+    const long long slot = slots[t];
+    if (slot >= num_slots) {
+        if (lane == 0) oxr_report(status, OXR_BAD_SLOT, t);
+    }
+    const bool can_store = slot >= 0 && slot < num_slots;
+    int pos = 0;
+    if (rotate) {
+        pos = positions[t];
+        if (pos < 0 || pos >= max_positions) {
+            if (lane == 0) oxr_report(status, OXR_BAD_POSITION, t);
+            pos = 0;
+        }
+    }
+    // ---- all loads first
+    float2 x1[HPW][STEPS], x2[HPW][STEPS];
+#pragma unroll
+    for (int hh = 0; hh < HPW; ++hh) {
+        const int head = head0 + hh;
+        const bool normed = head < H + KV;   // q or k
+#pragma unroll
+        for (int i = 0; i < STEPS; ++i) {
+            const int j = 2 * lane + 64 * i;
+            x1[hh][i] = x2[hh][i] = make_float2(0.f, 0.f);
+            if (head < heads && normed && j < half) {
+                x1[hh][i] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(row + (size_t)head * D + j));
+                x2[hh][i] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(row + (size_t)head * D + j + half));
+            }
+        }
+    }
+    float2 c[STEPS], sn[STEPS];
+#pragma unroll
+    for (int i = 0; i < STEPS; ++i) {
+        const int j = 2 * lane + 64 * i;
+        c[i] = make_float2(1.f, 1.f);
+        sn[i] = make_float2(0.f, 0.f);
+        if (rotate && j < half) {
+            c[i] = *reinterpret_cast<const float2*>(cos_table + (size_t)pos * half + j);
+            sn[i] = *reinterpret_cast<const float2*>(sin_table + (size_t)pos * half + j);
+        }
+    }
+#pragma unroll
+    for (int hh = 0; hh < HPW; ++hh) {
+        const int head = head0 + hh;
+        if (head >= heads) break;
+        if (head >= H + KV) {   // v: copied unchanged
+            if (can_store) {
+                const uint4* src = reinterpret_cast<const uint4*>(row + (size_t)head * D);
+                uint4* dst = reinterpret_cast<uint4*>(v_cache + (size_t)slot * KV * D + (size_t)(head - H - KV) * D);
+                for (int j = lane; j < D / 8; j += 32) dst[j] = src[j];
+            }
+            continue;
+        }
+        const bool is_q = head < H;
+        if (!is_q && !can_store) continue;
+        __nv_bfloat16* dst = is_q ? q_out + (size_t)t * H * D + (size_t)head * D : k_cache + (size_t)slot * KV * D + (size_t)(head - H) * D;
+        const bool do_norm = is_q ? norm_q : norm_k;
+        const float* w = is_q ? q_weight : k_weight;
+        float inv = 1.f;
+        if (do_norm) {
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < STEPS; ++i)
+                ss += x1[hh][i].x * x1[hh][i].x + x1[hh][i].y * x1[hh][i].y + x2[hh][i].x * x2[hh][i].x + x2[hh][i].y * x2[hh][i].y;
+            ss = warp_sum(ss);
+            inv = rsqrtf(ss / (float)D + eps);
+        }
+#pragma unroll
+        for (int i = 0; i < STEPS; ++i) {
+            const int j = 2 * lane + 64 * i;
+            if (j < half) {
+                float2 y1 = x1[hh][i], y2 = x2[hh][i];
+                if (do_norm) {
+                    const float2 w1 = *reinterpret_cast<const float2*>(w + j), w2 = *reinterpret_cast<const float2*>(w + j + half);
+                    y1.x = y1.x * inv * w1.x; y1.y = y1.y * inv * w1.y;
+                    y2.x = y2.x * inv * w2.x; y2.y = y2.y * inv * w2.y;
+                }
+                if (rotate) {
+                    const float2 r1 = make_float2(y1.x * c[i].x - y2.x * sn[i].x, y1.y * c[i].y - y2.y * sn[i].y);
+                    const float2 r2 = make_float2(y1.x * sn[i].x + y2.x * c[i].x, y1.y * sn[i].y + y2.y * c[i].y);
+                    y1 = r1;
+                    y2 = r2;
+                }
+                *reinterpret_cast<__nv_bfloat162*>(dst + j) = __float22bfloat162_rn(y1);
+                *reinterpret_cast<__nv_bfloat162*>(dst + j + half) = __float22bfloat162_rn(y2);
+            }
+        }
+    }
+}
+
 // dtype: 0 = float32, 1 = bfloat16 (qkv, q_out and the cache). head_dim: even, at most 512.
 // k_cache / v_cache: one layer's pool viewed as [num_slots, KV, D]. slots[t] < 0 skips the store.
 OXR_API int oxr_qk_norm_rope_store(void* q_out, void* k_cache, void* v_cache, const void* qkv, const float* q_weight,
@@ -107,6 +216,24 @@ OXR_API int oxr_qk_norm_rope_store(void* q_out, void* k_cache, void* v_cache, co
     const int warps = 4;
     const long long units = (long long)n_tokens * (H + 2 * KV);
     const unsigned blocks = (unsigned)((units + warps - 1) / warps);
+    if (dtype == 1 && D % 64 == 0 && D <= 512 && (uintptr_t)qkv % 16 == 0 && (uintptr_t)q_out % 16 == 0 && (uintptr_t)k_cache % 16 == 0 &&
+        (uintptr_t)v_cache % 16 == 0 && (q_weight == nullptr || (uintptr_t)q_weight % 8 == 0) &&
+        (k_weight == nullptr || (uintptr_t)k_weight % 8 == 0) && (cos_table == nullptr || ((uintptr_t)cos_table % 8 == 0 && (uintptr_t)sin_table % 8 == 0))) {
+        typedef __nv_bfloat16 B;
+        const int steps = (D / 2 + 63) / 64;   // 1..4
+        constexpr int HPW = 4;                  // heads per warp
+        const long long vunits = (long long)n_tokens * ((H + 2 * KV + HPW - 1) / HPW);
+        const unsigned vblocks = (unsigned)((vunits + warps - 1) / warps);
+#define LAUNCH_V(S)                                                                                                     \
+        qk_norm_rope_store_bf16x2_kernel<S, HPW><<<vblocks, warps * 32, 0, stream>>>(                                     \
+            (B*)q_out, (B*)k_cache, (B*)v_cache, (const B*)qkv, q_weight, k_weight, cos_table, sin_table, positions, slots, n_tokens, \
+            H, KV, D, eps, max_positions, num_slots, norm_q, norm_k, rotate, status)
+        if (steps <= 1) LAUNCH_V(1);
+        else if (steps <= 2) LAUNCH_V(2);
+        else LAUNCH_V(4);
+#undef LAUNCH_V
+        return oxr_launch_status();
+    }
     const int pairs = (D / 2 + 31) / 32;  // 1..8
 #define LAUNCH(T, P)                                                                                               \
     qk_norm_rope_store_kernel<T, P><<<blocks, warps * 32, 0, stream>>>(                                              \
