@@ -98,7 +98,7 @@ class ClockSampler:
 
 def reference_arm() -> int:
     print(json.dumps({"impl": "reference", "unavailable":
-                      "the reference cannot be installed: pip reports that /root/reference has neither setup.py nor "
+                      "the reference cannot be installed: pip reports that its source tree has neither setup.py nor "
                       "pyproject.toml, and its engine only loads its own vision+language model folder"}))
     return 0
 
