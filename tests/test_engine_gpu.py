@@ -212,3 +212,33 @@ def test_two_layers_at_qwen3_8b_sizes_match_the_plain_implementation(dtype):
         util.compare(got[-1], want[rows], dtype, f"portion of {c} at {pos}")
         pos += c
     runner.check()
+
+
+@pytest.mark.parametrize("name,dtype", [("B", "float32"), ("A", "float32")])
+def test_many_random_requests_under_page_pressure_equal_plain_greedy(folders, name, dtype):
+    """Forty requests of random lengths through a cache that holds only a few of them at a time, with a small token
+    budget: admission, portions, decoding in and out of CUDA graphs, growth, preemption and recomputation, release and
+    reuse of pages and state slots all happen many times; every request must still produce exactly the plain
+    implementation's greedy tokens."""
+    import random
+
+    from oxr_inference_b200.sampling import SamplingParams
+
+    folder = folders[name]
+    cfg, w = QP.read_model(folder)
+    rng = random.Random(5)
+    prompts = [token_ids(name, rng.choice([1, 2, 5, 9, 17, 33, 60, 90]), seed=100 + i) for i in range(40)]
+    steps = [rng.choice([1, 3, 8, 20]) for _ in prompts]
+    engine = _engine(folder, name, dtype, num_pages=12 if name == "A" else 22, max_running=5, max_step_tokens=40, prefill_chunk=24)
+    params = [SamplingParams(max_tokens=n, ignore_eos=True) for n in steps]
+    got = engine.generate(prompts, params)
+    assert engine.preemptions > 0, "the cache is meant to be too small for this workload"
+    assert engine.counters["graph_steps"] > 0
+    cache = {}
+    for p, n, c in zip(prompts, steps, got):
+        key = (tuple(p), n)
+        if key not in cache:
+            cache[key] = QP.greedy(cfg, w, p, n)
+        assert c.token_ids == cache[key] and c.finish_reason == "length"
+    engine.runner.cache.check()
+    assert engine.runner.cache.free_pages == engine.runner.cache.usable_pages and engine.runner.cache.free_slots == 5
