@@ -963,26 +963,28 @@ attn_tma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// Prefill attention on tcgen05: a tile is 128 rows (one TMEM lane each). Per 64-key block
+// Prefill attention on tcgen05: a tile is two halves of 128 rows (one TMEM lane per row); both halves use every 64-key
+// block that arrives, so K and V are fetched once per 256 rows and eight softmax warps keep the SM busy. Per block and half
 //   S = Q K^T      tcgen05.mma, Q and K from shared memory (K-major, 128-byte swizzle), S (128 x 64 fp32) in TMEM,
 //                  double-buffered so that the next block's S is computed while this block's softmax runs;
 //   softmax        four warps, ONE THREAD PER ROW: tcgen05.ld its row of S, mask, running maximum and sum without any
 //                  shuffle, P = exp2(S - m) written as bf16 into a swizzled shared-memory tile;
-//                  (two such blocks run per SM so that one's TMEM loads and barrier round trips hide behind the other's work)
 //   O += P V       tcgen05.mma, P from shared memory, V from the TMA stage as an MN-major operand, O (128 x D fp32) in TMEM.
 // The running maximum is only raised when a row's maximum grows by more than 8 (in log2 units): P then stays below
 // 2^8, which bf16 and the fp32 accumulator take without loss, and the rescale of O (tcgen05.ld, multiply, tcgen05.st)
 // becomes rare. K and V blocks arrive by TMA from a producer warp exactly as in the split-KV kernel.
-// Warp roles: 0 = TMA producer, 1 = MMA issuer and owner of the TMEM allocation, 2..5 = softmax and epilogue.
+// Warp roles: 0 = TMA producer, 1 = MMA issuer and owner of the TMEM allocation, 2..5 / 6..9 = softmax and epilogue of
+// the first / second half.
 // Every mbarrier wait is bounded.
 // ---------------------------------------------------------------------------------------------------------------------
-constexpr int BIG_ROWS = 128;
-constexpr int TC_STAGES = 2;
-constexpr int TC_THREADS = 192;
-constexpr int Q_PANEL_BYTES = BIG_ROWS * 128;                       // 128 rows x 64 d
-constexpr int P_BYTES = BIG_ROWS * 128;                             // 128 rows x 64 keys
-constexpr size_t TC_SMEM = (size_t)PANELS * Q_PANEL_BYTES + (size_t)TC_STAGES * KV_STAGE_BYTES + P_BYTES + 128;   // two blocks fit on an SM
-constexpr uint32_t TC_TMEM_COLS = D <= 128 ? 256 : 512;             // S0 (64) | S1 (64) | O (D)
+constexpr int HALF_ROWS = 128;                                      // rows of one accumulator (TMEM lanes)
+constexpr int BIG_ROWS = 2 * HALF_ROWS;                             // a tile is two such halves sharing every K/V block
+constexpr int TC_STAGES = 4;
+constexpr int TC_THREADS = 320;                                     // warp 0 TMA, warp 1 MMA, warps 2..9 softmax (4 per half)
+constexpr int Q_PANEL_BYTES = HALF_ROWS * 128;                      // 128 rows x 64 d
+constexpr int P_BYTES = HALF_ROWS * 128;                            // 128 rows x 64 keys
+constexpr size_t TC_SMEM = 2 * (size_t)PANELS * Q_PANEL_BYTES + (size_t)TC_STAGES * KV_STAGE_BYTES + 2 * P_BYTES + 256;
+constexpr uint32_t TC_TMEM_COLS = 512;                              // S[half][2] (4 x 64) | O[half] (2 x D)
 constexpr float RESCALE_THRESHOLD = 8.f;
 
 // K-major operand tile with 128-byte rows, 128-byte swizzle (Q, K, P): see gemm_tcgen05.cu
@@ -1042,23 +1044,23 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
-__global__ void __launch_bounds__(TC_THREADS, 2)
+__global__ void __launch_bounds__(TC_THREADS, 1)
 attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, int pool_row0, int box_rows, const AttnArgs a) {
     // The kernel has no static shared memory, so the dynamic part starts at the block's shared-memory origin, which
     // is 1024-byte aligned as the swizzled tiles need (checked below).
     extern __shared__ __align__(1024) unsigned char smem_dyn[];
     unsigned char* base = smem_dyn;
-    unsigned char* Qs = base;                                              // PANELS panels of [128 rows][128 B], swizzled
-    unsigned char* stages = Qs + (size_t)PANELS * Q_PANEL_BYTES;           // TC_STAGES x (K panels, V panels)
-    unsigned char* Ps = stages + (size_t)TC_STAGES * KV_STAGE_BYTES;       // [128 rows][128 B], swizzled
-    uint64_t* kv_full = reinterpret_cast<uint64_t*>(Ps + P_BYTES);
+    unsigned char* Qs = base;                                              // [half][PANELS] panels of [128 rows][128 B], swizzled
+    unsigned char* stages = Qs + 2 * (size_t)PANELS * Q_PANEL_BYTES;       // TC_STAGES x (K panels, V panels)
+    unsigned char* Ps = stages + (size_t)TC_STAGES * KV_STAGE_BYTES;       // [half] [128 rows][128 B], swizzled
+    uint64_t* kv_full = reinterpret_cast<uint64_t*>(Ps + 2 * P_BYTES);
     uint64_t* kv_empty = kv_full + TC_STAGES;
-    uint64_t* s_full = kv_empty + TC_STAGES;     // [2] S(b) is in TMEM
-    uint64_t* s_empty = s_full + 2;              // [2] the softmax warps have read S(b) (4 arrivals)
-    uint64_t* p_full = s_empty + 2;              // [2] P(b) is in shared memory and O is rescaled (4 arrivals); one buffer, two phases
-    uint64_t* o_done = p_full + 2;               // [2] O += P(b) V(b) has completed
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 2);
+    uint64_t* s_full = kv_empty + TC_STAGES;     // [half][2] S(b) is in TMEM
+    uint64_t* s_empty = s_full + 4;              // [half][2] the half's softmax warps have read S(b) (4 arrivals)
+    uint64_t* p_full = s_empty + 4;              // [half][2] P(b) is in shared memory and O is rescaled (4 arrivals)
+    uint64_t* o_done = p_full + 4;               // [half][2] O += P(b) V(b) has completed
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 4);
 
     // the list is in token order and later tiles of a prompt see more keys: start the long ones first
     const TileGeometry g = tile_geometry(a, BIG_ROWS, (int)(gridDim.x - 1 - blockIdx.x));
@@ -1075,7 +1077,7 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < TC_STAGES; ++i) { mbar_init(kv_full + i, 1); mbar_init(kv_empty + i, 1); }
-        for (int i = 0; i < 2; ++i) { mbar_init(s_full + i, 1); mbar_init(s_empty + i, 4); mbar_init(p_full + i, 4); mbar_init(o_done + i, 1); }
+        for (int i = 0; i < 4; ++i) { mbar_init(s_full + i, 1); mbar_init(s_empty + i, 4); mbar_init(p_full + i, 4); mbar_init(o_done + i, 1); }
         mbar_fence_init();
     }
     if (warp == 1) {
@@ -1087,14 +1089,15 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
         reinterpret_cast<uint4*>(stages)[i] = make_uint4(0, 0, 0, 0);
     // Q: every softmax thread copies its own row (D bf16) into the swizzled panels; rows without a (token, head) are zero.
     if (warp >= 2) {
-        const int r = (warp - 2) * 32 + lane;
+        const int half = (warp - 2) >> 2, rr = (warp & 3) * 32 + lane;   // row inside the half = its TMEM lane
         int tok, gh;
-        const bool ok = g.row(r, tok, gh);
+        const bool ok = g.row(half * HALF_ROWS + rr, tok, gh);
         const uint4* src = reinterpret_cast<const uint4*>(q + ((size_t)(g.q_begin + (ok ? tok : 0)) * a.H + (size_t)g.kvh * g.G + (ok ? gh : 0)) * D);
+        unsigned char* qh = Qs + (size_t)half * PANELS * Q_PANEL_BYTES;
 #pragma unroll
         for (int c = 0; c < D / 8; ++c) {
             const uint4 v = ok ? __ldg(src + c) : make_uint4(0, 0, 0, 0);
-            *reinterpret_cast<uint4*>(Qs + (size_t)(c >> 3) * Q_PANEL_BYTES + (size_t)r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
+            *reinterpret_cast<uint4*>(qh + (size_t)(c >> 3) * Q_PANEL_BYTES + (size_t)rr * 128 + (((c & 7) ^ (rr & 7)) << 4)) = v;
         }
     }
     fence_proxy_async();
@@ -1102,7 +1105,9 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_o = tmem_base + 128;
+    // TMEM columns: S of half h, buffer i at (2 h + i) * 64; O of half h at 256 + h * D
+    // the second half of a tile may be empty (short portions): its products and softmax are then skipped
+    const bool half1_live = g.tok0 + (HALF_ROWS / g.heads_per_tile) < g.tok_end || g.heads_per_tile > HALF_ROWS;
 
     if (warp == 0) {
         // ---------------------------------------------------------------------- TMA producer (all 32 lanes issue)
@@ -1144,62 +1149,75 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
     } else if (warp == 1) {
         // ---------------------------------------------------------------------- MMA issuer
         if (elect_one_lane()) {
-            constexpr uint32_t idesc_s = attn_idesc(BIG_ROWS, MMA_BN, false);
-            constexpr uint32_t idesc_o = attn_idesc(BIG_ROWS, D, true);
+            constexpr uint32_t idesc_s = attn_idesc(HALF_ROWS, MMA_BN, false);
+            constexpr uint32_t idesc_o = attn_idesc(HALF_ROWS, D, true);
             const uint32_t q_addr = smem_addr(Qs), p_addr = smem_addr(Ps);
+            const int halves = half1_live ? 2 : 1;
             bool ok = true;
-            // S(b) is issued one block ahead of O(b): S(0); then for each b: S(b + 1), wait P(b), O += P(b) V(b)
+            // S(b) of both halves is issued one block ahead of O(b): S(0); then for each b: S(b + 1), wait P(b), O += P(b) V(b)
             auto issue_s = [&](int b) -> bool {
                 const int st = b % TC_STAGES;
                 if (!mbar_wait(kv_full + st, (b / TC_STAGES) & 1)) { oxr_report(a.status, OXR_WAIT_EXPIRED, 31); return false; }
-                if (!mbar_wait(s_empty + (b & 1), ((b >> 1) & 1) ^ 1)) { oxr_report(a.status, OXR_WAIT_EXPIRED, 32); return false; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t k_addr = smem_addr(stages + (size_t)st * KV_STAGE_BYTES);
+                for (int h = 0; h < halves; ++h) {
+                    if (!mbar_wait(s_empty + 2 * h + (b & 1), ((b >> 1) & 1) ^ 1)) { oxr_report(a.status, OXR_WAIT_EXPIRED, 32); return false; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk)
-                    tc_mma(tmem_base + (uint32_t)((b & 1) * MMA_BN), desc_kmajor(q_addr + (kk >> 2) * Q_PANEL_BYTES + (kk & 3) * 32),
-                           desc_kmajor(k_addr + (kk >> 2) * PANEL_BYTES + (kk & 3) * 32), idesc_s, kk > 0 ? 1u : 0u);
-                tc_commit(s_full + (b & 1));
+                    for (int kk = 0; kk < D / 16; ++kk)
+                        tc_mma(tmem_base + (uint32_t)((2 * h + (b & 1)) * MMA_BN),
+                               desc_kmajor(q_addr + (h * PANELS + (kk >> 2)) * Q_PANEL_BYTES + (kk & 3) * 32),
+                               desc_kmajor(k_addr + (kk >> 2) * PANEL_BYTES + (kk & 3) * 32), idesc_s, kk > 0 ? 1u : 0u);
+                    tc_commit(s_full + 2 * h + (b & 1));
+                }
                 return true;
             };
             ok = issue_s(0);
             for (int b = 0; b < count && ok; ++b) {
                 if (b + 1 < count) ok = issue_s(b + 1);
                 if (!ok) break;
-                if (!mbar_wait(p_full + (b & 1), (b >> 1) & 1)) { oxr_report(a.status, OXR_WAIT_EXPIRED, 33); break; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const int st = b % TC_STAGES;
                 const uint32_t v_addr = smem_addr(stages + (size_t)st * KV_STAGE_BYTES + (size_t)PANELS * PANEL_BYTES);
+                for (int h = 0; h < halves && ok; ++h) {
+                    if (!mbar_wait(p_full + 2 * h + (b & 1), (b >> 1) & 1)) { oxr_report(a.status, OXR_WAIT_EXPIRED, 33); ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-                for (int kk = 0; kk < MMA_BN / 16; ++kk)
-                    tc_mma(tmem_o, desc_kmajor(p_addr + kk * 32), desc_mnmajor(v_addr + kk * 16 * 128), idesc_o,
-                           (b > 0 || kk > 0) ? 1u : 0u);
-                tc_commit(kv_empty + st);       // K and V of this stage have been read by both products
-                tc_commit(o_done + (b & 1));
+                    for (int kk = 0; kk < MMA_BN / 16; ++kk)
+                        tc_mma(tmem_base + 256 + (uint32_t)(h * D), desc_kmajor(p_addr + h * P_BYTES + kk * 32),
+                               desc_mnmajor(v_addr + kk * 16 * 128), idesc_o, (b > 0 || kk > 0) ? 1u : 0u);
+                    tc_commit(o_done + 2 * h + (b & 1));
+                }
+                if (!ok) break;
+                tc_commit(kv_empty + st);       // K and V of this stage have been read by all products of the block
             }
         }
-    } else {
+    } else if (warp - 2 < 4 || half1_live) {
         // ---------------------------------------------------------------------- softmax and epilogue: one thread per row
+        const int half = (warp - 2) >> 2;
         const int quarter = warp & 3;                        // TMEM lanes 32 * quarter .. + 31 belong to this warp
-        const int r = quarter * 32 + lane;
+        const int rr = quarter * 32 + lane;                  // row inside the half
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        const uint32_t tmem_o = tmem_base + 256 + (uint32_t)(half * D);
+        uint64_t* my_s_full = s_full + 2 * half;
+        uint64_t* my_s_empty = s_empty + 2 * half;
+        uint64_t* my_p_full = p_full + 2 * half;
+        uint64_t* my_o_done = o_done + 2 * half;
         int tok, gh;
-        const bool row_ok = g.row(r, tok, gh);
+        const bool row_ok = g.row(half * HALF_ROWS + rr, tok, gh);
         const int row_pos = g.pos0 + tok;
         const float scale_log2 = a.scale * LOG2E;
         float m_used = -INFINITY, l = 0.f;                   // the maximum P is taken against, the running sum
-        unsigned char* my_p_row = Ps + (size_t)r * 128;
+        unsigned char* my_p_row = Ps + (size_t)half * P_BYTES + (size_t)rr * 128;
         bool alive = true;
         for (int b = 0; b < count; ++b) {
             const int key0 = k_first + b * MMA_BN;
-            if (!mbar_wait(s_full + (b & 1), (b >> 1) & 1)) { if (lane == 0) oxr_report(a.status, OXR_WAIT_EXPIRED, 34); alive = false; break; }
+            if (!mbar_wait(my_s_full + (b & 1), (b >> 1) & 1)) { if (lane == 0) oxr_report(a.status, OXR_WAIT_EXPIRED, 34); alive = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             uint32_t sv[2][32];
-            tc_ld32(tmem_base + lane_base + (uint32_t)((b & 1) * MMA_BN), sv[0]);
-            tc_ld32(tmem_base + lane_base + (uint32_t)((b & 1) * MMA_BN + 32), sv[1]);
+            tc_ld32(tmem_base + lane_base + (uint32_t)((2 * half + (b & 1)) * MMA_BN), sv[0]);
+            tc_ld32(tmem_base + lane_base + (uint32_t)((2 * half + (b & 1)) * MMA_BN + 32), sv[1]);
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive(s_empty + (b & 1));    // S(b) is in registers: the buffer may take S(b + 2)
+            if (lane == 0) mbar_arrive(my_s_empty + (b & 1));    // S(b) is in registers: the buffer may take S(b + 2)
             // Blocks that this row sees in full need no per-key test; on the others the hidden keys become -inf.
             const bool whole = row_ok && key0 + MMA_BN - 1 <= row_pos && key0 >= k_lo && (a.window <= 0 || key0 > row_pos - a.window);
             if (!whole) {
@@ -1226,9 +1244,9 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
                 alpha = (m_used == -INFINITY) ? 0.f : fast_exp2(m_used - mx);
                 m_used = mx;
             }
-            // the one P buffer was last read by O(b - 1), which must also be finished before a raised maximum rescales O
+            // the half's one P buffer was last read by O(b - 1), which must also be finished before a raised maximum rescales O
             const bool any_raise = __any_sync(0xffffffffu, raise && b > 0);
-            if (b >= 1 && !mbar_wait(o_done + ((b - 1) & 1), ((b - 1) >> 1) & 1)) { if (lane == 0) oxr_report(a.status, OXR_WAIT_EXPIRED, 35); alive = false; break; }
+            if (b >= 1 && !mbar_wait(my_o_done + ((b - 1) & 1), ((b - 1) >> 1) & 1)) { if (lane == 0) oxr_report(a.status, OXR_WAIT_EXPIRED, 35); alive = false; break; }
             if (any_raise) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
@@ -1257,18 +1275,18 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
                         sum4[e] += p0 + p1;
                         cp[e] = __floats2bfloat162_rn(p0, p1);
                     }
-                    *reinterpret_cast<uint4*>(my_p_row + ((((h * 4 + c)) ^ (r & 7)) << 4)) = chunk;
+                    *reinterpret_cast<uint4*>(my_p_row + ((((h * 4 + c)) ^ (rr & 7)) << 4)) = chunk;
                 }
             const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             l = l * alpha + sum;
             fence_proxy_async();                      // P is read by the tensor core through the async proxy
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_full + (b & 1));
+            if (lane == 0) mbar_arrive(my_p_full + (b & 1));
         }
         // ---- epilogue: O / l -> out
         if (alive && count > 0) {
             const int last = count - 1;
-            if (!mbar_wait(o_done + (last & 1), (last >> 1) & 1)) { if (lane == 0) oxr_report(a.status, OXR_WAIT_EXPIRED, 37); alive = false; }
+            if (!mbar_wait(my_o_done + (last & 1), (last >> 1) & 1)) { if (lane == 0) oxr_report(a.status, OXR_WAIT_EXPIRED, 37); alive = false; }
         }
         alive = __all_sync(0xffffffffu, alive);
         if (alive) {
@@ -1314,7 +1332,7 @@ OXR_API int oxr_attn_decode_rows() { return DECODE_ROWS; }
 // before the first launch (the kernel leaves them zero), groups16 = ceil(G / min(G, 16)).
 // kv_maps (optional): the two tensor maps of oxr_attn_make_kv_maps for the pool that k_cache / v_cache are a layer
 // of, with pool_row0 = layer * num_pages * page_size; the split-KV kernel then fetches K and V by TMA.
-// long_rows: rows per long tile the host cut the long list for: 64 (cp.async kernel) or 128 (TMA kernel, needs kv_maps).
+// long_rows: rows per long tile the host cut the long list for: 64 (cp.async kernel) or 256 (tcgen05 kernel, needs kv_maps).
 OXR_API int oxr_paged_attention_bf16(void* out, const void* q, const void* k_cache, const void* v_cache,
                                      const int* short_req, const int* short_tok0, int n_short, const int* long_req,
                                      const int* long_tok0, int n_long, const int* cu_q, const int* ctx_lens,
@@ -1341,7 +1359,7 @@ OXR_API int oxr_paged_attention_bf16(void* out, const void* q, const void* k_cac
     a.heads_per_tile = a.tokens_per_tile = a.head_groups = 0;   // the tensor-core kernels derive these from their row count
     a.scale = scale; a.window = window; a.status = status;
     if (n_long > 0 && long_rows == BIG_ROWS) {
-        // long tiles of 128 rows: the tcgen05 kernel (the host made the tile list for 128 rows)
+        // long tiles of 256 rows: the tcgen05 kernel (the host made the tile list for 256 rows)
         if (!TMA_OK || D > 128 || kv_maps == nullptr || a.page_shift < 3 || !(scale > 0.f)) return OXR_BAD_ARGUMENT;
         static bool big_configured = false;
         if (!big_configured) {

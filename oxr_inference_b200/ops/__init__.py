@@ -254,7 +254,7 @@ def qk_norm_rope_store(qkv: torch.Tensor, q_weight: torch.Tensor | None, k_weigh
     return q
 
 
-GENERIC_ROWS, DECODE_ROWS, PREFILL_ROWS, PREFILL_ROWS_TMA = 16, 16, 64, 128
+GENERIC_ROWS, DECODE_ROWS, PREFILL_ROWS, PREFILL_ROWS_TMA = 16, 16, 64, 256
 SHORT_MAX_TOKENS = 8
 """Requests that bring at most this many tokens go to the split-KV kernel, longer portions to the prefill kernel."""
 MAX_SPLITS = 32
@@ -278,7 +278,7 @@ def attention_tile_specs(num_heads: int, num_kv_heads: int, head_dim: int, dtype
                          page_size: int | None = None) -> list[tuple[int, int, int]]:
     """The tile lists the attention kernels of this dtype read: (tokens per tile, fewest, most new tokens of the
     requests the list covers). The host cuts each request's new tokens into such tiles. With a ``page_size`` that
-    allows TMA gathers the long tiles are 128 rows (the TMA prefill kernel), else 64."""
+    allows TMA gathers the long tiles are 256 rows (the tcgen05 prefill kernel), else 64."""
     build.check_head_dim(head_dim)
     big = 1 << 30
     if dtype == torch.bfloat16:

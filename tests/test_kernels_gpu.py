@@ -446,7 +446,7 @@ def test_split_kv_decode_with_tma_gathers(ops, H, KV, D, P, window):
 
 @pytest.mark.parametrize("H,KV,D,P", [(32, 8, 128, 16), (6, 2, 64, 8), (3, 3, 64, 16), (4, 1, 128, 64), (40, 1, 64, 16)])
 def test_prefill_kernel_with_tma_gathers_on_long_portions(ops, H, KV, D, P):
-    """The 128-row prefill kernel (K and V by TMA): portions of hundreds of tokens from position 0 and deep inside a
+    """The tcgen05 prefill kernel (256-row tiles, K and V by TMA): portions of hundreds of tokens from position 0 and deep inside a
     context, beside short entries that go to the split-KV kernel in the same call."""
     g = torch.Generator(device=DEV).manual_seed(80 + D)
     q_lens = [300, 130, 64, 1, 9]
@@ -459,7 +459,7 @@ def test_prefill_kernel_with_tma_gathers_on_long_portions(ops, H, KV, D, P):
     maps = ops.make_kv_maps(k_pool, v_pool, P)
     assert maps is not None
     tiles = _tiles(ops, q_lens, H, KV, D, torch.bfloat16, P)
-    assert any(spec[0] == max(1, 128 // min(H // KV, 128)) and spec[1] > 1 for spec in tiles), "the long list is cut for 128-row tiles"
+    assert any(spec[0] == max(1, 256 // min(H // KV, 256)) and spec[1] > 1 for spec in tiles), "the long list is cut for 256-row tiles"
     status = ops.new_status(DEV)
     for window in (0, 77):
         got = ops.paged_attention(q, k_pool[layer], v_pool[layer], tiles=tiles, cu_q=torch.tensor(cu, dtype=torch.int32, device=DEV),
