@@ -11,6 +11,7 @@ A request's life: ``open`` (takes a state slot) -> any number of ``reserve(new_l
 
 from __future__ import annotations
 
+import itertools
 from dataclasses import dataclass, field
 
 import numpy as np
@@ -35,6 +36,9 @@ class RequestCache:
     closed: bool = False
     version: int = 0
     """Changes whenever ``tables`` changes (pages added or released), so that a copy of a table row can be reused."""
+    serial: int = field(default_factory=itertools.count().__next__)
+    """Unlike ``id()``, never given to a second request of this process: (serial, version) names one state of one
+    request's tables for good."""
 
 
 def pages_for(tokens: int, page_size: int) -> int:

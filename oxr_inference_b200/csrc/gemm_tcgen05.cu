@@ -1,33 +1,41 @@
 // bf16 GEMM on the 5th-generation tensor cores: C[M,N] = X[M,K] * W[N,K]^T, fp32 accumulation in tensor memory.
 //
 // The reference multiplies through nn.Linear / cuBLAS (oxr_runtime/language.py:223-244,261,268-269). This is the
-// engine's own kernel for the prefill-sized products (M > 64):
+// engine's own kernel for every product of more rows than the skinny kernel takes:
 //   * operands are staged in shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle), STAGES deep, each stage
 //     guarded by a pair of mbarriers (full: TMA -> MMA, empty: MMA -> TMA);
-//   * one thread issues tcgen05.mma (M = 128 rows of X, N = BN rows of W, K = 16 per instruction) with shared-memory
-//     matrix descriptors; the 128 x BN fp32 accumulator lives in tensor memory (TMEM), one column per output column;
+//   * one thread issues tcgen05.mma (M = 128 rows of X, N = bn rows of W, K = 16 per instruction) with shared-memory
+//     matrix descriptors; the 128 x bn fp32 accumulator lives in tensor memory (TMEM), one column per output column;
+//     bn is any multiple of 16 up to 256, chosen per product by the caller so that the tiles fill the SMs evenly;
 //   * tcgen05.commit releases a stage when the MMAs that read it are done, and signals the epilogue at the end;
 //   * four epilogue warps read the accumulator with tcgen05.ld (warp w owns TMEM lanes 32 (w % 4) .. +31, i.e. 32
 //     rows of the tile), round to the output type and store.
-// Blocks are persistent: one per SM, each walking over 128 x BN tiles, with two accumulators in TMEM so that the
+// Blocks are persistent: one per SM, each walking over 128 x bn tiles, with two accumulators in TMEM so that the
 // epilogue of one tile overlaps the MMAs of the next. Rows and columns beyond M, N and K are zero-filled by TMA on
 // the way in and masked on the way out. Every wait on an mbarrier is bounded: if one runs out, the block records
 // OXR_WAIT_EXPIRED in the status word, stops waiting, frees its tensor memory and returns.
+//
+// Few rows (a decode batch of tens of requests) and a narrow W give few tiles, fewer than SMs, while the product is
+// bound by streaming W. The SPLIT variant therefore deals the k steps of a tile out to `splits` shares and
+// makes (tile, share) the unit of work, so that every SM streams a part of W. A unit writes its fp32 partial tile to
+// a workspace and takes a ticket of its tile; the unit that draws the last ticket adds the partial tiles in the order
+// of the shares (so the sum does not depend on who came last), rounds and stores. Nothing waits for another block.
 #include "tma.cuh"
 
 namespace {
 constexpr int BM = 128;           // rows of X per tile = TMEM lanes
 constexpr int BK = 64;            // k per stage: 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
+constexpr int MAX_BN = 256;       // widest tile: one tcgen05.mma takes N <= 256, a TMA box 256 rows
+constexpr int MAX_STAGES = 10;
+constexpr int RED_ROWS = 8;       // rows per lane and pass when partial tiles are added
 constexpr int TC_THREADS = 192;   // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2..5: epilogue
+constexpr int A_BYTES = BM * BK * 2;
+constexpr int BARRIER_BYTES = 256;
+constexpr int SMEM_BYTES = 227 * 1024;                                  // all a block may have
+constexpr int RING_BYTES = SMEM_BYTES - 1024 /* alignment slack */ - BARRIER_BYTES;
 
-template <int BN> struct Cfg {
-    static constexpr int STAGES = BN >= 256 ? 4 : 6;
-    static constexpr int A_BYTES = BM * BK * 2;
-    static constexpr int B_BYTES = BN * BK * 2;
-    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
-};
+__host__ __device__ constexpr int stage_bytes(int bn) { return A_BYTES + bn * BK * 2; }
 
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte swizzle: rows 128 B apart,
 // groups of 8 rows 1024 B apart (stride byte offset), leading byte offset 1 (unused for swizzled K-major),
@@ -56,6 +64,7 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
 }
+// 32 lanes x 32 (or 16) consecutive columns of tensor memory: lane i of the warp gets row i's values.
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -64,6 +73,14 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
           "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
           "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
           "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr));
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
@@ -76,49 +93,96 @@ __device__ __forceinline__ bool elect_one() {
         : "=r"(pred));
     return pred != 0;
 }
+// Barrier 1 is the epilogue warps' own (128 threads); the other warps never touch it.
+__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ bool epilogue_all(bool v) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.u32 q, %1, 0;\n\t"
+        "bar.red.and.pred p, 1, 128, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(r) : "r"((uint32_t)v) : "memory");
+    return r != 0;
+}
 
 // Tile order: blocks that run at the same time share few W tiles and GROUP_M consecutive X tiles, so that W is
 // streamed from HBM once and the X tiles of a group stay in L2 (W can be far larger than L2, X of a group is not).
-template <int BN>
-__device__ __forceinline__ void tile_origin(int tile, int M, int N, int& m0, int& n0) {
+__device__ __forceinline__ void tile_origin(int tile, int M, int N, int bn, int& m0, int& n0) {
     constexpr int GROUP_M = 32;
-    const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+    const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + bn - 1) / bn;
     const int per_group = GROUP_M * tiles_n;
     const int group = tile / per_group, within = tile % per_group;
     const int group_rows = min(GROUP_M, tiles_m - group * GROUP_M);
     m0 = (group * GROUP_M + within % group_rows) * BM;
-    n0 = (within / group_rows) * BN;
+    n0 = (within / group_rows) * bn;
 }
 
-// Persistent: block b computes tiles b, b + gridDim.x, ... The accumulator is double-buffered in tensor memory
-// (2 x BN columns), so the epilogue warps drain tile i while the MMA warp already accumulates tile i + 1.
-template <int BN, typename TO>
+// `count` (16 or 32) consecutive fp32 values of one output row -> C, rounded to TO; columns from `col0` on, N in all.
+template <typename TO>
+__device__ __forceinline__ void store_row_piece(TO* dst, const uint32_t (&v)[32], int count, int col0, int N) {
+    if (col0 + count <= N && ((uintptr_t)dst % 16 == 0)) {
+        if constexpr (sizeof(TO) == 2) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (8 * j >= count) break;
+                uint4 o;
+                __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    op[e] = __floats2bfloat162_rn(__uint_as_float(v[8 * j + 2 * e]), __uint_as_float(v[8 * j + 2 * e + 1]));
+                reinterpret_cast<uint4*>(dst)[j] = o;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (4 * j >= count) break;
+                reinterpret_cast<uint4*>(dst)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (j < count && col0 + j < N) dst[j] = Num<TO>::from_f32(__uint_as_float(v[j]));
+    }
+}
+
+// Persistent: block b computes units b, b + gridDim.x, ... The accumulator is double-buffered in tensor memory
+// (two buffers `acc_stride` columns apart), so the epilogue warps drain one unit while the MMA warp already
+// accumulates the next. Without SPLIT a unit is a tile. With SPLIT it is (tile, share): unit u is share u % splits
+// of tile u / splits, and share r takes the 64-wide k steps r, r + splits, ...: the shares of a tile run side by
+// side, read neighbouring 128-byte pieces of W's rows, and finish together.
+template <typename TO, bool SPLIT>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tcgen05_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                    int M, int N, int K, int num_tiles, int* status) {
-    using C_ = Cfg<BN>;
-    constexpr int STAGES = C_::STAGES;
-    constexpr uint32_t TMEM_COLS = 2 * BN;
+                    int M, int N, int K, int bn, int stages, int tmem_cols, int num_tiles, int splits, float* __restrict__ partial,
+                    unsigned int* __restrict__ tickets, int* status) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);   // swizzle atoms are 1024 B
-    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + (size_t)STAGES * C_::STAGE_BYTES);
-    uint64_t* empty = full + STAGES;
-    uint64_t* accum_full = empty + STAGES;    // [2] MMA -> epilogue
-    uint64_t* accum_empty = accum_full + 2;   // [2] epilogue -> MMA (4 arrivals: one per epilogue warp)
+    const int stage_size = stage_bytes(bn);
+    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + (size_t)stages * stage_size);
+    uint64_t* empty = full + MAX_STAGES;
+    uint64_t* accum_full = empty + MAX_STAGES;   // [2] MMA -> epilogue
+    uint64_t* accum_empty = accum_full + 2;      // [2] epilogue -> MMA (4 arrivals: one per epilogue warp)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_empty + 2);
     uint32_t* gave_up = tmem_slot + 1;
+    uint32_t* drew_last = gave_up + 1;
+    static_assert((2 * MAX_STAGES + 4) * 8 + 12 <= BARRIER_BYTES, "barriers outgrow their space");
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_kb = (K + BK - 1) / BK;
+    const int kb_step = SPLIT ? splits : 1;
+    const int num_units = SPLIT ? num_tiles * splits : num_tiles;
+    const uint32_t acc_stride = (uint32_t)tmem_cols / 2;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
+        for (int s = 0; s < stages; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
         for (int i = 0; i < 2; ++i) { mbar_init(accum_full + i, 1); mbar_init(accum_empty + i, 4); }
         *gave_up = 0;
         mbar_fence_init();
     }
     if (warp == 1) {   // the whole warp allocates the tensor memory and gives up the permit to allocate more
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"((uint32_t)tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -129,49 +193,51 @@ gemm_tcgen05_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap map_
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (elect_one()) {
-            uint32_t kb_all = 0;   // k-blocks issued so far, over all tiles: the stage ring does not restart per tile
+            int s = 0;             // the stage ring does not restart per unit
+            uint32_t phase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
+                const int tile = SPLIT ? unit / splits : unit;
                 int m0, n0;
-                tile_origin<BN>(tile, M, N, m0, n0);
-                for (int kb = 0; kb < num_kb; ++kb, ++kb_all) {
-                    const int s = kb_all % STAGES;
-                    const uint32_t phase = (kb_all / STAGES) & 1;
+                tile_origin(tile, M, N, bn, m0, n0);
+                for (int kb = SPLIT ? unit % splits : 0; kb < num_kb; kb += kb_step) {
                     if (!mbar_wait(empty + s, phase ^ 1)) { atomicExch(gave_up, 1u); oxr_report(status, OXR_WAIT_EXPIRED, 0); ok = false; break; }
-                    unsigned char* a_dst = tiles + (size_t)s * C_::STAGE_BYTES;
-                    mbar_expect_tx(full + s, C_::STAGE_BYTES);
+                    unsigned char* a_dst = tiles + (size_t)s * stage_size;
+                    mbar_expect_tx(full + s, (uint32_t)stage_size);
                     tma_load_2d(a_dst, &map_x, kb * BK, m0, full + s);
-                    tma_load_2d(a_dst + C_::A_BYTES, &map_w, kb * BK, n0, full + s);
+                    tma_load_2d(a_dst + A_BYTES, &map_w, kb * BK, n0, full + s);
+                    if (++s == stages) { s = 0; phase ^= 1; }
                 }
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         if (elect_one()) {
-            constexpr uint32_t idesc = umma_idesc(BM, BN);
-            uint32_t kb_all = 0;
+            const uint32_t idesc = umma_idesc(BM, bn);
+            int s = 0;
+            uint32_t phase = 0;
             bool ok = true;
             int it = 0;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+            for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x, ++it) {
+                const int kb0 = SPLIT ? unit % splits : 0;
                 const int acc = it & 1;
                 const uint32_t acc_phase = (it >> 1) & 1;
                 if (!mbar_wait(accum_empty + acc, acc_phase ^ 1)) { atomicExch(gave_up, 1u); oxr_report(status, OXR_WAIT_EXPIRED, 3); ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
-                for (int kb = 0; kb < num_kb; ++kb, ++kb_all) {
-                    const int s = kb_all % STAGES;
-                    const uint32_t phase = (kb_all / STAGES) & 1;
+                const uint32_t tmem_d = tmem_base + (uint32_t)acc * acc_stride;
+                for (int kb = kb0; kb < num_kb; kb += kb_step) {
                     if (!mbar_wait(full + s, phase)) { atomicExch(gave_up, 1u); oxr_report(status, OXR_WAIT_EXPIRED, 1); ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t a_addr = smem_addr(tiles + (size_t)s * C_::STAGE_BYTES);
-                    const uint32_t b_addr = a_addr + C_::A_BYTES;
+                    const uint32_t a_addr = smem_addr(tiles + (size_t)s * stage_size);
+                    const uint32_t b_addr = a_addr + A_BYTES;
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k) {
                         // inside the 128-byte swizzle row, the next 16 k-values start 32 bytes further
                         umma_bf16(tmem_d, umma_desc(a_addr + k * UMMA_K * 2), umma_desc(b_addr + k * UMMA_K * 2), idesc,
-                                  (kb > 0 || k > 0) ? 1u : 0u);
+                                  (kb > kb0 || k > 0) ? 1u : 0u);
                     }
                     umma_commit(empty + s);   // the stage is free once these MMAs have read it
+                    if (++s == stages) { s = 0; phase ^= 1; }
                 }
                 umma_commit(accum_full + acc);   // arrives when every MMA issued so far is complete (also after giving up)
             }
@@ -180,9 +246,10 @@ gemm_tcgen05_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap map_
         // ------------------------------------------------------------------ epilogue: TMEM -> registers -> global
         const int quarter = warp & 3;                     // this warp may touch TMEM lanes 32 * quarter .. + 31
         int it = 0;
-        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+        for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x, ++it) {
+            const int tile = SPLIT ? unit / splits : unit;
             int m0, n0;
-            tile_origin<BN>(tile, M, N, m0, n0);
+            tile_origin(tile, M, N, bn, m0, n0);
             const int acc = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
             const int row = m0 + quarter * 32 + lane;
@@ -190,34 +257,26 @@ gemm_tcgen05_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap map_
             if (!ok) { atomicExch(gave_up, 1u); if (lane == 0) oxr_report(status, OXR_WAIT_EXPIRED, 2); }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             ok = ok && (*reinterpret_cast<volatile uint32_t*>(gave_up) == 0);
-            ok = __all_sync(0xffffffffu, ok);   // tcgen05.ld is warp-wide: all lanes take the same path
+            if constexpr (SPLIT) ok = epilogue_all(ok);   // the four warps meet at barriers below: they leave together
+            else ok = __all_sync(0xffffffffu, ok);        // tcgen05.ld is warp-wide: all lanes take the same path
             if (!ok) break;
+            const uint32_t acc_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)acc * acc_stride;
+            const size_t tile_floats = (size_t)BM * bn;
+            // SPLIT: this share's partial tile -> workspace [share][tile][BM][bn], rows of the matrix only
+            float* mine = SPLIT ? partial + ((size_t)(unit % splits) * num_tiles + tile) * tile_floats + (size_t)(quarter * 32 + lane) * bn : nullptr;
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
+            for (int c0 = 0; c0 < bn; c0 += 32) {
                 uint32_t v[32];
-                tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN + c * 32), v);
-                const int col0 = n0 + c * 32;
-                if (row < M && col0 < N) {
-                    TO* dst = C + (size_t)row * N + col0;
-                    const bool whole = col0 + 32 <= N && ((uintptr_t)dst % 16 == 0);
-                    if (whole) {
-                        if constexpr (sizeof(TO) == 2) {
+                const int count = min(32, bn - c0);   // 32, or 16 at the end of a tile whose width is an odd multiple of 16
+                if (count == 32) tmem_ld_32x32(acc_addr + (uint32_t)c0, v);
+                else tmem_ld_32x16(acc_addr + (uint32_t)c0, v);
+                if (row < M) {
+                    if constexpr (SPLIT) {
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                uint4 o;
-                                __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-                                for (int e = 0; e < 4; ++e)
-                                    op[e] = __floats2bfloat162_rn(__uint_as_float(v[8 * j + 2 * e]), __uint_as_float(v[8 * j + 2 * e + 1]));
-                                reinterpret_cast<uint4*>(dst)[j] = o;
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 8; ++j)
-                                reinterpret_cast<uint4*>(dst)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                        }
-                    } else {
-                        for (int j = 0; j < 32 && col0 + j < N; ++j) dst[j] = Num<TO>::from_f32(__uint_as_float(v[j]));
+                        for (int j = 0; j < 8; ++j)
+                            if (4 * j < count) reinterpret_cast<uint4*>(mine + c0)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                    } else if (n0 + c0 < N) {
+                        store_row_piece<TO>(C + (size_t)row * N + n0 + c0, v, count, n0 + c0, N);
                     }
                 }
             }
@@ -225,53 +284,123 @@ gemm_tcgen05_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap map_
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(accum_empty + acc);
+            if constexpr (SPLIT) {
+                // ticket: the partial tiles are published before it is drawn, and read only after the last one is
+                __threadfence();
+                epilogue_sync();
+                if (threadIdx.x == 64) {
+                    const unsigned int t = atomicAdd(tickets + tile, 1u);
+                    const bool last = t + 1 == (unsigned int)splits;
+                    if (last) tickets[tile] = 0;   // left zero for the next launch
+                    *drew_last = last ? 1u : 0u;
+                }
+                epilogue_sync();
+                if (*reinterpret_cast<volatile uint32_t*>(drew_last) != 0) {
+                    __threadfence();
+                    const int rows = min(BM, M - m0);
+                    const float* first = partial + (size_t)tile * tile_floats;
+                    const size_t share_stride = (size_t)num_tiles * tile_floats;
+                    // eight rows per pass and lane, the loads of four shares in flight together: the loads' latency
+                    // under a saturated memory system, not their number, is what this costs
+                    for (int c = lane * 4; c < bn; c += 128) {
+                        const int col = n0 + c;
+                        for (int r0 = quarter; r0 < rows; r0 += 4 * RED_ROWS) {
+                            float4 sum[RED_ROWS];
+#pragma unroll
+                            for (int i = 0; i < RED_ROWS; ++i) sum[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+                            for (int s = 0; s < splits; ++s) {
+                                float4 p[RED_ROWS];
+#pragma unroll
+                                for (int i = 0; i < RED_ROWS; ++i) {
+                                    const int r = min(r0 + 4 * i, rows - 1);
+                                    p[i] = __ldcg(reinterpret_cast<const float4*>(first + (size_t)s * share_stride + (size_t)r * bn + c));
+                                }
+#pragma unroll
+                                for (int i = 0; i < RED_ROWS; ++i) { sum[i].x += p[i].x; sum[i].y += p[i].y; sum[i].z += p[i].z; sum[i].w += p[i].w; }
+                            }
+#pragma unroll
+                            for (int i = 0; i < RED_ROWS; ++i) {
+                                const int r = r0 + 4 * i;
+                                if (r >= rows) break;
+                                TO* dst = C + (size_t)(m0 + r) * N + col;
+                                if (col + 4 <= N && (uintptr_t)dst % (4 * sizeof(TO)) == 0) {
+                                    if constexpr (sizeof(TO) == 2) {
+                                        uint2 o;
+                                        reinterpret_cast<__nv_bfloat162*>(&o)[0] = __floats2bfloat162_rn(sum[i].x, sum[i].y);
+                                        reinterpret_cast<__nv_bfloat162*>(&o)[1] = __floats2bfloat162_rn(sum[i].z, sum[i].w);
+                                        *reinterpret_cast<uint2*>(dst) = o;
+                                    } else {
+                                        *reinterpret_cast<float4*>(dst) = sum[i];
+                                    }
+                                } else {
+                                    const float e[4] = {sum[i].x, sum[i].y, sum[i].z, sum[i].w};
+                                    for (int j = 0; j < 4 && col + j < N; ++j) dst[j] = Num<TO>::from_f32(e[j]);
+                                }
+                            }
+                        }
+                    }
+                }
+            }
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)tmem_cols) : "memory");
     }
 }
 
 // ---------------------------------------------------------------------------------------------------- host side
-template <int BN, typename TO>
-int launch(void* C, const void* X, const void* W, int M, int N, int K, int* status, cudaStream_t stream) {
+template <typename TO, bool SPLIT>
+int launch(void* C, const void* X, const void* W, int M, int N, int K, int bn, int splits, float* partial, unsigned int* tickets, int* status,
+           cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<BN>::SMEM);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<TO, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         if (e != cudaSuccess) return 1000 + (int)e;
         configured = true;
     }
     CUtensorMap map_x, map_w;
-    if (!oxr_make_map_bf16(&map_x, X, M, K, BM) || !oxr_make_map_bf16(&map_w, W, N, K, BN)) return OXR_BAD_ARGUMENT;
-    const long long tiles = (long long)((N + BN - 1) / BN) * ((M + BM - 1) / BM);
-    if (tiles > 0x7fffffffLL) return OXR_BAD_ARGUMENT;
+    if (!oxr_make_map_bf16(&map_x, X, M, K, BM) || !oxr_make_map_bf16(&map_w, W, N, K, bn)) return OXR_BAD_ARGUMENT;
+    const long long tiles = (long long)((N + bn - 1) / bn) * ((M + BM - 1) / BM);
+    const long long units = tiles * (SPLIT ? splits : 1);
+    if (units > 0x7fffffffLL) return OXR_BAD_ARGUMENT;
     static int num_sms = 0;
     if (num_sms == 0) {
         int dev = 0;
         if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || num_sms <= 0)
             num_sms = 148;
     }
-    dim3 grid((unsigned)(tiles < num_sms ? tiles : num_sms));   // one block per SM (its shared memory fills the SM)
-    gemm_tcgen05_kernel<BN, TO><<<grid, TC_THREADS, Cfg<BN>::SMEM, stream>>>((TO*)C, map_x, map_w, M, N, K, (int)tiles, status);
+    int stages = RING_BYTES / stage_bytes(bn);
+    if (stages > MAX_STAGES) stages = MAX_STAGES;
+    int tmem_cols = 32;                      // a power of two that holds both accumulators
+    while (tmem_cols < 2 * bn) tmem_cols *= 2;
+    dim3 grid((unsigned)(units < num_sms ? units : num_sms));   // one block per SM (its shared memory fills the SM)
+    gemm_tcgen05_kernel<TO, SPLIT><<<grid, TC_THREADS, SMEM_BYTES, stream>>>((TO*)C, map_x, map_w, M, N, K, bn, stages, tmem_cols, (int)tiles, splits,
+                                                                              partial, tickets, status);
     return oxr_launch_status();
 }
 }  // namespace
 
 // out_dtype: 0 = float32, 1 = bfloat16. Requires K % 8 == 0 (rows are whole 16-byte words) and 16-byte aligned X, W.
-// tile_n: 128 or 256 columns of the output per block.
-OXR_API int oxr_gemm_tcgen05_bf16(void* C, const void* X, const void* W, int M, int N, int K, int out_dtype, int tile_n, int* status,
-                                  cudaStream_t stream) {
+// tile_n: columns of the output per tile, a multiple of 16 from 16 to 256.
+// splits > 1 deals the 64-wide k steps out to that many shares per tile (at most as many as steps); `partial` then
+// holds splits * tiles * 128 * tile_n floats (tiles = ceil(M / 128) * ceil(N / tile_n)) and `tickets` one zeroed
+// counter per tile, which the kernel leaves zeroed.
+OXR_API int oxr_gemm_tcgen05_bf16(void* C, const void* X, const void* W, int M, int N, int K, int out_dtype, int tile_n, int splits,
+                                  float* partial, unsigned int* tickets, int* status, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 != 0 || (uintptr_t)X % 16 != 0 || (uintptr_t)W % 16 != 0) return OXR_BAD_ARGUMENT;
-    if (tile_n == 256) {
-        if (out_dtype == 1) return launch<256, __nv_bfloat16>(C, X, W, M, N, K, status, stream);
-        if (out_dtype == 0) return launch<256, float>(C, X, W, M, N, K, status, stream);
-    } else if (tile_n == 128) {
-        if (out_dtype == 1) return launch<128, __nv_bfloat16>(C, X, W, M, N, K, status, stream);
-        if (out_dtype == 0) return launch<128, float>(C, X, W, M, N, K, status, stream);
+    if (tile_n < 16 || tile_n > MAX_BN || tile_n % 16 != 0) return OXR_BAD_ARGUMENT;
+    if (splits > 1) {
+        if (partial == nullptr || tickets == nullptr || (uintptr_t)partial % 16 != 0 || splits > (K + BK - 1) / BK) return OXR_BAD_ARGUMENT;
+        if (out_dtype == 1) return launch<__nv_bfloat16, true>(C, X, W, M, N, K, tile_n, splits, partial, tickets, status, stream);
+        if (out_dtype == 0) return launch<float, true>(C, X, W, M, N, K, tile_n, splits, partial, tickets, status, stream);
+        return OXR_BAD_ARGUMENT;
     }
+    if (out_dtype == 1) return launch<__nv_bfloat16, false>(C, X, W, M, N, K, tile_n, 1, nullptr, nullptr, status, stream);
+    if (out_dtype == 0) return launch<float, false>(C, X, W, M, N, K, tile_n, 1, nullptr, nullptr, status, stream);
     return OXR_BAD_ARGUMENT;
 }

@@ -216,7 +216,7 @@ class BatchBuilder:
             slots, table = seg(f"slots{g}"), seg(f"table{g}").reshape(n, w)
             fill = m.scratch_pages[g] if m.scratch_pages else 0
             for i, e in enumerate(entries):
-                key = (id(e.cache), e.cache.version)
+                key = (e.cache.serial, e.cache.version)   # not id(): a closed request's address is used again
                 if remembered is None or remembered[g * n + i] != key:
                     t = e.cache.tables[g]
                     if len(t) > w:

@@ -13,6 +13,7 @@ this package's own kernels; ``torch.mm`` is kept only for bf16 matrices whose ro
 from __future__ import annotations
 
 import ctypes
+import functools
 from ctypes import c_float, c_int, c_longlong, c_size_t, c_void_p
 
 import torch
@@ -20,7 +21,7 @@ import torch
 from oxr_inference_b200.ops import build
 from oxr_inference_b200.ops.build import BuildError  # noqa: F401
 
-SKINNY_MAX_ROWS = 64
+SKINNY_MAX_ROWS = 16
 STATUS_NAMES = {
     1: "token id outside the vocabulary", 2: "cache slot outside the pool", 3: "position outside the rotary table",
     4: "block table names a page outside the pool", 5: "a bounded wait inside a kernel ran out",
@@ -83,7 +84,7 @@ def _lib():
         lib.oxr_qk_norm_rope_store.argtypes = [p, p, p, p, p, p, p, p, p, p, i, i, i, i, f, i, c_longlong, i, i, i, i, p, p]
         lib.oxr_gemm_f32_nt.argtypes = [p, p, p, i, i, i, p]
         lib.oxr_gemm_skinny_bf16.argtypes = [p, p, p, i, i, i, i, p]
-        lib.oxr_gemm_tcgen05_bf16.argtypes = [p, p, p, i, i, i, i, i, p, p]
+        lib.oxr_gemm_tcgen05_bf16.argtypes = [p, p, p, i, i, i, i, i, i, p, p, p, p]
         lib.oxr_sample.argtypes = [p, p, i, i, p, p, p, p, p, p]
         lib.oxr_sample_chunks.argtypes = [i]
         lib.oxr_sample_chunks.restype = c_int
@@ -383,16 +384,87 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
 
 
 _counters: dict[torch.device, torch.Tensor] = {}
+_outgrown: list[torch.Tensor] = []
 
 
 def _ticket_counters(device: torch.device, units: int) -> torch.Tensor:
     """Zeroed ticket counters of the split-KV kernel, one per (tile, KV head group). The kernel leaves them zero, so
-    one array serves every launch on a stream."""
+    one array serves every launch on a stream. An array that is outgrown is kept, not freed: a captured CUDA graph
+    may hold its address."""
     t = _counters.get(device)
     if t is None or t.numel() < units:
+        if t is not None:
+            _outgrown.append(t)
         t = torch.zeros(max(units, 1 << 16), dtype=torch.int32, device=device)
         _counters[device] = t
     return t
+
+
+GEMM_SPLITS = (1, 2, 3, 4, 6, 8)
+GEMM_WORKSPACE_BYTES = 64 << 20
+_GEMM_RING_BYTES = 227 * 1024 - 1024 - 256    # shared memory the kernel's stage ring may fill
+_split_buffers: dict = {}
+
+
+def _gemm_cost(m: int, n: int, k: int, tile_n: int, splits: int) -> float:
+    """Microseconds the tcgen05 product is expected to take with tiles of 128 x ``tile_n`` and ``splits`` shares per
+    tile. The constants are fitted to this kernel on a B200 (Qwen3-8B's four products at 17 to 8192 rows):
+
+    * a 64-wide k step of one block takes 0.085 + 0.00144 * tile_n microseconds (shared-memory fill from L2), and no
+      less than 0.24 (the round trip of a stage through TMA and the tensor core, divided by the stages in flight);
+    * a wave of blocks takes at least the time HBM needs for the parts of W it streams (5.9 TB/s), and the two
+      limits overlap all but about 15 %;
+    * a split unit writes its partial tile and the last unit of a tile adds them up: 6.4 microseconds plus 0.065 per
+      row and 128 columns, which later waves hide only by half;
+    * 2.2 microseconds before the first block computes.
+    """
+    rows = -(-m // 128)
+    tiles, steps = rows * -(-n // tile_n), -(-k // 64)
+    per = -(-steps // splits)
+    step_us = max(0.24, 0.085 + 0.00144 * tile_n)
+    units = tiles * splits
+    w_bytes = tile_n * 128 * per / rows        # blocks of the same wave share the W tiles of their column
+    t = 2.2
+    full, rest = divmod(units, NUM_SMS)
+    for active, count in ((NUM_SMS, full), (rest, 1 if rest else 0)):
+        fill, stream = per * step_us, active * w_bytes / 5.9e6
+        t += count * (max(fill, stream) + 0.15 * min(fill, stream))
+    if splits > 1:
+        waves = -(-units // NUM_SMS)
+        t += (1 + 0.5 * (waves - 1)) * (6.4 + 0.065 * min(m, 128) * tile_n / 128)
+    return t
+
+
+@functools.lru_cache(maxsize=None)
+def _gemm_plan(m: int, n: int, k: int) -> tuple[int, int]:
+    """(tile width, shares of k per tile) of the tcgen05 product: the cheapest by ``_gemm_cost`` among widths of 32 to
+    256 columns in steps of 16 and 1 to 8 shares whose partial tiles fit the workspace; the first found among equals."""
+    best, best_cost = (128, 1), None
+    steps = -(-k // 64)
+    for tile_n in range(256, 16, -16):
+        tiles = -(-m // 128) * -(-n // tile_n)
+        for splits in GEMM_SPLITS:
+            if splits > steps or (splits > 1 and splits * tiles * 128 * tile_n * 4 > GEMM_WORKSPACE_BYTES):
+                continue
+            cost = _gemm_cost(m, n, k, tile_n, splits)
+            if best_cost is None or cost < best_cost - 1e-9:
+                best, best_cost = (tile_n, splits), cost
+    return best
+
+
+GEMM_MAX_SPLIT_TILES = GEMM_WORKSPACE_BYTES // (2 * 128 * 16 * 4)   # the most tiles a split product can have
+
+
+def _gemm_split_buffers(device: torch.device) -> tuple[torch.Tensor, torch.Tensor]:
+    """Workspace of the split product (one fp32 partial tile per unit) and its zeroed tickets (one per tile), made once
+    per device at their full size and never replaced: a captured CUDA graph keeps their addresses. Products on one
+    stream follow one another, and the kernel leaves the tickets zeroed."""
+    got = _split_buffers.get(device)
+    if got is None:
+        got = (torch.empty(GEMM_WORKSPACE_BYTES // 4, dtype=torch.float32, device=device),
+               torch.zeros(GEMM_MAX_SPLIT_TILES, dtype=torch.int32, device=device))
+        _split_buffers[device] = got
+    return got
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
@@ -425,10 +497,14 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
         return out
     if k % 8 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0:
         out = torch.empty((m, n), dtype=out_dtype, device=x.device)
-        # 128 x 256 tiles when they fill the GPU at least once, else 128 x 128 tiles for more blocks
-        tile_n = 256 if -(-m // 128) * -(-n // 256) >= NUM_SMS else 128
-        code = lib.oxr_gemm_tcgen05_bf16(out.data_ptr(), x.data_ptr(), weight.data_ptr(), m, n, k, _DT[out_dtype],
-                                         tile_n, new_status(x.device).data_ptr(), _stream())
+        tile_n, splits = _gemm_plan(m, n, k)
+        partial = tickets = None
+        if splits > 1:
+            if splits * -(-m // 128) * -(-n // tile_n) * 128 * tile_n * 4 > GEMM_WORKSPACE_BYTES:
+                raise KernelError(f"linear: {splits} shares of {m} x {n} in tiles of {tile_n} columns outgrow the workspace")
+            partial, tickets = _gemm_split_buffers(x.device)
+        code = lib.oxr_gemm_tcgen05_bf16(out.data_ptr(), x.data_ptr(), weight.data_ptr(), m, n, k, _DT[out_dtype], tile_n, splits,
+                                         _ptr(partial), _ptr(tickets), new_status(x.device).data_ptr(), _stream())
         _done(code, "gemm_tcgen05")
         return out
     # rows that are not whole 16-byte words cannot be fetched by TMA: the library product takes them

@@ -144,3 +144,18 @@ def test_window_never_releases_a_page_a_later_query_needs():
             live_pages = sum(p != RELEASED for p in rc.tables[0])
             assert live_pages <= (window + 3) // 4 + 2, "pages behind the window must have been given back"
         m.close(rc)
+
+
+def test_a_request_is_named_by_a_serial_that_is_never_given_twice():
+    """Copies of block-table rows are remembered by (serial, version). ``id()`` would not do: a closed request's
+    address goes to a later request, whose version numbers run through the same values."""
+    m = CacheManager(_plan(windows=(0, 12)), page_size=8, num_pages=8, max_requests=2)
+    seen = set()
+    for _ in range(50):
+        rc = m.open()
+        assert rc.serial not in seen
+        seen.add(rc.serial)
+        assert m.reserve(rc, 20)
+        m.advance(rc, 20)
+        m.close(rc)
+        del rc

@@ -1,0 +1,23 @@
+"""The planner of the tcgen05 matrix product (tile width and shares of k), which needs no GPU."""
+
+from oxr_inference_b200 import ops
+
+
+def test_gemm_plan_is_a_valid_launch():
+    """Whatever sizes come, the plan is a width the kernel takes and a number of shares its workspace holds."""
+    for m in (17, 64, 100, 128, 129, 500, 2048, 5000):
+        for n, k in ((64, 64), (509, 96), (4096, 4096), (24576, 4096), (4096, 12288), (151936, 4096), (5120, 25600)):
+            tile_n, splits = ops._gemm_plan(m, n, k)
+            assert 16 <= tile_n <= 256 and tile_n % 16 == 0
+            assert 1 <= splits <= -(-k // 64)
+            tiles = -(-m // 128) * -(-n // tile_n)
+            assert splits == 1 or splits * tiles * 128 * tile_n * 4 <= ops.GEMM_WORKSPACE_BYTES
+
+
+def test_gemm_plan_fills_the_gpu():
+    """Few rows and a narrow weight: shares of k or narrow tiles give about one block per SM; many rows: wide tiles."""
+    tile_n, splits = ops._gemm_plan(64, 4096, 12288)
+    assert 100 <= -(-4096 // tile_n) * splits <= ops.NUM_SMS
+    tile_n, splits = ops._gemm_plan(64, 24576, 4096)
+    assert splits == 1 and 100 <= -(-24576 // tile_n) <= ops.NUM_SMS
+    assert ops._gemm_plan(8192, 24576, 4096) == (256, 1)

@@ -152,7 +152,8 @@ def test_gemm_f32(ops, M, N, K):
 @pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 33, 64])
 @pytest.mark.parametrize("N,K", [(509, 96), (192, 160), (4096, 4096), (1000, 12288)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
-def test_gemm_skinny_bf16(ops, M, N, K, out_dtype):
+def test_gemm_skinny_bf16(ops, monkeypatch, M, N, K, out_dtype):
+    monkeypatch.setattr(ops, "SKINNY_MAX_ROWS", 64)   # every row count the kernel takes, also those linear() sends elsewhere
     g = torch.Generator(device=DEV).manual_seed(6)
     x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
     w = (torch.randn(N, K, device=DEV, generator=g) * 0.05).bfloat16()
@@ -169,8 +170,8 @@ def test_gemm_skinny_bf16(ops, M, N, K, out_dtype):
                                    (2048, 4096, 4096), (1000, 12288, 160), (77, 64, 64)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 def test_gemm_tcgen05_bf16(ops, M, N, K, out_dtype):
-    """The TMA + tcgen05 kernel that takes every bf16 product of more than 64 rows: whole tiles, ragged edges in
-    M, N and K, both tile widths, both output types."""
+    """The TMA + tcgen05 kernel that takes every bf16 product of more rows than the skinny kernel's: whole tiles,
+    ragged edges in M, N and K, both output types, with the tile width and shares that linear() plans."""
     g = torch.Generator(device=DEV).manual_seed(9)
     x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
     w = (torch.randn(N, K, device=DEV, generator=g) * 0.05).bfloat16()
@@ -178,6 +179,49 @@ def test_gemm_tcgen05_bf16(ops, M, N, K, out_dtype):
     got = ops.linear(x, w, out_dtype)
     ops.check_status(status)
     assert got.dtype == out_dtype and got.shape == (M, N)
+    want = x.float() @ w.float().T
+    if out_dtype == torch.float32:
+        torch.testing.assert_close(got, want, atol=2e-4 * math.sqrt(K) * 0.05, rtol=1e-4)
+    else:
+        torch.testing.assert_close(got.float(), want, atol=1e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("M,N,K,tile_n,splits", [(17, 509, 4096, 128, 8), (64, 4096, 12288, 96, 3), (100, 1000, 1032, 112, 6),
+                                                 (130, 136, 2048, 48, 4), (300, 1024, 8192, 256, 2), (33, 777, 520, 16, 8)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_tcgen05_split_k(ops, monkeypatch, M, N, K, tile_n, splits, out_dtype):
+    """Few tiles and a long K: the k steps of a tile are dealt out to shares, the partial tiles meet in the workspace
+    and the last unit of a tile adds them in the order of the shares. Twice in a row (the tickets are left zeroed),
+    bit-identical."""
+    monkeypatch.setattr(ops, "SKINNY_MAX_ROWS", 16)
+    monkeypatch.setattr(ops, "_gemm_plan", lambda m, n, k: (tile_n, splits))
+    g = torch.Generator(device=DEV).manual_seed(10)
+    x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=DEV, generator=g) * 0.05).bfloat16()
+    status = ops.new_status(DEV)
+    got = ops.linear(x, w, out_dtype)
+    again = ops.linear(x, w, out_dtype)
+    ops.check_status(status)
+    assert torch.equal(got, again)
+    want = x.float() @ w.float().T
+    if out_dtype == torch.float32:
+        torch.testing.assert_close(got, want, atol=2e-4 * math.sqrt(K) * 0.05, rtol=1e-4)
+    else:
+        torch.testing.assert_close(got.float(), want, atol=1e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("tile_n", [16, 48, 80, 144, 176, 208, 240, 256])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_tcgen05_every_tile_width(ops, monkeypatch, tile_n, out_dtype):
+    """The tile's width is a run-time choice, any multiple of 16 up to 256: ragged edges in M, N and K at each."""
+    monkeypatch.setattr(ops, "_gemm_plan", lambda m, n, k: (tile_n, 1))
+    M, N, K = 150, 1000, 328
+    g = torch.Generator(device=DEV).manual_seed(11)
+    x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=DEV, generator=g) * 0.05).bfloat16()
+    status = ops.new_status(DEV)
+    got = ops.linear(x, w, out_dtype)
+    ops.check_status(status)
     want = x.float() @ w.float().T
     if out_dtype == torch.float32:
         torch.testing.assert_close(got, want, atol=2e-4 * math.sqrt(K) * 0.05, rtol=1e-4)

@@ -34,10 +34,12 @@ def test_plain_matches_the_reference_models_logits():
 
 
 def test_rms_norm_and_rotation():
+    torch.manual_seed(3)
     x = torch.randn(5, 3, 8, dtype=torch.float64)
     w = torch.rand(8, dtype=torch.float64) + 0.5
     y = QP.rms_norm(x, w, 1e-6)
-    torch.testing.assert_close((y / w).pow(2).mean(-1), torch.ones(5, 3, dtype=torch.float64), atol=1e-5, rtol=0)
+    ms = x.pow(2).mean(-1)
+    torch.testing.assert_close((y / w).pow(2).mean(-1), ms / (ms + 1e-6), atol=1e-12, rtol=0)
     cos, sin = QP.rope_tables(8, 10000.0, 5, torch.float64)
     r = QP.rotate_half_split(x, cos, sin)
     # a rotation keeps the length of each (j, j + D/2) pair, and position 0 is the identity
