@@ -85,13 +85,14 @@ def _lib():
         lib.oxr_gemm_f32_nt.argtypes = [p, p, p, i, i, i, p]
         lib.oxr_gemm_skinny_bf16.argtypes = [p, p, p, i, i, i, i, p]
         lib.oxr_gemm_tcgen05_bf16.argtypes = [p, p, p, i, i, i, i, i, i, p, p, p, p]
+        lib.oxr_gemm_tcgen05_pair_bf16.argtypes = [p, p, p, i, i, i, i, i, p, p]
         lib.oxr_sample.argtypes = [p, p, i, i, p, p, p, p, p, p]
         lib.oxr_sample_chunks.argtypes = [i]
         lib.oxr_sample_chunks.restype = c_int
         lib.oxr_repetition_penalty.argtypes = [p, p, p, p, i, i, p]
         lib.oxr_mark_seen.argtypes = [p, p, p, i, i, p]
         for name in ("oxr_embedding", "oxr_add_rms_norm", "oxr_silu_mul", "oxr_cast", "oxr_qk_norm_rope_store",
-                     "oxr_gemm_f32_nt", "oxr_gemm_skinny_bf16", "oxr_gemm_tcgen05_bf16", "oxr_sample", "oxr_repetition_penalty", "oxr_mark_seen"):
+                     "oxr_gemm_f32_nt", "oxr_gemm_skinny_bf16", "oxr_gemm_tcgen05_bf16", "oxr_gemm_tcgen05_pair_bf16", "oxr_sample", "oxr_repetition_penalty", "oxr_mark_seen"):
             getattr(lib, name).restype = c_int
         _core = lib
     return _core
@@ -452,6 +453,27 @@ def _gemm_plan(m: int, n: int, k: int) -> tuple[int, int]:
     return best
 
 
+GEMM_PAIR_MIN_ROWS = 3072
+
+
+@functools.lru_cache(maxsize=None)
+def _gemm_pair_plan(m: int, n: int, k: int) -> int:
+    """Tile width for the two-SM product kernel (256 x width tiles, a pair of blocks each), or 0 where the one-SM
+    kernel is to run. Measured on a B200 the pair kernel is 5 to 10 % faster from about 3,000 rows on (a k step of a
+    256 x 256 tile takes a pair 0.42 microseconds, one SM 0.45 for 128 x 256) and no faster below. The width is the
+    one with the least waves of pairs times the time of a k step at that width."""
+    if m < GEMM_PAIR_MIN_ROWS:
+        return 0
+    pairs = NUM_SMS // 2
+    best, best_cost = 0, None
+    for tile_n in (256, 224, 192, 160, 128):
+        tiles = -(-m // 256) * -(-n // tile_n)
+        cost = -(-tiles // pairs) * (0.094 + 0.00128 * tile_n)
+        if best_cost is None or cost < best_cost - 1e-9:
+            best, best_cost = tile_n, cost
+    return best
+
+
 GEMM_MAX_SPLIT_TILES = GEMM_WORKSPACE_BYTES // (2 * 128 * 16 * 4)   # the most tiles a split product can have
 
 
@@ -497,6 +519,11 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
         return out
     if k % 8 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0:
         out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+        pair_tile = _gemm_pair_plan(m, n, k)
+        if pair_tile:
+            _done(lib.oxr_gemm_tcgen05_pair_bf16(out.data_ptr(), x.data_ptr(), weight.data_ptr(), m, n, k, _DT[out_dtype], pair_tile,
+                                                 new_status(x.device).data_ptr(), _stream()), "gemm_tcgen05_pair")
+            return out
         tile_n, splits = _gemm_plan(m, n, k)
         partial = tickets = None
         if splits > 1:

@@ -21,3 +21,10 @@ def test_gemm_plan_fills_the_gpu():
     tile_n, splits = ops._gemm_plan(64, 24576, 4096)
     assert splits == 1 and 100 <= -(-24576 // tile_n) <= ops.NUM_SMS
     assert ops._gemm_plan(8192, 24576, 4096) == (256, 1)
+
+
+def test_pair_kernel_takes_the_long_steps_only():
+    assert ops._gemm_pair_plan(2048, 4096, 4096) == 0
+    for n, k in ((6144, 4096), (24576, 4096), (4096, 12288)):
+        tile_n = ops._gemm_pair_plan(8192, n, k)
+        assert tile_n % 32 == 0 and 128 <= tile_n <= 256

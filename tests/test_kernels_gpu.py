@@ -229,6 +229,28 @@ def test_gemm_tcgen05_every_tile_width(ops, monkeypatch, tile_n, out_dtype):
         torch.testing.assert_close(got.float(), want, atol=1e-2, rtol=1e-2)
 
 
+@pytest.mark.parametrize("M,N,K,tile_n", [(256, 256, 64, 256), (300, 1000, 328, 192), (1000, 2664, 1032, 256), (130, 136, 2048, 64),
+                                          (700, 520, 4096, 32), (3100, 1536, 512, 224)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_tcgen05_pair(ops, monkeypatch, M, N, K, tile_n, out_dtype):
+    """The two-SM kernel (tcgen05 cta_group::2, each block of a pair stages half of W's tile): whole and ragged tiles,
+    a last pair whose second block has no rows at all, every k tail, widths from 32 to 256."""
+    monkeypatch.setattr(ops, "SKINNY_MAX_ROWS", 0)
+    monkeypatch.setattr(ops, "_gemm_pair_plan", lambda m, n, k: tile_n)
+    g = torch.Generator(device=DEV).manual_seed(12)
+    x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=DEV, generator=g) * 0.05).bfloat16()
+    status = ops.new_status(DEV)
+    got = ops.linear(x, w, out_dtype)
+    ops.check_status(status)
+    assert got.dtype == out_dtype and got.shape == (M, N)
+    want = x.float() @ w.float().T
+    if out_dtype == torch.float32:
+        torch.testing.assert_close(got, want, atol=2e-4 * math.sqrt(K) * 0.05, rtol=1e-4)
+    else:
+        torch.testing.assert_close(got.float(), want, atol=1e-2, rtol=1e-2)
+
+
 def test_linear_large_bf16_with_rows_that_are_not_16_byte_words_falls_to_the_library(ops):
     g = torch.Generator(device=DEV).manual_seed(7)
     x = torch.randn(200, 250, device=DEV, generator=g).bfloat16()
