@@ -572,8 +572,94 @@ attn_mma_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
 constexpr int DECODE_ROWS = 16;
 constexpr int DECODE_STAGES = 3;
 constexpr size_t DECODE_STAGE_SMEM = (size_t)(DECODE_ROWS + DECODE_STAGES * 2 * MMA_BN) * LDS * sizeof(bf16);
-constexpr size_t DECODE_MERGE_SMEM = (size_t)4 * DECODE_ROWS * (D + 2) * sizeof(float);
+constexpr int MERGE_STRIDE = D + 4;             // floats per row of the warps' merge area: O, m, l, and 16-byte alignment
+constexpr size_t DECODE_MERGE_SMEM = (size_t)4 * DECODE_ROWS * MERGE_STRIDE * sizeof(float);
 constexpr size_t DECODE_SMEM = DECODE_STAGE_SMEM > DECODE_MERGE_SMEM ? DECODE_STAGE_SMEM : DECODE_MERGE_SMEM;
+
+// The four warps of a block have each seen a quarter of the block's keys: their (O, m, l) per row stand in shared
+// memory `mo` [warp][row][MERGE_STRIDE]. Merge them in the order of the warps; with one piece per unit that is the
+// output, else it is this piece's partial result. Four d of one row per thread and pass.
+__device__ __forceinline__ void merge_warps(const float* mo, int rows_live, int splits, bf16* __restrict__ out, float* __restrict__ my_o,
+                                            float* __restrict__ my_ml, const TileGeometry& g, const AttnArgs& a) {
+    constexpr int DV = D / 4, MS = MERGE_STRIDE;
+    for (int idx = threadIdx.x; idx < rows_live * DV; idx += MMA_THREADS) {
+        const int r = idx / DV, d = (idx % DV) * 4;
+        int tok, gh;
+        if (!g.row(r, tok, gh)) continue;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, mo[((size_t)w * DECODE_ROWS + r) * MS + D]);
+        float L = 0.f;
+        float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float* src = mo + ((size_t)w * DECODE_ROWS + r) * MS;
+            const float f = (src[D] == -INFINITY) ? 0.f : exp2f(src[D] - M);
+            const float4 v = *reinterpret_cast<const float4*>(src + d);
+            L += src[D + 1] * f;
+            O.x += v.x * f; O.y += v.y * f; O.z += v.z * f; O.w += v.w * f;
+        }
+        if (splits == 1) {
+            const float inv = L > 0.f ? 1.f / L : 0.f;
+            uint2 packed;
+            packed.x = pack_bf16(O.x * inv, O.y * inv);
+            packed.y = pack_bf16(O.z * inv, O.w * inv);
+            *reinterpret_cast<uint2*>(out + ((size_t)(g.q_begin + tok) * a.H + (size_t)g.kvh * g.G + gh) * D + d) = packed;
+        } else {
+            *reinterpret_cast<float4*>(my_o + r * D + d) = O;
+            if (d == 0) { my_ml[2 * r] = M; my_ml[2 * r + 1] = L; }
+        }
+    }
+}
+
+// The block that drew the last ticket of a unit merges the pieces' partial results (m, l, unnormalised O per row) in
+// the order of the pieces and writes the output rows. Four d of one row per thread and pass; the loads of up to
+// eight pieces are issued together and none depends on a value loaded before it, because what the merge costs is the
+// latency of its loads from L2, not their number. An empty piece wrote (-inf, 0) and no O: its O is read (it is
+// memory of the workspace) and dropped by a select, never multiplied.
+__device__ __forceinline__ void merge_pieces(bf16* __restrict__ out, const float* __restrict__ all_ml, const float* __restrict__ all_o,
+                                             int splits, int rows_live, const TileGeometry& g, const AttnArgs& a) {
+    constexpr int CHUNK = 8, DV = D / 4;
+    for (int idx = threadIdx.x; idx < rows_live * DV; idx += MMA_THREADS) {
+        const int r = idx / DV, d = (idx % DV) * 4;
+        int tok, gh;
+        if (!g.row(r, tok, gh)) continue;
+        float M = -INFINITY, L = 0.f;
+        float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s0 = 0; s0 < splits; s0 += CHUNK) {
+            float2 pml[CHUNK];
+            float4 po[CHUNK];
+#pragma unroll
+            for (int j = 0; j < CHUNK; ++j) {
+                const int s2 = min(s0 + j, splits - 1);
+                pml[j] = __ldcg(reinterpret_cast<const float2*>(all_ml + ((size_t)s2 * DECODE_ROWS + r) * 2));
+                po[j] = __ldcg(reinterpret_cast<const float4*>(all_o + ((size_t)s2 * DECODE_ROWS + r) * D + d));
+            }
+            float m_new = M;
+#pragma unroll
+            for (int j = 0; j < CHUNK; ++j) {
+                if (s0 + j >= splits) pml[j].x = -INFINITY;   // a clamped repeat of the last piece
+                m_new = fmaxf(m_new, pml[j].x);
+            }
+            const float keep = (M == -INFINITY) ? 0.f : exp2f(M - m_new);
+            L *= keep;
+            O.x *= keep; O.y *= keep; O.z *= keep; O.w *= keep;
+#pragma unroll
+            for (int j = 0; j < CHUNK; ++j) {
+                if (pml[j].x == -INFINITY) continue;          // compile-time unrolled: a select, no load depends on it
+                const float f = exp2f(pml[j].x - m_new);
+                L += pml[j].y * f;
+                O.x += po[j].x * f; O.y += po[j].y * f; O.z += po[j].z * f; O.w += po[j].w * f;
+            }
+            M = m_new;
+        }
+        const float inv = L > 0.f ? 1.f / L : 0.f;
+        uint2 packed;
+        packed.x = pack_bf16(O.x * inv, O.y * inv);
+        packed.y = pack_bf16(O.z * inv, O.w * inv);
+        *reinterpret_cast<uint2*>(out + ((size_t)(g.q_begin + tok) * a.H + (size_t)g.kvh * g.G + gh) * D + d) = packed;
+    }
+}
 
 // Split-KV attention for tiles of 16 rows. Grid (tiles, KV * head groups, splits). Each block handles one piece
 // of the key range; its four warps each take a quarter of every 64-key block and are merged through shared
@@ -670,7 +756,7 @@ attn_mma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
         }
         // ---- merge the four warps (the K/V stages are free now: the loop ended with a barrier)
         float* mo = reinterpret_cast<float*>(smem_raw);   // [4 warps][16 rows][D + 2]: O then (m, l)
-        constexpr int MS = D + 2;
+        constexpr int MS = MERGE_STRIDE;
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
             float* dst = mo + ((size_t)warp * DECODE_ROWS + (lane >> 2) + 8 * r) * MS;
@@ -682,28 +768,7 @@ attn_mma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
             if ((lane & 3) == 0) { dst[D] = m[r]; dst[D + 1] = l[r]; }
         }
         __syncthreads();
-        for (int idx = threadIdx.x; idx < rows_live * D; idx += MMA_THREADS) {
-            const int r = idx / D, d = idx % D;
-            int tok, gh;
-            if (!g.row(r, tok, gh)) continue;
-            float M = -INFINITY;
-#pragma unroll
-            for (int w = 0; w < 4; ++w) M = fmaxf(M, mo[((size_t)w * DECODE_ROWS + r) * MS + D]);
-            float L = 0.f, O = 0.f;
-#pragma unroll
-            for (int w = 0; w < 4; ++w) {
-                const float* src = mo + ((size_t)w * DECODE_ROWS + r) * MS;
-                const float f = (src[D] == -INFINITY) ? 0.f : exp2f(src[D] - M);
-                L += src[D + 1] * f;
-                O += src[d] * f;
-            }
-            if (splits == 1) {
-                out[((size_t)(g.q_begin + tok) * a.H + (size_t)g.kvh * g.G + gh) * D + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
-            } else {
-                my_o[r * D + d] = O;
-                if (d == 0) { my_ml[2 * r] = M; my_ml[2 * r + 1] = L; }
-            }
-        }
+        merge_warps(mo, rows_live, splits, out, my_o, my_ml, g, a);
     } else if (splits > 1) {   // nothing for this piece: an empty partial
         for (int i = threadIdx.x; i < rows_live; i += MMA_THREADS) { my_ml[2 * i] = -INFINITY; my_ml[2 * i + 1] = 0.f; }
     }
@@ -719,22 +784,7 @@ attn_mma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
     if (threadIdx.x == 0) counters[unit] = 0;   // ready for the next launch (nobody else touches it any more)
     const float* all_ml = part_ml + unit * splits * DECODE_ROWS * 2;
     const float* all_o = part_o + unit * splits * DECODE_ROWS * D;
-    for (int idx = threadIdx.x; idx < rows_live * D; idx += MMA_THREADS) {
-        const int r = idx / D, d = idx % D;
-        int tok, gh;
-        if (!g.row(r, tok, gh)) continue;
-        float M = -INFINITY;
-        for (int s2 = 0; s2 < splits; ++s2) M = fmaxf(M, __ldcg(all_ml + ((size_t)s2 * DECODE_ROWS + r) * 2));
-        float L = 0.f, O = 0.f;
-        for (int s2 = 0; s2 < splits; ++s2) {
-            const float ms = __ldcg(all_ml + ((size_t)s2 * DECODE_ROWS + r) * 2);
-            if (ms == -INFINITY) continue;   // an empty piece wrote no output rows
-            const float f = exp2f(ms - M);
-            L += __ldcg(all_ml + ((size_t)s2 * DECODE_ROWS + r) * 2 + 1) * f;
-            O += __ldcg(all_o + ((size_t)s2 * DECODE_ROWS + r) * D + d) * f;
-        }
-        out[((size_t)(g.q_begin + tok) * a.H + (size_t)g.kvh * g.G + gh) * D + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
-    }
+    merge_pieces(out, all_ml, all_o, splits, rows_live, g, a);
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -754,6 +804,14 @@ constexpr int TMA_THREADS = 160;                             // 4 consumer warps
 constexpr size_t TMA_DECODE_TILES = (size_t)TMA_STAGES * KV_STAGE_BYTES;
 constexpr size_t TMA_DECODE_SMEM = 1024 + (TMA_DECODE_TILES > DECODE_MERGE_SMEM ? TMA_DECODE_TILES : DECODE_MERGE_SMEM) +
                                    (size_t)DECODE_ROWS * LDS * sizeof(bf16) + 128;
+
+// First key of the page piece to fetch for the piece that starts at key `kp`: itself when any of its `box_rows` keys
+// is visible (k_lo <= key < k_end), else the piece that holds the nearest visible key.
+__device__ __forceinline__ int piece_to_fetch(int kp, int box_rows, int k_lo, int k_end) {
+    if (kp >= k_end) return ((k_end - 1) / box_rows) * box_rows;
+    if (kp + box_rows <= k_lo) return (k_lo / box_rows) * box_rows;
+    return kp;
+}
 
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
@@ -793,11 +851,10 @@ attn_tma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
             s_gave_up = 0;
             mbar_fence_init();
         }
-        // Pages that lie wholly outside the visible range are not fetched; what they would have covered keeps what the
-        // stage held before, which must be finite numbers (it is multiplied by a probability of exactly zero): clear
-        // the stages once.
-        for (int i = threadIdx.x; i < (int)(TMA_DECODE_TILES / 16); i += TMA_THREADS) reinterpret_cast<uint4*>(stages)[i] = make_uint4(0, 0, 0, 0);
-        fence_proxy_async();
+        // Every page piece of a block is fetched, also one that lies wholly outside the visible range: its keys get a
+        // probability of exactly zero, but what stands in the stage is multiplied by that zero and must be finite
+        // numbers, which the pool's pages are and a fresh stage need not be. In place of such a piece (its page may
+        // have been given back behind a window) the nearest visible piece is fetched once more.
         __syncthreads();
 
         if (warp == 4) {
@@ -813,15 +870,13 @@ attn_tma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
                 }
                 const int k0 = k_first + (first + b) * MMA_BN;
                 unsigned char* dst = stages + (size_t)st * KV_STAGE_BYTES;
-                // which of this lane's loads are wanted, and where they come from
+                // where this lane's loads come from
                 int my_bytes = 0;
                 for (int i = lane; i < loads; i += 32) {
-                    const int kp = k0 + (i / (2 * PANELS)) * box_rows;
-                    if (kp < k_end && kp + box_rows > k_lo) {
-                        const int page = table_row[a.page_shift >= 0 ? (kp >> a.page_shift) : (kp / a.page_size)];
-                        if (page >= 0 && page < a.num_pages) my_bytes += box_rows * 128;
-                        else oxr_report(a.status, OXR_BAD_PAGE, g.req);
-                    }
+                    const int kp = piece_to_fetch(k0 + (i / (2 * PANELS)) * box_rows, box_rows, k_lo, k_end);
+                    const int page = table_row[a.page_shift >= 0 ? (kp >> a.page_shift) : (kp / a.page_size)];
+                    if (page >= 0 && page < a.num_pages) my_bytes += box_rows * 128;
+                    else oxr_report(a.status, OXR_BAD_PAGE, g.req);
                 }
                 const int total = __reduce_add_sync(0xffffffffu, my_bytes);
                 if (lane == 0) {
@@ -831,15 +886,13 @@ attn_tma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
                 __syncwarp();
                 for (int i = lane; i < loads; i += 32) {
                     const int box = i / (2 * PANELS), which = i % (2 * PANELS);     // which: K panels, then V panels
-                    const int kp = k0 + box * box_rows;
-                    if (kp < k_end && kp + box_rows > k_lo) {
-                        const int page = table_row[a.page_shift >= 0 ? (kp >> a.page_shift) : (kp / a.page_size)];
-                        if (page >= 0 && page < a.num_pages) {
-                            const int panel = which % PANELS;
-                            const int row = pool_row0 + page * a.page_size + (a.page_shift >= 0 ? (kp & (a.page_size - 1)) : (kp % a.page_size));
-                            unsigned char* d2 = dst + (size_t)which * PANEL_BYTES + (size_t)box * box_rows * 128;
-                            tma_load_2d(d2, which < PANELS ? &map_k : &map_v, g.kvh * D + panel * 64, row, full + st);
-                        }
+                    const int kp = piece_to_fetch(k0 + box * box_rows, box_rows, k_lo, k_end);
+                    const int page = table_row[a.page_shift >= 0 ? (kp >> a.page_shift) : (kp / a.page_size)];
+                    if (page >= 0 && page < a.num_pages) {
+                        const int panel = which % PANELS;
+                        const int row = pool_row0 + page * a.page_size + (a.page_shift >= 0 ? (kp & (a.page_size - 1)) : (kp % a.page_size));
+                        unsigned char* d2 = dst + (size_t)which * PANEL_BYTES + (size_t)box * box_rows * 128;
+                        tma_load_2d(d2, which < PANELS ? &map_k : &map_v, g.kvh * D + panel * 64, row, full + st);
                     }
                 }
             }
@@ -893,7 +946,7 @@ attn_tma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
         }
         consumer_sync();   // every consumer has left the loop: all fetched stages were read, the region is free
         float* mo = reinterpret_cast<float*>(stages);   // [4 warps][16 rows][D + 2]: O then (m, l)
-        constexpr int MS = D + 2;
+        constexpr int MS = MERGE_STRIDE;
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
             float* dst = mo + ((size_t)warp * DECODE_ROWS + (lane >> 2) + 8 * r) * MS;
@@ -905,28 +958,7 @@ attn_tma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
             if ((lane & 3) == 0) { dst[D] = m[r]; dst[D + 1] = l[r]; }
         }
         consumer_sync();
-        for (int idx = threadIdx.x; idx < rows_live * D; idx += MMA_THREADS) {
-            const int r = idx / D, d = idx % D;
-            int tok, gh;
-            if (!g.row(r, tok, gh)) continue;
-            float M = -INFINITY;
-#pragma unroll
-            for (int w = 0; w < 4; ++w) M = fmaxf(M, mo[((size_t)w * DECODE_ROWS + r) * MS + D]);
-            float L = 0.f, O = 0.f;
-#pragma unroll
-            for (int w = 0; w < 4; ++w) {
-                const float* src = mo + ((size_t)w * DECODE_ROWS + r) * MS;
-                const float f = (src[D] == -INFINITY) ? 0.f : exp2f(src[D] - M);
-                L += src[D + 1] * f;
-                O += src[d] * f;
-            }
-            if (splits == 1) {
-                out[((size_t)(g.q_begin + tok) * a.H + (size_t)g.kvh * g.G + gh) * D + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
-            } else {
-                my_o[r * D + d] = O;
-                if (d == 0) { my_ml[2 * r] = M; my_ml[2 * r + 1] = L; }
-            }
-        }
+        merge_warps(mo, rows_live, splits, out, my_o, my_ml, g, a);
     } else {
         if (warp == 4) return;
         if (splits > 1)   // nothing for this piece: an empty partial
@@ -944,22 +976,7 @@ attn_tma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
     if (threadIdx.x == 0) counters[unit] = 0;
     const float* all_ml = part_ml + unit * splits * DECODE_ROWS * 2;
     const float* all_o = part_o + unit * splits * DECODE_ROWS * D;
-    for (int idx = threadIdx.x; idx < rows_live * D; idx += MMA_THREADS) {
-        const int r = idx / D, d = idx % D;
-        int tok, gh;
-        if (!g.row(r, tok, gh)) continue;
-        float M = -INFINITY;
-        for (int s2 = 0; s2 < splits; ++s2) M = fmaxf(M, __ldcg(all_ml + ((size_t)s2 * DECODE_ROWS + r) * 2));
-        float L = 0.f, O = 0.f;
-        for (int s2 = 0; s2 < splits; ++s2) {
-            const float ms = __ldcg(all_ml + ((size_t)s2 * DECODE_ROWS + r) * 2);
-            if (ms == -INFINITY) continue;
-            const float f = exp2f(ms - M);
-            L += __ldcg(all_ml + ((size_t)s2 * DECODE_ROWS + r) * 2 + 1) * f;
-            O += __ldcg(all_o + ((size_t)s2 * DECODE_ROWS + r) * D + d) * f;
-        }
-        out[((size_t)(g.q_begin + tok) * a.H + (size_t)g.kvh * g.G + gh) * D + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
-    }
+    merge_pieces(out, all_ml, all_o, splits, rows_live, g, a);
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
