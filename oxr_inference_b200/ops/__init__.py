@@ -295,13 +295,22 @@ DECODE_BLOCKS_PER_SM = 2
 
 
 def attention_splits(n_short_tiles: int, num_heads: int, num_kv_heads: int, kv_len_bound: int) -> int:
-    """Into how many pieces the split-KV kernel cuts each request's keys: as many as still run all at once (one wave
-    of blocks), no piece shorter than 128 keys. Depends only on sizes the host knows before the step (fixed inside a
-    CUDA graph)."""
+    """Into how many pieces the split-KV kernel cuts each request's keys. Blocks run in waves of
+    ``NUM_SMS * DECODE_BLOCKS_PER_SM``; a block walks its piece's 64-key blocks one after the other and spends about
+    as long as 4.5 of them before its first keys arrive and after its last (measured on a B200: 7 us against 1.6 us per
+    block). The number of pieces with the least waves x (4.5 + blocks per piece) wins, the smaller among equals; no
+    piece is shorter than 128 keys. Depends only on sizes the host knows before the step (fixed inside a CUDA
+    graph)."""
     group = num_heads // num_kv_heads
     blocks = max(1, n_short_tiles * num_kv_heads * -(-group // min(group, DECODE_ROWS)))
-    want = (NUM_SMS * DECODE_BLOCKS_PER_SM) // blocks
-    return max(1, min(want, max(1, kv_len_bound // 128), MAX_SPLITS))
+    slots = NUM_SMS * DECODE_BLOCKS_PER_SM
+    key_blocks = max(1, -(-kv_len_bound // 64))
+    best, best_cost = 1, None
+    for splits in range(1, max(1, min(MAX_SPLITS, kv_len_bound // 128)) + 1):
+        cost = -(-blocks * splits // slots) * (4.5 + -(-key_blocks // splits))
+        if best_cost is None or cost < best_cost:
+            best, best_cost = splits, cost
+    return best
 
 
 class KVMaps:
