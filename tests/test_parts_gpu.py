@@ -294,3 +294,154 @@ def test_a_toy_architecture_with_a_stateful_mixer_registers_builds_and_steps(tmp
     assert c.state_slot == a.state_slot and runner.cache.reserve(c, 37)
     again = runner.step([StepEntry(c, seqs["a"], list(range(37)))])
     torch.testing.assert_close(again.cpu(), want["a"], atol=1e-4, rtol=1e-4)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# A second toy architecture, also defined here: layer 0 is the built-in attention (no q/k norm) under a position
+# encoding of its own (angles that grow linearly in the pair index) with a feed-forward that ROUTES each token to two
+# of four small experts; layer 1 is the built-in attention with NO position encoding and a window, with the built-in
+# feed-forward; the head is untied. Parts are chosen layer by layer; nothing under oxr_inference_b200/ knows them.
+# ---------------------------------------------------------------------------------------------------------------
+TOY2 = {"architectures": ["ToyRoutedForTests"], "hidden_size": 48, "intermediate_size": 40, "vocab_size": 61, "heads": 6,
+        "kv_heads": 3, "head_dim": 16, "eps": 1e-6, "experts": 4, "expert_size": 24, "window": 6, "max_positions": 96}
+
+
+def _register_toy2():
+    from oxr_inference_b200.config.registry import ARCHITECTURES, Architecture, register_architecture
+    from oxr_inference_b200.parts import (FEED_FORWARDS, POSITION_ENCODINGS, FeedForward, LayerSpec, ModelSpec, ParamInfo, PartSpec,
+                                          PositionEncoding, ScheduleEntry)
+
+    if "toy_linear_angles" not in POSITION_ENCODINGS:
+        @POSITION_ENCODINGS.register("toy_linear_angles")
+        class LinearAngles(PositionEncoding):
+            """Pair j of a head turns by position * (j + 1) / 7 radians: the same rotation kernel, another table."""
+
+            def __init__(self, runtime, *, dim):
+                angles = torch.outer(torch.arange(runtime.max_positions, dtype=torch.float), (torch.arange(dim // 2, dtype=torch.float) + 1) / 7)
+                self.cos, self.sin = angles.cos().to(runtime.device), angles.sin().to(runtime.device)
+
+            def tables(self):
+                return self.cos, self.sin
+
+    if "toy_top2_experts" not in FEED_FORWARDS:
+        @FEED_FORWARDS.register("toy_top2_experts")
+        class Top2Experts(FeedForward):
+            """Router logits in fp32 -> softmax -> the two largest, renormalised -> sum of p * W_out[e] relu(W_in[e] h)."""
+
+            def __init__(self, runtime, *, hidden_size, experts, expert_size):
+                self.runtime, self.h, self.e, self.i = runtime, hidden_size, experts, expert_size
+                self.w = {}
+
+            def parameters(self):
+                return {"router.weight": ParamInfo((self.e, self.h), role="vector"),
+                        "w_in": ParamInfo((self.e, self.i, self.h)), "w_out": ParamInfo((self.e, self.h, self.i))}
+
+            def assign(self, name, tensor):
+                info = self.parameters()[name]
+                self.w[name] = tensor.to(self.runtime.device, self.runtime.store_dtype(info, tensor.dtype))
+
+            def forward(self, h):
+                p = torch.softmax(h.float() @ self.w["router.weight"].float().T, -1)
+                top, idx = p.topk(2, -1)
+                top = top / top.sum(-1, keepdim=True)
+                out = torch.zeros_like(h, dtype=torch.float32)
+                for e in range(self.e):
+                    rows, slot = (idx == e).nonzero(as_tuple=True)
+                    if rows.numel():
+                        x = h[rows].float()
+                        y = torch.relu(x @ self.w["w_in"][e].float().T) @ self.w["w_out"][e].float().T
+                        out.index_add_(0, rows, y * top[rows, slot][:, None])
+                return out.to(h.dtype)
+
+    if "ToyRoutedForTests" not in ARCHITECTURES:
+        def spec(c):
+            H = c["hidden_size"]
+            norm = lambda p: PartSpec("rms_norm", {"size": H, "eps": c["eps"]}, prefix=p)  # noqa: E731
+
+            def attn(i, **more):
+                return PartSpec("gqa_attention", {"hidden_size": H, "num_heads": c["heads"], "num_kv_heads": c["kv_heads"], "head_dim": c["head_dim"],
+                                                  "scale": c["head_dim"] ** -0.5, "eps": c["eps"], **more}, prefix=f"model.layers.{i}.self_attn.")
+            layers = (
+                LayerSpec(attn(0, qk_norm=False), norm("model.layers.0.input_layernorm."),
+                          PartSpec("toy_top2_experts", {"hidden_size": H, "experts": c["experts"], "expert_size": c["expert_size"]}, prefix="model.layers.0.moe."),
+                          norm("model.layers.0.post_attention_layernorm."), position=PartSpec("toy_linear_angles", {"dim": c["head_dim"]})),
+                LayerSpec(attn(1, window=c["window"]), norm("model.layers.1.input_layernorm."),
+                          PartSpec("swiglu", {"hidden_size": H, "intermediate_size": c["intermediate_size"]}, prefix="model.layers.1.mlp."),
+                          norm("model.layers.1.post_attention_layernorm."), position=None),
+            )
+            return ModelSpec(
+                architecture="ToyRoutedForTests", hidden_size=H, vocab_size=c["vocab_size"],
+                embedding=PartSpec("token_embedding", {"vocab_size": c["vocab_size"], "hidden_size": H}, prefix="model.embed_tokens."),
+                layers=layers, schedule=(ScheduleEntry(0), ScheduleEntry(1)), final_norm=norm("model.norm."),
+                head=PartSpec("linear_head", {"vocab_size": c["vocab_size"], "hidden_size": H, "tied": False}, prefix="lm_head."),
+                max_positions=c["max_positions"])
+
+        register_architecture(Architecture("ToyRoutedForTests", lambda raw, gen: dict(raw), spec))
+
+
+def _toy2_plain(w, ids):
+    c, n, eps = TOY2, len(ids), TOY2["eps"]
+    H, KV, D = c["heads"], c["kv_heads"], c["head_dim"]
+    x = w["model.embed_tokens.weight"][torch.tensor(ids)]
+    angles = torch.outer(torch.arange(n, dtype=torch.float), (torch.arange(D // 2, dtype=torch.float) + 1) / 7)
+    for layer in (0, 1):
+        p = f"model.layers.{layer}."
+        h = QP.rms_norm(x, w[p + "input_layernorm.weight"], eps)
+        q = (h @ w[p + "self_attn.q_proj.weight"].T).view(n, H, D)
+        k = (h @ w[p + "self_attn.k_proj.weight"].T).view(n, KV, D)
+        v = (h @ w[p + "self_attn.v_proj.weight"].T).view(n, KV, D)
+        if layer == 0:   # no q/k norm, linear angles
+            q, k = QP.rotate_half_split(q, angles.cos(), angles.sin()), QP.rotate_half_split(k, angles.cos(), angles.sin())
+            a = QP.causal_attention(q, k, v, D ** -0.5)
+        else:            # q/k norm, no rotation, window
+            q, k = QP.rms_norm(q, w[p + "self_attn.q_norm.weight"], eps), QP.rms_norm(k, w[p + "self_attn.k_norm.weight"], eps)
+            a = QP.causal_attention(q, k, v, D ** -0.5, window=c["window"])
+        x = x + a.reshape(n, H * D) @ w[p + "self_attn.o_proj.weight"].T
+        h = QP.rms_norm(x, w[p + "post_attention_layernorm.weight"], eps)
+        if layer == 0:
+            prob = torch.softmax(h @ w[p + "moe.router.weight"].T, -1)
+            top, idx = prob.topk(2, -1)
+            top = top / top.sum(-1, keepdim=True)
+            y = torch.zeros_like(h)
+            for t in range(n):
+                for j in range(2):
+                    e = int(idx[t, j])
+                    y[t] += top[t, j] * (torch.relu(h[t] @ w[p + "moe.w_in"][e].T) @ w[p + "moe.w_out"][e].T)
+            x = x + y
+        else:
+            x = x + QP.swiglu(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+    return QP.rms_norm(x, w["model.norm.weight"], eps) @ w["lm_head.weight"].T
+
+
+def test_a_toy_architecture_with_routed_experts_and_its_own_position_encoding(tmp_path):
+    from safetensors.torch import load_file
+
+    from oxr_inference_b200.engine.batch import StepEntry
+    from oxr_inference_b200.engine.runtime import ModelRunner
+    from oxr_inference_b200.weights import write_random_model
+
+    _register_toy2()
+    folder = write_random_model(TOY2, tmp_path / "toy2", seed=4, dtype="float32", std=0.2)
+    w = load_file(str(folder / "model.safetensors"))
+    assert w["model.layers.0.moe.w_in"].shape == (4, 24, 48) and "model.layers.0.self_attn.q_norm.weight" not in w
+    assert "model.layers.1.self_attn.q_norm.weight" in w and "lm_head.weight" in w
+    runner = ModelRunner.from_folder(folder, dtype="float32", page_size=8, num_pages=24, max_requests=2)
+    plan = runner.model.cache_plan
+    assert len(plan.groups) == 2, "a layer that keeps all keys and a layer with a window have pools of their own"
+
+    g = torch.Generator().manual_seed(6)
+    ids = torch.randint(0, TOY2["vocab_size"], (45,), generator=g).tolist()
+    want = _toy2_plain(w, ids)
+    # the routing must actually vary, or the test would not see a wrong expert
+    h0 = QP.rms_norm(w["model.embed_tokens.weight"][torch.tensor(ids)], w["model.layers.0.input_layernorm.weight"], TOY2["eps"])
+    assert len({int(i) for i in (h0 @ w["model.layers.0.moe.router.weight"].T).argmax(-1)}) >= 3
+    rc = runner.cache.open("r")
+    got, pos = [], 0
+    for c in (17, 2, 9, 1, 1, 15):
+        assert runner.cache.reserve(rc, pos + c)
+        got.append(runner.step([StepEntry(rc, ids[pos:pos + c], list(range(c)))]))
+        pos += c
+    runner.check()
+    torch.testing.assert_close(torch.cat(got).cpu(), want, atol=1e-4, rtol=1e-4)
+    # the window's pages were given back as it passed them
+    assert sum(p == -1 for p in rc.tables[1]) >= 3 and all(p != -1 for p in rc.tables[0])
