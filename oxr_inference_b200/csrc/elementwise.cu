@@ -203,34 +203,50 @@ OXR_API int oxr_add_rms_norm(void* out, float* residual_out, const void* x, cons
 }
 
 // ---------------------------------------------------------------------------------------------- SiLU * up
-// gate_up is [n, 2*inter]: gate = first half, up = second half (oxr_runtime/language.py:102-104).
+// gate_up is [n, 2*inter]. Side by side (`interleave` 0): gate = first half, up = second half
+// (oxr_runtime/language.py:102-104). Interleaved by 8: columns 16j .. 16j+7 are gate 8j .. 8j+7 and columns
+// 16j+8 .. 16j+15 the matching up values, which is what a product with a weight whose gate and up rows alternate in
+// groups of 8 writes (the decode kernel that applies SiLU in its epilogue needs both in one block).
+__device__ __forceinline__ void gate_up_at(size_t row, size_t col, int inter, int interleave, size_t& g, size_t& u) {
+    if (interleave) {
+        g = row * 2 * inter + (col / 8) * 16 + col % 8;
+        u = g + 8;
+    } else {
+        g = row * 2 * inter + col;
+        u = g + inter;
+    }
+}
 template <typename T>
-__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int inter, size_t total) {
+__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int inter, int interleave, size_t total) {
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-        const size_t row = i / inter, col = i % inter;
-        const float g = Num<T>::to_f32(gate_up[row * 2 * inter + col]);
-        const float u = Num<T>::to_f32(gate_up[row * 2 * inter + inter + col]);
+        size_t gi, ui;
+        gate_up_at(i / inter, i % inter, inter, interleave, gi, ui);
+        const float g = Num<T>::to_f32(gate_up[gi]);
+        const float u = Num<T>::to_f32(gate_up[ui]);
         out[i] = Num<T>::from_f32(g / (1.f + __expf(-g)) * u);
     }
 }
 template <>
-__global__ void silu_mul_kernel<float>(float* __restrict__ out, const float* __restrict__ gate_up, int inter, size_t total) {
+__global__ void silu_mul_kernel<float>(float* __restrict__ out, const float* __restrict__ gate_up, int inter, int interleave, size_t total) {
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-        const size_t row = i / inter, col = i % inter;
-        const float g = gate_up[row * 2 * inter + col];
-        const float u = gate_up[row * 2 * inter + inter + col];
+        size_t gi, ui;
+        gate_up_at(i / inter, i % inter, inter, interleave, gi, ui);
+        const float g = gate_up[gi];
+        const float u = gate_up[ui];
         out[i] = g / (1.f + expf(-g)) * u;   // full-precision exp on the 32-bit path
     }
 }
 
 // bf16, inter a multiple of 8: 16-byte loads and stores. Grid (column chunks, rows): no division per element.
+// With INTERLEAVED the gate word of output word `col` is word 2 col of the row and its up word the next one.
+template <bool INTERLEAVED>
 __global__ void silu_mul_bf16x8_kernel(uint4* __restrict__ out, const uint4* __restrict__ gate_up, int inter8) {
     const size_t row = blockIdx.y;
     const uint4* g_row = gate_up + row * 2 * inter8;
     uint4* o_row = out + row * inter8;
     for (int col = blockIdx.x * blockDim.x + threadIdx.x; col < inter8; col += gridDim.x * blockDim.x) {
-        uint4 g = __ldg(g_row + col);
-        uint4 u = __ldg(g_row + inter8 + col);
+        uint4 g = __ldg(g_row + (INTERLEAVED ? 2 * col : col));
+        uint4 u = __ldg(g_row + (INTERLEAVED ? 2 * col + 1 : inter8 + col));
         const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g);
         const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&u);
         uint4 o;
@@ -247,9 +263,11 @@ __global__ void silu_mul_bf16x8_kernel(uint4* __restrict__ out, const uint4* __r
     }
 }
 
-OXR_API int oxr_silu_mul(void* out, const void* gate_up, int n_rows, int inter, int dtype, cudaStream_t stream) {
+// interleave: 0 (gate | up side by side) or 8 (alternating groups of 8 columns; inter must then be a multiple of 8).
+OXR_API int oxr_silu_mul(void* out, const void* gate_up, int n_rows, int inter, int interleave, int dtype, cudaStream_t stream) {
     const size_t total = (size_t)n_rows * inter;
     if (total == 0) return 0;
+    if (interleave != 0 && (interleave != 8 || inter % 8 != 0)) return OXR_BAD_ARGUMENT;
     const int threads = 256;
     if (dtype == 1 && inter % 8 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)gate_up % 16 == 0) {
         const int inter8 = inter / 8;
@@ -257,17 +275,19 @@ OXR_API int oxr_silu_mul(void* out, const void* gate_up, int n_rows, int inter, 
         while (rows_done < n_rows) {   // grid.y holds at most 65535 rows per launch
             const int rows = n_rows - rows_done < 65535 ? n_rows - rows_done : 65535;
             dim3 grid((inter8 + threads - 1) / threads, rows);
-            silu_mul_bf16x8_kernel<<<grid, threads, 0, stream>>>((uint4*)out + (size_t)rows_done * inter8,
-                                                               (const uint4*)gate_up + (size_t)rows_done * 2 * inter8, inter8);
+            uint4* o = (uint4*)out + (size_t)rows_done * inter8;
+            const uint4* gu = (const uint4*)gate_up + (size_t)rows_done * 2 * inter8;
+            if (interleave) silu_mul_bf16x8_kernel<true><<<grid, threads, 0, stream>>>(o, gu, inter8);
+            else silu_mul_bf16x8_kernel<false><<<grid, threads, 0, stream>>>(o, gu, inter8);
             rows_done += rows;
         }
         return oxr_launch_status();
     }
     const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
     if (dtype == 0)
-        silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((float*)out, (const float*)gate_up, inter, total);
+        silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((float*)out, (const float*)gate_up, inter, interleave, total);
     else if (dtype == 1)
-        silu_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up, inter, total);
+        silu_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up, inter, interleave, total);
     else
         return OXR_BAD_ARGUMENT;
     return oxr_launch_status();

@@ -32,7 +32,11 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint3
 constexpr int SKINNY_WARPS = 8;
 
 // TILES = number of 8-row groups of X (M <= 8 * TILES). TO = output type.
-template <int TILES, typename TO>
+// GATED: W's rows alternate in groups of 8 between a gate and an up projection (rows 16j .. 16j+7 gate 8j .. 8j+7,
+// rows 16j+8 .. 16j+15 the matching up rows), so a block's 16 rows are 8 gates and their 8 ups, and the epilogue
+// writes silu(gate) * up (oxr_runtime/language.py:102-104) into C [M, N / 2]: the decode step's SiLU kernel and the
+// round trip of the gate-up activations through memory are gone. SiLU is applied to the fp32 sums.
+template <int TILES, typename TO, bool GATED = false>
 __global__ void __launch_bounds__(SKINNY_WARPS * 32, TILES <= 2 ? 2 : 1)
 gemm_skinny_kernel(TO* __restrict__ C, const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W, int M,
                    int N, int K) {
@@ -86,13 +90,25 @@ gemm_skinny_kernel(TO* __restrict__ C, const __nv_bfloat16* __restrict__ X, cons
         partial[warp][g + 8][8 * i + 2 * t + 1] = acc[i][3];
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < 16 * 8 * TILES; idx += SKINNY_WARPS * 32) {
-        const int r = idx % 16, m = idx / 16;   // consecutive threads -> consecutive n: coalesced stores
-        if (m < M && n0 + r < N) {
-            float s = 0.f;
+    if constexpr (GATED) {
+        for (int idx = threadIdx.x; idx < 8 * 8 * TILES; idx += SKINNY_WARPS * 32) {
+            const int r = idx % 8, m = idx / 8;
+            if (m < M && n0 + r + 8 < N) {
+                float gate = 0.f, up = 0.f;
 #pragma unroll
-            for (int w = 0; w < SKINNY_WARPS; ++w) s += partial[w][r][m];
-            C[(size_t)m * N + n0 + r] = Num<TO>::from_f32(s);
+                for (int w = 0; w < SKINNY_WARPS; ++w) { gate += partial[w][r][m]; up += partial[w][r + 8][m]; }
+                C[(size_t)m * (N / 2) + n0 / 2 + r] = Num<TO>::from_f32(gate / (1.f + __expf(-gate)) * up);
+            }
+        }
+    } else {
+        for (int idx = threadIdx.x; idx < 16 * 8 * TILES; idx += SKINNY_WARPS * 32) {
+            const int r = idx % 16, m = idx / 16;   // consecutive threads -> consecutive n: coalesced stores
+            if (m < M && n0 + r < N) {
+                float s = 0.f;
+#pragma unroll
+                for (int w = 0; w < SKINNY_WARPS; ++w) s += partial[w][r][m];
+                C[(size_t)m * N + n0 + r] = Num<TO>::from_f32(s);
+            }
         }
     }
 }
@@ -118,5 +134,21 @@ OXR_API int oxr_gemm_skinny_bf16(void* C, const void* X, const void* W, int M, i
     else return OXR_BAD_ARGUMENT;
 #undef BY_TILES
 #undef LAUNCH
+    return oxr_launch_status();
+}
+
+// C [M, N / 2] = silu(X Wg^T) * (X Wu^T) in bf16, for W [N, K] whose gate and up rows alternate in groups of 8
+// (N a multiple of 16). Requires M <= 64, K % 8 == 0 and 16-byte aligned X and W.
+OXR_API int oxr_gemm_skinny_gated_bf16(void* C, const void* X, const void* W, int M, int N, int K, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (M > 64 || N % 16 != 0 || K <= 0 || K % 8 != 0 || (uintptr_t)X % 16 != 0 || (uintptr_t)W % 16 != 0) return OXR_BAD_ARGUMENT;
+    const unsigned blocks = N / 16;
+    using bf = __nv_bfloat16;
+#define LAUNCH_GATED(TL) gemm_skinny_kernel<TL, bf, true><<<blocks, SKINNY_WARPS * 32, 0, stream>>>((bf*)C, (const bf*)X, (const bf*)W, M, N, K)
+    if (M <= 8) LAUNCH_GATED(1);
+    else if (M <= 16) LAUNCH_GATED(2);
+    else if (M <= 32) LAUNCH_GATED(4);
+    else LAUNCH_GATED(8);
+#undef LAUNCH_GATED
     return oxr_launch_status();
 }

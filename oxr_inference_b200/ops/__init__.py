@@ -79,11 +79,12 @@ def _lib():
         p, i, f = c_void_p, c_int, c_float
         lib.oxr_embedding.argtypes = [p, p, p, i, i, i, i, i, p, p]
         lib.oxr_add_rms_norm.argtypes = [p, p, p, p, p, p, i, i, f, i, p]
-        lib.oxr_silu_mul.argtypes = [p, p, i, i, i, p]
+        lib.oxr_silu_mul.argtypes = [p, p, i, i, i, i, p]
         lib.oxr_cast.argtypes = [p, p, c_size_t, i, i, p]
         lib.oxr_qk_norm_rope_store.argtypes = [p, p, p, p, p, p, p, p, p, p, i, i, i, i, f, i, c_longlong, i, i, i, i, p, p]
         lib.oxr_gemm_f32_nt.argtypes = [p, p, p, i, i, i, p]
         lib.oxr_gemm_skinny_bf16.argtypes = [p, p, p, i, i, i, i, p]
+        lib.oxr_gemm_skinny_gated_bf16.argtypes = [p, p, p, i, i, i, p]
         lib.oxr_gemm_tcgen05_bf16.argtypes = [p, p, p, i, i, i, i, i, i, p, p, p, p]
         lib.oxr_gemm_tcgen05_pair_bf16.argtypes = [p, p, p, i, i, i, i, i, p, p]
         lib.oxr_sample.argtypes = [p, p, i, i, p, p, p, p, p, p]
@@ -92,7 +93,7 @@ def _lib():
         lib.oxr_repetition_penalty.argtypes = [p, p, p, p, i, i, p]
         lib.oxr_mark_seen.argtypes = [p, p, p, i, i, p]
         for name in ("oxr_embedding", "oxr_add_rms_norm", "oxr_silu_mul", "oxr_cast", "oxr_qk_norm_rope_store",
-                     "oxr_gemm_f32_nt", "oxr_gemm_skinny_bf16", "oxr_gemm_tcgen05_bf16", "oxr_gemm_tcgen05_pair_bf16", "oxr_sample", "oxr_repetition_penalty", "oxr_mark_seen"):
+                     "oxr_gemm_f32_nt", "oxr_gemm_skinny_bf16", "oxr_gemm_skinny_gated_bf16", "oxr_gemm_tcgen05_bf16", "oxr_gemm_tcgen05_pair_bf16", "oxr_sample", "oxr_repetition_penalty", "oxr_mark_seen"):
             getattr(lib, name).restype = c_int
         _core = lib
     return _core
@@ -194,16 +195,42 @@ def add_rms_norm(x: torch.Tensor, residual: torch.Tensor | None, weight: torch.T
     return out, res_out
 
 
-def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
-    """``silu(gate) * up`` for ``gate_up = [gate | up]`` along the last axis (oxr_runtime/language.py:102-104)."""
+def silu_mul(gate_up: torch.Tensor, interleave: int = 0) -> torch.Tensor:
+    """``silu(gate) * up`` (oxr_runtime/language.py:102-104) for ``gate_up = [gate | up]`` along the last axis, or,
+    with ``interleave`` 8, for gate and up alternating in groups of 8 columns (what ``GATE_UP_INTERLEAVE`` rows of a
+    stacked weight produce)."""
     _need(gate_up, "gate_up")
     n, two_i = gate_up.shape
     if two_i % 2:
         raise KernelError("gate_up must have an even number of columns")
+    if interleave not in (0, GATE_UP_INTERLEAVE) or (interleave and two_i % (2 * interleave)):
+        raise KernelError(f"silu_mul: interleave {interleave} with {two_i} columns")
     out = torch.empty((n, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
-    code = _lib().oxr_silu_mul(out.data_ptr(), gate_up.data_ptr(), n, two_i // 2, _dtype_code(gate_up), _stream())
+    code = _lib().oxr_silu_mul(out.data_ptr(), gate_up.data_ptr(), n, two_i // 2, interleave, _dtype_code(gate_up), _stream())
     _done(code, "silu_mul")
     return out
+
+
+GATE_UP_INTERLEAVE = 8
+"""Rows per group when a weight stacks a gate and an up projection alternately: what one block of the skinny GEMM sees
+as its rows g and g + 8."""
+
+
+def gated_silu_linear(x: torch.Tensor, weight: torch.Tensor, interleave: int = 0) -> torch.Tensor:
+    """``silu(x Wg^T) * (x Wu^T)`` for a weight that stacks Wg and Wu: side by side (``interleave`` 0: one product,
+    then the SiLU kernel) or alternating in groups of 8 rows. With alternating rows a decode-sized bf16 batch runs the
+    skinny kernel whose epilogue applies SiLU to its fp32 sums and writes the product alone; everything else runs the
+    product and then the SiLU kernel on the interleaved columns."""
+    _need(x, "x")
+    _need(weight, "weight")
+    m, k = x.shape
+    n = weight.shape[0]
+    if (interleave == GATE_UP_INTERLEAVE and m <= SKINNY_MAX_ROWS and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+            and n % 16 == 0 and k % 8 == 0 and weight.shape[1] == k and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0):
+        out = torch.empty((m, n // 2), dtype=torch.bfloat16, device=x.device)
+        _done(_lib().oxr_gemm_skinny_gated_bf16(out.data_ptr(), x.data_ptr(), weight.data_ptr(), m, n, k, _stream()), "gemm_skinny_gated")
+        return out
+    return silu_mul(linear(x, weight), interleave)
 
 
 def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:

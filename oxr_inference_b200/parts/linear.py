@@ -13,9 +13,14 @@ class StackedLinear:
     tensors. The reference concatenates q|k|v and gate|up after loading (oxr_runtime/language.py:234-245); here
     each tensor is copied straight into its rows of one buffer, so no second copy of the weights ever exists."""
 
-    def __init__(self, runtime: Runtime, in_features: int, outs: dict[str, int]):
+    def __init__(self, runtime: Runtime, in_features: int, outs: dict[str, int], interleave: int = 0):
+        """``interleave`` > 0 (two tensors of equal height, a multiple of it): rows alternate between the two tensors in
+        groups of that many, rows [2 g i, 2 g i + g) from the first and the next g from the second, instead of one
+        tensor after the other."""
         self.runtime, self.in_features = runtime, int(in_features)
         self.outs = {k: int(v) for k, v in outs.items()}
+        heights = list(self.outs.values())
+        self.interleave = int(interleave) if interleave and len(heights) == 2 and heights[0] == heights[1] and heights[0] % interleave == 0 else 0
         self.offsets: dict[str, int] = {}
         row = 0
         for name, n in self.outs.items():
@@ -32,6 +37,10 @@ class StackedLinear:
         if self.weight is None:
             dtype = self.runtime.store_dtype(info, tensor.dtype)
             self.weight = torch.empty((self.out_features, self.in_features), dtype=dtype, device=self.runtime.device)
+        if self.interleave:
+            g, which = self.interleave, list(self.outs).index(name)
+            self.weight.view(-1, 2, g, self.in_features)[:, which].copy_(tensor.view(-1, g, self.in_features))
+            return
         lo = self.offsets[name]
         self.weight[lo:lo + self.outs[name]].copy_(tensor)
 

@@ -86,6 +86,46 @@ def test_silu_mul(ops, dtype, inter):
     torch.testing.assert_close(ops.silu_mul(gu).float(), KP.silu_mul(gu), **_tol(dtype))
 
 
+def _interleave8(gate, up):
+    """[.., I] and [.., I] -> [.., 2 I] with groups of 8 columns (or rows of a weight, given as [I, K]) alternating."""
+    return torch.stack([gate.reshape(*gate.shape[:-1], -1, 8), up.reshape(*up.shape[:-1], -1, 8)], dim=-2).reshape(*gate.shape[:-1], -1)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("inter", [160, 24, 12288])
+def test_silu_mul_on_interleaved_columns(ops, dtype, inter):
+    g = torch.Generator(device=DEV).manual_seed(2)
+    gu = (torch.randn(9, 2 * inter, device=DEV, generator=g) * 3).to(dtype)
+    mixed = _interleave8(gu[:, :inter], gu[:, inter:]).contiguous()
+    assert torch.equal(ops.silu_mul(mixed, interleave=8), ops.silu_mul(gu))
+    with pytest.raises(ops.KernelError):
+        ops.silu_mul(gu[:, :20].contiguous(), interleave=8)
+
+
+@pytest.mark.parametrize("M", [1, 5, 8, 13, 16])
+@pytest.mark.parametrize("inter,K", [(160, 96), (24, 64), (12288, 4096), (1000, 1032)])
+def test_gated_skinny_gemm_applies_silu_in_its_epilogue(ops, M, inter, K):
+    """silu(x Wg^T) * (x Wu^T) from ONE kernel when the weight's gate and up rows alternate in groups of 8, against the
+    plain formula; and the same call beyond the skinny kernel's rows, which runs product and SiLU kernel apart."""
+    g = torch.Generator(device=DEV).manual_seed(21)
+    x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+    wg = (torch.randn(inter, K, device=DEV, generator=g) * 0.05).bfloat16()
+    wu = (torch.randn(inter, K, device=DEV, generator=g) * 0.05).bfloat16()
+    w = _interleave8(wg.T.contiguous(), wu.T.contiguous()).T.contiguous()     # rows alternate
+    assert torch.equal(w[:8], wg[:8]) and torch.equal(w[8:16], wu[:8]) and torch.equal(w[16:24], wg[8:16])
+    before = ops.launch_count
+    got = ops.gated_silu_linear(x, w, interleave=8)
+    assert ops.launch_count == before + 1, "one kernel"
+    want = KP.silu_mul(torch.cat([x.float() @ wg.float().T, x.float() @ wu.float().T], dim=1))
+    torch.testing.assert_close(got.float(), want, atol=1e-2, rtol=2e-2)
+    rows = 40
+    x2 = torch.randn(rows, K, device=DEV, generator=g).bfloat16()
+    want2 = KP.silu_mul(torch.cat([x2.float() @ wg.float().T, x2.float() @ wu.float().T], dim=1))
+    torch.testing.assert_close(ops.gated_silu_linear(x2, w, interleave=8).float(), want2, atol=2e-2, rtol=2e-2)
+    side_by_side = torch.cat([wg, wu]).contiguous()
+    torch.testing.assert_close(ops.gated_silu_linear(x2, side_by_side).float(), want2, atol=2e-2, rtol=2e-2)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,KV,D", [(4, 2, 16), (6, 2, 32), (5, 5, 48), (32, 8, 128), (3, 1, 256)])
 def test_qk_norm_rope_store(ops, dtype, H, KV, D):

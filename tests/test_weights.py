@@ -59,7 +59,11 @@ def test_loads_fused_projections_by_name_and_keeps_dtypes(tmp_path):
     assert torch.equal(attn.qkv.weight[192:256], stored["model.layers.1.self_attn.k_proj.weight"])
     assert torch.equal(attn.qkv.weight[256:], stored["model.layers.1.self_attn.v_proj.weight"])
     ff = model.blocks[2].feed_forward
-    assert torch.equal(ff.gate_up.weight[160:], stored["model.layers.2.mlp.up_proj.weight"])
+    # gate and up rows alternate in groups of 8: rows 16j .. 16j+7 are gate 8j .. 8j+7, the next 8 the matching up rows
+    both = ff.gate_up.weight.view(-1, 2, 8, 96)
+    assert ff.gate_up.interleave == 8 and ff.gate_up.weight.shape == (320, 96)
+    assert torch.equal(both[:, 0].reshape(160, 96), stored["model.layers.2.mlp.gate_proj.weight"])
+    assert torch.equal(both[:, 1].reshape(160, 96), stored["model.layers.2.mlp.up_proj.weight"])
     # small vectors are kept in fp32 whatever the path
     assert attn.q_norm.dtype == torch.float32 and model.final_norm.weight.dtype == torch.float32
     assert torch.equal(attn.q_norm, stored["model.layers.1.self_attn.q_norm.weight"].float())
