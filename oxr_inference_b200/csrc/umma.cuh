@@ -100,4 +100,42 @@ __device__ __forceinline__ void store_row_piece(TO* dst, const uint32_t (&v)[32]
     }
 }
 
+
+// The same piece of a product whose columns alternate in groups of 8 between a gate and an up projection (columns
+// 16j .. 16j+7 gate 8j .. 8j+7, 16j+8 .. 16j+15 the matching up values; col0 a multiple of 16): writes
+// silu(gate) * up (oxr_runtime/language.py:102-104), `count / 2` values, into a row of N / 2 columns. `dst` points at
+// column col0 / 2 of that row.
+template <typename TO>
+__device__ __forceinline__ void store_row_piece_gated(TO* dst, const uint32_t (&v)[32], int count, int col0, int N) {
+    float o[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const float g = __uint_as_float(v[(j / 8) * 16 + j % 8]), u = __uint_as_float(v[(j / 8) * 16 + 8 + j % 8]);
+        o[j] = g / (1.f + __expf(-g)) * u;
+    }
+    const int outs = count / 2;
+    if (col0 + count <= N && ((uintptr_t)dst % 16 == 0)) {
+        if constexpr (sizeof(TO) == 2) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                if (8 * j >= outs) break;
+                uint4 w;
+                __nv_bfloat162* wp = reinterpret_cast<__nv_bfloat162*>(&w);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) wp[e] = __floats2bfloat162_rn(o[8 * j + 2 * e], o[8 * j + 2 * e + 1]);
+                reinterpret_cast<uint4*>(dst)[j] = w;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (4 * j >= outs) break;
+                reinterpret_cast<float4*>(dst)[j] = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+            if (j < outs && col0 + (j / 8) * 16 + 8 + j % 8 < N) dst[j] = Num<TO>::from_f32(o[j]);
+    }
+}
 }  // namespace

@@ -87,13 +87,16 @@ def _lib():
         lib.oxr_gemm_skinny_gated_bf16.argtypes = [p, p, p, i, i, i, p]
         lib.oxr_gemm_tcgen05_bf16.argtypes = [p, p, p, i, i, i, i, i, i, p, p, p, p]
         lib.oxr_gemm_tcgen05_pair_bf16.argtypes = [p, p, p, i, i, i, i, i, p, p]
+        lib.oxr_gemm_tcgen05_gated_bf16.argtypes = [p, p, p, i, i, i, i, p, p]
+        lib.oxr_gemm_tcgen05_pair_gated_bf16.argtypes = [p, p, p, i, i, i, i, p, p]
         lib.oxr_sample.argtypes = [p, p, i, i, p, p, p, p, p, p]
         lib.oxr_sample_chunks.argtypes = [i]
         lib.oxr_sample_chunks.restype = c_int
         lib.oxr_repetition_penalty.argtypes = [p, p, p, p, i, i, p]
         lib.oxr_mark_seen.argtypes = [p, p, p, i, i, p]
         for name in ("oxr_embedding", "oxr_add_rms_norm", "oxr_silu_mul", "oxr_cast", "oxr_qk_norm_rope_store",
-                     "oxr_gemm_f32_nt", "oxr_gemm_skinny_bf16", "oxr_gemm_skinny_gated_bf16", "oxr_gemm_tcgen05_bf16", "oxr_gemm_tcgen05_pair_bf16", "oxr_sample", "oxr_repetition_penalty", "oxr_mark_seen"):
+                     "oxr_gemm_f32_nt", "oxr_gemm_skinny_bf16", "oxr_gemm_skinny_gated_bf16", "oxr_gemm_tcgen05_bf16", "oxr_gemm_tcgen05_pair_bf16", "oxr_gemm_tcgen05_gated_bf16",
+                     "oxr_gemm_tcgen05_pair_gated_bf16", "oxr_sample", "oxr_repetition_penalty", "oxr_mark_seen"):
             getattr(lib, name).restype = c_int
         _core = lib
     return _core
@@ -218,17 +221,27 @@ as its rows g and g + 8."""
 
 def gated_silu_linear(x: torch.Tensor, weight: torch.Tensor, interleave: int = 0) -> torch.Tensor:
     """``silu(x Wg^T) * (x Wu^T)`` for a weight that stacks Wg and Wu: side by side (``interleave`` 0: one product,
-    then the SiLU kernel) or alternating in groups of 8 rows. With alternating rows a decode-sized bf16 batch runs the
-    skinny kernel whose epilogue applies SiLU to its fp32 sums and writes the product alone; everything else runs the
-    product and then the SiLU kernel on the interleaved columns."""
+    then the SiLU kernel) or alternating in groups of 8 rows. With alternating rows a bf16 product runs the kernel
+    ``linear`` would pick for its size (skinny, one-SM or two-SM tcgen05) with an epilogue that applies SiLU to the fp32
+    sums and writes the gated product alone; 32-bit runs the product and then the SiLU kernel on interleaved columns."""
     _need(x, "x")
     _need(weight, "weight")
     m, k = x.shape
     n = weight.shape[0]
-    if (interleave == GATE_UP_INTERLEAVE and m <= SKINNY_MAX_ROWS and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
-            and n % 16 == 0 and k % 8 == 0 and weight.shape[1] == k and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0):
+    fused = (interleave == GATE_UP_INTERLEAVE and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and n % 16 == 0
+             and k % 8 == 0 and weight.shape[1] == k and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+    if fused:
+        lib = _lib()
         out = torch.empty((m, n // 2), dtype=torch.bfloat16, device=x.device)
-        _done(_lib().oxr_gemm_skinny_gated_bf16(out.data_ptr(), x.data_ptr(), weight.data_ptr(), m, n, k, _stream()), "gemm_skinny_gated")
+        if m <= SKINNY_MAX_ROWS:
+            _done(lib.oxr_gemm_skinny_gated_bf16(out.data_ptr(), x.data_ptr(), weight.data_ptr(), m, n, k, _stream()), "gemm_skinny_gated")
+        elif _gemm_pair_plan(m, n, k):
+            _done(lib.oxr_gemm_tcgen05_pair_gated_bf16(out.data_ptr(), x.data_ptr(), weight.data_ptr(), m, n, k, _gemm_pair_plan(m, n, k),
+                                                       new_status(x.device).data_ptr(), _stream()), "gemm_tcgen05_pair_gated")
+        else:
+            tile_n, _ = _gemm_plan(m, n, k, False)   # the gated epilogue has no shares of k
+            _done(lib.oxr_gemm_tcgen05_gated_bf16(out.data_ptr(), x.data_ptr(), weight.data_ptr(), m, n, k, tile_n,
+                                                  new_status(x.device).data_ptr(), _stream()), "gemm_tcgen05_gated")
         return out
     return silu_mul(linear(x, weight), interleave)
 
@@ -473,14 +486,14 @@ def _gemm_cost(m: int, n: int, k: int, tile_n: int, splits: int) -> float:
 
 
 @functools.lru_cache(maxsize=None)
-def _gemm_plan(m: int, n: int, k: int) -> tuple[int, int]:
+def _gemm_plan(m: int, n: int, k: int, may_split: bool = True) -> tuple[int, int]:
     """(tile width, shares of k per tile) of the tcgen05 product: the cheapest by ``_gemm_cost`` among widths of 32 to
     256 columns in steps of 16 and 1 to 8 shares whose partial tiles fit the workspace; the first found among equals."""
     best, best_cost = (128, 1), None
     steps = -(-k // 64)
     for tile_n in range(256, 16, -16):
         tiles = -(-m // 128) * -(-n // tile_n)
-        for splits in GEMM_SPLITS:
+        for splits in (GEMM_SPLITS if may_split else (1,)):
             if splits > steps or (splits > 1 and splits * tiles * 128 * tile_n * 4 > GEMM_WORKSPACE_BYTES):
                 continue
             cost = _gemm_cost(m, n, k, tile_n, splits)

@@ -118,12 +118,29 @@ def test_gated_skinny_gemm_applies_silu_in_its_epilogue(ops, M, inter, K):
     assert ops.launch_count == before + 1, "one kernel"
     want = KP.silu_mul(torch.cat([x.float() @ wg.float().T, x.float() @ wu.float().T], dim=1))
     torch.testing.assert_close(got.float(), want, atol=1e-2, rtol=2e-2)
-    rows = 40
-    x2 = torch.randn(rows, K, device=DEV, generator=g).bfloat16()
-    want2 = KP.silu_mul(torch.cat([x2.float() @ wg.float().T, x2.float() @ wu.float().T], dim=1))
-    torch.testing.assert_close(ops.gated_silu_linear(x2, w, interleave=8).float(), want2, atol=2e-2, rtol=2e-2)
     side_by_side = torch.cat([wg, wu]).contiguous()
-    torch.testing.assert_close(ops.gated_silu_linear(x2, side_by_side).float(), want2, atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(ops.gated_silu_linear(x, side_by_side).float(), want, atol=1e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("M,pair_tile", [(40, 0), (150, 0), (300, 64), (3100, 0)])
+@pytest.mark.parametrize("inter,K", [(160, 96), (24, 64), (1000, 1032), (12288, 512)])
+def test_gated_tcgen05_gemm_applies_silu_in_its_epilogue(ops, monkeypatch, M, pair_tile, inter, K):
+    """The same from the tcgen05 kernels (one SM per tile, and the pair kernel where it is forced or planned): tile
+    widths that are odd multiples of 16, ragged edges, both against the plain formula."""
+    if pair_tile:
+        monkeypatch.setattr(ops, "_gemm_pair_plan", lambda m, n, k: pair_tile)
+    g = torch.Generator(device=DEV).manual_seed(22)
+    x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+    wg = (torch.randn(inter, K, device=DEV, generator=g) * 0.05).bfloat16()
+    wu = (torch.randn(inter, K, device=DEV, generator=g) * 0.05).bfloat16()
+    w = _interleave8(wg.T.contiguous(), wu.T.contiguous()).T.contiguous()
+    status = ops.new_status(DEV)
+    before = ops.launch_count
+    got = ops.gated_silu_linear(x, w, interleave=8)
+    assert ops.launch_count == before + 1, "one kernel"
+    ops.check_status(status)
+    want = KP.silu_mul(torch.cat([x.float() @ wg.float().T, x.float() @ wu.float().T], dim=1))
+    torch.testing.assert_close(got.float(), want, atol=1e-2, rtol=2e-2)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
