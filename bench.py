@@ -216,7 +216,7 @@ def main() -> int:
         assert plan.decode_only and len(plan.entries) == batch
         entries = [StepEntry(p.request.cache, p.request.tokens[p.start:p.start + 1], [0], counter=len(p.request.output))
                    for p in plan.entries]
-        tokens = engine.graphs.run(entries)  # captures at first use, fills the static inputs
+        tokens, _ = engine.graphs.run(entries)  # captures at first use, fills the static inputs
         key = next(k for k in engine.graphs._graphs if k[0] >= batch)
         key = min((k for k in engine.graphs._graphs if k[0] >= batch), key=lambda k: k)
         graph = engine.graphs._graphs[key][0]

@@ -134,9 +134,15 @@ class Engine:
             self._mark_new(plan)
         tokens = None
         if self.graphs is not None and plan.decode_only and not penalised:
-            tokens = self.graphs.run(entries)
-            if tokens is not None:
+            replayed = self.graphs.run(entries)
+            if replayed is not None:
+                # the graph copied the tokens and the status word to pinned memory itself
                 self.counters["graph_steps"] += 1
+                torch.cuda.current_stream().synchronize()
+                host = replayed[1].tolist()
+                if host[-2] != 0:
+                    ops.check_status(rt.status)
+                return host[:len(entries)]
         if tokens is None:
             ctx = self.runner.builder.build(entries)
             logits = self.runner.model.step(ctx, self.runner.cache)

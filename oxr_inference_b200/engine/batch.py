@@ -78,6 +78,9 @@ class BatchBuilder:
         self._rows: dict[int, list] = {}
         """Per fixed device block: which (request, table version) each block-table row was last filled from, so that
         rows that did not change are not written again."""
+        self._same_requests: dict[int, tuple] = {}
+        """Per fixed device block: the serials of the requests its rows were last filled for. While the same requests
+        decode on, only what moves with a token is written again."""
 
     # ---- host memory
     def _staging(self, words: int, fixed_block: torch.Tensor | None) -> torch.Tensor:
@@ -94,6 +97,10 @@ class BatchBuilder:
         if self._pinned is None or self._pinned.numel() < words:
             self._pinned = torch.empty(max(words, 4096), dtype=torch.int32).pin_memory()
         return self._pinned
+
+    def staging_of(self, device_block: torch.Tensor) -> torch.Tensor:
+        """The pinned block that ``build`` fills for this fixed device block (after its first ``build``)."""
+        return self._fixed_pinned[id(device_block)]
 
     def eager_layout(self, entries: list[StepEntry]) -> Layout:
         m = self.manager
@@ -117,9 +124,11 @@ class BatchBuilder:
     # ---- the build
     @torch.inference_mode()
     def build(self, entries: list[StepEntry], layout: Layout | None = None,
-              device_block: torch.Tensor | None = None) -> StepContext:
+              device_block: torch.Tensor | None = None, copy: bool = True) -> StepContext:
         """Fill the staging block for ``entries`` and copy it. With ``layout``/``device_block`` (graph replay) the
-        entries must be single tokens and at most ``layout.requests``; the remaining rows are padding."""
+        entries must be single tokens and at most ``layout.requests``; the remaining rows are padding. ``copy=False``
+        (fixed layouts only) leaves the copy to the caller, whose graph holds it (``staging_of`` names the source); the
+        caller then also sees to it that the step has run before the next ``build`` for this block."""
         m = self.manager
         fixed = layout is not None
         if not fixed:
@@ -136,6 +145,11 @@ class BatchBuilder:
             return host[at:at + size]
 
         n, T = layout.requests, layout.tokens
+        if fixed:
+            signature = tuple(e.cache.serial for e in entries)
+            known = self._same_requests.get(id(device_block))
+            if known is not None and known[0] == signature:
+                return self._advance_fixed(entries, layout, device_block, pinned, seg, copy)
         q_lens = [len(e.tokens) for e in entries] + [1] * (n - n_real)
         starts = [e.cache.length for e in entries] + [0] * (n - n_real)
         cu = np.zeros(n + 1, dtype=np.int64)
@@ -252,17 +266,56 @@ class BatchBuilder:
 
         if device_block is None:
             device_block = torch.empty(layout.total, dtype=torch.int32, device=self.device)
-        device_block[:layout.total].copy_(pinned[:layout.total], non_blocking=True)
-        self._copied = torch.cuda.Event()
-        self._copied.record()
+        if copy or not fixed:
+            device_block[:layout.total].copy_(pinned[:layout.total], non_blocking=True)
+            self._copied = torch.cuda.Event()
+            self._copied.record()
         ctx_lens = [s + q for s, q in zip(starts, q_lens)]
         if fixed:   # the views into a fixed block never change: make them once
+            self._same_requests[id(device_block)] = (signature,)
             ctx = self._fixed_views.get(id(device_block))
             if ctx is None:
                 ctx = self._fixed_views[id(device_block)] = self.views(layout, device_block, tiles_n, q_lens, ctx_lens, max(layout.widths) * P)
             ctx.q_lens, ctx.ctx_lens_host = q_lens, ctx_lens
             return ctx
         return self.views(layout, device_block, tiles_n, q_lens, ctx_lens, max(ctx_lens))
+
+    def _advance_fixed(self, entries: list[StepEntry], layout: Layout, device_block: torch.Tensor, pinned: torch.Tensor, seg,
+                       copy: bool) -> StepContext:
+        """The same requests as in this block's last step, each one token further: the staging block still holds
+        everything that belongs to a request as such (its rows, sampling parameters, state slot, tile entries, the
+        padding); written again are the token, its position and cache slot, the context length, the output index
+        and a block-table row whose request got or gave back a page."""
+        m = self.manager
+        n, n_real = layout.requests, len(entries)
+        starts = [e.cache.length for e in entries]
+        seg("token_ids")[:n_real] = [e.tokens[0] for e in entries]
+        seg("positions")[:n_real] = starts
+        seg("ctx_lens")[:n_real] = [s + 1 for s in starts]
+        seg("counter")[:n_real] = [e.counter for e in entries]
+        remembered = self._rows[id(device_block)]
+        for g in range(len(m.pools)):
+            w = layout.widths[g]
+            slots, table = seg(f"slots{g}"), None
+            for i, e in enumerate(entries):
+                key = (e.cache.serial, e.cache.version)
+                if remembered[g * n + i] != key:
+                    if table is None:
+                        table = seg(f"table{g}").reshape(n, w)
+                    t = e.cache.tables[g]
+                    if len(t) > w:
+                        raise ValueError(f"a block table of {len(t)} pages does not fit the layout's width {w}")
+                    table[i, :len(t)] = t
+                    table[i, len(t):] = m.scratch_pages[g] if m.scratch_pages else 0
+                    remembered[g * n + i] = key
+                slots[i] = m.slot(e.cache, g, starts[i])
+        if copy:
+            device_block[:layout.total].copy_(pinned[:layout.total], non_blocking=True)
+            self._copied = torch.cuda.Event()
+            self._copied.record()
+        ctx = self._fixed_views[id(device_block)]
+        ctx.q_lens, ctx.ctx_lens_host = [1] * n, [s + 1 for s in starts] + [1] * (n - n_real)
+        return ctx
 
     def views(self, layout: Layout, block: torch.Tensor, tiles_n: dict, q_lens: list[int], ctx_lens: list[int],
               kv_len_bound: int) -> StepContext:

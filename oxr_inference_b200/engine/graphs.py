@@ -3,8 +3,10 @@
 As in the reference (oxr_runtime/decode_graph.py:33-119): batch sizes are rounded up to buckets, the inputs live
 in fixed device memory filled from pinned host memory before each replay, rows beyond the real requests point at
 a scratch page, and the graph holds the whole step: embedding, every layer, output head and the choice of the
-next token. Differences: graphs are captured at first use instead of all at start-up, and a graph is keyed by
-(batch bucket, block-table width bucket) so that short contexts do not pay for the widest possible table.
+next token. Differences: graphs are captured at first use instead of all at start-up, a graph is keyed by
+(batch bucket, block-table width bucket) so that short contexts do not pay for the widest possible table, and the
+graph also holds the copy of its inputs from pinned memory and the copy of the chosen tokens and the kernels'
+status word back to pinned memory: a step is one launch and one synchronisation for the host.
 """
 
 from __future__ import annotations
@@ -36,9 +38,11 @@ class DecodeGraphs:
         return min(w, max(self.max_width, need))
 
     @torch.inference_mode()
-    def run(self, entries: list[StepEntry]) -> torch.Tensor | None:
-        """Replay the step for single-token entries; returns the chosen tokens (int32, one per entry; the view
-        is overwritten by the next replay) or None when the batch is larger than the largest bucket."""
+    def run(self, entries: list[StepEntry]) -> tuple[torch.Tensor, torch.Tensor] | None:
+        """Replay the step for single-token entries. Returns (the chosen tokens on the device, int32, one per entry;
+        the pinned host tensor that holds, once the stream has been synchronised, the same tokens followed by the
+        first two words of the status word), both overwritten by the next replay; or None when the batch is larger
+        than the largest bucket. The caller synchronises before it builds the next step."""
         n = len(entries)
         bucket = next((b for b in self.buckets if b >= n), None)
         if bucket is None:
@@ -46,12 +50,12 @@ class DecodeGraphs:
         key = (bucket, self._width_bucket(entries))
         if key not in self._graphs:
             self._capture(key, entries)
-        graph, layout, block, tokens, tiles_n = self._graphs[key]
-        self.runner.builder.build(entries, layout=layout, device_block=block)
+        graph, layout, block, tokens, readback = self._graphs[key]
+        self.runner.builder.build(entries, layout=layout, device_block=block, copy=False)
         graph.replay()
         self.replays += 1
         ops.launch_count += self.kernels_per_replay[key]
-        return tokens[:n]
+        return tokens[:n], readback
 
     def _forward(self, ctx) -> torch.Tensor:
         logits = self.runner.model.step(ctx, self.runner.cache)
@@ -78,8 +82,14 @@ class DecodeGraphs:
         if self._pool is None:
             self._pool = torch.cuda.graph_pool_handle()
         before = ops.launch_count
+        staging = b.staging_of(block)
+        readback = torch.zeros(bucket + 2, dtype=torch.int32).pin_memory()
+        status = self.runner.model.runtime.status
         with torch.cuda.graph(graph, pool=self._pool):
+            block.copy_(staging, non_blocking=True)
             tokens = self._forward(ctx)
+            readback[:bucket].copy_(tokens, non_blocking=True)
+            readback[bucket:].copy_(status[:2], non_blocking=True)
         self.kernels_per_replay[key] = ops.launch_count - before
         ops.launch_count = before  # capturing launches nothing
-        self._graphs[key] = (graph, layout, block, tokens, ctx.tiles)
+        self._graphs[key] = (graph, layout, block, tokens, readback)
