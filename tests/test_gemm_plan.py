@@ -28,3 +28,11 @@ def test_pair_kernel_takes_the_long_steps_only():
     for n, k in ((6144, 4096), (24576, 4096), (4096, 12288)):
         tile_n = ops._gemm_pair_plan(8192, n, k)
         assert tile_n % 32 == 0 and 128 <= tile_n <= 256
+
+
+def test_few_rows_form_where_w_is_narrow_and_rows_are_few():
+    assert ops._gemm_few_rows_plan(64, 4096, 12288) == 4       # 32 tiles: four shares each
+    assert ops._gemm_few_rows_plan(64, 6144, 4096) == 3
+    assert ops._gemm_few_rows_plan(64, 24576, 4096) == 0       # 192 tiles fill the SMs as they are
+    assert ops._gemm_few_rows_plan(129, 4096, 12288) == 0
+    assert ops._gemm_few_rows_plan(64, 4096, 64) == 0          # one k step cannot be shared

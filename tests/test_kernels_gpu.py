@@ -251,6 +251,7 @@ def test_gemm_tcgen05_split_k(ops, monkeypatch, M, N, K, tile_n, splits, out_dty
     and the last unit of a tile adds them in the order of the shares. Twice in a row (the tickets are left zeroed),
     bit-identical."""
     monkeypatch.setattr(ops, "SKINNY_MAX_ROWS", 16)
+    monkeypatch.setattr(ops, "_gemm_few_rows_plan", lambda m, n, k: 0)
     monkeypatch.setattr(ops, "_gemm_plan", lambda m, n, k: (tile_n, splits))
     g = torch.Generator(device=DEV).manual_seed(10)
     x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
@@ -267,10 +268,34 @@ def test_gemm_tcgen05_split_k(ops, monkeypatch, M, N, K, tile_n, splits, out_dty
         torch.testing.assert_close(got.float(), want, atol=1e-2, rtol=1e-2)
 
 
+@pytest.mark.parametrize("M,N,K,shares", [(64, 256, 64, 1), (17, 509, 96, 1), (100, 1000, 1032, 3), (256, 136, 2048, 8), (33, 4096, 4096, 4),
+                                          (5, 300, 328, 2), (200, 777, 520, 1), (128, 4096, 12288, 4)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_tcgen05_few_rows(ops, monkeypatch, M, N, K, shares, out_dtype):
+    """The few-rows form: the kernel computes the transpose (W's rows on the 128-row side of the tiles, the rows of x
+    as the tile's width) and its epilogue stores it back transposed; with and without shares of k, twice in a row."""
+    monkeypatch.setattr(ops, "SKINNY_MAX_ROWS", 0)
+    monkeypatch.setattr(ops, "_gemm_few_rows_plan", lambda m, n, k: shares)
+    g = torch.Generator(device=DEV).manual_seed(13)
+    x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=DEV, generator=g) * 0.05).bfloat16()
+    status = ops.new_status(DEV)
+    got = ops.linear(x, w, out_dtype)
+    again = ops.linear(x, w, out_dtype)
+    ops.check_status(status)
+    assert got.shape == (M, N) and torch.equal(got, again)
+    want = x.float() @ w.float().T
+    if out_dtype == torch.float32:
+        torch.testing.assert_close(got, want, atol=2e-4 * math.sqrt(K) * 0.05, rtol=1e-4)
+    else:
+        torch.testing.assert_close(got.float(), want, atol=1e-2, rtol=1e-2)
+
+
 @pytest.mark.parametrize("tile_n", [16, 48, 80, 144, 176, 208, 240, 256])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 def test_gemm_tcgen05_every_tile_width(ops, monkeypatch, tile_n, out_dtype):
     """The tile's width is a run-time choice, any multiple of 16 up to 256: ragged edges in M, N and K at each."""
+    monkeypatch.setattr(ops, "_gemm_few_rows_plan", lambda m, n, k: 0)
     monkeypatch.setattr(ops, "_gemm_plan", lambda m, n, k: (tile_n, 1))
     M, N, K = 150, 1000, 328
     g = torch.Generator(device=DEV).manual_seed(11)
@@ -293,6 +318,7 @@ def test_gemm_tcgen05_pair(ops, monkeypatch, M, N, K, tile_n, out_dtype):
     """The two-SM kernel (tcgen05 cta_group::2, each block of a pair stages half of W's tile): whole and ragged tiles,
     a last pair whose second block has no rows at all, every k tail, widths from 32 to 256."""
     monkeypatch.setattr(ops, "SKINNY_MAX_ROWS", 0)
+    monkeypatch.setattr(ops, "_gemm_few_rows_plan", lambda m, n, k: 0)
     monkeypatch.setattr(ops, "_gemm_pair_plan", lambda m, n, k: tile_n)
     g = torch.Generator(device=DEV).manual_seed(12)
     x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
