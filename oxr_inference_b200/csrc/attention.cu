@@ -856,6 +856,7 @@ attn_tma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
         // numbers, which the pool's pages are and a fresh stage need not be. In place of such a piece (its page may
         // have been given back behind a window) the nearest visible piece is fetched once more.
         __syncthreads();
+        pdl_wait();   // the kernel before this one wrote q and the newest keys and values
 
         if (warp == 4) {
             // ------------------------------------------------------------------ producer
@@ -896,6 +897,7 @@ attn_tma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
                     }
                 }
             }
+            pdl_trigger();
             return;   // the producer takes no part in the merge
         }
 
@@ -944,6 +946,7 @@ attn_tma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
             l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
             l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
         }
+        pdl_trigger();     // the cache is read: the next kernel may set itself up during the merges
         consumer_sync();   // every consumer has left the loop: all fetched stages were read, the region is free
         float* mo = reinterpret_cast<float*>(stages);   // [4 warps][16 rows][D + 2]: O then (m, l)
         constexpr int MS = MERGE_STRIDE;
@@ -960,6 +963,7 @@ attn_tma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
         consumer_sync();
         merge_warps(mo, rows_live, splits, out, my_o, my_ml, g, a);
     } else {
+        pdl_wait();
         if (warp == 4) return;
         if (splits > 1)   // nothing for this piece: an empty partial
             for (int i = threadIdx.x; i < rows_live; i += MMA_THREADS) { my_ml[2 * i] = -INFINITY; my_ml[2 * i + 1] = 0.f; }
@@ -1420,7 +1424,7 @@ OXR_API int oxr_paged_attention_bf16(void* out, const void* q, const void* k_cac
             }
             const CUtensorMap* maps = reinterpret_cast<const CUtensorMap*>(kv_maps);
             const int box_rows = page_size < MMA_BN ? page_size : MMA_BN;
-            attn_tma_decode_kernel<<<dim3(n_short, KV * groups, splits), TMA_THREADS, TMA_DECODE_SMEM, stream>>>(
+            oxr_launch(attn_tma_decode_kernel, dim3(n_short, KV * groups, splits), dim3(TMA_THREADS), TMA_DECODE_SMEM, stream, true,
                 (bf16*)out, part_o, part_ml, counters, (const bf16*)q, maps[0], maps[1], pool_row0, box_rows, a);
             return oxr_launch_status();
         }
@@ -1472,3 +1476,6 @@ OXR_API int oxr_attn_make_kv_maps(void* out_maps, const void* k_pool, const void
     if (!oxr_make_map_bf16(&maps[1], v_pool, total_rows, (unsigned long long)row_elems, box_rows)) return OXR_BAD_ARGUMENT;
     return 0;
 }
+
+// Whether this library's split-KV kernel is launched programmatically dependent on the kernel before it (common.cuh).
+OXR_API void oxr_set_chain(int on) { oxr_chain_kernels = on ? 1 : 0; }

@@ -118,6 +118,8 @@ __global__ void add_rms_norm_bf16x8_kernel(__nv_bfloat16* __restrict__ out, floa
                                            const float* residual_in, const float* __restrict__ weight,
                                            const int* __restrict__ rows, int hidden, float eps) {
     __shared__ float red[32];
+    if (gridDim.x <= 296) pdl_trigger();   // a decode step's few blocks: the next kernel may set itself up beside them
+    pdl_wait();
     const int r = blockIdx.x;
     const size_t src = (size_t)(rows ? rows[r] : r) * hidden;
     const size_t dst = (size_t)r * hidden;
@@ -183,7 +185,7 @@ OXR_API int oxr_add_rms_norm(void* out, float* residual_out, const void* x, cons
         const int words = hidden / 8;
         const int vt = words <= 128 ? 128 : (words <= 256 ? 256 : 512);
         const int per = (words + vt - 1) / vt;
-#define NORM_VEC(P) add_rms_norm_bf16x8_kernel<P><<<n_rows, vt, 0, stream>>>((__nv_bfloat16*)out, residual_out, (const __nv_bfloat16*)x, residual_in, weight, rows, hidden, eps)
+#define NORM_VEC(P) oxr_launch(add_rms_norm_bf16x8_kernel<P>, dim3(n_rows), dim3(vt), 0, stream, true, (__nv_bfloat16*)out, residual_out, (const __nv_bfloat16*)x, residual_in, weight, rows, hidden, eps)
         if (per <= 1) NORM_VEC(1);
         else if (per <= 2) NORM_VEC(2);
         else NORM_VEC(4);
@@ -312,3 +314,7 @@ OXR_API int oxr_cast(void* dst, const void* src, size_t n, int src_dtype, int ds
         return OXR_BAD_ARGUMENT;
     return oxr_launch_status();
 }
+
+// Whether the kernels of this library that are written for it are launched programmatically dependent on the kernel
+// before them (see common.cuh). Off until set.
+OXR_API void oxr_set_chain(int on) { oxr_chain_kernels = on ? 1 : 0; }

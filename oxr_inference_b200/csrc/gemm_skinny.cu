@@ -58,8 +58,8 @@ gemm_skinny_kernel(TO* __restrict__ C, const __nv_bfloat16* __restrict__ X, cons
     constexpr int SKINNY_UNROLL = TILES <= 2 ? 8 : 4;   // 16-byte weight loads in flight per lane and row
     const int chunks = (K + 31) / 32;
     const uint4 zero = make_uint4(0, 0, 0, 0);
-    for (int c0 = warp; c0 < chunks; c0 += SKINNY_WARPS * SKINNY_UNROLL) {
-        uint4 fa[SKINNY_UNROLL], fb[SKINNY_UNROLL];
+    uint4 fa[SKINNY_UNROLL], fb[SKINNY_UNROLL];
+    auto load_weights = [&](int c0) {
 #pragma unroll
         for (int u = 0; u < SKINNY_UNROLL; ++u) {
             const int k = (c0 + u * SKINNY_WARPS) * 32 + 8 * t;
@@ -67,6 +67,9 @@ gemm_skinny_kernel(TO* __restrict__ C, const __nv_bfloat16* __restrict__ X, cons
             fa[u] = (in && ok_a) ? ld_stream_16(wa + k) : zero;
             fb[u] = (in && ok_b) ? ld_stream_16(wb + k) : zero;
         }
+    };
+    for (int c0 = warp; c0 < chunks; c0 += SKINNY_WARPS * SKINNY_UNROLL) {
+        load_weights(c0);
 #pragma unroll
         for (int u = 0; u < SKINNY_UNROLL; ++u) {
             const int k = (c0 + u * SKINNY_WARPS) * 32 + 8 * t;
@@ -80,6 +83,7 @@ gemm_skinny_kernel(TO* __restrict__ C, const __nv_bfloat16* __restrict__ X, cons
             }
         }
     }
+    pdl_trigger();   // the weights are read: a chained kernel after this one may set itself up while the sums are gathered
 
     // C fragment: acc[i][0..1] = (weight row g, batch rows 8i + 2t, 2t+1); acc[i][2..3] = weight row g + 8.
 #pragma unroll
@@ -121,7 +125,7 @@ OXR_API int oxr_gemm_skinny_bf16(void* C, const void* X, const void* W, int M, i
     const unsigned blocks = (N + 15) / 16;
     const int tiles = M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8));
 #define LAUNCH(TL, TO) \
-    gemm_skinny_kernel<TL, TO><<<blocks, SKINNY_WARPS * 32, 0, stream>>>((TO*)C, (const __nv_bfloat16*)X, (const __nv_bfloat16*)W, M, N, K)
+    gemm_skinny_kernel<TL, TO, false><<<blocks, SKINNY_WARPS * 32, 0, stream>>>((TO*)C, (const __nv_bfloat16*)X, (const __nv_bfloat16*)W, M, N, K)
 #define BY_TILES(TO)                    \
     switch (tiles) {                    \
         case 1: LAUNCH(1, TO); break;   \

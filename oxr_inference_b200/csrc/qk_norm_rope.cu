@@ -106,6 +106,8 @@ __global__ void qk_norm_rope_store_bf16x2_kernel(
     const float* __restrict__ cos_table, const float* __restrict__ sin_table, const int* __restrict__ positions,
     const int* __restrict__ slots, int n_tokens, int H, int KV, int D, float eps, int max_positions, long long num_slots,
     int norm_q, int norm_k, int rotate, int* status) {
+    if (gridDim.x <= 296) pdl_trigger();   // a decode step's few blocks: the next kernel may set itself up beside them
+    pdl_wait();
     const int warps_per_block = blockDim.x >> 5;
     const int lane = threadIdx.x & 31;
     const long long unit = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
@@ -225,7 +227,7 @@ OXR_API int oxr_qk_norm_rope_store(void* q_out, void* k_cache, void* v_cache, co
         const long long vunits = (long long)n_tokens * ((H + 2 * KV + HPW - 1) / HPW);
         const unsigned vblocks = (unsigned)((vunits + warps - 1) / warps);
 #define LAUNCH_V(S)                                                                                                     \
-        qk_norm_rope_store_bf16x2_kernel<S, HPW><<<vblocks, warps * 32, 0, stream>>>(                                     \
+        oxr_launch(qk_norm_rope_store_bf16x2_kernel<S, HPW>, dim3(vblocks), dim3(warps * 32), 0, stream, true,           \
             (B*)q_out, (B*)k_cache, (B*)v_cache, (const B*)qkv, q_weight, k_weight, cos_table, sin_table, positions, slots, n_tokens, \
             H, KV, D, eps, max_positions, num_slots, norm_q, norm_k, rotate, status)
         if (steps <= 1) LAUNCH_V(1);

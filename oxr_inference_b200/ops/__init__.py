@@ -14,6 +14,7 @@ from __future__ import annotations
 
 import ctypes
 import functools
+import os
 from ctypes import c_float, c_int, c_longlong, c_size_t, c_void_p
 
 import torch
@@ -27,6 +28,11 @@ STATUS_NAMES = {
     4: "block table names a page outside the pool", 5: "a bounded wait inside a kernel ran out",
 }
 _DT = {torch.float32: 0, torch.bfloat16: 1}
+
+CHAIN_KERNELS = os.environ.get("OXR_B200_CHAIN", "1") != "0"
+"""Whether RMSNorm, q/k norm + RoPE and split-KV attention are launched programmatically dependent on the kernel before
+them: each is scheduled while its predecessor finishes and waits with ``griddepcontrol.wait`` before it touches
+activations. ``OXR_B200_CHAIN=0`` turns it off."""
 
 launch_count = 0
 """Kernels of this package launched so far in this process (cuBLAS calls are not counted)."""
@@ -99,6 +105,9 @@ def _lib():
                      "oxr_gemm_f32_nt", "oxr_gemm_skinny_bf16", "oxr_gemm_skinny_gated_bf16", "oxr_gemm_tcgen05_bf16", "oxr_gemm_tcgen05_pair_bf16", "oxr_gemm_tcgen05_gated_bf16", "oxr_gemm_tcgen05_few_rows_bf16",
                      "oxr_gemm_tcgen05_pair_gated_bf16", "oxr_sample", "oxr_repetition_penalty", "oxr_mark_seen"):
             getattr(lib, name).restype = c_int
+        lib.oxr_set_chain.argtypes = [c_int]
+        lib.oxr_set_chain.restype = None
+        lib.oxr_set_chain(int(CHAIN_KERNELS))
         _core = lib
     return _core
 
@@ -121,6 +130,9 @@ def _attn_lib(head_dim: int):
         lib.oxr_attn_head_dim.restype = c_int
         if lib.oxr_attn_head_dim() != head_dim:
             raise BuildError(f"attention library for head size {head_dim} reports {lib.oxr_attn_head_dim()}")
+        lib.oxr_set_chain.argtypes = [c_int]
+        lib.oxr_set_chain.restype = None
+        lib.oxr_set_chain(int(CHAIN_KERNELS))
         _attn[head_dim] = lib
     return lib
 
