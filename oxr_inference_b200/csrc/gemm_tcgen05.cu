@@ -121,6 +121,7 @@ gemm_tcgen05_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap map_
                     if (++s == stages) { s = 0; phase ^= 1; }
                 }
             }
+            pdl_trigger();   // every load of this block is issued: a chained kernel after this one may be scheduled
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer

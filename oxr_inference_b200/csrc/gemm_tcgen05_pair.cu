@@ -125,6 +125,7 @@ gemm_tcgen05_pair_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap
                     if (++s == stages) { s = 0; phase ^= 1; }
                 }
             }
+            pdl_trigger();   // every load of this block is issued: a chained kernel after this one may be scheduled
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer (the leader's one thread)
