@@ -133,19 +133,50 @@ def serving_workload(which: str) -> int:
     engine.generate(prompts[:2], [SamplingParams(max_tokens=4, ignore_eos=True)] * 2)   # warm-up: libraries, first graphs
     before = dict(engine.counters)
     launches = ops.launch_count
+    # Engine.generate's loop, written out so that every step is timed (a step ends with its one synchronisation)
+    pending = list(zip(prompts, params))
+    requests, steps = [], []   # steps: (ms, tokens in the step, decode only?, tokens held by the running requests)
     torch.cuda.synchronize()
     t0 = time.perf_counter()
-    done = engine.generate(prompts, params)
+    while pending or engine.has_work():
+        while pending and len(engine.scheduler.waiting) < engine.scheduler.max_waiting:
+            prompt, p = pending.pop(0)
+            requests.append(engine.add_request(prompt, p))
+        tokens_before, graphs_before = engine.counters["step_tokens"], engine.counters["graph_steps"]
+        held = sum(r.cache.length for r in engine.scheduler.running if r.cache is not None)
+        t = time.perf_counter()
+        engine.step()
+        steps.append(((time.perf_counter() - t) * 1e3, engine.counters["step_tokens"] - tokens_before,
+                      engine.counters["graph_steps"] > graphs_before, held))
     torch.cuda.synchronize()
     seconds = time.perf_counter() - t0
+    done = [engine._done.pop(r.id) for r in requests]
     out_tokens = sum(len(c.token_ids) for c in done)
     in_tokens = sum(len(p) for p in prompts)
     assert all(len(c.token_ids) == o for c, (_, o) in zip(done, work))
+
+    def percentiles(values):
+        v = sorted(values)
+        return {f"p{q}": round(v[min(len(v) - 1, len(v) * q // 100)], 3) for q in (50, 90, 99)} if v else {}
+
+    h, layers, inter = cfg["hidden_size"], cfg["num_hidden_layers"], cfg["intermediate_size"]
+    heads, kv, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    layer_params = h * (heads + 2 * kv) * d + heads * d * h + 3 * h * inter
+    weight_bytes = 2 * (layers * layer_params + V * h)           # every matrix a decode step reads, the head included
+    kv_bytes_per_token = 2 * 2 * layers * kv * d
+    hbm_gbs, bf16_tflops, source = peaks()
+    decode = [(ms, n, held) for ms, n, graph, held in steps if graph]
+    mixed = [(ms, n) for ms, n, graph, held in steps if not graph]
+    decode_fracs = [(weight_bytes + kv_bytes_per_token * held) / (ms * 1e-3) / 1e9 / hbm_gbs for ms, n, held in decode]
+    mixed_flops = [2 * n * (layers * layer_params) / (ms * 1e-3) / 1e12 / bf16_tflops for ms, n in mixed if n >= 1024]
     print(json.dumps({
         "workload": which, "model": "Qwen3-4B shape (tied)" if which == "continuous" else "Qwen3-32B shape", "requests": len(work),
         "prompt_tokens": in_tokens, "output_tokens": out_tokens, "seconds": round(seconds, 3),
         "output_tok_s": round(out_tokens / seconds, 1), "total_tok_s": round((in_tokens + out_tokens) / seconds, 1),
         "steps": engine.counters["steps"] - before["steps"], "graph_steps": engine.counters["graph_steps"] - before["graph_steps"],
+        "decode_step_ms": percentiles([ms for ms, _, _ in decode]), "mixed_step_ms": percentiles([ms for ms, _ in mixed]),
+        "decode_step_hbm_frac": percentiles(decode_fracs), "mixed_step_gemm_frac": percentiles(mixed_flops),
+        "weight_gb_per_decode_step": round(weight_bytes / 1e9, 2), "peaks": source,
         "preemptions": engine.preemptions, "gpu_launches": ops.launch_count - launches, "dtype": "bf16",
         "data": "synthetic uniform token ids, random weights N(0, 0.02)"}))
     return 0

@@ -100,7 +100,7 @@ class Engine:
             entries = []
             for p in plan.entries:
                 r = p.request
-                entries.append(StepEntry(r.cache, r.tokens[p.start:p.start + p.count], [p.count - 1] if p.wants_logits else [],
+                entries.append(StepEntry(r.cache, r.tokens_from(p.start, p.count), [p.count - 1] if p.wants_logits else [],
                                          temperature=r.params.temperature, seed=r.params.seed, counter=len(r.output),
                                          penalty=r.params.repetition_penalty))
             try:

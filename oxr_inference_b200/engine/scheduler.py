@@ -37,7 +37,7 @@ class Busy(RuntimeError):
     """The waiting queue already holds ``max_waiting`` requests (oxr_runtime/engine.py:139-141,367-368)."""
 
 
-@dataclass
+@dataclass(eq=False)   # a request is itself, not its field values: membership tests and removals compare identities
 class Request:
     id: int
     prompt_ids: list[int]
@@ -52,6 +52,16 @@ class Request:
     @property
     def tokens(self) -> list[int]:
         return self.prompt_ids + self.output
+
+    def tokens_from(self, start: int, count: int) -> list[int]:
+        """``tokens[start:start + count]`` without joining the two lists first (a decode step asks for one token of each
+        of hundreds of long requests)."""
+        n = len(self.prompt_ids)
+        if start >= n:
+            return self.output[start - n:start - n + count]
+        if start + count <= n:
+            return self.prompt_ids[start:start + count]
+        return self.prompt_ids[start:] + self.output[:start + count - n]
 
     @property
     def computed(self) -> int:
@@ -130,7 +140,8 @@ class Scheduler:
         # 1 and 2: running requests, decodes first, then prompt portions, each group in admission order
         for phase_is_decode in (True, False):
             for request in list(self.running):
-                if request not in self.running or request.id in chosen or (request.pending == 1) != phase_is_decode:
+                # a request that was preempted or retired earlier in this pass has no cache any more
+                if request.cache is None or request.id in chosen or (request.pending == 1) != phase_is_decode:
                     continue
                 count = min(request.pending, self.prefill_chunk, budget)
                 if count <= 0:

@@ -209,3 +209,16 @@ def test_random_workloads_under_page_pressure(seed):
         else:
             assert r.output == _expected(prompt, len(r.output))
     assert s.cache.free_pages == s.cache.usable_pages and s.cache.free_slots == s.max_running
+
+
+def test_tokens_from_equals_a_slice_of_the_joined_lists():
+    from oxr_inference_b200.engine.scheduler import Request
+    from oxr_inference_b200.sampling import SamplingParams
+
+    r = Request(1, [10, 11, 12, 13], SamplingParams(), output=[20, 21, 22])
+    for start in range(8):
+        for count in range(0, 8 - start):
+            assert r.tokens_from(start, count) == r.tokens[start:start + count]
+    # two requests with equal fields are still two requests
+    twin = Request(1, [10, 11, 12, 13], SamplingParams(), output=[20, 21, 22])
+    assert r != twin and [r, twin].index(twin) == 1
