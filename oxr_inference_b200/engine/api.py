@@ -97,6 +97,10 @@ class Engine:
         plan = self.scheduler.schedule()
         finished = list(plan.finished)
         if plan.entries:
+            if plan.decode_only and len(plan.entries) > 1:
+                # longest context first: the split-KV kernel's blocks start in this order, and a long one that starts
+                # last would run on alone (the order stays the same from step to step while the same requests decode)
+                plan.entries.sort(key=lambda p: -p.start)
             entries = []
             for p in plan.entries:
                 r = p.request
