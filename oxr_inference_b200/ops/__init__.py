@@ -531,20 +531,22 @@ def _gemm_few_rows_plan(m: int, n: int, k: int) -> int:
     return shares if shares >= 2 else 0
 
 
-GEMM_PAIR_MIN_ROWS = 3072
+GEMM_PAIR_MIN_ROWS = 512
 
 
 @functools.lru_cache(maxsize=None)
 def _gemm_pair_plan(m: int, n: int, k: int) -> int:
     """Tile width for the two-SM product kernel (256 x width tiles, a pair of blocks each), or 0 where the one-SM
-    kernel is to run. Measured on a B200 the pair kernel is 5 to 10 % faster from about 3,000 rows on (a k step of a
-    256 x 256 tile takes a pair 0.42 microseconds, one SM 0.45 for 128 x 256) and no faster below. The width is the
-    one with the least waves of pairs times the time of a k step at that width."""
+    kernel is to run. In isolated short runs the two kernels are level below about 3,000 rows; in long runs, where
+    the power cap sets the clock, the pair kernel (a third less shared-memory traffic per flop) is 5 to 8 % faster
+    from 512 rows on (sum of Qwen3-8B's four products, 150 calls each: 173 against 190 us at 512 rows, 604 against
+    649 us at 2,048), and a 2,048-token prefill step takes 28.1 instead of 30.5 ms. The width is the one with the
+    least waves of pairs times the time of a k step at that width (0.094 + 0.00128 width microseconds)."""
     if m < GEMM_PAIR_MIN_ROWS:
         return 0
     pairs = NUM_SMS // 2
     best, best_cost = 0, None
-    for tile_n in (256, 224, 192, 160, 128):
+    for tile_n in (256, 224, 192, 160, 128, 96, 64):
         tiles = -(-m // 256) * -(-n // tile_n)
         cost = -(-tiles // pairs) * (0.094 + 0.00128 * tile_n)
         if best_cost is None or cost < best_cost - 1e-9:

@@ -24,10 +24,12 @@ def test_gemm_plan_fills_the_gpu():
 
 
 def test_pair_kernel_takes_the_long_steps_only():
-    assert ops._gemm_pair_plan(2048, 4096, 4096) == 0
-    for n, k in ((6144, 4096), (24576, 4096), (4096, 12288)):
-        tile_n = ops._gemm_pair_plan(8192, n, k)
-        assert tile_n % 32 == 0 and 128 <= tile_n <= 256
+    assert ops._gemm_pair_plan(256, 4096, 4096) == 0
+    for m in (512, 2048, 8192):
+        for n, k in ((6144, 4096), (24576, 4096), (4096, 12288)):
+            tile_n = ops._gemm_pair_plan(m, n, k)
+            assert tile_n % 32 == 0 and 64 <= tile_n <= 256
+    assert ops._gemm_pair_plan(512, 4096, 4096) == 128          # 64 tiles for 74 pairs, not 32 wide ones
 
 
 def test_few_rows_form_where_w_is_narrow_and_rows_are_few():
