@@ -856,13 +856,16 @@ attn_tma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
         // numbers, which the pool's pages are and a fresh stage need not be. In place of such a piece (its page may
         // have been given back behind a window) the nearest visible piece is fetched once more.
         __syncthreads();
-        pdl_wait();   // the kernel before this one wrote q and the newest keys and values
 
         if (warp == 4) {
             // ------------------------------------------------------------------ producer
+            // The kernel before this one (when this one is launched dependent on it) writes q and the keys and values
+            // of the NEW tokens; every older key is in the cache already. So the blocks of old keys are fetched at
+            // once, while that kernel may still run, and the wait comes before the first block that reaches pos0.
             const int* table_row = a.block_table + (size_t)g.req * a.table_width;
             const int boxes = MMA_BN / box_rows;              // page pieces per block
             const int loads = boxes * 2 * PANELS;             // TMA instructions per block
+            bool waited = false;
             for (int b = 0; b < count; ++b) {
                 const int st = b % TMA_STAGES;
                 if (!mbar_wait(empty + st, ((b / TMA_STAGES) & 1) ^ 1)) {
@@ -870,6 +873,10 @@ attn_tma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
                     break;
                 }
                 const int k0 = k_first + (first + b) * MMA_BN;
+                if (!waited && k0 + MMA_BN > g.pos0) {
+                    pdl_wait();
+                    waited = true;
+                }
                 unsigned char* dst = stages + (size_t)st * KV_STAGE_BYTES;
                 // where this lane's loads come from
                 int my_bytes = 0;
@@ -902,6 +909,7 @@ attn_tma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
         }
 
         // ---------------------------------------------------------------------- consumers (warps 0..3)
+        pdl_wait();   // q comes from the kernel before this one
         load_q_rows(Qs, q, a, g, DECODE_ROWS);   // strided over MMA_THREADS = the 128 consumer threads
         cp_async_commit();
         int row_pos[2];
