@@ -108,16 +108,38 @@ gemm_tcgen05_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap map_
             int s = 0;             // the stage ring does not restart per unit
             uint32_t phase = 0;
             bool ok = true;
+            // No kernel writes the weights, so their tiles of the first ring of stages are requested before this kernel
+            // (when it is launched dependent on the one before) waits for that one to finish; the activations' tiles
+            // of the same stages follow after the wait. With TRANS the weights are the operand behind map_x.
+            int early = 0;
+            for (int unit = blockIdx.x; unit < num_units && early < stages; unit += gridDim.x) {
+                const int tile = SPLIT ? unit / splits : unit;
+                int m0, n0;
+                tile_origin(tile, M, N, bn, m0, n0);
+                for (int kb = SPLIT ? unit % splits : 0; kb < num_kb && early < stages; kb += kb_step, ++early) {
+                    unsigned char* a_dst = tiles + (size_t)early * stage_size;
+                    mbar_expect_tx(full + early, (uint32_t)stage_size);
+                    if constexpr (TRANS) tma_load_2d(a_dst, &map_x, kb * BK, m0, full + early);
+                    else tma_load_2d(a_dst + A_BYTES, &map_w, kb * BK, n0, full + early);
+                }
+            }
+            pdl_wait();
+            int step = 0;
             for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
                 const int tile = SPLIT ? unit / splits : unit;
                 int m0, n0;
                 tile_origin(tile, M, N, bn, m0, n0);
-                for (int kb = SPLIT ? unit % splits : 0; kb < num_kb; kb += kb_step) {
-                    if (!mbar_wait(empty + s, phase ^ 1)) { atomicExch(gave_up, 1u); oxr_report(status, OXR_WAIT_EXPIRED, 0); ok = false; break; }
+                for (int kb = SPLIT ? unit % splits : 0; kb < num_kb; kb += kb_step, ++step) {
                     unsigned char* a_dst = tiles + (size_t)s * stage_size;
-                    mbar_expect_tx(full + s, (uint32_t)stage_size);
-                    tma_load_2d(a_dst, &map_x, kb * BK, m0, full + s);
-                    tma_load_2d(a_dst + A_BYTES, &map_w, kb * BK, n0, full + s);
+                    if (step < early) {   // first ring: the stage is free and armed, its weight tile is on its way
+                        if constexpr (TRANS) tma_load_2d(a_dst + A_BYTES, &map_w, kb * BK, n0, full + s);
+                        else tma_load_2d(a_dst, &map_x, kb * BK, m0, full + s);
+                    } else {
+                        if (!mbar_wait(empty + s, phase ^ 1)) { atomicExch(gave_up, 1u); oxr_report(status, OXR_WAIT_EXPIRED, 0); ok = false; break; }
+                        mbar_expect_tx(full + s, (uint32_t)stage_size);
+                        tma_load_2d(a_dst, &map_x, kb * BK, m0, full + s);
+                        tma_load_2d(a_dst + A_BYTES, &map_w, kb * BK, n0, full + s);
+                    }
                     if (++s == stages) { s = 0; phase ^= 1; }
                 }
             }
@@ -157,6 +179,7 @@ gemm_tcgen05_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap map_
         }
     } else {
         // ------------------------------------------------------------------ epilogue: TMEM -> registers -> global
+        pdl_wait();   // C and the workspace may still be read by the kernels before this one
         const int quarter = warp & 3;                     // this warp may touch TMEM lanes 32 * quarter .. + 31
         int it = 0;
         for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x, ++it) {
@@ -345,8 +368,8 @@ int launch(void* C, const void* X, const void* W, int M, int N, int K, int bn, i
     int tmem_cols = 32;                      // a power of two that holds both accumulators
     while (tmem_cols < 2 * bn) tmem_cols *= 2;
     dim3 grid((unsigned)(units < num_sms ? units : num_sms));   // one block per SM (its shared memory fills the SM)
-    gemm_tcgen05_kernel<TO, SPLIT, GATED, TRANS><<<grid, TC_THREADS, SMEM_BYTES, stream>>>((TO*)C, map_x, map_w, M, N, K, bn, stages, tmem_cols, (int)tiles, splits,
-                                                                              partial, tickets, status);
+    oxr_launch(gemm_tcgen05_kernel<TO, SPLIT, GATED, TRANS>, grid, dim3(TC_THREADS), SMEM_BYTES, stream, true, (TO*)C, map_x, map_w, M, N, K, bn,
+               stages, tmem_cols, (int)tiles, splits, partial, tickets, status);
     return oxr_launch_status();
 }
 }  // namespace

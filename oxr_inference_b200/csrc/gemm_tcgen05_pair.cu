@@ -112,16 +112,35 @@ gemm_tcgen05_pair_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap
             int s = 0;
             uint32_t phase = 0;
             bool ok = true;
+            // No kernel writes the weights: this block's halves of W's tiles for the first ring of stages are requested
+            // before the kernel (when it is launched dependent on the one before) waits for that one; the rows of X for
+            // the same stages follow after the wait. The leader arms each of these stages for both blocks' bytes.
+            int early = 0;
+            for (int tile = pair; tile < num_tiles && early < stages; tile += num_pairs) {
+                int m0, n0;
+                pair_tile_origin(tile, M, N, bn, m0, n0);
+                for (int kb = 0; kb < num_kb && early < stages; ++kb, ++early) {
+                    if (rank == 0) mbar_expect_tx(full + early, 2u * (uint32_t)stage_size);
+                    tma_load_2d_pair(tiles + (size_t)early * stage_size + A_BYTES, &map_w, kb * BK, n0 + (int)rank * (bn / 2),
+                                     in_block(smem_addr(full + early), 0));
+                }
+            }
+            pdl_wait();
+            int step = 0;
             for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
                 int m0, n0;
                 pair_tile_origin(tile, M, N, bn, m0, n0);
-                for (int kb = 0; kb < num_kb; ++kb) {
-                    if (!mbar_wait(empty + s, phase ^ 1)) { atomicExch(gave_up, 1u); oxr_report(status, OXR_WAIT_EXPIRED, 10); ok = false; break; }
+                for (int kb = 0; kb < num_kb; ++kb, ++step) {
                     unsigned char* a_dst = tiles + (size_t)s * stage_size;
-                    if (rank == 0) mbar_expect_tx(full + s, 2u * (uint32_t)stage_size);   // both blocks' bytes
                     const uint32_t leader_full = in_block(smem_addr(full + s), 0);
-                    tma_load_2d_pair(a_dst, &map_x, kb * BK, m0 + (int)rank * BM, leader_full);
-                    tma_load_2d_pair(a_dst + A_BYTES, &map_w, kb * BK, n0 + (int)rank * (bn / 2), leader_full);
+                    if (step < early) {   // first ring: the stage is free and armed, its half of W's tile is on its way
+                        tma_load_2d_pair(a_dst, &map_x, kb * BK, m0 + (int)rank * BM, leader_full);
+                    } else {
+                        if (!mbar_wait(empty + s, phase ^ 1)) { atomicExch(gave_up, 1u); oxr_report(status, OXR_WAIT_EXPIRED, 10); ok = false; break; }
+                        if (rank == 0) mbar_expect_tx(full + s, 2u * (uint32_t)stage_size);   // both blocks' bytes
+                        tma_load_2d_pair(a_dst, &map_x, kb * BK, m0 + (int)rank * BM, leader_full);
+                        tma_load_2d_pair(a_dst + A_BYTES, &map_w, kb * BK, n0 + (int)rank * (bn / 2), leader_full);
+                    }
                     if (++s == stages) { s = 0; phase ^= 1; }
                 }
             }
@@ -157,6 +176,7 @@ gemm_tcgen05_pair_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap
         }
     } else {
         // ------------------------------------------------------------------ epilogue: this block's 128 rows
+        pdl_wait();   // C may still be read by the kernels before this one
         const int quarter = warp & 3;
         int it = 0;
         for (int tile = pair; tile < num_tiles; tile += num_pairs, ++it) {
@@ -232,8 +252,8 @@ int launch_pair(void* C, const void* X, const void* W, int M, int N, int K, int 
     int tmem_cols = 32;
     while (tmem_cols < 2 * bn) tmem_cols *= 2;
     const unsigned pairs = (unsigned)(tiles < max_pairs ? tiles : max_pairs);
-    gemm_tcgen05_pair_kernel<TO, GATED><<<dim3(2 * pairs), PAIR_THREADS, SMEM_BYTES, stream>>>((TO*)C, map_x, map_w, M, N, K, bn, stages, tmem_cols, (int)tiles,
-                                                                                       status);
+    oxr_launch(gemm_tcgen05_pair_kernel<TO, GATED>, dim3(2 * pairs), dim3(PAIR_THREADS), SMEM_BYTES, stream, true, (TO*)C, map_x, map_w, M, N, K,
+               bn, stages, tmem_cols, (int)tiles, status);
     return oxr_launch_status();
 }
 }  // namespace

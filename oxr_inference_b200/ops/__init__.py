@@ -30,9 +30,10 @@ STATUS_NAMES = {
 _DT = {torch.float32: 0, torch.bfloat16: 1}
 
 CHAIN_KERNELS = os.environ.get("OXR_B200_CHAIN", "1") != "0"
-"""Whether RMSNorm, q/k norm + RoPE and split-KV attention are launched programmatically dependent on the kernel before
-them: each is scheduled while its predecessor finishes and waits with ``griddepcontrol.wait`` before it touches
-activations. ``OXR_B200_CHAIN=0`` turns it off."""
+"""Whether RMSNorm, q/k norm + RoPE, split-KV attention and the tcgen05 GEMMs are launched programmatically
+dependent on the kernel before them: each is scheduled while its predecessor finishes, fetches what no kernel of the step
+writes (weights, old keys) and waits with ``griddepcontrol.wait`` before it touches activations. ``OXR_B200_CHAIN=0``
+turns it off."""
 
 launch_count = 0
 """Kernels of this package launched so far in this process (cuBLAS calls are not counted)."""
