@@ -58,6 +58,16 @@ def peaks() -> tuple[float, float, str]:
     return 6650.0, 1590.0, "fallback"
 
 
+def sustained_tflops() -> float | None:
+    """The measured bf16 throughput of a seconds-long loop under the power cap, if the peaks file has it: the figure
+    for a product timed inside a long step."""
+    path = ROOT / "MEASURED_PEAKS.json"
+    try:
+        return float(json.loads(path.read_text())["bf16_tflops_sustained"])
+    except (OSError, KeyError, ValueError, TypeError):
+        return None
+
+
 class ClockSampler:
     """nvidia-smi clock and throttle-reason samples while a timed region runs."""
 
@@ -327,7 +337,8 @@ def main() -> int:
                    "l2": "step inputs (15 GB of weights) exceed L2", "peaks": peak_kind},
         "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": layout_words * 4, "d2h_bytes_per_step": (8 + 2) * 4},
         "gpu_launches": kernels_per_step * K,
-        "prefill": {"value": round(T / (prefill_ms * 1e-3), 1), "tokens": T, "ms": round(prefill_ms, 3), "frac": round(prefill_frac, 4)},
+        "prefill": {"value": round(T / (prefill_ms * 1e-3), 1), "tokens": T, "ms": round(prefill_ms, 3), "frac": round(prefill_frac, 4),
+                    **({"frac_of_sustained": round(flops / (prefill_ms * 1e-3) / (sustained_tflops() * 1e12), 4)} if sustained_tflops() else {})},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_gbs, "unit": "GB/s", "frac": round(achieved / hbm_gbs, 4)},
         "points": points,
         "clocks": clocks,
