@@ -12,7 +12,7 @@ from __future__ import annotations
 import logging
 import time
 from pathlib import Path
-from typing import Any, Mapping, Sequence
+from typing import Any, Callable, Mapping, Sequence
 
 import torch
 
@@ -64,6 +64,7 @@ class Engine:
         self.graphs = DecodeGraphs(self.runner, max_batch=s.max_running, max_positions=self.max_positions) if s.cuda_graphs else None
         self._seen: torch.Tensor | None = None  # [slots + 1, vocab] uint8, made when a request first asks for a penalty
         self._done: dict[int, Completion] = {}
+        self._callbacks: dict[int, Callable[[Completion], None]] = {}
         self._readback: torch.Tensor | None = None  # pinned: sampled tokens + status word of a step
         self.tokenizer = None
         if model_dir is not None and (Path(model_dir) / "tokenizer.json").is_file():
@@ -73,14 +74,19 @@ class Engine:
         self.counters = {"steps": 0, "graph_steps": 0, "prompt_tokens": 0, "generated_tokens": 0, "step_tokens": 0}
 
     # ---- requests
-    def add_request(self, prompt: Sequence[int] | str, params: SamplingParams | None = None) -> Request:
-        """Queue a request; raises ``Busy`` when ``max_waiting`` requests are queued already."""
+    def add_request(self, prompt: Sequence[int] | str, params: SamplingParams | None = None,
+                    done: Callable[[Completion], None] | None = None) -> Request:
+        """Queue a request; raises ``Busy`` when ``max_waiting`` requests are queued already. ``done`` is called with the
+        request's ``Completion`` from the ``step()`` in which it ends (oxr_runtime/engine.py:343-371); the returned
+        ``Request`` has ``cancel()``."""
         if isinstance(prompt, str):
             if self.tokenizer is None:
                 raise ValueError("text prompts need a tokenizer.json in the model folder; pass token ids instead")
             prompt = self.tokenizer.encode(prompt, add_special_tokens=False).ids
         request = self.scheduler.add([int(t) for t in prompt], params or SamplingParams())
         self.counters["prompt_tokens"] += len(request.prompt_ids)
+        if done is not None:
+            self._callbacks[request.id] = done
         return request
 
     def has_work(self) -> bool:
@@ -129,6 +135,9 @@ class Engine:
             c = Scheduler.completion(r, text)
             self._done[r.id] = c
             out.append(c)
+            callback = self._callbacks.pop(r.id, None)
+            if callback is not None:
+                callback(c)
         return out
 
     def _run(self, plan: StepPlan, entries: list[StepEntry]) -> list[int]:

@@ -49,6 +49,11 @@ class Request:
     cancelled: bool = False
     finish_reason: str | None = None
 
+    def cancel(self) -> None:
+        """Ask for the request to be dropped: at the next step it leaves the queue or gives its pages back and ends with
+        ``cancelled`` (oxr_runtime/engine.py:162-171,472-475)."""
+        self.cancelled = True
+
     @property
     def tokens(self) -> list[int]:
         return self.prompt_ids + self.output

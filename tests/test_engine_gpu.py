@@ -162,6 +162,29 @@ def test_step_failure_is_loud_and_pages_come_back(folders):
     assert len(ok[0].token_ids) == 2, "the engine stays usable after a failed step"
 
 
+def test_done_callback_and_cancel(folders):
+    """A request's ``done`` callback gets its completion in the step in which it ends; ``cancel()`` ends a running request
+    at the next step, gives its pages back and leaves the others' tokens as they would have been."""
+    from oxr_inference_b200.sampling import SamplingParams
+
+    engine = _engine(folders["A"], "A", "float32")
+    alone = engine.generate([token_ids("A", 9, seed=4)], SamplingParams(max_tokens=12, ignore_eos=True))[0]
+    seen = []
+    keep = engine.add_request(token_ids("A", 9, seed=4), SamplingParams(max_tokens=12, ignore_eos=True), done=seen.append)
+    drop = engine.add_request(token_ids("A", 30, seed=5), SamplingParams(max_tokens=50, ignore_eos=True), done=seen.append)
+    for _ in range(4):
+        engine.step()
+    assert not seen and len(drop.output) >= 2
+    drop.cancel()
+    while engine.has_work():
+        engine.step()
+    assert [c.request_id for c in seen] == [drop.id, keep.id]
+    assert seen[0].finish_reason == "cancelled" and seen[1].finish_reason == "length"
+    assert seen[1].token_ids == alone.token_ids
+    engine.runner.check()
+    assert not engine.runner.cache.open_requests()
+
+
 def test_command_line(folders, tmp_path):
     folder = folders["A"]
     cfg, w = QP.read_model(folder)

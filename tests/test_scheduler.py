@@ -177,7 +177,7 @@ def test_cancel_frees_pages():
     a = s.add(list(range(10)), SamplingParams(max_tokens=50))
     b = s.add(list(range(10)), SamplingParams(max_tokens=50))
     s.commit(s.schedule(), {a.id: 1, b.id: 2})
-    a.cancelled = True
+    a.cancel()
     plan = s.schedule()
     assert a in plan.finished and a.finish_reason == "cancelled" and a.cache is None
     assert [p.request.id for p in plan.entries] == [b.id]
