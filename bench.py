@@ -186,6 +186,7 @@ def serving_workload(which: str) -> int:
         "steps": engine.counters["steps"] - before["steps"], "graph_steps": engine.counters["graph_steps"] - before["graph_steps"],
         "decode_step_ms": percentiles([ms for ms, _, _ in decode]), "mixed_step_ms": percentiles([ms for ms, _ in mixed]),
         "decode_step_hbm_frac": percentiles(decode_fracs, (10, 50, 90)), "mixed_step_gemm_frac": percentiles(mixed_flops, (10, 50, 90)),
+        "slowest_steps_ms": [round(ms, 1) for ms, *_ in sorted(steps, reverse=True)[:4]],
         "weight_gb_per_decode_step": round(weight_bytes / 1e9, 2), "peaks": source,
         "preemptions": engine.preemptions, "gpu_launches": ops.launch_count - launches, "dtype": "bf16",
         "data": "synthetic uniform token ids, random weights N(0, 0.02)"}))

@@ -148,7 +148,7 @@ class Scheduler:
                 # a request that was preempted or retired earlier in this pass has no cache any more
                 if request.cache is None or request.id in chosen or (request.pending == 1) != phase_is_decode:
                     continue
-                count = min(request.pending, self.prefill_chunk, budget)
+                count = self._portion(request, budget)
                 if count <= 0:
                     continue
                 if self._make_room(request, count, plan, chosen):
@@ -157,7 +157,9 @@ class Scheduler:
         # 3: admit from the head of the queue
         while self.waiting and budget > 0 and len(self.running) < self.max_running and self.cache.free_slots > 0:
             request = self.waiting[0]
-            count = min(request.pending, self.prefill_chunk, budget)
+            count = self._portion(request, budget)
+            if count <= 0:
+                break
             needed = pages_for(count, self.cache.page_size)
             if needed > self.cache.usable_pages and not self.running:
                 # its first portion alone is beyond the whole cache: shrink the portion to what the cache holds
@@ -180,6 +182,26 @@ class Scheduler:
 
         plan.entries = [chosen[r.id] for r in self.running if r.id in chosen]
         return plan
+
+    STEP_TILE = 256
+    """Rows of the widest GEMM tile: a step of a few tokens more than a multiple of it pays for a whole tile row."""
+
+    def _portion(self, request: Request, budget: int) -> int:
+        """How many of the request's pending tokens this step takes: all of them, or what the chunk size and the step's
+        remaining budget allow. A portion that does not finish its prompt is trimmed by up to an eighth so that the step's
+        tokens so far come to a whole number of GEMM tile rows: 2,048 prompt tokens beside 32 decode tokens would occupy
+        nine tile rows of 256, 2,016 beside 32 occupy eight, and the 32 tokens left over ride along with a later step.
+        For the same reason a long step does not take a sliver (less than a tile row) of another prompt."""
+        count = min(request.pending, self.prefill_chunk, budget)
+        planned = self.max_step_tokens - budget
+        if 0 < count < request.pending:
+            if count >= 2 * self.STEP_TILE:
+                over = (planned + count) % self.STEP_TILE
+                if 0 < over <= count // 8:
+                    count -= over
+            elif count < self.STEP_TILE and planned >= 2 * self.STEP_TILE and (planned + count) % self.STEP_TILE:
+                count = 0   # a sliver of a prompt at the end of a long step would only open another tile row
+        return count
 
     def _make_room(self, request: Request, count: int, plan: StepPlan, chosen: dict[int, Planned]) -> bool:
         """Reserve pages for ``count`` more tokens of a running request, preempting from the back if needed.

@@ -222,3 +222,26 @@ def test_tokens_from_equals_a_slice_of_the_joined_lists():
     # two requests with equal fields are still two requests
     twin = Request(1, [10, 11, 12, 13], SamplingParams(), output=[20, 21, 22])
     assert r != twin and [r, twin].index(twin) == 1
+
+
+def test_a_portion_that_does_not_finish_its_prompt_is_trimmed_to_whole_tile_rows():
+    """32 running requests decode (32 tokens), a 4,096-token prompt gets portions: 2,048 would make the step 2,080 tokens,
+    nine GEMM tile rows of 256; it gets 2,016 (eight rows), then 2,016 again, then its last 64."""
+    from oxr_inference_b200.engine.scheduler import Scheduler
+
+    s = Scheduler.__new__(Scheduler)
+    s.prefill_chunk, s.max_step_tokens = 2048, 2080
+
+    class R:
+        def __init__(self, pending):
+            self.pending = pending
+    assert s._portion(R(4096), 2080 - 32) == 2016
+    assert s._portion(R(2080), 2080 - 32) == 2016
+    assert s._portion(R(64), 2080 - 32) == 64              # a portion that finishes the prompt is never trimmed
+    assert s._portion(R(2048), 2080 - 32) == 2048
+    assert s._portion(R(4096), 2080) == 2048               # nothing else in the step: already whole rows
+    assert s._portion(R(4096), 300) == 300                 # small portions of a short step are left alone
+    assert s._portion(R(4096), 32) == 0                    # but a sliver after 2,048 tokens would open a ninth tile row
+    assert s._portion(R(20), 32) == 20                     # unless it finishes its prompt
+    s.prefill_chunk, s.max_step_tokens = 1000, 2048
+    assert s._portion(R(4096), 2048 - 40) == 1000 - (40 + 1000) % 256   # 1040 -> 1024 tokens in the step
