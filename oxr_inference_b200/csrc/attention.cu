@@ -437,16 +437,18 @@ struct TileGeometry {
         return r < rows_used && tok < tok_end && gh < G;
     }
 };
-// `tile`: index into the tile list (default: the block's x index).
-__device__ __forceinline__ TileGeometry tile_geometry(const AttnArgs& a, int rows, int tile = -1) {
+// `tile`: index into the tile list (default: the block's x index); `y`: (KV head, head group) index (default: the
+// block's y index).
+__device__ __forceinline__ TileGeometry tile_geometry(const AttnArgs& a, int rows, int tile = -1, int y = -1) {
     if (tile < 0) tile = blockIdx.x;
+    if (y < 0) y = blockIdx.y;
     TileGeometry g;
     g.G = a.H / a.KV;
     g.heads_per_tile = g.G < rows ? g.G : rows;
     const int tokens_per_tile = rows / g.heads_per_tile;
     const int head_groups = (g.G + g.heads_per_tile - 1) / g.heads_per_tile;
-    g.kvh = blockIdx.y / head_groups;
-    g.hg = blockIdx.y % head_groups;
+    g.kvh = y / head_groups;
+    g.hg = y % head_groups;
     g.req = a.tile_req[tile];
     g.tok0 = a.tile_tok0[tile];
     g.q_begin = a.cu_q[g.req];
@@ -579,21 +581,23 @@ constexpr size_t DECODE_SMEM = DECODE_STAGE_SMEM > DECODE_MERGE_SMEM ? DECODE_ST
 // The four warps of a block have each seen a quarter of the block's keys: their (O, m, l) per row stand in shared
 // memory `mo` [warp][row][MERGE_STRIDE]. Merge them in the order of the warps; with one piece per unit that is the
 // output, else it is this piece's partial result. Four d of one row per thread and pass.
-__device__ __forceinline__ void merge_warps(const float* mo, int rows_live, int splits, bf16* __restrict__ out, float* __restrict__ my_o,
-                                            float* __restrict__ my_ml, const TileGeometry& g, const AttnArgs& a) {
+// `mo` holds rows row0 .. row0 + nrows - 1 of the tile, `rows_stride` rows per warp.
+__device__ __forceinline__ void merge_warps(const float* mo, int nrows, int splits, bf16* __restrict__ out, float* __restrict__ my_o,
+                                            float* __restrict__ my_ml, const TileGeometry& g, const AttnArgs& a, int row0 = 0,
+                                            int rows_stride = DECODE_ROWS) {
     constexpr int DV = D / 4, MS = MERGE_STRIDE;
-    for (int idx = threadIdx.x; idx < rows_live * DV; idx += MMA_THREADS) {
-        const int r = idx / DV, d = (idx % DV) * 4;
+    for (int idx = threadIdx.x; idx < nrows * DV; idx += MMA_THREADS) {
+        const int r = row0 + idx / DV, d = (idx % DV) * 4;
         int tok, gh;
         if (!g.row(r, tok, gh)) continue;
         float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) M = fmaxf(M, mo[((size_t)w * DECODE_ROWS + r) * MS + D]);
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, mo[((size_t)w * rows_stride + r - row0) * MS + D]);
         float L = 0.f;
         float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
-            const float* src = mo + ((size_t)w * DECODE_ROWS + r) * MS;
+            const float* src = mo + ((size_t)w * rows_stride + r - row0) * MS;
             const float f = (src[D] == -INFINITY) ? 0.f : exp2f(src[D] - M);
             const float4 v = *reinterpret_cast<const float4*>(src + d);
             L += src[D + 1] * f;
@@ -989,6 +993,220 @@ attn_tma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
     const float* all_ml = part_ml + unit * splits * DECODE_ROWS * 2;
     const float* all_o = part_o + unit * splits * DECODE_ROWS * D;
     merge_pieces(out, all_ml, all_o, splits, rows_live, g, a);
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// The split-KV kernel for more pieces than blocks fit on the GPU at once: the grid is one round of blocks, and block b
+// walks over the pieces b, b + gridDim.x, ... (piece i = tile i / (Y S), KV-head group (i / S) % Y, split i % S). The
+// producer warp does not stop between pieces: while the consumer warps merge their quarters of one piece, draw its
+// ticket and perhaps merge a request's pieces, the ring already fills with the next piece's keys, so what a piece
+// costs beside its streaming (the wait for its first block, the merges) is hidden after the first piece. Because of
+// that the ring cannot lend its memory to the warps' merge, which has an area of its own and, to keep two blocks per
+// SM, takes the tile's rows in rounds of four.
+// ---------------------------------------------------------------------------------------------------------------------
+constexpr int WALK_ROWS = 4;                                         // rows per round of the warps' merge
+constexpr size_t WALK_MERGE_BYTES = (size_t)4 * WALK_ROWS * MERGE_STRIDE * sizeof(float);
+constexpr size_t WALK_SMEM = 1024 + TMA_DECODE_TILES + WALK_MERGE_BYTES + (size_t)DECODE_ROWS * LDS * sizeof(bf16) + 128;
+
+__device__ __forceinline__ bool consumer_any(bool v) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.u32 q, %1, 0;\n\t"
+        "bar.red.or.pred p, 1, 128, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(r) : "r"((uint32_t)v) : "memory");
+    return r != 0;
+}
+
+struct Piece {
+    TileGeometry g;
+    size_t unit;
+    int split, rows_live, k_end, k_lo, k_first, first, count;
+};
+__device__ __forceinline__ Piece piece_of(const AttnArgs& a, int item, int groups_y, int splits) {
+    Piece p;
+    p.split = item % splits;
+    const int y = (item / splits) % groups_y, tile = item / (splits * groups_y);
+    p.g = tile_geometry(a, DECODE_ROWS, tile, y);
+    p.unit = (size_t)tile * groups_y + y;
+    p.rows_live = p.g.tok0 < p.g.tok_end ? (p.g.tok_end - p.g.tok0) * p.g.heads_per_tile : 0;
+    p.k_end = p.g.pos0 + p.g.tok_end;
+    p.k_lo = a.window > 0 ? max(0, p.g.pos0 + p.g.tok0 - a.window + 1) : 0;
+    p.k_first = (p.k_lo / MMA_BN) * MMA_BN;
+    const int n_blocks = (p.k_end - p.k_first + MMA_BN - 1) / MMA_BN;
+    const int per = (n_blocks + splits - 1) / splits;
+    p.first = p.split * per;
+    p.count = p.rows_live > 0 ? max(0, min(per, n_blocks - p.first)) : 0;
+    return p;
+}
+
+__global__ void __launch_bounds__(TMA_THREADS)
+attn_tma_decode_walk_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters,
+                            const bf16* __restrict__ q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                            int pool_row0, int box_rows, int n_tiles, int groups_y, int splits, const AttnArgs a) {
+    extern __shared__ unsigned char smem_dyn[];
+    __shared__ int s_ticket;
+    __shared__ int s_gave_up;
+    unsigned char* stages = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+    float* mo = reinterpret_cast<float*>(stages + TMA_DECODE_TILES);        // [4 warps][WALK_ROWS][MERGE_STRIDE]
+    bf16* Qs = reinterpret_cast<bf16*>(stages + TMA_DECODE_TILES + WALK_MERGE_BYTES);
+    uint64_t* full = reinterpret_cast<uint64_t*>(stages + TMA_DECODE_TILES + WALK_MERGE_BYTES + (size_t)DECODE_ROWS * LDS * sizeof(bf16));
+    uint64_t* empty = full + TMA_STAGES;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int items = n_tiles * groups_y * splits;
+
+    if (threadIdx.x == 0) {
+        for (int s2 = 0; s2 < TMA_STAGES; ++s2) { mbar_init(full + s2, 1); mbar_init(empty + s2, 4); }
+        s_gave_up = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    if (warp == 4) {
+        // ---------------------------------------------------------------------- producer: piece after piece, one ring
+        const int boxes = MMA_BN / box_rows;
+        const int loads = boxes * 2 * PANELS;
+        uint32_t n = 0;          // blocks requested so far: stage n % TMA_STAGES, use n / TMA_STAGES of that stage
+        bool waited = false, ok = true;
+        for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
+            const Piece p = piece_of(a, item, groups_y, splits);
+            const int* table_row = a.block_table + (size_t)p.g.req * a.table_width;
+            for (int b = 0; b < p.count; ++b, ++n) {
+                const int st = n % TMA_STAGES;
+                if (!mbar_wait(empty + st, ((n / TMA_STAGES) & 1) ^ 1)) {
+                    if (lane == 0) { atomicExch(&s_gave_up, 1); oxr_report(a.status, OXR_WAIT_EXPIRED, 20); }
+                    ok = false;
+                    break;
+                }
+                const int k0 = p.k_first + (p.first + b) * MMA_BN;
+                if (!waited && k0 + MMA_BN > p.g.pos0) {   // old keys are fetched while the kernel before this one may still run
+                    pdl_wait();
+                    waited = true;
+                }
+                unsigned char* dst = stages + (size_t)st * KV_STAGE_BYTES;
+                int my_bytes = 0;
+                for (int i = lane; i < loads; i += 32) {
+                    const int kp = piece_to_fetch(k0 + (i / (2 * PANELS)) * box_rows, box_rows, p.k_lo, p.k_end);
+                    const int page = table_row[a.page_shift >= 0 ? (kp >> a.page_shift) : (kp / a.page_size)];
+                    if (page >= 0 && page < a.num_pages) my_bytes += box_rows * 128;
+                    else oxr_report(a.status, OXR_BAD_PAGE, p.g.req);
+                }
+                const int total = __reduce_add_sync(0xffffffffu, my_bytes);
+                if (lane == 0) {
+                    if (total > 0) mbar_expect_tx(full + st, (uint32_t)total);
+                    else mbar_arrive(full + st);
+                }
+                __syncwarp();
+                for (int i = lane; i < loads; i += 32) {
+                    const int box = i / (2 * PANELS), which = i % (2 * PANELS);
+                    const int kp = piece_to_fetch(k0 + box * box_rows, box_rows, p.k_lo, p.k_end);
+                    const int page = table_row[a.page_shift >= 0 ? (kp >> a.page_shift) : (kp / a.page_size)];
+                    if (page >= 0 && page < a.num_pages) {
+                        const int panel = which % PANELS;
+                        const int row = pool_row0 + page * a.page_size + (a.page_shift >= 0 ? (kp & (a.page_size - 1)) : (kp % a.page_size));
+                        unsigned char* d2 = dst + (size_t)which * PANEL_BYTES + (size_t)box * box_rows * 128;
+                        tma_load_2d(d2, which < PANELS ? &map_k : &map_v, p.g.kvh * D + panel * 64, row, full + st);
+                    }
+                }
+            }
+        }
+        pdl_trigger();
+        return;
+    }
+
+    // -------------------------------------------------------------------------- consumers (warps 0..3)
+    pdl_wait();   // q comes from the kernel before this one
+    const float scale_log2 = a.scale * LOG2E;
+    constexpr int MS = MERGE_STRIDE;
+    uint32_t n = 0;
+    for (int item = blockIdx.x; item < items; item += gridDim.x) {
+        // the barrier frees Qs, the merge area and s_ticket of the piece before; all warps leave together once a wait
+        // has run out anywhere in the block
+        if (consumer_any(*reinterpret_cast<volatile int*>(&s_gave_up) != 0)) return;
+        const Piece p = piece_of(a, item, groups_y, splits);
+        if (p.rows_live == 0) continue;   // every piece of this unit passes here: no tickets are drawn
+        const TileGeometry& g = p.g;
+        float* my_ml = part_ml + (p.unit * splits + p.split) * DECODE_ROWS * 2;
+        float* my_o = part_o + (p.unit * splits + p.split) * DECODE_ROWS * D;
+        if (p.count > 0) {
+            load_q_rows(Qs, q, a, g, DECODE_ROWS);
+            cp_async_commit();
+            int row_pos[2];
+            bool row_ok[2];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                int tok, gh;
+                row_ok[r] = g.row((lane >> 2) + 8 * r, tok, gh);
+                row_pos[r] = g.pos0 + tok;
+            }
+            float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+            float o[DT8][4];
+#pragma unroll
+            for (int i = 0; i < DT8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+            uint32_t qf[Q_IN_REGS ? KSTEPS : 1][4];
+            const int tile_first_pos = g.pos0 + g.tok0, tile_last_pos = g.pos0 + g.tok_end - 1;
+            cp_async_wait<0>();
+            consumer_sync();
+            if constexpr (Q_IN_REGS) {
+#pragma unroll
+                for (int kk = 0; kk < KSTEPS; ++kk)
+                    ldsm_x4(qf[kk], Qs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + kk * 16 + 8 * (lane >> 4));
+            }
+            for (int b = 0; b < p.count; ++b, ++n) {
+                const int st = n % TMA_STAGES;
+                if (!mbar_wait(full + st, (n / TMA_STAGES) & 1)) {
+                    if (lane == 0) { atomicExch(&s_gave_up, 1); oxr_report(a.status, OXR_WAIT_EXPIRED, 21); }
+                    break;
+                }
+                const bf16* Kst = reinterpret_cast<const bf16*>(stages + (size_t)st * KV_STAGE_BYTES);
+                const bf16* Vst = Kst + PANELS * (PANEL_BYTES / 2);
+                const int key0 = p.k_first + (p.first + b) * MMA_BN + warp * 16;
+                const bool full_block = key0 + 15 <= tile_first_pos && key0 >= p.k_lo && (a.window <= 0 || key0 > tile_last_pos - a.window);
+                warp_block<16, true>(qf, Qs, Kst + warp * 16 * 64, Vst + warp * 16 * 64, key0, row_pos, row_ok, a.window, full_block,
+                                     scale_log2, m, l, o);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty + st);
+            }
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+                l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+            }
+            // the four warps' quarters meet in the merge area, WALK_ROWS rows of the tile per round
+            for (int r0 = 0; r0 < p.rows_live; r0 += WALK_ROWS) {
+                if (r0 > 0) consumer_sync();   // the round before is read
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    const int row = (lane >> 2) + 8 * r;
+                    if (row >= r0 && row < r0 + WALK_ROWS) {
+                        float* dst = mo + ((size_t)warp * WALK_ROWS + row - r0) * MS;
+#pragma unroll
+                        for (int i = 0; i < DT8; ++i) {
+                            dst[i * 8 + 2 * (lane & 3)] = o[i][2 * r];
+                            dst[i * 8 + 2 * (lane & 3) + 1] = o[i][2 * r + 1];
+                        }
+                        if ((lane & 3) == 0) { dst[D] = m[r]; dst[D + 1] = l[r]; }
+                    }
+                }
+                consumer_sync();
+                merge_warps(mo, min(WALK_ROWS, p.rows_live - r0), splits, out, my_o, my_ml, g, a, r0, WALK_ROWS);
+            }
+        } else if (splits > 1) {   // nothing for this piece: an empty partial
+            for (int i = threadIdx.x; i < p.rows_live; i += MMA_THREADS) { my_ml[2 * i] = -INFINITY; my_ml[2 * i + 1] = 0.f; }
+        }
+        if (splits == 1) continue;
+        // ---- ticket: the last piece of a unit to finish merges them all
+        __threadfence();
+        consumer_sync();
+        if (threadIdx.x == 0) s_ticket = atomicAdd(&counters[p.unit], 1);
+        consumer_sync();
+        if (s_ticket == splits - 1) {
+            __threadfence();
+            if (threadIdx.x == 0) counters[p.unit] = 0;
+            merge_pieces(out, part_ml + p.unit * splits * DECODE_ROWS * 2, part_o + p.unit * splits * DECODE_ROWS * D, splits, p.rows_live, g, a);
+        }
+    }
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -1432,6 +1650,25 @@ OXR_API int oxr_paged_attention_bf16(void* out, const void* q, const void* k_cac
             }
             const CUtensorMap* maps = reinterpret_cast<const CUtensorMap*>(kv_maps);
             const int box_rows = page_size < MMA_BN ? page_size : MMA_BN;
+            const long long pieces = (long long)n_short * KV * groups * splits;
+            if (pieces > 0x7fffffffLL) return OXR_BAD_ARGUMENT;
+            static int slots = 0;   // blocks of this kernel that the GPU holds at once
+            if (slots == 0) {
+                cudaError_t e = cudaFuncSetAttribute(attn_tma_decode_walk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WALK_SMEM);
+                if (e != cudaSuccess) return 1000 + (int)e;
+                int dev = 0, sms = 0, per_sm = 0;
+                if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+                    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_tma_decode_walk_kernel, TMA_THREADS, WALK_SMEM) != cudaSuccess ||
+                    sms <= 0 || per_sm <= 0)
+                    return OXR_BAD_ARGUMENT;
+                slots = sms * per_sm;
+            }
+            if (pieces > slots) {
+                // more pieces than fit at once: one round of blocks that walk over them
+                oxr_launch(attn_tma_decode_walk_kernel, dim3(slots), dim3(TMA_THREADS), WALK_SMEM, stream, true,
+                    (bf16*)out, part_o, part_ml, counters, (const bf16*)q, maps[0], maps[1], pool_row0, box_rows, n_short, KV * groups, splits, a);
+                return oxr_launch_status();
+            }
             oxr_launch(attn_tma_decode_kernel, dim3(n_short, KV * groups, splits), dim3(TMA_THREADS), TMA_DECODE_SMEM, stream, true,
                 (bf16*)out, part_o, part_ml, counters, (const bf16*)q, maps[0], maps[1], pool_row0, box_rows, a);
             return oxr_launch_status();
