@@ -206,6 +206,118 @@ __global__ void qk_norm_rope_store_bf16x2_kernel(
     }
 }
 
+// bf16 with head size 16 * LPH (64, 128, 256) for steps of many tokens: LPH lanes share a head, lane j of them holds
+// elements 8j .. 8j+7 of the head's first half and their rotation partners in the second half, one 16-byte word each,
+// so that a warp reads and writes whole 32-byte sectors with two loads and two stores per lane and head; the sum of
+// squares goes over the LPH lanes by shuffles. A warp takes WIDE_PASSES * 32 / LPH consecutive heads of a token and
+// issues the loads of all of them before it works on any.
+constexpr int WIDE_PASSES = 2;
+template <int LPH>
+__global__ void qk_norm_rope_store_bf16x8_kernel(
+    __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
+    const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ q_weight, const float* __restrict__ k_weight,
+    const float* __restrict__ cos_table, const float* __restrict__ sin_table, const int* __restrict__ positions,
+    const int* __restrict__ slots, int n_tokens, int H, int KV, float eps, int max_positions, long long num_slots,
+    int norm_q, int norm_k, int rotate, int* status) {
+    constexpr int D = 16 * LPH, HPW = 32 / LPH, half = D / 2;
+    if (gridDim.x <= 296) pdl_trigger();
+    pdl_wait();
+    const int warps_per_block = blockDim.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const long long unit = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+    const int heads = H + 2 * KV;
+    const int groups = (heads + WIDE_PASSES * HPW - 1) / (WIDE_PASSES * HPW);
+    if (unit >= (long long)n_tokens * groups) return;
+    const int t = (int)(unit / groups), head0 = (int)(unit % groups) * WIDE_PASSES * HPW + lane / LPH, j = lane % LPH;
+    const long long slot = slots[t];
+    if (slot >= num_slots && lane == 0) oxr_report(status, OXR_BAD_SLOT, t);
+    const bool can_store = slot >= 0 && slot < num_slots;
+    int pos = 0;
+    if (rotate) {
+        pos = positions[t];
+        if (pos < 0 || pos >= max_positions) {
+            if (lane == 0) oxr_report(status, OXR_BAD_POSITION, t);
+            pos = 0;
+        }
+    }
+    uint4 a[WIDE_PASSES], b[WIDE_PASSES];
+#pragma unroll
+    for (int p = 0; p < WIDE_PASSES; ++p) {
+        const int head = head0 + p * HPW;
+        a[p] = b[p] = make_uint4(0, 0, 0, 0);
+        if (head < heads) {
+            const __nv_bfloat16* src = qkv + ((size_t)t * heads + head) * D + 8 * j;
+            a[p] = *reinterpret_cast<const uint4*>(src);
+            b[p] = *reinterpret_cast<const uint4*>(src + half);
+        }
+    }
+    float c[8], sn[8];
+    if (rotate) {
+        const float* cp = cos_table + (size_t)pos * half + 8 * j;
+        const float* sp = sin_table + (size_t)pos * half + 8 * j;
+        const float4 ca = *reinterpret_cast<const float4*>(cp), cb = *reinterpret_cast<const float4*>(cp + 4);
+        const float4 sa = *reinterpret_cast<const float4*>(sp), sb = *reinterpret_cast<const float4*>(sp + 4);
+        c[0] = ca.x; c[1] = ca.y; c[2] = ca.z; c[3] = ca.w; c[4] = cb.x; c[5] = cb.y; c[6] = cb.z; c[7] = cb.w;
+        sn[0] = sa.x; sn[1] = sa.y; sn[2] = sa.z; sn[3] = sa.w; sn[4] = sb.x; sn[5] = sb.y; sn[6] = sb.z; sn[7] = sb.w;
+    }
+#pragma unroll
+    for (int p = 0; p < WIDE_PASSES; ++p) {
+        const int head = head0 + p * HPW;
+        const bool live = head < heads, is_q = head < H, is_v = head >= H + KV;
+        float x1[8], x2[8];
+        const __nv_bfloat162* ap = reinterpret_cast<const __nv_bfloat162*>(&a[p]);
+        const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&b[p]);
+        float ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f1 = __bfloat1622float2(ap[e]), f2 = __bfloat1622float2(bp[e]);
+            x1[2 * e] = f1.x; x1[2 * e + 1] = f1.y; x2[2 * e] = f2.x; x2[2 * e + 1] = f2.y;
+            ss += f1.x * f1.x + f1.y * f1.y + f2.x * f2.x + f2.y * f2.y;
+        }
+#pragma unroll
+        for (int o = 1; o < LPH; o <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);   // every lane takes part
+        if (!live) continue;
+        if (is_v) {
+            if (can_store) {
+                __nv_bfloat16* dst = v_cache + ((size_t)slot * KV + (head - H - KV)) * D + 8 * j;
+                *reinterpret_cast<uint4*>(dst) = a[p];
+                *reinterpret_cast<uint4*>(dst + half) = b[p];
+            }
+            continue;
+        }
+        if (!is_q && !can_store) continue;
+        if (is_q ? norm_q : norm_k) {
+            const float* w = (is_q ? q_weight : k_weight) + 8 * j;
+            const float inv = rsqrtf(ss / (float)D + eps);
+            const float4 w1a = *reinterpret_cast<const float4*>(w), w1b = *reinterpret_cast<const float4*>(w + 4);
+            const float4 w2a = *reinterpret_cast<const float4*>(w + half), w2b = *reinterpret_cast<const float4*>(w + half + 4);
+            const float w1[8] = {w1a.x, w1a.y, w1a.z, w1a.w, w1b.x, w1b.y, w1b.z, w1b.w};
+            const float w2[8] = {w2a.x, w2a.y, w2a.z, w2a.w, w2b.x, w2b.y, w2b.z, w2b.w};
+#pragma unroll
+            for (int e = 0; e < 8; ++e) { x1[e] = x1[e] * inv * w1[e]; x2[e] = x2[e] * inv * w2[e]; }
+        }
+        if (rotate) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float r1 = x1[e] * c[e] - x2[e] * sn[e], r2 = x1[e] * sn[e] + x2[e] * c[e];
+                x1[e] = r1;
+                x2[e] = r2;
+            }
+        }
+        uint4 o1, o2;
+        __nv_bfloat162* p1 = reinterpret_cast<__nv_bfloat162*>(&o1);
+        __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&o2);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            p1[e] = __floats2bfloat162_rn(x1[2 * e], x1[2 * e + 1]);
+            p2[e] = __floats2bfloat162_rn(x2[2 * e], x2[2 * e + 1]);
+        }
+        __nv_bfloat16* dst = (is_q ? q_out + ((size_t)t * H + head) * D : k_cache + ((size_t)slot * KV + (head - H)) * D) + 8 * j;
+        *reinterpret_cast<uint4*>(dst) = o1;
+        *reinterpret_cast<uint4*>(dst + half) = o2;
+    }
+}
+
 // dtype: 0 = float32, 1 = bfloat16 (qkv, q_out and the cache). head_dim: even, at most 512.
 // k_cache / v_cache: one layer's pool viewed as [num_slots, KV, D]. slots[t] < 0 skips the store.
 OXR_API int oxr_qk_norm_rope_store(void* q_out, void* k_cache, void* v_cache, const void* qkv, const float* q_weight,
@@ -222,6 +334,23 @@ OXR_API int oxr_qk_norm_rope_store(void* q_out, void* k_cache, void* v_cache, co
         (uintptr_t)v_cache % 16 == 0 && (q_weight == nullptr || (uintptr_t)q_weight % 8 == 0) &&
         (k_weight == nullptr || (uintptr_t)k_weight % 8 == 0) && (cos_table == nullptr || ((uintptr_t)cos_table % 8 == 0 && (uintptr_t)sin_table % 8 == 0))) {
         typedef __nv_bfloat16 B;
+        const bool wide_ok = (D == 64 || D == 128 || D == 256) && n_tokens >= 64 && (q_weight == nullptr || (uintptr_t)q_weight % 16 == 0) &&
+                             (k_weight == nullptr || (uintptr_t)k_weight % 16 == 0) &&
+                             (cos_table == nullptr || ((uintptr_t)cos_table % 16 == 0 && (uintptr_t)sin_table % 16 == 0));
+        if (wide_ok) {   // steps of many tokens: 16-byte accesses, D / 16 lanes per head
+            const int hpw = WIDE_PASSES * 32 / (D / 16);
+            const long long wunits = (long long)n_tokens * ((H + 2 * KV + hpw - 1) / hpw);
+            const unsigned wblocks = (unsigned)((wunits + warps - 1) / warps);
+#define LAUNCH_W(L)                                                                                                     \
+            oxr_launch(qk_norm_rope_store_bf16x8_kernel<L>, dim3(wblocks), dim3(warps * 32), 0, stream, true,             \
+                (B*)q_out, (B*)k_cache, (B*)v_cache, (const B*)qkv, q_weight, k_weight, cos_table, sin_table, positions, slots, n_tokens, \
+                H, KV, eps, max_positions, num_slots, norm_q, norm_k, rotate, status)
+            if (D == 64) LAUNCH_W(4);
+            else if (D == 128) LAUNCH_W(8);
+            else LAUNCH_W(16);
+#undef LAUNCH_W
+            return oxr_launch_status();
+        }
         const int steps = (D / 2 + 63) / 64;   // 1..4
         constexpr int HPW = 4;                  // heads per warp
         const long long vunits = (long long)n_tokens * ((H + 2 * KV + HPW - 1) / HPW);

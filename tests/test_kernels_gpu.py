@@ -144,10 +144,12 @@ def test_gated_tcgen05_gemm_applies_silu_in_its_epilogue(ops, monkeypatch, M, pa
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,KV,D", [(4, 2, 16), (6, 2, 32), (5, 5, 48), (32, 8, 128), (3, 1, 256)])
-def test_qk_norm_rope_store(ops, dtype, H, KV, D):
+@pytest.mark.parametrize("H,KV,D,n", [(4, 2, 16, 23), (6, 2, 32, 23), (5, 5, 48, 23), (32, 8, 128, 23), (3, 1, 256, 23),
+                                      # many tokens: the kernel with 16-byte accesses (bf16, head sizes 64, 128, 256)
+                                      (5, 3, 64, 150), (32, 8, 128, 300), (3, 1, 256, 77), (7, 1, 128, 64)])
+def test_qk_norm_rope_store(ops, dtype, H, KV, D, n):
     g = torch.Generator(device=DEV).manual_seed(3)
-    n, pages, P, maxpos, eps = 23, 7, 8, 300, 1e-5
+    pages, P, maxpos, eps = 50, 8, 300, 1e-5
     qkv = torch.randn(n, (H + 2 * KV) * D, device=DEV, generator=g).to(dtype)
     qw = 1 + 0.2 * torch.randn(D, device=DEV, generator=g)
     kw = 1 + 0.2 * torch.randn(D, device=DEV, generator=g)
