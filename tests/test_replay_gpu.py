@@ -131,3 +131,83 @@ def test_mixed_requests_with_pages_used_again(replay):
             live.remove(k)
         step_no += 1
         assert step_no < 2000
+
+
+def _qwen3(h, inter, layers, heads, kv, d, vocab, eps=1e-6, theta=1e4, tie=False, window=None, types=None):
+    c = {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "hidden_size": h, "intermediate_size": inter,
+         "num_hidden_layers": layers, "num_attention_heads": heads, "num_key_value_heads": kv, "rms_norm_eps": eps,
+         "rope_theta": theta, "vocab_size": vocab, "tie_word_embeddings": tie, "max_position_embeddings": 512,
+         "eos_token_id": vocab - 1}
+    if d is not None:
+        c["head_dim"] = d
+    if window:
+        c.update(use_sliding_window=True, sliding_window=window, layer_types=types)
+    return c
+
+
+# Sizes that the two tiny configurations do not reach: a width and an intermediate size that are no multiple of 8
+# (66: not even of 4), head sizes 48, 80, 96 and 112, one head, as many groups as heads, a window of 17 on the first layer.
+ODD_SIZES = {
+    "width100": _qwen3(100, 100, 2, 7, 1, 16, 1001),
+    "width66": _qwen3(66, 36, 2, 11, 11, 16, 97),
+    "head48": _qwen3(80, 72, 1, 5, 5, 48, 1000),
+    "head80": _qwen3(136, 200, 4, 3, 1, 80, 333, eps=1e-5, theta=5e5, tie=True),
+    "head96_window": _qwen3(192, 264, 2, 2, 2, 96, 777, window=17, types=["sliding_attention", "full_attention"]),
+    "head112": _qwen3(224, 96, 1, 2, 1, 112, 50, eps=1e-3),
+    "one_head256": _qwen3(64, 48, 1, 1, 1, 256, 64),
+}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(ODD_SIZES))
+def test_random_trace_at_odd_sizes(name, dtype, tmp_path):
+    """A seeded random trace (up to four live requests, random portions and sit-outs, random wanted places, some
+    requests dropped before their end, 448 tokens of cache) on a configuration of odd sizes."""
+    import random
+
+    rng = random.Random(len(name) * 131 + len(dtype))
+    util.CONFIGS[name] = ODD_SIZES[name]
+    try:
+        folder = make_folder(tmp_path, name, seed=7)
+    finally:
+        del util.CONFIGS[name]
+    vocab = ODD_SIZES[name]["vocab_size"]
+    r = Replay(folder, dtype, tmp_path / "out", max_tokens=448, page_size=rng.choice([8, 16, 64]))
+    lengths = [rng.choice([1, 2, 3, 15, 16, 17, 33, 64, 65, 100, 129, rng.randint(1, 190)]) for _ in range(8)]
+    seqs = {f"q{i}": [rng.randrange(vocab) for _ in range(n)] for i, n in enumerate(lengths)}
+    want = {k: plain_logits(folder, v) for k, v in seqs.items()}
+    stop_at = {k: (len(v) if rng.random() < 0.8 else rng.randint(1, len(v))) for k, v in seqs.items()}
+    pos = {k: 0 for k in seqs}
+    waiting, live, step_no = list(seqs), [], 0
+
+    def held(k):
+        return -(-len(seqs[k]) // 64) * 64
+
+    while waiting or live:
+        while waiting and len(live) < 4 and sum(held(k) for k in live) + held(waiting[0]) <= 448:
+            live.append(waiting.pop(0))
+        entries, checks, ended = [], {}, []
+        for k in live:
+            if rng.random() < 0.2:
+                continue
+            left = stop_at[k] - pos[k]
+            c = min(left, rng.choice([1, 1, 1, 1, 2, 2, 3, 5, 8, 15, 16, 17, 31, 33, 64]))
+            wanted = sorted(rng.sample(range(c), rng.randint(0, min(c, 3))))
+            entries.append({"id": k, "tokens": seqs[k][pos[k]:pos[k] + c], "want": wanted})
+            checks[k] = [pos[k] + w for w in wanted]
+            pos[k] += c
+            if c == left:
+                ended.append(k)
+        if entries:
+            rng.shuffle(entries)
+            got = r.step(entries, end=ended)
+            row = 0
+            for e in entries:
+                for p in checks[e["id"]]:
+                    compare(got[row:row + 1], want[e["id"]][p:p + 1], dtype, f"{name} step {step_no}: request {e['id']} position {p}")
+                    row += 1
+        for k in ended:
+            live.remove(k)
+        step_no += 1
+        assert step_no < 5000
+    assert r.close() == 0
