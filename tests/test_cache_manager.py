@@ -2,7 +2,6 @@
 
 import random
 
-import numpy as np
 import pytest
 
 from oxr_inference_b200.cache import RELEASED, CacheManager, PagePool, make_cache_plan, pages_for
