@@ -122,10 +122,6 @@ class CacheManager:
         w = self.windows[group]
         return 0 if w <= 0 else max(0, start - w + 1) // self.page_size
 
-    def pages_needed(self, rc: RequestCache, new_length: int) -> list[int]:
-        """Per group, pages to add so that positions [rc.length, new_length) can be written."""
-        return [max(0, pages_for(new_length, self.page_size) - len(table)) for table in rc.tables]
-
     def reserve(self, rc: RequestCache, new_length: int) -> bool:
         """Make room for the tokens at positions [rc.length, new_length). False, with nothing taken, if any
         group lacks the pages."""

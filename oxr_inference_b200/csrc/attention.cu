@@ -1568,9 +1568,17 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
 }  // namespace
 
 OXR_API int oxr_attn_head_dim() { return D; }
-OXR_API int oxr_attn_tile_rows() { return BM; }
-OXR_API int oxr_attn_prefill_rows() { return PREFILL_ROWS; }
-OXR_API int oxr_attn_decode_rows() { return DECODE_ROWS; }
+// Rows of a tile for each kind of tile list that the host builds: 0 generic, 1 decode, 2 prefill (mma.sync), 3 prefill
+// (tcgen05). The host keeps the same numbers and compares them when it loads the library.
+OXR_API int oxr_attn_tile_rows(int kind) {
+    switch (kind) {
+        case 0: return BM;
+        case 1: return DECODE_ROWS;
+        case 2: return PREFILL_ROWS;
+        case 3: return BIG_ROWS;
+        default: return -1;
+    }
+}
 
 // bfloat16 on the tensor cores. Two tile lists made by the host: `short` tiles (16 rows each; decoded tokens and
 // portions of a few tokens) go to the split-KV kernel, `long` tiles (64 rows each) to the prefill kernel. With

@@ -111,12 +111,6 @@ class BatchBuilder:
                 for spec in self.tile_specs}
         return Layout(tokens, len(entries), rows, widths, caps)
 
-    def decode_layout(self, bucket: int, max_positions: int) -> Layout:
-        """Fixed layout of a decode-only step of ``bucket`` rows with the widest possible block tables."""
-        m = self.manager
-        width = (max_positions + m.page_size - 1) // m.page_size
-        return Layout(bucket, bucket, bucket, [width] * len(m.pools), self.decode_tile_caps(bucket))
-
     def decode_tile_caps(self, bucket: int) -> dict[tuple[int, int, int], int]:
         """Single-token requests make one tile each in every list that covers them, none in the others."""
         return {spec: (bucket if spec[1] <= 1 else 0) for spec in self.tile_specs}

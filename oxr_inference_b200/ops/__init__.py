@@ -127,10 +127,15 @@ def _attn_lib(head_dim: int):
         lib.oxr_attn_make_kv_maps.argtypes = [p, p, p, ctypes.c_ulonglong, i, i]
         lib.oxr_attn_make_kv_maps.restype = c_int
         lib.oxr_paged_attention_bf16.restype = c_int
+        lib.oxr_attn_tile_rows.argtypes = [i]
         lib.oxr_attn_tile_rows.restype = c_int
         lib.oxr_attn_head_dim.restype = c_int
         if lib.oxr_attn_head_dim() != head_dim:
             raise BuildError(f"attention library for head size {head_dim} reports {lib.oxr_attn_head_dim()}")
+        rows = tuple(lib.oxr_attn_tile_rows(kind) for kind in range(4))
+        if rows != (GENERIC_ROWS, DECODE_ROWS, PREFILL_ROWS, PREFILL_ROWS_TMA):
+            raise BuildError(f"attention library tiles have {rows} rows; the host builds its tile lists for "
+                             f"{(GENERIC_ROWS, DECODE_ROWS, PREFILL_ROWS, PREFILL_ROWS_TMA)}")
         lib.oxr_set_chain.argtypes = [c_int]
         lib.oxr_set_chain.restype = None
         lib.oxr_set_chain(int(CHAIN_KERNELS))

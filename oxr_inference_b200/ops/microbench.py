@@ -6,6 +6,7 @@ command to put under ``ncu``.
     python -m oxr_inference_b200.ops.microbench attention --batch 8 --q-len 1 --context 2048
     python -m oxr_inference_b200.ops.microbench attention --batch 1 --q-len 2048 --context 2048
     python -m oxr_inference_b200.ops.microbench norm --rows 8 --hidden 4096
+    python -m oxr_inference_b200.ops.microbench rope --tokens 2048
 """
 
 from __future__ import annotations
@@ -110,6 +111,28 @@ def norm(args) -> dict:
             "GB/s": round(rows * hidden * (2 + 4 + 4 + 2) / us / 1e3, 1)}
 
 
+def rope(args) -> dict:
+    """q/k head norm + rotation + store of K and V into a layer's pages, for ``tokens`` new tokens."""
+    H, KV, D, P, T = args.heads, args.kv_heads, args.head_dim, args.page_size, args.tokens
+    width = (H + 2 * KV) * D
+    copies = max(2, int(300e6 // (T * width * 4)) + 1) if T * width * 4 > 1e6 else 4
+    qkvs = [torch.randn(T, width, device="cuda").bfloat16() for _ in range(copies)]
+    qw, kw = torch.ones(D, device="cuda"), torch.ones(D, device="cuda")
+    angles = torch.outer(torch.arange(max(T, 4096), dtype=torch.float), 1.0 / (1e6 ** (torch.arange(0, D, 2, dtype=torch.float) / D)))
+    cos, sin = angles.cos().cuda(), angles.sin().cuda()
+    pos = torch.arange(T, dtype=torch.int32, device="cuda")
+    pages = -(-T // P)
+    slots = (torch.randperm(pages, device="cuda").int().repeat_interleave(P)[:T] * P + pos % P).int()
+    pools = [(torch.zeros(pages, P, KV, D, device="cuda", dtype=torch.bfloat16), torch.zeros(pages, P, KV, D, device="cuda", dtype=torch.bfloat16))
+             for _ in range(copies)]
+    status = ops.new_status("cuda")
+    us = _time(lambda i: ops.qk_norm_rope_store(qkvs[i % copies], qw, kw, cos, sin, pos, slots, pools[i % copies][0], pools[i % copies][1],
+                                                H, KV, D, 1e-6, status), args.reps)
+    ops.check_status(status)
+    return {"kernel": "qk_norm_rope_store", "tokens": T, "heads": H, "kv_heads": KV, "head_dim": D, "us": round(us, 2),
+            "GB/s": round(T * width * 2 * 2 / us / 1e3, 1)}
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="what", required=True)
@@ -134,7 +157,14 @@ def main() -> None:
     n.add_argument("--rows", type=int, default=8)
     n.add_argument("--hidden", type=int, default=4096)
     n.set_defaults(run=norm)
-    for p in (g, a, n):
+    r = sub.add_parser("rope")
+    r.add_argument("--tokens", type=int, default=2048)
+    r.add_argument("--heads", type=int, default=32)
+    r.add_argument("--kv-heads", type=int, default=8)
+    r.add_argument("--head-dim", type=int, default=128)
+    r.add_argument("--page-size", type=int, default=16)
+    r.set_defaults(run=rope)
+    for p in (g, a, n, r):
         p.add_argument("--reps", type=int, default=20)
     args = ap.parse_args()
     torch.backends.cuda.matmul.allow_tf32 = False
