@@ -15,8 +15,8 @@
 // the way in and masked on the way out. Every wait on an mbarrier is bounded: if one runs out, the block records
 // OXR_WAIT_EXPIRED in the status word, stops waiting, frees its tensor memory and returns.
 //
-// Few rows (a decode batch of tens of requests) and a narrow W give few tiles, fewer than SMs, while the product is
-// bound by streaming W. The SPLIT variant therefore deals the k steps of a tile out to `splits` shares and
+// A few hundred rows and a narrow W give few tiles, fewer than SMs, while the product is still bound by streaming W
+// (fewer rows than that take the few-rows kernel of gemm_tcgen05_few_rows.cu). The SPLIT variant therefore deals the k steps of a tile out to `splits` shares and
 // makes (tile, share) the unit of work, so that every SM streams a part of W. A unit writes its fp32 partial tile to
 // a workspace and takes a ticket of its tile; the unit that draws the last ticket adds the partial tiles in the order
 // of the shares (so the sum does not depend on who came last), rounds and stores. Nothing waits for another block.
@@ -53,22 +53,19 @@ __device__ __forceinline__ void tile_origin(int tile, int M, int N, int bn, int&
     n0 = (within / group_rows) * bn;
 }
 
-// TRANS: the caller wants the transpose of what the kernel computes: C is [N, M] in memory, element (row, col) of the
-// tile goes to C[col][row]. That is how a product of FEW rows runs with W as the operand of 128 rows per tile and
-// the few rows as the tile's width (no shared memory spent on padding rows): the caller passes W as X and X as W.
-// GATED (never with SPLIT or TRANS): W's rows alternate in groups of 8 between a gate and an up projection, and the epilogue
+// GATED (never with SPLIT): W's rows alternate in groups of 8 between a gate and an up projection, and the epilogue
 // writes silu(gate) * up into C [M, N / 2] instead of the product itself.
 // Persistent: block b computes units b, b + gridDim.x, ... The accumulator is double-buffered in tensor memory
 // (two buffers `acc_stride` columns apart), so the epilogue warps drain one unit while the MMA warp already
 // accumulates the next. Without SPLIT a unit is a tile. With SPLIT it is (tile, share): unit u is share u % splits
 // of tile u / splits, and share r takes the 64-wide k steps r, r + splits, ...: the shares of a tile run side by
 // side, read neighbouring 128-byte pieces of W's rows, and finish together.
-template <typename TO, bool SPLIT, bool GATED, bool TRANS>
+template <typename TO, bool SPLIT, bool GATED>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tcgen05_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     int M, int N, int K, int bn, int stages, int tmem_cols, int num_tiles, int splits, float* __restrict__ partial,
                     unsigned int* __restrict__ tickets, int* status) {
-    static_assert(!(GATED && (SPLIT || TRANS)), "the gated epilogue is the plain one's variant only");
+    static_assert(!(GATED && SPLIT), "the gated epilogue is the plain one's variant only");
     extern __shared__ unsigned char smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);   // swizzle atoms are 1024 B
     const int stage_size = stage_bytes(bn);
@@ -110,7 +107,7 @@ gemm_tcgen05_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap map_
             bool ok = true;
             // No kernel writes the weights, so their tiles of the first ring of stages are requested before this kernel
             // (when it is launched dependent on the one before) waits for that one to finish; the activations' tiles
-            // of the same stages follow after the wait. With TRANS the weights are the operand behind map_x.
+            // of the same stages follow after the wait.
             int early = 0;
             for (int unit = blockIdx.x; unit < num_units && early < stages; unit += gridDim.x) {
                 const int tile = SPLIT ? unit / splits : unit;
@@ -119,8 +116,7 @@ gemm_tcgen05_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap map_
                 for (int kb = SPLIT ? unit % splits : 0; kb < num_kb && early < stages; kb += kb_step, ++early) {
                     unsigned char* a_dst = tiles + (size_t)early * stage_size;
                     mbar_expect_tx(full + early, (uint32_t)stage_size);
-                    if constexpr (TRANS) tma_load_2d(a_dst, &map_x, kb * BK, m0, full + early);
-                    else tma_load_2d(a_dst + A_BYTES, &map_w, kb * BK, n0, full + early);
+                    tma_load_2d(a_dst + A_BYTES, &map_w, kb * BK, n0, full + early);
                 }
             }
             pdl_wait();
@@ -132,8 +128,7 @@ gemm_tcgen05_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap map_
                 for (int kb = SPLIT ? unit % splits : 0; kb < num_kb; kb += kb_step, ++step) {
                     unsigned char* a_dst = tiles + (size_t)s * stage_size;
                     if (step < early) {   // first ring: the stage is free and armed, its weight tile is on its way
-                        if constexpr (TRANS) tma_load_2d(a_dst + A_BYTES, &map_w, kb * BK, n0, full + s);
-                        else tma_load_2d(a_dst, &map_x, kb * BK, m0, full + s);
+                        tma_load_2d(a_dst, &map_x, kb * BK, m0, full + s);
                     } else {
                         if (!mbar_wait(empty + s, phase ^ 1)) { atomicExch(gave_up, 1u); oxr_report(status, OXR_WAIT_EXPIRED, 0); ok = false; break; }
                         mbar_expect_tx(full + s, (uint32_t)stage_size);
@@ -198,10 +193,8 @@ gemm_tcgen05_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap map_
             if (!ok) break;
             const uint32_t acc_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)acc * acc_stride;
             const size_t tile_floats = (size_t)BM * bn;
-            // SPLIT: this share's partial tile -> workspace [share][tile][BM][bn], rows of the matrix only; with TRANS
-            // [share][tile][bn][BM], so that a warp's 32 rows lie side by side
-            float* mine = !SPLIT ? nullptr
-                        : partial + ((size_t)(unit % splits) * num_tiles + tile) * tile_floats + (TRANS ? (size_t)(quarter * 32 + lane) : (size_t)(quarter * 32 + lane) * bn);
+            // SPLIT: this share's partial tile -> workspace [share][tile][BM][bn], rows of the matrix only
+            float* mine = !SPLIT ? nullptr : partial + ((size_t)(unit % splits) * num_tiles + tile) * tile_floats + (size_t)(quarter * 32 + lane) * bn;
 #pragma unroll 1
             for (int c0 = 0; c0 < bn; c0 += 32) {
                 uint32_t v[32];
@@ -209,17 +202,7 @@ gemm_tcgen05_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap map_
                 if (count == 32) tmem_ld_32x32(acc_addr + (uint32_t)c0, v);
                 else tmem_ld_32x16(acc_addr + (uint32_t)c0, v);
                 if (row < M) {
-                    if constexpr (SPLIT && TRANS) {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (j < count && n0 + c0 + j < N) mine[(size_t)(c0 + j) * BM] = __uint_as_float(v[j]);
-                    } else if constexpr (TRANS) {
-                        // C is [N, M] in memory (the caller's product, this kernel computed its transpose): the warp's
-                        // 32 rows are 32 neighbours of one row of C
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (j < count && n0 + c0 + j < N) C[(size_t)(n0 + c0 + j) * M + row] = Num<TO>::from_f32(__uint_as_float(v[j]));
-                    } else if constexpr (SPLIT) {
+                    if constexpr (SPLIT) {
 #pragma unroll
                         for (int j = 0; j < 8; ++j)
                             if (4 * j < count) reinterpret_cast<uint4*>(mine + c0)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
@@ -249,47 +232,6 @@ gemm_tcgen05_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap map_
                     const int rows = min(BM, M - m0);
                     const float* first = partial + (size_t)tile * tile_floats;
                     const size_t share_stride = (size_t)num_tiles * tile_floats;
-                    if constexpr (TRANS) {
-                        // [bn][BM] partial tiles: a lane adds four neighbouring rows (a float4 of C's row) for eight
-                        // columns per pass
-                        const int cols = min(bn, N - n0);
-                        const int r4 = lane * 4;
-                        for (int c0 = quarter; c0 < cols; c0 += 4 * RED_ROWS) {
-                            float4 sum[RED_ROWS];
-#pragma unroll
-                            for (int i = 0; i < RED_ROWS; ++i) sum[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
-                            for (int s = 0; s < splits; ++s) {
-                                float4 p[RED_ROWS];
-#pragma unroll
-                                for (int i = 0; i < RED_ROWS; ++i) {
-                                    const int c = min(c0 + 4 * i, cols - 1);
-                                    p[i] = __ldcg(reinterpret_cast<const float4*>(first + (size_t)s * share_stride + (size_t)c * BM + r4));
-                                }
-#pragma unroll
-                                for (int i = 0; i < RED_ROWS; ++i) { sum[i].x += p[i].x; sum[i].y += p[i].y; sum[i].z += p[i].z; sum[i].w += p[i].w; }
-                            }
-#pragma unroll
-                            for (int i = 0; i < RED_ROWS; ++i) {
-                                const int c = c0 + 4 * i;
-                                if (c >= cols || r4 >= rows) break;
-                                TO* dst = C + (size_t)(n0 + c) * M + m0 + r4;
-                                if (r4 + 4 <= rows && (uintptr_t)dst % (4 * sizeof(TO)) == 0) {
-                                    if constexpr (sizeof(TO) == 2) {
-                                        uint2 o;
-                                        reinterpret_cast<__nv_bfloat162*>(&o)[0] = __floats2bfloat162_rn(sum[i].x, sum[i].y);
-                                        reinterpret_cast<__nv_bfloat162*>(&o)[1] = __floats2bfloat162_rn(sum[i].z, sum[i].w);
-                                        *reinterpret_cast<uint2*>(dst) = o;
-                                    } else {
-                                        *reinterpret_cast<float4*>(dst) = sum[i];
-                                    }
-                                } else {
-                                    const float e[4] = {sum[i].x, sum[i].y, sum[i].z, sum[i].w};
-                                    for (int j = 0; j < 4 && r4 + j < rows; ++j) dst[j] = Num<TO>::from_f32(e[j]);
-                                }
-                            }
-                        }
-                    } else
                     // eight rows per pass and lane, the loads of four shares in flight together: the loads' latency
                     // under a saturated memory system, not their number, is what this costs
                     for (int c = lane * 4; c < bn; c += 128) {
@@ -343,12 +285,12 @@ gemm_tcgen05_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap map_
 }
 
 // ---------------------------------------------------------------------------------------------------- host side
-template <typename TO, bool SPLIT, bool GATED = false, bool TRANS = false>
+template <typename TO, bool SPLIT, bool GATED = false>
 int launch(void* C, const void* X, const void* W, int M, int N, int K, int bn, int splits, float* partial, unsigned int* tickets, int* status,
            cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<TO, SPLIT, GATED, TRANS>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<TO, SPLIT, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         if (e != cudaSuccess) return 1000 + (int)e;
         configured = true;
     }
@@ -368,7 +310,7 @@ int launch(void* C, const void* X, const void* W, int M, int N, int K, int bn, i
     int tmem_cols = 32;                      // a power of two that holds both accumulators
     while (tmem_cols < 2 * bn) tmem_cols *= 2;
     dim3 grid((unsigned)(units < num_sms ? units : num_sms));   // one block per SM (its shared memory fills the SM)
-    oxr_launch(gemm_tcgen05_kernel<TO, SPLIT, GATED, TRANS>, grid, dim3(TC_THREADS), SMEM_BYTES, stream, true, (TO*)C, map_x, map_w, M, N, K, bn,
+    oxr_launch(gemm_tcgen05_kernel<TO, SPLIT, GATED>, grid, dim3(TC_THREADS), SMEM_BYTES, stream, true, (TO*)C, map_x, map_w, M, N, K, bn,
                stages, tmem_cols, (int)tiles, splits, partial, tickets, status);
     return oxr_launch_status();
 }
@@ -403,23 +345,4 @@ OXR_API int oxr_gemm_tcgen05_gated_bf16(void* C, const void* X, const void* W, i
     if (N % 16 != 0 || K <= 0 || K % 8 != 0 || (uintptr_t)X % 16 != 0 || (uintptr_t)W % 16 != 0 || (uintptr_t)C % 16 != 0) return OXR_BAD_ARGUMENT;
     if (tile_n < 16 || tile_n > MAX_BN || tile_n % 16 != 0) return OXR_BAD_ARGUMENT;
     return launch<__nv_bfloat16, false, true>(C, X, W, M, N, K, tile_n, 1, nullptr, nullptr, status, stream);
-}
-
-// The same product for few rows (M <= 256), computed as C^T = W X^T: W's rows fill the 128-row side of the tiles and
-// the M rows of X are the tile's width (M rounded up to 16), so every byte staged in shared memory is a byte of W or
-// of a real row. out [M, N] as always. splits, partial, tickets as above, with tiles = ceil(N / 128).
-OXR_API int oxr_gemm_tcgen05_few_rows_bf16(void* C, const void* X, const void* W, int M, int N, int K, int out_dtype, int splits, float* partial,
-                                           unsigned int* tickets, int* status, cudaStream_t stream) {
-    if (M <= 0 || N <= 0) return 0;
-    if (M > MAX_BN || K <= 0 || K % 8 != 0 || (uintptr_t)X % 16 != 0 || (uintptr_t)W % 16 != 0) return OXR_BAD_ARGUMENT;
-    const int width = (M + 15) / 16 * 16;
-    if (splits > 1) {
-        if (partial == nullptr || tickets == nullptr || (uintptr_t)partial % 16 != 0 || splits > (K + BK - 1) / BK) return OXR_BAD_ARGUMENT;
-        if (out_dtype == 1) return launch<__nv_bfloat16, true, false, true>(C, W, X, N, M, K, width, splits, partial, tickets, status, stream);
-        if (out_dtype == 0) return launch<float, true, false, true>(C, W, X, N, M, K, width, splits, partial, tickets, status, stream);
-        return OXR_BAD_ARGUMENT;
-    }
-    if (out_dtype == 1) return launch<__nv_bfloat16, false, false, true>(C, W, X, N, M, K, width, 1, nullptr, nullptr, status, stream);
-    if (out_dtype == 0) return launch<float, false, false, true>(C, W, X, N, M, K, width, 1, nullptr, nullptr, status, stream);
-    return OXR_BAD_ARGUMENT;
 }

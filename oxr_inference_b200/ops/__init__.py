@@ -95,7 +95,8 @@ def _lib():
         lib.oxr_gemm_tcgen05_bf16.argtypes = [p, p, p, i, i, i, i, i, i, p, p, p, p]
         lib.oxr_gemm_tcgen05_pair_bf16.argtypes = [p, p, p, i, i, i, i, i, p, p]
         lib.oxr_gemm_tcgen05_gated_bf16.argtypes = [p, p, p, i, i, i, i, p, p]
-        lib.oxr_gemm_tcgen05_few_rows_bf16.argtypes = [p, p, p, i, i, i, i, i, p, p, p, p]
+        lib.oxr_gemm_few_rows_cluster_bf16.argtypes = [p, p, p, i, i, i, i, i, p, p]
+        lib.oxr_gemm_few_rows_max_clusters.argtypes = [i]
         lib.oxr_gemm_tcgen05_pair_gated_bf16.argtypes = [p, p, p, i, i, i, i, p, p]
         lib.oxr_sample.argtypes = [p, p, i, i, p, p, p, p, p, p]
         lib.oxr_sample_chunks.argtypes = [i]
@@ -103,7 +104,7 @@ def _lib():
         lib.oxr_repetition_penalty.argtypes = [p, p, p, p, i, i, p]
         lib.oxr_mark_seen.argtypes = [p, p, p, i, i, p]
         for name in ("oxr_embedding", "oxr_add_rms_norm", "oxr_silu_mul", "oxr_cast", "oxr_qk_norm_rope_store",
-                     "oxr_gemm_f32_nt", "oxr_gemm_skinny_bf16", "oxr_gemm_skinny_gated_bf16", "oxr_gemm_tcgen05_bf16", "oxr_gemm_tcgen05_pair_bf16", "oxr_gemm_tcgen05_gated_bf16", "oxr_gemm_tcgen05_few_rows_bf16",
+                     "oxr_gemm_f32_nt", "oxr_gemm_skinny_bf16", "oxr_gemm_skinny_gated_bf16", "oxr_gemm_tcgen05_bf16", "oxr_gemm_tcgen05_pair_bf16", "oxr_gemm_tcgen05_gated_bf16", "oxr_gemm_few_rows_cluster_bf16", "oxr_gemm_few_rows_max_clusters",
                      "oxr_gemm_tcgen05_pair_gated_bf16", "oxr_sample", "oxr_repetition_penalty", "oxr_mark_seen"):
             getattr(lib, name).restype = c_int
         lib.oxr_set_chain.argtypes = [c_int]
@@ -521,20 +522,32 @@ def _gemm_plan(m: int, n: int, k: int, may_split: bool = True) -> tuple[int, int
     return best
 
 
-GEMM_FEW_ROWS = 128
+GEMM_FEW_ROWS = 256          # the widest tile of a tcgen05 product
+GEMM_FEW_ROWS_ANY_SHARES = 192
+
+
+@functools.lru_cache(maxsize=None)
+def _few_rows_clusters(shares: int) -> int:
+    """Clusters of ``shares`` blocks of the few-rows kernel that the GPU holds at a time."""
+    return int(_lib().oxr_gemm_few_rows_max_clusters(shares))
 
 
 def _gemm_few_rows_plan(m: int, n: int, k: int) -> int:
-    """Shares of k for the few-rows form of the tcgen05 product (W on the 128-row side of the tiles, the rows of x as
-    the tile's width), or 0 where the ordinary form is to run. The few-rows form stages no padding rows, which pays
-    when W is narrow: N / 128 tiles are then far fewer than SMs and k is dealt out so that about one unit per SM
-    results. Measured on a B200 (Qwen3-8B and 32B products at 17 to 128 rows) it is 1 to 5 us faster than the
-    ordinary form where at least two shares per tile fit, level or slower elsewhere."""
+    """Shares of k for the few-rows kernel (W on the 128-row side of the tiles, the rows of x as the tile's width, the
+    shares of a tile the blocks of one cluster), or 0 where the ordinary kernel is to run. It stages no padding rows
+    and adds the shares' partial tiles through distributed shared memory, which pays when W is narrow: N / 128 tiles
+    are then far fewer than SMs and k is dealt out so that about one block per SM results. The plan is the most shares
+    (at most 8, a portable cluster) with which the clusters of all tiles run at once, and at least two. Measured on
+    a B200 with Qwen3-8B's and 32B's products: level with cuBLAS or ahead of it from 17 to 128 rows (down projection at
+    64 rows: 20.0 us, cuBLAS 22.1, the ordinary kernel with shares through a workspace 23.1); from 193 rows on only
+    three shares or more still beat the ordinary kernel (each block fetches all rows of x for its k steps)."""
     if m > GEMM_FEW_ROWS:
         return 0
     tiles, steps = -(-n // 128), -(-k // 64)
-    shares = min(8, NUM_SMS // tiles, steps)
-    return shares if shares >= 2 else 0
+    for shares in range(min(8, NUM_SMS // tiles, steps), 1, -1):
+        if tiles <= _few_rows_clusters(shares):
+            return shares if (m <= GEMM_FEW_ROWS_ANY_SHARES or shares >= 3) else 0
+    return 0
 
 
 GEMM_PAIR_MIN_ROWS = 512
@@ -607,13 +620,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
         out = torch.empty((m, n), dtype=out_dtype, device=x.device)
         few = _gemm_few_rows_plan(m, n, k)
         if few:
-            partial = tickets = None
-            if few > 1:
-                if few * -(-n // 128) * 128 * (-(-m // 16) * 16) * 4 > GEMM_WORKSPACE_BYTES:
-                    raise KernelError(f"linear: {few} shares of {m} x {n} outgrow the workspace")
-                partial, tickets = _gemm_split_buffers(x.device)
-            _done(lib.oxr_gemm_tcgen05_few_rows_bf16(out.data_ptr(), x.data_ptr(), weight.data_ptr(), m, n, k, _DT[out_dtype], few,
-                                                     _ptr(partial), _ptr(tickets), new_status(x.device).data_ptr(), _stream()), "gemm_tcgen05_few_rows")
+            _done(lib.oxr_gemm_few_rows_cluster_bf16(out.data_ptr(), x.data_ptr(), weight.data_ptr(), m, n, k, _DT[out_dtype], few,
+                                                     new_status(x.device).data_ptr(), _stream()), "gemm_few_rows_cluster")
             return out
         pair_tile = _gemm_pair_plan(m, n, k)
         if pair_tile:

@@ -32,9 +32,19 @@ def test_pair_kernel_takes_the_long_steps_only():
     assert ops._gemm_pair_plan(512, 4096, 4096) == 128          # 64 tiles for 74 pairs, not 32 wide ones
 
 
-def test_few_rows_form_where_w_is_narrow_and_rows_are_few():
+def test_few_rows_form_where_w_is_narrow_and_rows_are_few(monkeypatch):
+    # clusters of 1 to 8 blocks that run at a time, as a GPU of 148 SMs in 8 groups of 18 or 19 would report them
+    monkeypatch.setattr(ops, "_few_rows_clusters", lambda shares: {1: 148, 2: 72, 3: 48, 4: 32, 5: 24, 6: 24, 7: 16, 8: 16}[shares])
     assert ops._gemm_few_rows_plan(64, 4096, 12288) == 4       # 32 tiles: four shares each
     assert ops._gemm_few_rows_plan(64, 6144, 4096) == 3
     assert ops._gemm_few_rows_plan(64, 24576, 4096) == 0       # 192 tiles fill the SMs as they are
-    assert ops._gemm_few_rows_plan(129, 4096, 12288) == 0
+    assert ops._gemm_few_rows_plan(192, 4096, 12288) == 4
+    assert ops._gemm_few_rows_plan(257, 4096, 12288) == 0      # a tile is at most 256 wide
     assert ops._gemm_few_rows_plan(64, 4096, 64) == 0          # one k step cannot be shared
+    assert ops._gemm_few_rows_plan(64, 5120, 8192) == 3        # 40 tiles: clusters of 3 all run at once
+    monkeypatch.setattr(ops, "_few_rows_clusters", lambda shares: 30 if shares == 4 else 148 // shares)
+    assert ops._gemm_few_rows_plan(64, 4096, 12288) == 3       # 32 clusters of 4 would not run at once
+    monkeypatch.setattr(ops, "_few_rows_clusters", lambda shares: {1: 148, 2: 74, 3: 45, 4: 33, 5: 26, 6: 22, 7: 15, 8: 15}[shares])
+    assert ops._gemm_few_rows_plan(192, 6144, 4096) == 2       # 48 tiles: 45 clusters of 3 are too few
+    assert ops._gemm_few_rows_plan(200, 6144, 4096) == 0       # from 193 rows on two shares do not pay
+    assert ops._gemm_few_rows_plan(256, 4096, 12288) == 4

@@ -271,11 +271,13 @@ def test_gemm_tcgen05_split_k(ops, monkeypatch, M, N, K, tile_n, splits, out_dty
 
 
 @pytest.mark.parametrize("M,N,K,shares", [(64, 256, 64, 1), (17, 509, 96, 1), (100, 1000, 1032, 3), (256, 136, 2048, 8), (33, 4096, 4096, 4),
-                                          (5, 300, 328, 2), (200, 777, 520, 1), (128, 4096, 12288, 4)])
+                                          (5, 300, 328, 2), (200, 777, 520, 1), (128, 4096, 12288, 4), (250, 900, 1100, 5), (96, 6144, 4096, 3),
+                                          (1, 130, 8, 1), (77, 128, 4096, 7)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
-def test_gemm_tcgen05_few_rows(ops, monkeypatch, M, N, K, shares, out_dtype):
-    """The few-rows form: the kernel computes the transpose (W's rows on the 128-row side of the tiles, the rows of x
-    as the tile's width) and its epilogue stores it back transposed; with and without shares of k, twice in a row."""
+def test_gemm_few_rows_cluster(ops, monkeypatch, M, N, K, shares, out_dtype):
+    """The few-rows kernel: it computes the transpose (W's rows on the 128-row side of the tiles, the rows of x as the
+    tile's width), the shares of a tile's k steps are the blocks of a cluster and add their partial tiles through
+    distributed shared memory; with one share and with several, twice in a row."""
     monkeypatch.setattr(ops, "SKINNY_MAX_ROWS", 0)
     monkeypatch.setattr(ops, "_gemm_few_rows_plan", lambda m, n, k: shares)
     g = torch.Generator(device=DEV).manual_seed(13)
