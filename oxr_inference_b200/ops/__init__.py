@@ -537,14 +537,17 @@ def _gemm_few_rows_plan(m: int, n: int, k: int) -> int:
     shares of a tile the blocks of one cluster), or 0 where the ordinary kernel is to run. It stages no padding rows
     and adds the shares' partial tiles through distributed shared memory, which pays when W is narrow: N / 128 tiles
     are then far fewer than SMs and k is dealt out so that about one block per SM results. The plan is the most shares
-    (at most 8, a portable cluster) with which the clusters of all tiles run at once, and at least two. Measured on
+    with which the clusters of all tiles run at once, at least two and at most four (clusters of five and more were
+    level or up to 1.5 us slower, except with many rows and a long k: from 193 rows and 128 k steps on at most 8, a
+    portable cluster). Measured on
     a B200 with Qwen3-8B's and 32B's products: level with cuBLAS or ahead of it from 17 to 128 rows (down projection at
     64 rows: 20.0 us, cuBLAS 22.1, the ordinary kernel with shares through a workspace 23.1); from 193 rows on only
     three shares or more still beat the ordinary kernel (each block fetches all rows of x for its k steps)."""
     if m > GEMM_FEW_ROWS:
         return 0
     tiles, steps = -(-n // 128), -(-k // 64)
-    for shares in range(min(8, NUM_SMS // tiles, steps), 1, -1):
+    most = 8 if (m > GEMM_FEW_ROWS_ANY_SHARES and steps >= 128) else 4
+    for shares in range(min(most, NUM_SMS // tiles, steps), 1, -1):
         if tiles <= _few_rows_clusters(shares):
             return shares if (m <= GEMM_FEW_ROWS_ANY_SHARES or shares >= 3) else 0
     return 0

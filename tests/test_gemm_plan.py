@@ -48,3 +48,6 @@ def test_few_rows_form_where_w_is_narrow_and_rows_are_few(monkeypatch):
     assert ops._gemm_few_rows_plan(192, 6144, 4096) == 2       # 48 tiles: 45 clusters of 3 are too few
     assert ops._gemm_few_rows_plan(200, 6144, 4096) == 0       # from 193 rows on two shares do not pay
     assert ops._gemm_few_rows_plan(256, 4096, 12288) == 4
+    assert ops._gemm_few_rows_plan(64, 2560, 9728) == 4        # 20 tiles: 6 shares would run, 4 are as fast or faster
+    assert ops._gemm_few_rows_plan(256, 2560, 9728) == 6       # many rows and a long k: more shares pay
+    assert ops._gemm_few_rows_plan(256, 2560, 4096) == 4
