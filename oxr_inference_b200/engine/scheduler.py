@@ -143,16 +143,21 @@ class Scheduler:
             budget -= count
 
         # 1 and 2: running requests, decodes first, then prompt portions, each group in admission order
-        for phase_is_decode in (True, False):
-            for request in list(self.running):
-                # a request that was preempted or retired earlier in this pass has no cache any more
-                if request.cache is None or request.id in chosen or (request.pending == 1) != phase_is_decode:
-                    continue
-                count = self._portion(request, budget)
-                if count <= 0:
-                    continue
-                if self._make_room(request, count, plan, chosen):
-                    take(request, count)
+        later: list[Request] = []
+        for request in list(self.running):
+            # a request that was preempted or retired earlier in this pass has no cache any more
+            if request.cache is None:
+                continue
+            if request.pending != 1:
+                later.append(request)
+            elif budget > 0 and self._make_room(request, 1, plan, chosen):   # a single token is never trimmed
+                take(request, 1)
+        for request in later:
+            if request.cache is None:
+                continue
+            count = self._portion(request, budget)
+            if count > 0 and self._make_room(request, count, plan, chosen):
+                take(request, count)
 
         # 3: admit from the head of the queue
         while self.waiting and budget > 0 and len(self.running) < self.max_running and self.cache.free_slots > 0:
