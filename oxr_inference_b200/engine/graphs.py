@@ -69,13 +69,13 @@ class DecodeGraphs:
         m = self.runner.cache
         layout = Layout(bucket, bucket, bucket, [width] * len(m.pools), b.decode_tile_caps(bucket))
         block = torch.zeros(layout.total, dtype=torch.int32, device=b.device)
-        # Warm-up with the real entries: what they write into the cache is what the replay writes again.
+        # One eager run first, so that whatever is set up at a first call (kernel attributes, plans, workspaces) is set
+        # up outside the capture. It runs the real entries: what it writes into the cache is what the replay writes again.
         ctx = b.build(entries, layout=layout, device_block=block)
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
-            for _ in range(2):
-                self._forward(ctx)
+            self._forward(ctx)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
