@@ -60,13 +60,14 @@ def _need(t: torch.Tensor, name: str, dtype: torch.dtype | None = None) -> None:
 
 
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_raw_device = getattr(torch._C, "_cuda_getDevice", None) or torch.cuda.current_device
 
 
 def _stream() -> int:
     """Handle of the current CUDA stream. The raw getter costs a fraction of a microsecond; `torch.cuda.current_stream()`
     builds a Stream object per call (several microseconds, per kernel launch of an eager step)."""
     if _raw_stream is not None:
-        return _raw_stream(torch.cuda.current_device())
+        return _raw_stream(_raw_device())
     return torch.cuda.current_stream().cuda_stream
 
 
