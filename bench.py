@@ -200,6 +200,7 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"], help="fewer layers than the model has (named in config)")
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64 (quick runs)")
+    ap.add_argument("--context", type=int, default=CONTEXT, help="tokens each request holds when the decode steps are timed")
     ap.add_argument("--workload", default="decode", choices=("decode", "continuous", "chunked"),
                     help="decode: the headline line (default); continuous / chunked: the two serving workloads, one line each")
     args = ap.parse_args()
@@ -222,10 +223,14 @@ def main() -> int:
 
     cfg = dict(QWEN3_8B, num_hidden_layers=args.layers)
     page = 16
-    pages = 64 * ((CONTEXT + 2 * (K + W) + 64) // page + 2) + 64
+    context = args.context
+    kv_per_token = 2 * 2 * args.layers * cfg["num_key_value_heads"] * cfg["head_dim"]
+    # batch 1 and 64 ride along where 64 requests of this context fit beside the weights (they do at 2,048 tokens)
+    batches = (8,) if args.skip_points or 64 * context * kv_per_token > 100e9 else (8, 1, 64)
+    pages = max(batches) * ((context + 2 * (K + W) + 64) // page + 2) + 64
     engine = Engine(random_config=cfg, seed=0, settings=EngineSettings(
         dtype="bfloat16", page_size=page, num_pages=pages, max_running=64, max_step_tokens=8192, prefill_chunk=2048,
-        max_positions=4096, cuda_graphs=True))
+        max_positions=max(4096, context + 2 * (K + W) + 128), cuda_graphs=True))
     model = engine.runner.model
     gen = torch.Generator().manual_seed(0)
     hbm_gbs, bf16_tflops, peak_kind = peaks()
@@ -237,10 +242,10 @@ def main() -> int:
     kv_bytes_per_token = 2 * L * KV * D * 2
 
     def prompts(n: int) -> list[list[int]]:
-        return [torch.randint(0, V, (CONTEXT,), generator=gen).tolist() for _ in range(n)]
+        return [torch.randint(0, V, (context,), generator=gen).tolist() for _ in range(n)]
 
     def fill(batch: int, budget: int) -> None:
-        """`batch` requests, each with CONTEXT tokens in the cache and one token left to decode."""
+        """`batch` requests, each with `context` tokens in the cache and one token left to decode."""
         for r in list(engine.scheduler.running) + list(engine.scheduler.waiting):
             r.cancelled = True
         engine.step()
@@ -258,8 +263,7 @@ def main() -> int:
         entries = [StepEntry(p.request.cache, p.request.tokens[p.start:p.start + 1], [0], counter=len(p.request.output))
                    for p in plan.entries]
         tokens, _ = engine.graphs.run(entries)  # captures at first use, fills the static inputs
-        key = next(k for k in engine.graphs._graphs if k[0] >= batch)
-        key = min((k for k in engine.graphs._graphs if k[0] >= batch), key=lambda k: k)
+        key = min(k for k in engine.graphs._graphs if k[0] >= batch)
         graph = engine.graphs._graphs[key][0]
         for _ in range(W):
             graph.replay()
@@ -297,8 +301,8 @@ def main() -> int:
     layout_words = next(v[1].total for k, v in engine.graphs._graphs.items() if k[0] == 8)
 
     points = {}
-    if not args.skip_points:
-        for b in (1, 64):
+    if len(batches) > 1:
+        for b in batches[1:]:
             ms, _, _ = decode_device(b)
             points[f"decode_b{b}"] = round(b * 1000.0 / ms, 1)
 
@@ -328,12 +332,12 @@ def main() -> int:
 
     clocks = sampler.stop()
     out = {
-        "metric": METRIC, "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
+        "metric": METRIC.replace(str(CONTEXT), str(context)), "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": round(ms8, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic uniform token ids, random weights N(0, 0.02)", "impl": "ours",
         "config": {"model": "Qwen3-8B shape", "layers": L, "layers_of_model": QWEN3_8B["num_hidden_layers"], "hidden": h,
                    "heads": H, "kv_heads": KV, "head_dim": D, "intermediate": I, "vocab": V, "global_batch": 8,
-                   "seq_len": CONTEXT, "page_size": page, "tied": False, "parallelism": "single GPU",
+                   "seq_len": context, "page_size": page, "tied": False, "parallelism": "single GPU",
                    "l2": "step inputs (15 GB of weights) exceed L2", "peaks": peak_kind},
         "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": layout_words * 4, "d2h_bytes_per_step": (8 + 2) * 4},
         "gpu_launches": kernels_per_step * K,
