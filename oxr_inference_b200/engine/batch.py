@@ -20,7 +20,7 @@ from oxr_inference_b200.cache.manager import CacheManager, RequestCache
 from oxr_inference_b200.parts.base import StepContext
 
 
-@dataclass
+@dataclass(slots=True)
 class StepEntry:
     cache: RequestCache
     tokens: list[int]

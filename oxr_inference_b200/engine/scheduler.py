@@ -78,7 +78,7 @@ class Request:
         return len(self.prompt_ids) + len(self.output) - self.computed
 
 
-@dataclass
+@dataclass(slots=True)
 class Planned:
     request: Request
     start: int
@@ -146,12 +146,16 @@ class Scheduler:
         later: list[Request] = []
         for request in list(self.running):
             # a request that was preempted or retired earlier in this pass has no cache any more
-            if request.cache is None:
+            rc = request.cache
+            if rc is None:
                 continue
-            if request.pending != 1:
+            length = rc.length
+            if len(request.prompt_ids) + len(request.output) - length != 1:
                 later.append(request)
-            elif budget > 0 and self._make_room(request, 1, plan, chosen):   # a single token is never trimmed
-                take(request, 1)
+            elif budget > 0 and (length < rc.room or self._make_room(request, 1, plan, chosen)):
+                # a single token is never trimmed, and mostly its page is there already
+                chosen[request.id] = Planned(request, length, 1, True)
+                budget -= 1
         for request in later:
             if request.cache is None:
                 continue
