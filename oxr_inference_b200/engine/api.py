@@ -103,18 +103,25 @@ class Engine:
         plan = self.scheduler.schedule()
         finished = list(plan.finished)
         if plan.entries:
-            if plan.decode_only and len(plan.entries) > 1:
+            decode_only = plan.decode_only
+            entries = []
+            if decode_only:
                 # longest context first: the split-KV kernel's blocks start in this order, and a long one that starts
                 # last would run on alone (the order stays the same from step to step while the same requests decode)
                 plan.entries.sort(key=lambda p: -p.start)
-            entries = []
-            for p in plan.entries:
-                r = p.request
-                entries.append(StepEntry(r.cache, r.tokens_from(p.start, p.count), [p.count - 1] if p.wants_logits else [],
-                                         temperature=r.params.temperature, seed=r.params.seed, counter=len(r.output),
-                                         penalty=r.params.repetition_penalty))
+                for p in plan.entries:   # one token each, the last the request holds: hundreds of these per step
+                    r = p.request
+                    out, params = r.output, r.params
+                    entries.append(StepEntry(r.cache, [out[-1] if out else r.prompt_ids[-1]], [0], params.temperature, params.seed,
+                                             len(out), params.repetition_penalty))
+            else:
+                for p in plan.entries:
+                    r = p.request
+                    entries.append(StepEntry(r.cache, r.tokens_from(p.start, p.count), [p.count - 1] if p.wants_logits else [],
+                                             temperature=r.params.temperature, seed=r.params.seed, counter=len(r.output),
+                                             penalty=r.params.repetition_penalty))
             try:
-                tokens = self._run(plan, entries)
+                tokens = self._run(plan, entries, decode_only)
             except Exception:
                 # every running request fails, the engine stays usable (oxr_runtime/engine.py:483-487,512-516)
                 log.exception("step failed")
@@ -140,13 +147,13 @@ class Engine:
                 callback(c)
         return out
 
-    def _run(self, plan: StepPlan, entries: list[StepEntry]) -> list[int]:
+    def _run(self, plan: StepPlan, entries: list[StepEntry], decode_only: bool) -> list[int]:
         rt = self.runner.model.runtime
         penalised = any(e.penalty != 1.0 for e in entries)
         if penalised:
             self._mark_new(plan)
         tokens = None
-        if self.graphs is not None and plan.decode_only and not penalised:
+        if self.graphs is not None and decode_only and not penalised:
             replayed = self.graphs.run(entries)
             if replayed is not None:
                 # the graph copied the tokens and the status word to pinned memory itself
