@@ -39,6 +39,8 @@ class RequestCache:
     room: int = 0
     """Tokens that the pages held so far can take (the shortest table times the page size): lets the two calls that every
     request makes in every step, ``reserve`` and ``advance``, answer the common case with one comparison."""
+    released: list[int] = field(default_factory=list)
+    """Per group: how many pages at the front of the table a window has passed and given back."""
     serial: int = field(default_factory=itertools.count().__next__)
     """Unlike ``id()``, never given to a second request of this process: (serial, version) names one state of one
     request's tables for good."""
@@ -115,7 +117,7 @@ class CacheManager:
         if not self._free_slots:
             return None
         slot = self._free_slots.pop()
-        rc = RequestCache(key=key, state_slot=slot, tables=[[] for _ in self.pools])
+        rc = RequestCache(key=key, state_slot=slot, tables=[[] for _ in self.pools], released=[0] * len(self.pools))
         self._open[id(rc)] = rc
         for state in self.states:
             state[slot].zero_()
@@ -153,12 +155,12 @@ class CacheManager:
         rc.length = new_length
         for g in self._windowed:
             table, pool = rc.tables[g], self.pools[g]
-            keep_from = self._first_needed_page(g, new_length)  # the next query sits at position new_length
-            gone = [p for p in table[:keep_from] if p != RELEASED]
-            if gone:
-                pool.release(gone)
-                for i in range(min(keep_from, len(table))):
-                    table[i] = RELEASED
+            keep_from = min(self._first_needed_page(g, new_length), len(table))  # the next query sits at position new_length
+            done = rc.released[g]
+            if keep_from > done:   # the pages given back are a prefix of the table: only what is new is touched
+                pool.release(table[done:keep_from])
+                table[done:keep_from] = [RELEASED] * (keep_from - done)
+                rc.released[g] = keep_from
                 rc.version += 1
 
     def close(self, rc: RequestCache) -> None:
@@ -174,6 +176,7 @@ class CacheManager:
         rc.version += 1
         rc.length = 0
         rc.room = 0
+        rc.released = [0] * len(self.pools)
         del self._open[id(rc)]
 
     def open_requests(self) -> list[RequestCache]:
