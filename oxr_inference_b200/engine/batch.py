@@ -288,21 +288,28 @@ class BatchBuilder:
         seg("ctx_lens")[:n_real] = [s + 1 for s in starts]
         seg("counter")[:n_real] = [e.counter for e in entries]
         remembered = self._rows[id(device_block)]
+        P = m.page_size
         for g in range(len(m.pools)):
             w = layout.widths[g]
-            slots, table = seg(f"slots{g}"), None
+            table = None
+            slots = []
             for i, e in enumerate(entries):
-                key = (e.cache.serial, e.cache.version)
+                rc = e.cache
+                key = (rc.serial, rc.version)
+                t = rc.tables[g]
                 if remembered[g * n + i] != key:
                     if table is None:
                         table = seg(f"table{g}").reshape(n, w)
-                    t = e.cache.tables[g]
                     if len(t) > w:
                         raise ValueError(f"a block table of {len(t)} pages does not fit the layout's width {w}")
                     table[i, :len(t)] = t
                     table[i, len(t):] = m.scratch_pages[g] if m.scratch_pages else 0
                     remembered[g * n + i] = key
-                slots[i] = m.slot(e.cache, g, starts[i])
+                page = t[starts[i] // P]
+                if page < 0:
+                    raise ValueError("a position to be written lies on a released page")
+                slots.append(page * P + starts[i] % P)
+            seg(f"slots{g}")[:n_real] = slots   # one write for all requests: hundreds of them per step
         if copy:
             device_block[:layout.total].copy_(pinned[:layout.total], non_blocking=True)
             self._copied = torch.cuda.Event()
