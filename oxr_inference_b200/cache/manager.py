@@ -200,6 +200,13 @@ class CacheManager:
                 raise AssertionError(f"group {g}: pool says {sorted(held)} are held, tables say {sorted(owners)}")
             if len(held) + pool.free != pool.num_pages:
                 raise AssertionError(f"group {g}: {len(held)} held + {pool.free} free != {pool.num_pages}")
+        for rc in self._open.values():
+            if rc.room != min(len(t) for t in rc.tables) * self.page_size:
+                raise AssertionError(f"request {rc.key!r}: room {rc.room} does not match its tables")
+            for g, table in enumerate(rc.tables):
+                k = rc.released[g]
+                if any(p != RELEASED for p in table[:k]) or any(p == RELEASED for p in table[k:]):
+                    raise AssertionError(f"request {rc.key!r}, group {g}: the released pages are not the first {k}")
         slots = [rc.state_slot for rc in self._open.values()]
         if len(set(slots)) != len(slots) or set(slots) & set(self._free_slots):
             raise AssertionError("a state slot is held twice or is both held and free")
