@@ -158,3 +158,23 @@ def test_a_request_is_named_by_a_serial_that_is_never_given_twice():
         m.advance(rc, 20)
         m.close(rc)
         del rc
+
+
+def test_room_is_what_the_held_pages_can_take():
+    """``room`` lets reserve and advance answer with one comparison; it follows the shortest table."""
+    m = CacheManager(_plan(windows=(0, 12)), page_size=8, num_pages=10, max_requests=2)
+    r = m.open("a")
+    assert r.room == 0 and r.released == [0, 0]
+    assert m.reserve(r, 9) and r.room == 16 and [len(t) for t in r.tables] == [2, 2]
+    version = r.version
+    assert m.reserve(r, 16) and r.version == version          # nothing new was needed
+    with pytest.raises(ValueError):
+        m.advance(r, 17)                                       # beyond what was reserved
+    m.advance(r, 16)
+    assert m.reserve(r, 40) and r.room == 40
+    m.advance(r, 40)                                           # the window of 12 has passed positions 0..28: pages 0..2
+    assert r.released == [0, 3] and r.tables[1][:3] == [RELEASED] * 3 and r.room == 40
+    m.check()
+    m.close(r)
+    assert r.room == 0 and r.released == [0, 0]
+    m.check()
