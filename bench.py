@@ -105,11 +105,12 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(sm)}
 
 
-def reference_arm() -> int:
-    print(json.dumps({"impl": "reference", "unavailable":
-                      "the reference cannot be installed: pip reports that its source tree has neither setup.py nor "
-                      "pyproject.toml, and its engine only loads its own vision+language model folder"}))
-    return 0
+def reference_arm(args) -> int:
+    """The unmodified reference's language path at the same config (see baseline/reference_arm.py); nothing of this
+    repository's package is imported on this path."""
+    sys.path.insert(0, str(ROOT / "baseline"))
+    import reference_arm as arm
+    return arm.run(args, QWEN3_8B, args.context, PREFILL_TOKENS, METRIC.replace(str(CONTEXT), str(args.context)), peaks, ClockSampler)
 
 
 def serving_workload(which: str) -> int:
@@ -204,11 +205,11 @@ def main() -> int:
     ap.add_argument("--workload", default="decode", choices=("decode", "continuous", "chunked"),
                     help="decode: the headline line (default); continuous / chunked: the two serving workloads, one line each")
     args = ap.parse_args()
-    if args.impl == "reference":
-        return reference_arm()
     if args.gpus != 1:
         print(f"this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.impl == "reference":
+        return reference_arm(args)
     if args.workload != "decode":
         return serving_workload(args.workload)
     K, W = args.steps, max(args.warmup, 3)
@@ -327,7 +328,9 @@ def main() -> int:
     engine.runner.check()
     prefill_ms = statistics.median(times)
     T = PREFILL_TOKENS
-    flops = 2 * T * L * layer_params + 2 * V * h + L * 2 * H * D * T * (T + 1)
+    # the fraction counts the matrix products alone (attention's flops are named beside it, not added to it)
+    flops = 2 * T * L * layer_params + 2 * V * h
+    attn_flops = L * 2 * H * D * T * (T + 1)
     prefill_frac = flops / (prefill_ms * 1e-3) / (bf16_tflops * 1e12)
 
     clocks = sampler.stop()
@@ -342,6 +345,7 @@ def main() -> int:
         "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": layout_words * 4, "d2h_bytes_per_step": (8 + 2) * 4},
         "gpu_launches": kernels_per_step * K,
         "prefill": {"value": round(T / (prefill_ms * 1e-3), 1), "tokens": T, "ms": round(prefill_ms, 3), "frac": round(prefill_frac, 4),
+                    "attention_tflops_in_step": round(attn_flops / 1e12, 3),
                     **({"frac_of_sustained": round(flops / (prefill_ms * 1e-3) / (sustained_tflops() * 1e12), 4)} if sustained_tflops() else {})},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_gbs, "unit": "GB/s", "frac": round(achieved / hbm_gbs, 4)},
         "points": points,
