@@ -32,8 +32,9 @@ class EngineSettings:
     """Replay decode-only steps from CUDA graphs (oxr_runtime/decode_graph.py)."""
     dtype: str = "bfloat16"
     """``bfloat16``: the serving kernels; ``float32``: every operation in true 32-bit."""
-    max_logit_rows: int = 4096
-    """Most positions whose logits one step may return."""
+    step_tile: int | None = None
+    """Rows of the widest tile of the kernels that run a step; the scheduler trims prompt portions so that a step's
+    tokens come to whole tile rows. None asks the kernels (``ops.STEP_TILE_ROWS``), 0 turns the trimming off."""
 
     def __post_init__(self) -> None:
         if self.dtype not in ("bfloat16", "float32"):

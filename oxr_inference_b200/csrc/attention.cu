@@ -1568,6 +1568,10 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
 }  // namespace
 
 OXR_API int oxr_attn_head_dim() { return D; }
+// Which split-KV kernel the last call with short tiles launched: 0 none yet, 1 cp.async gathers, 2 TMA gathers with one
+// block per piece, 3 TMA gathers with one round of blocks that walk over the pieces. For tests and profiles.
+static int oxr_last_short_kernel = 0;
+OXR_API int oxr_attn_last_short_kernel() { return oxr_last_short_kernel; }
 // Rows of a tile for each kind of tile list that the host builds: 0 generic, 1 decode, 2 prefill (mma.sync), 3 prefill
 // (tcgen05). The host keeps the same numbers and compares them when it loads the library.
 OXR_API int oxr_attn_tile_rows(int kind) {
@@ -1673,14 +1677,17 @@ OXR_API int oxr_paged_attention_bf16(void* out, const void* q, const void* k_cac
             }
             if (pieces > slots) {
                 // more pieces than fit at once: one round of blocks that walk over them
+                oxr_last_short_kernel = 3;
                 oxr_launch(attn_tma_decode_walk_kernel, dim3(slots), dim3(TMA_THREADS), WALK_SMEM, stream, true,
                     (bf16*)out, part_o, part_ml, counters, (const bf16*)q, maps[0], maps[1], pool_row0, box_rows, n_short, KV * groups, splits, a);
                 return oxr_launch_status();
             }
+            oxr_last_short_kernel = 2;
             oxr_launch(attn_tma_decode_kernel, dim3(n_short, KV * groups, splits), dim3(TMA_THREADS), TMA_DECODE_SMEM, stream, true,
                 (bf16*)out, part_o, part_ml, counters, (const bf16*)q, maps[0], maps[1], pool_row0, box_rows, a);
             return oxr_launch_status();
         }
+        oxr_last_short_kernel = 1;
         attn_mma_decode_kernel<<<dim3(n_short, KV * groups, splits), MMA_THREADS, DECODE_SMEM, stream>>>(
             (bf16*)out, part_o, part_ml, counters, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, a);
         int rc = oxr_launch_status();

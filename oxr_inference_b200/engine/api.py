@@ -60,7 +60,8 @@ class Engine:
                  time.perf_counter() - started)
         self.scheduler = Scheduler(self.runner.cache, max_running=s.max_running, max_waiting=s.max_waiting,
                                    max_step_tokens=s.max_step_tokens, prefill_chunk=s.prefill_chunk,
-                                   max_positions=self.max_positions, eos_token_ids=model.spec.eos_token_ids)
+                                   max_positions=self.max_positions, eos_token_ids=model.spec.eos_token_ids,
+                                   step_tile=ops.STEP_TILE_ROWS if s.step_tile is None else s.step_tile)
         self.graphs = DecodeGraphs(self.runner, max_batch=s.max_running, max_positions=self.max_positions) if s.cuda_graphs else None
         self._seen: torch.Tensor | None = None  # [slots + 1, vocab] uint8, made when a request first asks for a penalty
         self._done: dict[int, Completion] = {}

@@ -49,7 +49,7 @@ class DecodeGraphs:
             return None
         key = (bucket, self._width_bucket(entries))
         if key not in self._graphs:
-            self._capture(key, entries)
+            self._capture(key)
         graph, layout, block, tokens, readback = self._graphs[key]
         self.runner.builder.build(entries, layout=layout, device_block=block, copy=False)
         graph.replay()
@@ -63,15 +63,18 @@ class DecodeGraphs:
         return ops.sample(logits, s["temperature"], s["seed_lo"], s["seed_hi"], s["counter"])
 
     @torch.inference_mode()
-    def _capture(self, key: tuple[int, int], entries: list[StepEntry]) -> None:
+    def _capture(self, key: tuple[int, int]) -> None:
         bucket, width = key
         b = self.runner.builder
         m = self.runner.cache
         layout = Layout(bucket, bucket, bucket, [width] * len(m.pools), b.decode_tile_caps(bucket))
         block = torch.zeros(layout.total, dtype=torch.int32, device=b.device)
         # One eager run first, so that whatever is set up at a first call (kernel attributes, plans, workspaces) is set
-        # up outside the capture. It runs the real entries: what it writes into the cache is what the replay writes again.
-        ctx = b.build(entries, layout=layout, device_block=block)
+        # up outside the capture. It runs padding rows only (no entries: every row reads and writes the scratch page and
+        # the scratch state slot), so the requests' step runs exactly once, in the replay that follows the capture: a
+        # mixer that keeps per-request state must not see a token twice (oxr_runtime/decode_graph.py:84-90 warms up on
+        # whatever its static buffers hold, which at start-up is the scratch page as well).
+        ctx = b.build([], layout=layout, device_block=block)
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):

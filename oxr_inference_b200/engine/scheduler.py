@@ -48,6 +48,8 @@ class Request:
     submitted: float = field(default_factory=time.monotonic)
     cancelled: bool = False
     finish_reason: str | None = None
+    skipped: int = 0
+    """Steps in a row in which the request was running, inside its prompt, and got no tokens."""
 
     def cancel(self) -> None:
         """Ask for the request to be dropped: at the next step it leaves the queue or gives its pages back and ends with
@@ -104,8 +106,12 @@ class StepPlan:
 
 class Scheduler:
     def __init__(self, cache: CacheManager, *, max_running: int, max_waiting: int, max_step_tokens: int,
-                 prefill_chunk: int, max_positions: int, eos_token_ids: tuple[int, ...] = ()):
+                 prefill_chunk: int, max_positions: int, eos_token_ids: tuple[int, ...] = (), step_tile: int = 0):
+        """``step_tile``: rows of the widest tile of the kernels that will run the step (whoever builds the scheduler asks
+        the kernels, or passes a setting); portions are trimmed so that a step's tokens come to whole tile rows. 0: no
+        trimming."""
         self.cache = cache
+        self.step_tile = int(step_tile)
         self.max_running, self.max_waiting = max_running, max_waiting
         self.max_step_tokens, self.prefill_chunk, self.max_positions = max_step_tokens, prefill_chunk, max_positions
         self.eos = set(eos_token_ids)
@@ -142,6 +148,14 @@ class Scheduler:
             chosen[request.id] = Planned(request, request.computed, count, wants_logits=count == request.pending)
             budget -= count
 
+        def make_room(request: Request, count: int) -> bool:
+            """``_make_room``; the tokens of requests that it pushed out of this step go back into the budget."""
+            nonlocal budget
+            before = sum(p.count for p in chosen.values())
+            ok = self._make_room(request, count, plan, chosen)
+            budget += before - sum(p.count for p in chosen.values())
+            return ok
+
         # 1 and 2: running requests, decodes first, then prompt portions, each group in admission order
         later: list[Request] = []
         for request in list(self.running):
@@ -152,7 +166,7 @@ class Scheduler:
             length = rc.length
             if len(request.prompt_ids) + len(request.output) - length != 1:
                 later.append(request)
-            elif budget > 0 and (length < rc.room or self._make_room(request, 1, plan, chosen)):
+            elif budget > 0 and (length < rc.room or make_room(request, 1)):
                 # a single token is never trimmed, and mostly its page is there already
                 chosen[request.id] = Planned(request, length, 1, True)
                 budget -= 1
@@ -160,14 +174,18 @@ class Scheduler:
             if request.cache is None:
                 continue
             count = self._portion(request, budget)
-            if count > 0 and self._make_room(request, count, plan, chosen):
+            if count > 0 and make_room(request, count):
                 take(request, count)
+                request.skipped = 0
+            elif request.cache is not None:
+                request.skipped += 1
 
         # 3: admit from the head of the queue
         while self.waiting and budget > 0 and len(self.running) < self.max_running and self.cache.free_slots > 0:
             request = self.waiting[0]
             count = self._portion(request, budget)
             if count <= 0:
+                request.skipped += 1
                 break
             needed = pages_for(count, self.cache.page_size)
             if needed > self.cache.usable_pages and not self.running:
@@ -188,27 +206,28 @@ class Scheduler:
             request.cache = rc
             self.running.append(request)
             take(request, count)
+            request.skipped = 0
 
         plan.entries = [chosen[r.id] for r in self.running if r.id in chosen]
         return plan
 
-    STEP_TILE = 256
-    """Rows of the widest GEMM tile: a step of a few tokens more than a multiple of it pays for a whole tile row."""
-
     def _portion(self, request: Request, budget: int) -> int:
         """How many of the request's pending tokens this step takes: all of them, or what the chunk size and the step's
-        remaining budget allow. A portion that does not finish its prompt is trimmed by up to an eighth so that the step's
-        tokens so far come to a whole number of GEMM tile rows: 2,048 prompt tokens beside 32 decode tokens would occupy
-        nine tile rows of 256, 2,016 beside 32 occupy eight, and the 32 tokens left over ride along with a later step.
-        For the same reason a long step does not take a sliver (less than a tile row) of another prompt."""
+        remaining budget allow. With a ``step_tile`` (rows of the widest tile of the kernels: a step of a few tokens more
+        than a multiple of it pays for a whole tile row) a portion that does not finish its prompt is trimmed by up to an
+        eighth so that the step's tokens so far come to a whole number of tile rows: with tiles of 256 rows, 2,048 prompt
+        tokens beside 32 decode tokens would occupy nine tile rows, 2,016 beside 32 occupy eight, and the 32 tokens left
+        over ride along with a later step. For the same reason a long step does not take a sliver (less than a tile row)
+        of another prompt, unless that prompt got nothing in the step before either: no request waits two steps in a row."""
         count = min(request.pending, self.prefill_chunk, budget)
         planned = self.max_step_tokens - budget
-        if 0 < count < request.pending:
-            if count >= 2 * self.STEP_TILE:
-                over = (planned + count) % self.STEP_TILE
+        tile = self.step_tile
+        if tile and 0 < count < request.pending:
+            if count >= 2 * tile:
+                over = (planned + count) % tile
                 if 0 < over <= count // 8:
                     count -= over
-            elif count < self.STEP_TILE and planned >= 2 * self.STEP_TILE and (planned + count) % self.STEP_TILE:
+            elif count < tile and planned >= 2 * tile and (planned + count) % tile and request.skipped == 0:
                 count = 0   # a sliver of a prompt at the end of a long step would only open another tile row
         return count
 

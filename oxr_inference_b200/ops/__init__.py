@@ -139,6 +139,7 @@ def _attn_lib(head_dim: int):
         lib.oxr_attn_tile_rows.argtypes = [i]
         lib.oxr_attn_tile_rows.restype = c_int
         lib.oxr_attn_head_dim.restype = c_int
+        lib.oxr_attn_last_short_kernel.restype = c_int
         if lib.oxr_attn_head_dim() != head_dim:
             raise BuildError(f"attention library for head size {head_dim} reports {lib.oxr_attn_head_dim()}")
         rows = tuple(lib.oxr_attn_tile_rows(kind) for kind in range(4))
@@ -150,6 +151,14 @@ def _attn_lib(head_dim: int):
         lib.oxr_set_chain(int(CHAIN_KERNELS))
         _attn[head_dim] = lib
     return lib
+
+
+SHORT_KERNELS = {0: None, 1: "attn_mma_decode_kernel", 2: "attn_tma_decode_kernel", 3: "attn_tma_decode_walk_kernel"}
+
+
+def last_short_attention_kernel(head_dim: int) -> str | None:
+    """Name of the split-KV kernel that the last ``paged_attention`` call with short tiles launched for this head size."""
+    return SHORT_KERNELS[_attn_lib(head_dim).oxr_attn_last_short_kernel()]
 
 
 def warm_up(head_dims: tuple[int, ...] = ()) -> None:
@@ -328,7 +337,15 @@ GENERIC_ROWS, DECODE_ROWS, PREFILL_ROWS, PREFILL_ROWS_TMA = 16, 16, 64, 256
 SHORT_MAX_TOKENS = 8
 """Requests that bring at most this many tokens go to the split-KV kernel, longer portions to the prefill kernel."""
 MAX_SPLITS = 32
-NUM_SMS = 148
+
+
+@functools.lru_cache(maxsize=None)
+def num_sms() -> int:
+    """Multiprocessors of the current device (the launchers ask the device as well); where no device is present, as
+    when plans are inspected on a machine without a GPU, a B200's 148."""
+    if torch.cuda.is_available():
+        return int(torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count)
+    return 148
 
 
 def _tokens_per_tile(num_heads: int, num_kv_heads: int, rows: int) -> int:
@@ -364,14 +381,14 @@ DECODE_BLOCKS_PER_SM = 2
 
 def attention_splits(n_short_tiles: int, num_heads: int, num_kv_heads: int, kv_len_bound: int) -> int:
     """Into how many pieces the split-KV kernel cuts each request's keys. Blocks run in waves of
-    ``NUM_SMS * DECODE_BLOCKS_PER_SM``; a block walks its piece's 64-key blocks one after the other and spends about
+    ``num_sms() * DECODE_BLOCKS_PER_SM``; a block walks its piece's 64-key blocks one after the other and spends about
     as long as 4.5 of them before its first keys arrive and after its last (measured on a B200: 7 us against 1.6 us per
     block). The number of pieces with the least waves x (4.5 + blocks per piece) wins, the smaller among equals; no
     piece is shorter than 128 keys. Depends only on sizes the host knows before the step (fixed inside a CUDA
     graph)."""
     group = num_heads // num_kv_heads
     blocks = max(1, n_short_tiles * num_kv_heads * -(-group // min(group, DECODE_ROWS)))
-    slots = NUM_SMS * DECODE_BLOCKS_PER_SM
+    slots = num_sms() * DECODE_BLOCKS_PER_SM
     key_blocks = max(1, -(-kv_len_bound // 64))
     best, best_cost = 1, None
     for splits in range(1, max(1, min(MAX_SPLITS, kv_len_bound // 128)) + 1):
@@ -503,12 +520,12 @@ def _gemm_cost(m: int, n: int, k: int, tile_n: int, splits: int) -> float:
     units = tiles * splits
     w_bytes = tile_n * 128 * per / rows        # blocks of the same wave share the W tiles of their column
     t = 2.2
-    full, rest = divmod(units, NUM_SMS)
-    for active, count in ((NUM_SMS, full), (rest, 1 if rest else 0)):
+    full, rest = divmod(units, num_sms())
+    for active, count in ((num_sms(), full), (rest, 1 if rest else 0)):
         fill, stream = per * step_us, active * w_bytes / 5.9e6
         t += count * (max(fill, stream) + 0.15 * min(fill, stream))
     if splits > 1:
-        waves = -(-units // NUM_SMS)
+        waves = -(-units // num_sms())
         t += (1 + 0.5 * (waves - 1)) * (6.4 + 0.065 * min(m, 128) * tile_n / 128)
     return t
 
@@ -555,13 +572,16 @@ def _gemm_few_rows_plan(m: int, n: int, k: int) -> int:
         return 0
     tiles, steps = -(-n // 128), -(-k // 64)
     most = 8 if (m > GEMM_FEW_ROWS_ANY_SHARES and steps >= 128) else 4
-    for shares in range(min(most, NUM_SMS // tiles, steps), 1, -1):
+    for shares in range(min(most, num_sms() // tiles, steps), 1, -1):
         if tiles <= _few_rows_clusters(shares):
             return shares if (m <= GEMM_FEW_ROWS_ANY_SHARES or shares >= 3) else 0
     return 0
 
 
 GEMM_PAIR_MIN_ROWS = 512
+STEP_TILE_ROWS = 256
+"""Rows of the widest GEMM tile (the two-SM kernel's): a step of a few tokens more than a multiple of it pays for a whole
+tile row. Whoever plans steps may ask for it."""
 
 
 @functools.lru_cache(maxsize=None)
@@ -574,7 +594,7 @@ def _gemm_pair_plan(m: int, n: int, k: int) -> int:
     least waves of pairs times the time of a k step at that width (0.094 + 0.00128 width microseconds)."""
     if m < GEMM_PAIR_MIN_ROWS:
         return 0
-    pairs = NUM_SMS // 2
+    pairs = num_sms() // 2
     best, best_cost = 0, None
     for tile_n in (256, 224, 192, 160, 128, 96, 64):
         tiles = -(-m // 256) * -(-n // tile_n)

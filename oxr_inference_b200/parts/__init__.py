@@ -1,9 +1,9 @@
 """Parts a decoder is assembled from; importing the package registers the built-in ones."""
 
 from oxr_inference_b200.parts import attention, block, mlp, norm, rope  # noqa: F401  (register themselves)
-from oxr_inference_b200.parts.base import (ARRANGEMENTS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, FeedForward,
-                                           GroupView, LayerCache, Mixer, Norm, PagedKVNeed, ParamInfo, Part,
-                                           PositionEncoding, Runtime, StateNeed, StepContext)
+from oxr_inference_b200.parts.base import (ARRANGEMENTS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS,
+                                           Embedding, FeedForward, GroupView, Head, LayerCache, Mixer, Norm, PagedKVNeed,
+                                           ParamInfo, Part, PositionEncoding, Runtime, StateNeed, StepContext)
 from oxr_inference_b200.parts.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
 
 
@@ -18,7 +18,7 @@ def __getattr__(name: str):
 
 
 __all__ = [
-    "ARRANGEMENTS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITION_ENCODINGS", "DecoderModel", "FeedForward", "GroupView",
-    "LayerCache", "LayerSpec", "Mixer", "ModelSpec", "Norm", "PagedKVNeed", "ParamInfo", "Part", "PartSpec",
+    "ARRANGEMENTS", "EMBEDDINGS", "FEED_FORWARDS", "HEADS", "MIXERS", "NORMS", "POSITION_ENCODINGS", "DecoderModel", "Embedding",
+    "FeedForward", "GroupView", "Head", "LayerCache", "LayerSpec", "Mixer", "ModelSpec", "Norm", "PagedKVNeed", "ParamInfo", "Part", "PartSpec",
     "PositionEncoding", "Runtime", "ScheduleEntry", "StateNeed", "StepContext",
 ]

@@ -10,6 +10,7 @@ Families and what each must provide:
   or nothing. ``tile_specs()`` (optional) asks the batch builder for tile lists.
 * **FeedForward** – ``forward(h) -> y``.
 * **Block arrangement** – puts a mixer and a feed-forward behind their norms.
+* **Embedding** – ``forward(ids) -> x``; **Head** – ``forward(h) -> fp32 logits`` (it is handed the embedding part).
 
 Every part lists its tensors with :meth:`Part.parameters` (local names; the spec's prefix makes them checkpoint
 names) and receives them one by one through :meth:`Part.assign`. No part knows which model it is in.
@@ -176,6 +177,21 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class Embedding(Part):
+    """Token ids (int32 ``[tokens]``) to the first hidden states, in the runtime's activation dtype."""
+
+    def forward(self, ids: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Head(Part):
+    """Normalised hidden states of the wanted rows to fp32 logits ``[rows, vocab]``. A head is built with the model's
+    embedding part as its second argument, so that it can share the table."""
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+
 # ------------------------------------------------------------------------------------------- registries
 class Registry:
     def __init__(self, family: str):
@@ -208,3 +224,5 @@ POSITION_ENCODINGS = Registry("position encoding")
 MIXERS = Registry("mixer")
 FEED_FORWARDS = Registry("feed-forward")
 ARRANGEMENTS = Registry("block arrangement")
+EMBEDDINGS = Registry("embedding")
+HEADS = Registry("output head")

@@ -8,12 +8,13 @@ import torch
 
 from oxr_inference_b200 import ops
 from oxr_inference_b200.cache.plan import CachePlan, make_cache_plan
-from oxr_inference_b200.parts.base import (ARRANGEMENTS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, ParamInfo,
-                                           Part, Runtime, StepContext)
+from oxr_inference_b200.parts.base import (ARRANGEMENTS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS,
+                                           Embedding, Head, ParamInfo, Part, Runtime, StepContext)
 from oxr_inference_b200.parts.spec import ModelSpec, PartSpec
 
 
-class TokenEmbedding(Part):
+@EMBEDDINGS.register("token_embedding")
+class TokenEmbedding(Embedding):
     """``x = table[ids]`` (oxr_runtime/language.py:155, oxr_runtime/decode_graph.py:75)."""
 
     def __init__(self, runtime: Runtime, *, vocab_size: int, hidden_size: int):
@@ -33,11 +34,12 @@ class TokenEmbedding(Part):
         return ops.embedding(ids, self.weight, self.runtime.dtype, self.runtime.status)
 
 
-class OutputHead(Part):
+@HEADS.register("linear_head")
+class OutputHead(Head):
     """``logits = h W^T`` in fp32 (oxr_runtime/language.py:158,213-214). ``tied``: W is the embedding table, which
     the reference does not offer (its head is always a tensor of its own)."""
 
-    def __init__(self, runtime: Runtime, embedding: TokenEmbedding, *, vocab_size: int, hidden_size: int, tied: bool):
+    def __init__(self, runtime: Runtime, embedding: Embedding, *, vocab_size: int, hidden_size: int, tied: bool):
         self.runtime, self.embedding = runtime, embedding
         self.vocab, self.hidden, self.tied = int(vocab_size), int(hidden_size), bool(tied)
         self.weight: torch.Tensor | None = None
@@ -62,7 +64,7 @@ class DecoderModel:
         self._named: dict[str, tuple[Part, str, ParamInfo]] = {}
         self._positions: dict[tuple, Any] = {}
 
-        self.embedding = TokenEmbedding(runtime, **spec.embedding.params)
+        self.embedding = EMBEDDINGS.build(spec.embedding.kind, runtime, **spec.embedding.params)
         self._register(self.embedding, spec.embedding.prefix)
 
         self.blocks = []
@@ -79,7 +81,7 @@ class DecoderModel:
 
         self.final_norm = NORMS.build(spec.final_norm.kind, runtime, **spec.final_norm.params)
         self._register(self.final_norm, spec.final_norm.prefix)
-        self.head = OutputHead(runtime, self.embedding, **spec.head.params)
+        self.head = HEADS.build(spec.head.kind, runtime, self.embedding, **spec.head.params)
         self._register(self.head, spec.head.prefix)
 
         for i, entry in enumerate(spec.schedule):

@@ -34,9 +34,13 @@ class StackedLinear:
 
     def assign(self, name: str, tensor: torch.Tensor) -> None:
         info = self.parameters()[name]
+        dtype = self.runtime.store_dtype(info, tensor.dtype)
         if self.weight is None:
-            dtype = self.runtime.store_dtype(info, tensor.dtype)
             self.weight = torch.empty((self.out_features, self.in_features), dtype=dtype, device=self.runtime.device)
+        elif dtype == torch.float32 and self.weight.dtype != torch.float32:
+            # one of the stacked tensors is stored in 32-bit: the whole product is then kept and multiplied in 32-bit,
+            # whichever tensor the file happens to list first
+            self.weight = self.weight.float()
         if self.interleave:
             g, which = self.interleave, list(self.outs).index(name)
             self.weight.view(-1, 2, g, self.in_features)[:, which].copy_(tensor.view(-1, g, self.in_features))

@@ -52,8 +52,9 @@ def test_greedy_generation_float32_is_the_plain_implementations(folders, name, g
 
 @pytest.mark.parametrize("name", ["A", "B"])
 def test_greedy_generation_bfloat16_picks_near_maxima_of_the_plain_logits(folders, name):
-    """bfloat16 may break a near-tie the other way; every token it picks must still be within the bfloat16 error
-    bound of the plain implementation's maximum, given the engine's own earlier tokens."""
+    """bfloat16 may break a near-tie the other way; every token it picks must still be within twice the largest
+    bfloat16 error seen on these models (2.4e-2 of the logits' scale, on both logits of a near-tie) of the plain
+    implementation's maximum, given the engine's own earlier tokens."""
     from oxr_inference_b200.sampling import SamplingParams
 
     folder = folders[name]
@@ -66,7 +67,7 @@ def test_greedy_generation_bfloat16_picks_near_maxima_of_the_plain_logits(folder
         scale = logits.abs().max().item()
         for i, tok in enumerate(c.token_ids):
             row = logits[len(prompt) - 1 + i]
-            assert row[tok] >= row.max() - 2 * 8e-2 * scale, f"token {i} = {tok} is not near the plain maximum"
+            assert row[tok] >= row.max() - 2 * 2.5e-2 * scale, f"token {i} = {tok} is not near the plain maximum"
 
 
 def test_cuda_graph_replay_equals_eager_steps(folders):
@@ -145,8 +146,7 @@ def test_repetition_penalty_follows_the_reference_rule(folders):
     engine = _engine(folder, "A", "float32")
     got = engine.generate([prompt], SamplingParams(max_tokens=8, repetition_penalty=1.8, ignore_eos=True))[0]
     assert got.token_ids == want
-    plain_greedy = QP.greedy(cfg, w, prompt, 8)
-    assert want != plain_greedy or True  # the penalty usually changes the tokens; equality is not an error
+    assert want != QP.greedy(cfg, w, prompt, 8), "this prompt and penalty were chosen so that the penalty changes the tokens"
 
 
 def test_step_failure_is_loud_and_pages_come_back(folders):
@@ -198,43 +198,44 @@ def test_command_line(folders, tmp_path):
     assert json.loads(out.read_text())["results"][0]["finish_reason"] == "length"
 
 
+def test_text_goes_in_and_out_through_the_tokenizer_of_the_model_folder(folders, tmp_path):
+    """With a ``tokenizer.json`` beside the weights a prompt may be text and the completion carries text
+    (oxr_runtime/prompt.py:26-38 loads the folder's tokenizer the same way); without one, text is refused."""
+    import shutil
+
+    from tokenizers import Tokenizer
+    from tokenizers.models import WordLevel
+    from tokenizers.pre_tokenizers import Whitespace
+
+    from oxr_inference_b200.sampling import SamplingParams
+
+    folder = tmp_path / "with_tokenizer"
+    shutil.copytree(folders["A"], folder)
+    words = ["<unk>", "the", "page", "reads", "a", "table", "of", "rows", "and", "columns", "total", "sum"]
+    vocab = {word: 20 + 3 * i for i, word in enumerate(words)}       # ids inside the model's 256, not 0..n
+    tok = Tokenizer(WordLevel(vocab, unk_token="<unk>"))
+    tok.pre_tokenizer = Whitespace()
+    tok.save(str(folder / "tokenizer.json"))
+    cfg, w = QP.read_model(folder)
+    text = "the page reads a table of rows"
+    ids = [vocab[x] for x in text.split()]
+    engine = _engine(folder, "A", "float32")
+    assert engine.tokenizer is not None
+    by_text, by_ids = engine.generate([text, ids], SamplingParams(max_tokens=6, ignore_eos=True))
+    want = QP.greedy(cfg, w, ids, 6)
+    assert by_text.token_ids == want and by_ids.token_ids == want and by_text.prompt_tokens == len(ids)
+    known = {i: word for word, i in vocab.items()}
+    assert by_text.text == " ".join(known[t] for t in want if t in known)   # ids without a word decode to nothing
+    plain = _engine(folders["A"], "A", "float32")
+    assert plain.tokenizer is None and plain.generate([ids], SamplingParams(max_tokens=2, ignore_eos=True))[0].text is None
+    with pytest.raises(ValueError, match="tokenizer.json"):
+        plain.add_request(text)
+
+
 def test_smoke_entry():
     import __graft_entry__
 
     __graft_entry__.smoke()
-
-
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_two_layers_at_qwen3_8b_sizes_match_the_plain_implementation(dtype):
-    """The serving sizes (hidden 4096, 32 query and 8 KV heads of 128, feed-forward 12288, vocabulary 151936, untied)
-    with two layers and random weights drawn on the device: logits of a prompt cut into a long portion (the prefill
-    kernels), a short one and single tokens (the decode kernels) against the plain implementation run in fp32 on the
-    same device with the same weights."""
-    from oxr_inference_b200.engine.batch import StepEntry
-    from oxr_inference_b200.engine.runtime import ModelRunner
-    from oxr_inference_b200.weights import random_tensor
-
-    cfg = {"architectures": ["Qwen3ForCausalLM"], "hidden_size": 4096, "intermediate_size": 12288, "num_hidden_layers": 2,
-           "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0,
-           "vocab_size": 151936, "tie_word_embeddings": False, "max_position_embeddings": 4096}
-    torch.backends.cuda.matmul.allow_tf32 = False
-    runner = ModelRunner.from_config(cfg, seed=5, dtype=dtype, page_size=16, num_pages=40, max_requests=2)
-    # the same weights for the plain implementation: same seed, same names, same device -> the same draws (bf16-rounded)
-    w = {name: random_tensor(name, info, 5, std=0.02, norm_std=0.1, device="cuda", dtype=torch.bfloat16).float()
-         for name, (_, _, info) in runner.model.named_parameters().items()}
-    g = torch.Generator().manual_seed(8)
-    ids = torch.randint(0, cfg["vocab_size"], (300,), generator=g).tolist()
-    want = QP.logits(cfg, w, ids)
-    del w
-    rc = runner.cache.open("r")
-    got, pos = [], 0
-    for c in (270, 6, 1, 1, 22):
-        assert runner.cache.reserve(rc, pos + c)
-        got.append(runner.step([StepEntry(rc, ids[pos:pos + c], [0, c - 1] if c > 1 else [0])]))
-        rows = [pos, pos + c - 1] if c > 1 else [pos]
-        util.compare(got[-1], want[rows], dtype, f"portion of {c} at {pos}")
-        pos += c
-    runner.check()
 
 
 @pytest.mark.parametrize("name,dtype", [("B", "float32"), ("A", "float32")])

@@ -17,9 +17,9 @@ def test_gemm_plan_is_a_valid_launch():
 def test_gemm_plan_fills_the_gpu():
     """Few rows and a narrow weight: shares of k or narrow tiles give about one block per SM; many rows: wide tiles."""
     tile_n, splits = ops._gemm_plan(64, 4096, 12288)
-    assert 100 <= -(-4096 // tile_n) * splits <= ops.NUM_SMS
+    assert 100 <= -(-4096 // tile_n) * splits <= ops.num_sms()
     tile_n, splits = ops._gemm_plan(64, 24576, 4096)
-    assert splits == 1 and 100 <= -(-24576 // tile_n) <= ops.NUM_SMS
+    assert splits == 1 and 100 <= -(-24576 // tile_n) <= ops.num_sms()
     assert ops._gemm_plan(8192, 24576, 4096) == (256, 1)
 
 

@@ -379,6 +379,17 @@ def _paged_case(g, q_lens, ctx_lens, H, KV, D, P, dtype, extra_pages=3):
     return q, k_cache, v_cache, table.to(DEV), cu
 
 
+def _release_behind_window(table, q_lens, ctx_lens, P, window):
+    """What the cache manager does as a window moves on: the block-table entries of pages that lie wholly behind the
+    window of a request's first new token become -1 (the pages were given back, and may hold another request's keys)."""
+    if window <= 0:
+        return table
+    table = table.clone()
+    for r, (ql, c) in enumerate(zip(q_lens, ctx_lens)):
+        table[r, :max(0, c - ql - window + 1) // P] = -1
+    return table
+
+
 def _tiles(ops, q_lens, H, KV, D, dtype, page_size=None):
     """The tile lists the kernels of this dtype want: each request's new tokens cut into tiles (with a page size: the
     lists for a cache whose K and V are fetched by TMA)."""
@@ -419,6 +430,7 @@ def test_paged_attention_mixed_batch(ops, dtype, generic, H, KV, D, P, window):
     q_lens = [1, 37, 2, 1, 70, 8, 9]      # decode tokens beside prompt portions, around the short/long boundary
     ctx_lens = [1, 37, 130, 200, 75, 8, 140]  # position 0 alone; a whole prompt; portions deep into a context
     q, k_cache, v_cache, table, cu = _paged_case(g, q_lens, ctx_lens, H, KV, D, P, dtype)
+    table = _release_behind_window(table, q_lens, ctx_lens, P, window)
     scale = D ** -0.5
     got = _run_attn(ops, q, k_cache, v_cache, table, cu, q_lens, ctx_lens, scale, window, generic)
     want = KP.paged_attention(q, k_cache, v_cache, cu, ctx_lens, table, scale, window)
@@ -495,7 +507,9 @@ def test_split_kv_decode_on_long_contexts(ops, H, KV, D, P, window):
     ctx_lens = [1500, 333, 1, 1029]
     assert ops.attention_splits(4 if H // KV <= 16 else 8, H, KV, max(ctx_lens)) > 1
     q, k_cache, v_cache, table, cu = _paged_case(g, q_lens, ctx_lens, H, KV, D, P, torch.bfloat16)
+    table = _release_behind_window(table, q_lens, ctx_lens, P, window)
     got = _run_attn(ops, q, k_cache, v_cache, table, cu, q_lens, ctx_lens, D ** -0.5, window)
+    assert ops.last_short_attention_kernel(D) == "attn_mma_decode_kernel"
     want = KP.paged_attention(q, k_cache, v_cache, cu, ctx_lens, table, D ** -0.5, window)
     torch.testing.assert_close(got.float(), want, atol=2e-2, rtol=2e-2)
 
@@ -508,7 +522,8 @@ def test_prefill_kernel_on_long_portions(ops, H, KV, D, P):
     ctx_lens = [300, 517, 1000]
     q, k_cache, v_cache, table, cu = _paged_case(g, q_lens, ctx_lens, H, KV, D, P, torch.bfloat16)
     for window in (0, 77):
-        got = _run_attn(ops, q, k_cache, v_cache, table, cu, q_lens, ctx_lens, D ** -0.5, window)
+        released = _release_behind_window(table, q_lens, ctx_lens, P, window)
+        got = _run_attn(ops, q, k_cache, v_cache, released, cu, q_lens, ctx_lens, D ** -0.5, window)
         want = KP.paged_attention(q, k_cache, v_cache, cu, ctx_lens, table, D ** -0.5, window)
         torch.testing.assert_close(got.float(), want, atol=2e-2, rtol=2e-2)
 
@@ -579,6 +594,8 @@ def test_split_kv_decode_with_tma_gathers(ops, H, KV, D, P, window):
     ctx_lens = [1500, 333, 1, 1029, 64]
     layers, layer = 3, 1
     q, k_cache, v_cache, table, cu = _paged_case(g, q_lens, ctx_lens, H, KV, D, P, torch.bfloat16)
+    table = _release_behind_window(table, q_lens, ctx_lens, P, window)
+    assert window == 0 or (table[0] == -1).sum() >= (1500 - 300) // P - 1
     k_pool = torch.randn(layers, *k_cache.shape, device=DEV, generator=g).bfloat16()
     v_pool = torch.randn(layers, *v_cache.shape, device=DEV, generator=g).bfloat16()
     k_pool[layer], v_pool[layer] = k_cache, v_cache
@@ -590,6 +607,7 @@ def test_split_kv_decode_with_tma_gathers(ops, H, KV, D, P, window):
     common = dict( cu_q=torch.tensor(cu, dtype=torch.int32, device=DEV), ctx_lens=torch.tensor(ctx_lens, dtype=torch.int32, device=DEV),
                   block_table=table, page_size=P, scale=D ** -0.5, window=window, kv_len_bound=max(ctx_lens), status=status)
     got = ops.paged_attention(q, k_pool[layer], v_pool[layer], tiles=tma_tiles, kv_maps=maps, layer_in_pool=layer, **common)
+    assert ops.last_short_attention_kernel(D) == "attn_tma_decode_kernel"
     plain_gather = ops.paged_attention(q, k_pool[layer], v_pool[layer], tiles=tiles, **common)
     ops.check_status(status)
     want = KP.paged_attention(q, k_cache, v_cache, cu, ctx_lens, table, D ** -0.5, window)
@@ -615,12 +633,44 @@ def test_prefill_kernel_with_tma_gathers_on_long_portions(ops, H, KV, D, P):
     assert any(spec[0] == max(1, 256 // min(H // KV, 256)) and spec[1] > 1 for spec in tiles), "the long list is cut for 256-row tiles"
     status = ops.new_status(DEV)
     for window in (0, 77):
+        released = _release_behind_window(table, q_lens, ctx_lens, P, window)
         got = ops.paged_attention(q, k_pool[layer], v_pool[layer], tiles=tiles, cu_q=torch.tensor(cu, dtype=torch.int32, device=DEV),
-                                  ctx_lens=torch.tensor(ctx_lens, dtype=torch.int32, device=DEV), block_table=table, page_size=P,
+                                  ctx_lens=torch.tensor(ctx_lens, dtype=torch.int32, device=DEV), block_table=released, page_size=P,
                                   scale=D ** -0.5, window=window, kv_len_bound=max(ctx_lens), status=status, kv_maps=maps, layer_in_pool=layer)
         ops.check_status(status)
         want = KP.paged_attention(q, k_cache, v_cache, cu, ctx_lens, table, D ** -0.5, window)
         torch.testing.assert_close(got.float(), want, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("H,KV,D,P,n_req,long_ctx", [(32, 8, 128, 16, 80, 2000), (16, 4, 64, 8, 50, 6000), (16, 16, 128, 32, 30, 1300)])
+@pytest.mark.parametrize("window", [0, 300])
+def test_split_kv_decode_walking_over_more_pieces_than_blocks_fit(ops, H, KV, D, P, n_req, long_ctx, window):
+    """More (request, KV head, split) pieces than blocks fit on the GPU at once: the launcher then starts one round of
+    blocks that walk over the pieces. Ragged contexts (one key; around a key block's edge; thousands), mostly one
+    decoded token each and a few short portions; a shape with one split and shapes with several; behind a window the
+    block tables name released pages."""
+    g = torch.Generator(device=DEV).manual_seed(90 + D + n_req)
+    ctx_lens = ([1, 63, 64, 65, long_ctx, 129, 2, 700] * n_req)[:n_req]
+    q_lens = [1] * n_req
+    q_lens[3], q_lens[7] = 3, 8         # short portions ride in the same kernel
+    ctx_lens = [max(c, ql) for c, ql in zip(ctx_lens, q_lens)]
+    q, k_cache, v_cache, table, cu = _paged_case(g, q_lens, ctx_lens, H, KV, D, P, torch.bfloat16)
+    released = _release_behind_window(table, q_lens, ctx_lens, P, window)
+    maps = ops.make_kv_maps(k_cache[None], v_cache[None], P)
+    assert maps is not None
+    tiles = _tiles(ops, q_lens, H, KV, D, torch.bfloat16, P)
+    short = ops.attention_tile_specs(H, KV, D, torch.bfloat16, P)[0]
+    splits = ops.attention_splits(tiles[short][2], H, KV, max(ctx_lens))
+    assert tiles[short][2] * KV * splits > 2 * ops.num_sms(), "the case must outgrow one round of blocks"
+    assert (n_req == 30) == (splits == 1), "one shape with a single piece per request, the others with several"
+    status = ops.new_status(DEV)
+    got = ops.paged_attention(q, k_cache, v_cache, tiles=tiles, cu_q=torch.tensor(cu, dtype=torch.int32, device=DEV),
+                              ctx_lens=torch.tensor(ctx_lens, dtype=torch.int32, device=DEV), block_table=released, page_size=P,
+                              scale=D ** -0.5, window=window, kv_len_bound=max(ctx_lens), status=status, kv_maps=maps, layer_in_pool=0)
+    ops.check_status(status)
+    assert ops.last_short_attention_kernel(D) == "attn_tma_decode_walk_kernel"
+    want = KP.paged_attention(q, k_cache, v_cache, cu, ctx_lens, table, D ** -0.5, window)
+    torch.testing.assert_close(got.float(), want, atol=2e-2, rtol=2e-2)
 
 
 def test_tma_gathers_are_refused_for_sizes_they_cannot_do(ops):

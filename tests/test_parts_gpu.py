@@ -186,15 +186,16 @@ def _register_toy():
                 return StateNeed((self.hidden,), torch.float32)
 
             def forward(self, h, ctx, cache):
-                out = torch.empty_like(h)
-                cu = ctx.cu_q.tolist()
-                for r in range(ctx.n_requests):
-                    a, b = cu[r], cu[r + 1]
-                    slot = int(ctx.state_slots[r])
-                    run = cache.state[slot] + torch.cumsum(h[a:b].float(), 0)
-                    cache.state[slot] = run[-1]
-                    out[a:b] = (run / (ctx.positions[a:b].float() + 1)[:, None] * self.gain).to(h.dtype)
-                return out
+                # no host round trip (the step may be captured in a CUDA graph): a running sum over the packed tokens,
+                # minus what the requests before this one brought, plus the request's sum so far from its state slot
+                x = h.float()
+                total = torch.cumsum(x, 0)
+                cu, req = ctx.cu_q.long(), ctx.req_of_token.long()
+                before = (total[cu[:-1]] - x[cu[:-1]])[req]
+                slots = ctx.state_slots.long()
+                run = cache.state[slots][req] + total - before
+                cache.state.index_copy_(0, slots, run[cu[1:] - 1])
+                return (run / (ctx.positions.float() + 1)[:, None] * self.gain).to(h.dtype)
 
     if "ToyScheduleForTests" not in ARCHITECTURES:
         def spec(c):
@@ -296,20 +297,94 @@ def test_a_toy_architecture_with_a_stateful_mixer_registers_builds_and_steps(tmp
     torch.testing.assert_close(again.cpu(), want["a"], atol=1e-4, rtol=1e-4)
 
 
+def test_the_toy_stateful_architecture_generates_through_the_engine_with_and_without_cuda_graphs(tmp_path):
+    """The same toy model through ``Engine.generate``: with CUDA graphs a step whose bucket is captured for the first
+    time must still advance each request's state once, not twice; with so few pages that requests are preempted, a
+    recomputed request starts from zeroed state again. Greedy tokens equal the plain statement's either way."""
+    from safetensors.torch import load_file
+
+    from oxr_inference_b200.config import EngineSettings
+    from oxr_inference_b200.engine.api import Engine
+    from oxr_inference_b200.sampling import SamplingParams
+    from oxr_inference_b200.weights import write_random_model
+
+    _register_toy()
+    folder = write_random_model(TOY, tmp_path / "toy", seed=3, dtype="float32", std=0.15)
+    w = load_file(str(folder / "model.safetensors"))
+    g = torch.Generator().manual_seed(9)
+    prompts = [torch.randint(0, 50, (n,), generator=g).tolist() for n in (3, 17, 9, 30, 1)]
+    new = 24
+
+    def plain_greedy(ids):
+        ids, out = list(ids), []
+        for _ in range(new):
+            out.append(int(_toy_plain(w, ids)[-1].argmax()))
+            ids.append(out[-1])
+        return out
+
+    want = [plain_greedy(p) for p in prompts]
+    for graphs, pages in ((True, 64), (False, 64), (True, 14)):
+        engine = Engine(folder, EngineSettings(dtype="float32", page_size=8, num_pages=pages, max_running=4, cuda_graphs=graphs,
+                                               max_step_tokens=64, prefill_chunk=16))
+        got = engine.generate(prompts, SamplingParams(max_tokens=new, ignore_eos=True))
+        assert [c.token_ids for c in got] == want, f"cuda_graphs={graphs}, {pages} pages"
+        assert (engine.counters["graph_steps"] > 0) == graphs
+        if pages == 14:
+            assert engine.preemptions > 0, "the small pool was meant to force a preemption"
+        engine.runner.cache.check()
+
+
 # ---------------------------------------------------------------------------------------------------------------
 # A second toy architecture, also defined here: layer 0 is the built-in attention (no q/k norm) under a position
 # encoding of its own (angles that grow linearly in the pair index) with a feed-forward that ROUTES each token to two
 # of four small experts; layer 1 is the built-in attention with NO position encoding and a window, with the built-in
-# feed-forward; the head is untied. Parts are chosen layer by layer; nothing under oxr_inference_b200/ knows them.
+# feed-forward; the embedding is scaled by a constant and the head, untied, adds a bias (both defined here). Parts are
+# chosen layer by layer; nothing under oxr_inference_b200/ knows them.
 # ---------------------------------------------------------------------------------------------------------------
 TOY2 = {"architectures": ["ToyRoutedForTests"], "hidden_size": 48, "intermediate_size": 40, "vocab_size": 61, "heads": 6,
-        "kv_heads": 3, "head_dim": 16, "eps": 1e-6, "experts": 4, "expert_size": 24, "window": 6, "max_positions": 96}
+        "kv_heads": 3, "head_dim": 16, "eps": 1e-6, "experts": 4, "expert_size": 24, "window": 6, "max_positions": 96,
+        "embedding_scale": 3.0}
 
 
 def _register_toy2():
     from oxr_inference_b200.config.registry import ARCHITECTURES, Architecture, register_architecture
-    from oxr_inference_b200.parts import (FEED_FORWARDS, POSITION_ENCODINGS, FeedForward, LayerSpec, ModelSpec, ParamInfo, PartSpec,
-                                          PositionEncoding, ScheduleEntry)
+    from oxr_inference_b200 import ops
+    from oxr_inference_b200.parts import (EMBEDDINGS, FEED_FORWARDS, HEADS, POSITION_ENCODINGS, Embedding, FeedForward, Head, LayerSpec,
+                                          ModelSpec, ParamInfo, PartSpec, PositionEncoding, ScheduleEntry)
+
+    if "toy_scaled_embedding" not in EMBEDDINGS:
+        @EMBEDDINGS.register("toy_scaled_embedding")
+        class ScaledEmbedding(Embedding):
+            """x = scale * table[ids]"""
+
+            def __init__(self, runtime, *, vocab_size, hidden_size, scale):
+                self.runtime, self.shape, self.scale, self.weight = runtime, (vocab_size, hidden_size), scale, None
+
+            def parameters(self):
+                return {"weight": ParamInfo(self.shape)}
+
+            def assign(self, name, tensor):
+                self.weight = tensor.to(self.runtime.device, self.runtime.store_dtype(self.parameters()[name], tensor.dtype))
+
+            def forward(self, ids):
+                return (self.weight[ids.long()].float() * self.scale).to(self.runtime.dtype)
+
+    if "toy_biased_head" not in HEADS:
+        @HEADS.register("toy_biased_head")
+        class BiasedHead(Head):
+            """logits = h W^T + b, with a matrix of its own"""
+
+            def __init__(self, runtime, embedding, *, vocab_size, hidden_size):
+                self.runtime, self.v, self.h, self.w = runtime, vocab_size, hidden_size, {}
+
+            def parameters(self):
+                return {"weight": ParamInfo((self.v, self.h)), "bias": ParamInfo((self.v,), role="vector")}
+
+            def assign(self, name, tensor):
+                self.w[name] = tensor.to(self.runtime.device, self.runtime.store_dtype(self.parameters()[name], tensor.dtype)).contiguous()
+
+            def forward(self, h):
+                return ops.linear(h, self.w["weight"], torch.float32) + self.w["bias"]
 
     if "toy_linear_angles" not in POSITION_ENCODINGS:
         @POSITION_ENCODINGS.register("toy_linear_angles")
@@ -371,9 +446,10 @@ def _register_toy2():
             )
             return ModelSpec(
                 architecture="ToyRoutedForTests", hidden_size=H, vocab_size=c["vocab_size"],
-                embedding=PartSpec("token_embedding", {"vocab_size": c["vocab_size"], "hidden_size": H}, prefix="model.embed_tokens."),
+                embedding=PartSpec("toy_scaled_embedding", {"vocab_size": c["vocab_size"], "hidden_size": H, "scale": c["embedding_scale"]},
+                                   prefix="model.embed_tokens."),
                 layers=layers, schedule=(ScheduleEntry(0), ScheduleEntry(1)), final_norm=norm("model.norm."),
-                head=PartSpec("linear_head", {"vocab_size": c["vocab_size"], "hidden_size": H, "tied": False}, prefix="lm_head."),
+                head=PartSpec("toy_biased_head", {"vocab_size": c["vocab_size"], "hidden_size": H}, prefix="lm_head."),
                 max_positions=c["max_positions"])
 
         register_architecture(Architecture("ToyRoutedForTests", lambda raw, gen: dict(raw), spec))
@@ -382,7 +458,7 @@ def _register_toy2():
 def _toy2_plain(w, ids):
     c, n, eps = TOY2, len(ids), TOY2["eps"]
     H, KV, D = c["heads"], c["kv_heads"], c["head_dim"]
-    x = w["model.embed_tokens.weight"][torch.tensor(ids)]
+    x = c["embedding_scale"] * w["model.embed_tokens.weight"][torch.tensor(ids)]
     angles = torch.outer(torch.arange(n, dtype=torch.float), (torch.arange(D // 2, dtype=torch.float) + 1) / 7)
     for layer in (0, 1):
         p = f"model.layers.{layer}."
@@ -410,7 +486,7 @@ def _toy2_plain(w, ids):
             x = x + y
         else:
             x = x + QP.swiglu(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
-    return QP.rms_norm(x, w["model.norm.weight"], eps) @ w["lm_head.weight"].T
+    return QP.rms_norm(x, w["model.norm.weight"], eps) @ w["lm_head.weight"].T + w["lm_head.bias"]
 
 
 def test_a_toy_architecture_with_routed_experts_and_its_own_position_encoding(tmp_path):
@@ -424,7 +500,7 @@ def test_a_toy_architecture_with_routed_experts_and_its_own_position_encoding(tm
     folder = write_random_model(TOY2, tmp_path / "toy2", seed=4, dtype="float32", std=0.2)
     w = load_file(str(folder / "model.safetensors"))
     assert w["model.layers.0.moe.w_in"].shape == (4, 24, 48) and "model.layers.0.self_attn.q_norm.weight" not in w
-    assert "model.layers.1.self_attn.q_norm.weight" in w and "lm_head.weight" in w
+    assert "model.layers.1.self_attn.q_norm.weight" in w and "lm_head.weight" in w and w["lm_head.bias"].shape == (61,)
     runner = ModelRunner.from_folder(folder, dtype="float32", page_size=8, num_pages=24, max_requests=2)
     plan = runner.model.cache_plan
     assert len(plan.groups) == 2, "a layer that keeps all keys and a layer with a window have pools of their own"
@@ -433,7 +509,8 @@ def test_a_toy_architecture_with_routed_experts_and_its_own_position_encoding(tm
     ids = torch.randint(0, TOY2["vocab_size"], (45,), generator=g).tolist()
     want = _toy2_plain(w, ids)
     # the routing must actually vary, or the test would not see a wrong expert
-    h0 = QP.rms_norm(w["model.embed_tokens.weight"][torch.tensor(ids)], w["model.layers.0.input_layernorm.weight"], TOY2["eps"])
+    x0 = TOY2["embedding_scale"] * w["model.embed_tokens.weight"][torch.tensor(ids)]
+    h0 = QP.rms_norm(x0, w["model.layers.0.input_layernorm.weight"], TOY2["eps"])
     assert len({int(i) for i in (h0 @ w["model.layers.0.moe.router.weight"].T).argmax(-1)}) >= 3
     rc = runner.cache.open("r")
     got, pos = [], 0

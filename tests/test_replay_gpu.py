@@ -146,7 +146,7 @@ def _qwen3(h, inter, layers, heads, kv, d, vocab, eps=1e-6, theta=1e4, tie=False
 
 
 # Sizes that the two tiny configurations do not reach: a width and an intermediate size that are no multiple of 8
-# (66: not even of 4), head sizes 48, 80, 96 and 112, one head, as many groups as heads, a window of 17 on the first layer.
+# (66: not even of 4), head sizes 48, 80, 96, 112 and 256, one head, as many groups as heads, windows on some layers.
 ODD_SIZES = {
     "width100": _qwen3(100, 100, 2, 7, 1, 16, 1001),
     "width66": _qwen3(66, 36, 2, 11, 11, 16, 97),
@@ -155,7 +155,16 @@ ODD_SIZES = {
     "head96_window": _qwen3(192, 264, 2, 2, 2, 96, 777, window=17, types=["sliding_attention", "full_attention"]),
     "head112": _qwen3(224, 96, 1, 2, 1, 112, 50, eps=1e-3),
     "one_head256": _qwen3(64, 48, 1, 1, 1, 256, 64),
+    # head sizes 64 and 128 with a windowed layer and small pages: in bfloat16 these run the TMA split-KV kernel and the
+    # tcgen05 prefill kernel over block tables whose front pages the window has passed and given back
+    "head64_window": _qwen3(128, 96, 2, 4, 2, 64, 300, window=40, types=["sliding_attention", "full_attention"]),
+    "head128_window": _qwen3(256, 128, 3, 2, 1, 128, 211, eps=1e-5, window=33,
+                             types=["full_attention", "sliding_attention", "sliding_attention"]),
 }
+# Tokens per page of each: sizes that do not divide 64 (24, 40), that are larger than 64 (128, 256), and the small
+# powers of two that TMA gathers take.
+ODD_PAGES = {"width100": 24, "width66": 40, "head48": 256, "head80": 8, "head96_window": 16, "head112": 128, "one_head256": 64,
+             "head64_window": 8, "head128_window": 16}
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -172,7 +181,9 @@ def test_random_trace_at_odd_sizes(name, dtype, tmp_path):
     finally:
         del util.CONFIGS[name]
     vocab = ODD_SIZES[name]["vocab_size"]
-    r = Replay(folder, dtype, tmp_path / "out", max_tokens=448, page_size=rng.choice([8, 16, 64]))
+    page_size = ODD_PAGES[name]
+    max_tokens = 448 if page_size <= 64 else 3 * page_size   # few pages either way, so that they are used again
+    r = Replay(folder, dtype, tmp_path / "out", max_tokens=max_tokens, page_size=page_size)
     lengths = [rng.choice([1, 2, 3, 15, 16, 17, 33, 64, 65, 100, 129, rng.randint(1, 190)]) for _ in range(8)]
     seqs = {f"q{i}": [rng.randrange(vocab) for _ in range(n)] for i, n in enumerate(lengths)}
     want = {k: plain_logits(folder, v) for k, v in seqs.items()}
@@ -180,11 +191,13 @@ def test_random_trace_at_odd_sizes(name, dtype, tmp_path):
     pos = {k: 0 for k in seqs}
     waiting, live, step_no = list(seqs), [], 0
 
+    unit = max(64, page_size)   # a request's count is rounded up to 64, or to the engine's pages if those are larger
+
     def held(k):
-        return -(-len(seqs[k]) // 64) * 64
+        return -(-len(seqs[k]) // unit) * unit
 
     while waiting or live:
-        while waiting and len(live) < 4 and sum(held(k) for k in live) + held(waiting[0]) <= 448:
+        while waiting and len(live) < 4 and sum(held(k) for k in live) + held(waiting[0]) <= max_tokens:
             live.append(waiting.pop(0))
         entries, checks, ended = [], {}, []
         for k in live:

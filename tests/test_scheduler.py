@@ -230,11 +230,11 @@ def test_a_portion_that_does_not_finish_its_prompt_is_trimmed_to_whole_tile_rows
     from oxr_inference_b200.engine.scheduler import Scheduler
 
     s = Scheduler.__new__(Scheduler)
-    s.prefill_chunk, s.max_step_tokens = 2048, 2080
+    s.prefill_chunk, s.max_step_tokens, s.step_tile = 2048, 2080, 256
 
     class R:
-        def __init__(self, pending):
-            self.pending = pending
+        def __init__(self, pending, skipped=0):
+            self.pending, self.skipped = pending, skipped
     assert s._portion(R(4096), 2080 - 32) == 2016
     assert s._portion(R(2080), 2080 - 32) == 2016
     assert s._portion(R(64), 2080 - 32) == 64              # a portion that finishes the prompt is never trimmed
@@ -243,5 +243,48 @@ def test_a_portion_that_does_not_finish_its_prompt_is_trimmed_to_whole_tile_rows
     assert s._portion(R(4096), 300) == 300                 # small portions of a short step are left alone
     assert s._portion(R(4096), 32) == 0                    # but a sliver after 2,048 tokens would open a ninth tile row
     assert s._portion(R(20), 32) == 20                     # unless it finishes its prompt
+    assert s._portion(R(4096, skipped=1), 32) == 32        # or it got nothing in the step before either
     s.prefill_chunk, s.max_step_tokens = 1000, 2048
     assert s._portion(R(4096), 2048 - 40) == 1000 - (40 + 1000) % 256   # 1040 -> 1024 tokens in the step
+    s.step_tile = 0                                        # no tile size given: portions are what chunk and budget allow
+    assert s._portion(R(4096), 2048 - 40) == 1000 and s._portion(R(4096), 8) == 8
+
+
+def test_a_prompt_is_not_skipped_two_steps_in_a_row_by_the_sliver_rule():
+    """Decoding requests nearly fill a long step; what is left is less than a tile row. The running prompt is passed
+    over once, then takes its sliver."""
+    plan = make_cache_plan([PagedKVNeed(1, 16, 0)], [None])
+    cache = CacheManager(plan, page_size=4, num_pages=4000, max_requests=600)
+    s = Scheduler(cache, max_running=600, max_waiting=1000, max_step_tokens=560, prefill_chunk=64, max_positions=10000,
+                  eos_token_ids=(), step_tile=256)
+    for _ in range(540):
+        s.add([1], SamplingParams(max_tokens=50, ignore_eos=True))
+    long_one = s.add(list(range(3, 80)) * 8, SamplingParams(max_tokens=2, ignore_eos=True))
+    got = []
+    for _ in range(8):
+        plan_ = s.schedule()
+        got.append(sum(p.count for p in plan_.entries if p.request is long_one))
+        s.commit(plan_, {p.request.id: 5 for p in plan_.entries if p.wants_logits})
+        s.cache.check()
+    zeros = [i for i, c in enumerate(got) if c == 0]
+    assert zeros and all(b - a > 1 for a, b in zip(zeros, zeros[1:])), f"portions per step: {got}"
+    assert sum(got) > 0 and all(c in (0, 20) for c in got), f"portions per step: {got}"
+
+
+def test_tokens_of_a_request_preempted_inside_a_step_go_back_into_the_budget():
+    """A decoding request needs a page, the newest request (already chosen for this step) is preempted: its token is no
+    longer counted against the step."""
+    s = _scheduler(num_pages=5, page_size=4, max_running=3, max_step_tokens=3, prefill_chunk=16)
+    a = s.add([1, 2, 3], SamplingParams(max_tokens=40, ignore_eos=True))
+    b = s.add([4, 5, 6], SamplingParams(max_tokens=40, ignore_eos=True))
+    # run until both decode and the pool (4 usable pages) is full
+    for _ in range(200):
+        plan_ = s.schedule()
+        s.commit(plan_, {p.request.id: 7 for p in plan_.entries if p.wants_logits})
+        s.cache.check()
+        if plan_.preempted:
+            break
+    else:
+        raise AssertionError("no preemption happened")
+    assert plan_.preempted == [b] and [p.request for p in plan_.entries] == [a]
+    assert sum(p.count for p in plan_.entries) == 1

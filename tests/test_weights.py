@@ -135,3 +135,26 @@ def test_shape_only_model_lists_names():
     named = shape_only_model(TINY_A).named_parameters()
     assert "model.layers.1.self_attn.o_proj.weight" in named and "lm_head.weight" not in named
     assert named["model.layers.0.self_attn.q_norm.weight"][2].role == "vector"
+
+
+def test_stacked_tensors_of_mixed_dtype_are_kept_in_32_bit_whatever_their_order():
+    """q/k/v (or gate/up) share one buffer. If any of them is stored in 32-bit the buffer is 32-bit, and the values of
+    all of them are exact, whichever came first."""
+    import torch
+
+    from oxr_inference_b200.parts.base import Runtime
+    from oxr_inference_b200.parts.linear import StackedLinear
+
+    rt = Runtime(device=torch.device("cpu"), dtype=torch.bfloat16, max_positions=8, status=torch.zeros(4, dtype=torch.int32))
+    a32 = torch.randn(4, 8)
+    b16 = torch.randn(6, 8).bfloat16()
+    for order in (("a", "b"), ("b", "a")):
+        lin = StackedLinear(rt, 8, {"a": 4, "b": 6})
+        for name in order:
+            lin.assign(name, a32 if name == "a" else b16)
+        assert lin.weight.dtype == torch.float32
+        assert torch.equal(lin.weight[:4], a32) and torch.equal(lin.weight[4:], b16.float())
+    lin = StackedLinear(rt, 8, {"a": 4, "b": 6})
+    lin.assign("a", a32.bfloat16())
+    lin.assign("b", b16)
+    assert lin.weight.dtype == torch.bfloat16

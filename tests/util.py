@@ -68,9 +68,26 @@ def plain_logits(folder: Path, ids: list[int]) -> torch.Tensor:
     return _plain_cache[key]
 
 
+OBSERVED: dict[str, list[float]] = {}
+"""Largest bfloat16 errors seen per test (rms of rms, largest of scale); written as JSON to the file that the
+environment variable OXR_TEST_ERRORS names, when it is set, as the process ends."""
+
+
+def _record(rms: float, worst: float) -> None:
+    import atexit
+    import os
+
+    if not OBSERVED and os.environ.get("OXR_TEST_ERRORS"):
+        atexit.register(lambda: Path(os.environ["OXR_TEST_ERRORS"]).write_text(json.dumps(OBSERVED, indent=1)))
+    key = os.environ.get("PYTEST_CURRENT_TEST", "?").split(" ")[0]
+    seen = OBSERVED.setdefault(key, [0.0, 0.0])
+    seen[0], seen[1] = max(seen[0], rms), max(seen[1], worst)
+
+
 def compare(got: torch.Tensor, want: torch.Tensor, dtype: str, what: str = "") -> None:
     """float32: 1e-4 of the logits' scale, absolute and relative. bfloat16: rms error <= 3e-2 of the rms, largest
-    error <= 8e-2 of the largest logit (about twice what the roundings of a few layers add up to)."""
+    error <= 5e-2 of the largest logit. Observed on a B200 over all cuttings: at most 1.7e-2 / 2.4e-2 on the tiny
+    configurations and the odd sizes, 2.5e-2 / 2.7e-2 on four layers of Qwen3-8B's sizes with sharpened attention."""
     got, want = got.float().cpu(), want.float().cpu()
     assert got.shape == want.shape, f"{what}: shape {tuple(got.shape)} vs {tuple(want.shape)}"
     assert torch.isfinite(got).all(), f"{what}: non-finite logits"
@@ -83,7 +100,8 @@ def compare(got: torch.Tensor, want: torch.Tensor, dtype: str, what: str = "") -
     else:
         rms = (err.pow(2).mean().sqrt() / want.pow(2).mean().sqrt()).item()
         worst_row = int(err.max(1).values.argmax())
-        assert rms <= 3e-2 and err.max().item() <= 8e-2 * scale, (
+        _record(rms, err.max().item() / scale)
+        assert rms <= 3e-2 and err.max().item() <= 5e-2 * scale, (
             f"{what}: rms error {rms:.3e} of rms, largest {err.max().item() / scale:.3e} of scale, at row {worst_row}")
 
 
