@@ -42,6 +42,8 @@ QWEN3_32B = {
 }
 CONTEXT = 2048
 PREFILL_TOKENS = 2048
+LONG_CONTEXTS = (8192, 32768)      # further decode points at batch 8
+LONG_PREFILL_TOKENS = 8192         # a further prefill point
 METRIC = "Qwen3-8B bf16 decode tok/s at batch 8 (context 2048)"
 
 
@@ -137,30 +139,20 @@ def serving_workload(which: str) -> int:
     V = cfg["vocab_size"]
     engine = Engine(random_config=cfg, seed=0, settings=EngineSettings(
         dtype="bfloat16", page_size=16, kv_cache_gb=kv_gb, max_running=max_running, max_step_tokens=budget, prefill_chunk=2048,
-        max_positions=cfg["max_position_embeddings"], cuda_graphs=True))
+        max_positions=cfg["max_position_embeddings"], cuda_graphs=True, profile=True))
     prompts = [[rng.randrange(V) for _ in range(p)] for p, _ in work]
     params = [SamplingParams(max_tokens=o, ignore_eos=True) for _, o in work]
     engine.generate(prompts[:2], [SamplingParams(max_tokens=4, ignore_eos=True)] * 2)   # warm-up: libraries, first graphs
     before = dict(engine.counters)
     launches = ops.launch_count
-    # Engine.generate's loop, written out so that every step is timed (a step ends with its one synchronisation)
-    pending = list(zip(prompts, params))
-    requests, steps = [], []   # steps: (ms, tokens in the step, decode only?, tokens held by the running requests)
+    engine.profile.steps.clear()
     torch.cuda.synchronize()
     t0 = time.perf_counter()
-    while pending or engine.has_work():
-        while pending and len(engine.scheduler.waiting) < engine.scheduler.max_waiting:
-            prompt, p = pending.pop(0)
-            requests.append(engine.add_request(prompt, p))
-        tokens_before, graphs_before = engine.counters["step_tokens"], engine.counters["graph_steps"]
-        held = sum(r.cache.length for r in engine.scheduler.running if r.cache is not None)
-        t = time.perf_counter()
-        engine.step()
-        steps.append(((time.perf_counter() - t) * 1e3, engine.counters["step_tokens"] - tokens_before,
-                      engine.counters["graph_steps"] > graphs_before, held))
+    done = engine.generate(prompts, params)
     torch.cuda.synchronize()
     seconds = time.perf_counter() - t0
-    done = [engine._done.pop(r.id) for r in requests]
+    # the engine's own per-step log: device milliseconds between two CUDA events around each step
+    steps = [(st["ms"], st["tokens"], st["graph"], st["held"]) for st in engine.profile.steps]
     out_tokens = sum(len(c.token_ids) for c in done)
     in_tokens = sum(len(p) for p in prompts)
     assert all(len(c.token_ids) == o for c, (_, o) in zip(done, work))
@@ -188,6 +180,7 @@ def serving_workload(which: str) -> int:
         "decode_step_hbm_frac": percentiles(decode_fracs, (10, 50, 90)), "mixed_step_gemm_frac": percentiles(mixed_flops, (10, 50, 90)),
         "slowest_steps_ms": [round(ms, 1) for ms, *_ in sorted(steps, reverse=True)[:4]],
         "weight_gb_per_decode_step": round(weight_bytes / 1e9, 2), "peaks": source,
+        "stages": engine.profile.summary(),
         "preemptions": engine.preemptions, "gpu_launches": ops.launch_count - launches, "dtype": "bf16",
         "data": "synthetic uniform token ids, random weights N(0, 0.02)"}))
     return 0
@@ -200,7 +193,8 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"], help="fewer layers than the model has (named in config)")
-    ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64 (quick runs)")
+    ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64 and the further points (quick runs)")
+    ap.add_argument("--skip-serving", action="store_true", help="leave the two serving workloads out of `points`")
     ap.add_argument("--context", type=int, default=CONTEXT, help="tokens each request holds when the decode steps are timed")
     ap.add_argument("--workload", default="decode", choices=("decode", "continuous", "chunked"),
                     help="decode: the headline line (default); continuous / chunked: the two serving workloads, one line each")
@@ -228,10 +222,14 @@ def main() -> int:
     kv_per_token = 2 * 2 * args.layers * cfg["num_key_value_heads"] * cfg["head_dim"]
     # batch 1 and 64 ride along where 64 requests of this context fit beside the weights (they do at 2,048 tokens)
     batches = (8,) if args.skip_points or 64 * context * kv_per_token > 100e9 else (8, 1, 64)
-    pages = max(batches) * ((context + 2 * (K + W) + 64) // page + 2) + 64
+    # further points: batch 8 at longer contexts, and a longer prompt
+    long_contexts = () if args.skip_points else LONG_CONTEXTS
+    long_prefill = 0 if args.skip_points else LONG_PREFILL_TOKENS
+    spare = 2 * (K + W) + 64
+    pages = max([max(batches) * ((context + spare) // page + 2)] + [8 * ((c + spare) // page + 2) for c in long_contexts]) + 64
     engine = Engine(random_config=cfg, seed=0, settings=EngineSettings(
         dtype="bfloat16", page_size=page, num_pages=pages, max_running=64, max_step_tokens=8192, prefill_chunk=2048,
-        max_positions=max(4096, context + 2 * (K + W) + 128), cuda_graphs=True))
+        max_positions=max([4096, context + spare + 64, long_prefill + 64] + [c + spare + 64 for c in long_contexts]), cuda_graphs=True))
     model = engine.runner.model
     gen = torch.Generator().manual_seed(0)
     hbm_gbs, bf16_tflops, peak_kind = peaks()
@@ -242,29 +240,27 @@ def main() -> int:
     weight_bytes = 2 * (L * layer_params + V * h) + 4 * (L * (2 * h + 2 * D) + h)
     kv_bytes_per_token = 2 * L * KV * D * 2
 
-    def prompts(n: int) -> list[list[int]]:
-        return [torch.randint(0, V, (context,), generator=gen).tolist() for _ in range(n)]
-
-    def fill(batch: int, budget: int) -> None:
-        """`batch` requests, each with `context` tokens in the cache and one token left to decode."""
+    def fill(batch: int, budget: int, tokens: int) -> None:
+        """`batch` requests, each with `tokens` tokens in the cache and one token left to decode."""
         for r in list(engine.scheduler.running) + list(engine.scheduler.waiting):
             r.cancelled = True
         engine.step()
-        for p in prompts(batch):
+        for _ in range(batch):
+            p = torch.randint(0, V, (tokens,), generator=gen).tolist()
             engine.add_request(p, SamplingParams(max_tokens=budget, ignore_eos=True))
         while engine.scheduler.waiting or any(r.pending > 1 for r in engine.scheduler.running):
             engine.step()
         assert len(engine.scheduler.running) == batch
 
-    def decode_device(batch: int) -> tuple[float, int, int]:
+    def decode_device(batch: int, tokens: int = context) -> tuple[float, int, int]:
         """ms per decode step on the device (K replays after W), kernels per step, context length."""
-        fill(batch, 2 * (K + W) + 8)
+        fill(batch, 2 * (K + W) + 8, tokens)
         plan = engine.scheduler.schedule()
         assert plan.decode_only and len(plan.entries) == batch
         entries = [StepEntry(p.request.cache, p.request.tokens[p.start:p.start + 1], [0], counter=len(p.request.output))
                    for p in plan.entries]
         tokens, _ = engine.graphs.run(entries)  # captures at first use, fills the static inputs
-        key = min(k for k in engine.graphs._graphs if k[0] >= batch)
+        key = engine.graphs.last_key
         graph = engine.graphs._graphs[key][0]
         for _ in range(W):
             graph.replay()
@@ -302,38 +298,66 @@ def main() -> int:
     layout_words = next(v[1].total for k, v in engine.graphs._graphs.items() if k[0] == 8)
 
     points = {}
-    if len(batches) > 1:
-        for b in batches[1:]:
-            ms, _, _ = decode_device(b)
-            points[f"decode_b{b}"] = round(b * 1000.0 / ms, 1)
+    for b in batches[1:]:
+        ms, _, ctx = decode_device(b)
+        points[f"decode_b{b}"] = round(b * 1000.0 / ms, 1)
+        points[f"decode_b{b}_hbm_frac"] = round((weight_bytes + b * ctx * kv_bytes_per_token) / (ms * 1e-3) / 1e9 / hbm_gbs, 4)
+    for c in long_contexts:
+        ms, _, ctx = decode_device(8, c)
+        points[f"decode_b8_ctx{c}"] = round(8 * 1000.0 / ms, 1)
+        points[f"decode_b8_ctx{c}_hbm_frac"] = round((weight_bytes + 8 * ctx * kv_bytes_per_token) / (ms * 1e-3) / 1e9 / hbm_gbs, 4)
 
-    # ---- prefill: one prompt of 2,048 tokens in one step
+    # ---- prefill: one prompt in one step
     for r in list(engine.scheduler.running):
         r.cancelled = True
     engine.step()
-    ids = torch.randint(0, V, (PREFILL_TOKENS,), generator=gen).tolist()
-    times = []
-    for i in range(W + 5):
-        rc = engine.runner.cache.open("prefill")
-        assert engine.runner.cache.reserve(rc, PREFILL_TOKENS)
-        torch.cuda.synchronize()
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        engine.runner.step([StepEntry(rc, ids, [PREFILL_TOKENS - 1])])
-        end.record()
-        torch.cuda.synchronize()
-        if i >= W:
-            times.append(start.elapsed_time(end))
-        engine.runner.cache.close(rc)
-    engine.runner.check()
-    prefill_ms = statistics.median(times)
+
+    def prefill_ms_of(T: int) -> float:
+        ids = torch.randint(0, V, (T,), generator=gen).tolist()
+        times = []
+        for i in range(W + 5):
+            rc = engine.runner.cache.open("prefill")
+            assert engine.runner.cache.reserve(rc, T)
+            torch.cuda.synchronize()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            engine.runner.step([StepEntry(rc, ids, [T - 1])])
+            end.record()
+            torch.cuda.synchronize()
+            if i >= W:
+                times.append(start.elapsed_time(end))
+            engine.runner.cache.close(rc)
+        engine.runner.check()
+        return statistics.median(times)
+
     T = PREFILL_TOKENS
+    prefill_ms = prefill_ms_of(T)
     # the fraction counts the matrix products alone (attention's flops are named beside it, not added to it)
     flops = 2 * T * L * layer_params + 2 * V * h
     attn_flops = L * 2 * H * D * T * (T + 1)
     prefill_frac = flops / (prefill_ms * 1e-3) / (bf16_tflops * 1e12)
+    if long_prefill:
+        ms = prefill_ms_of(long_prefill)
+        points[f"prefill_{long_prefill}"] = round(long_prefill / (ms * 1e-3), 1)
+        points[f"prefill_{long_prefill}_gemm_frac"] = round((2 * long_prefill * L * layer_params + 2 * V * h) / (ms * 1e-3) / (bf16_tflops * 1e12), 4)
 
     clocks = sampler.stop()
+    launches_of_step = kernels_per_step * K
+    if not (args.skip_points or args.skip_serving):
+        # the two serving workloads, each in a process of its own once this one's model is gone
+        del engine, model
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        for which in ("continuous", "chunked"):
+            try:
+                res = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--workload", which], capture_output=True, text=True, timeout=900)
+                line = json.loads(res.stdout.strip().splitlines()[-1])
+                points[f"{which}_output_tok_s"] = line["output_tok_s"]
+                points[f"{which}_decode_hbm_frac_p50"] = line["decode_step_hbm_frac"].get("p50")
+                points[f"{which}_mixed_gemm_frac_p50"] = line["mixed_step_gemm_frac"].get("p50")
+            except Exception as exc:   # a serving workload that fails does not take the headline with it
+                points[f"{which}_error"] = f"{type(exc).__name__}: {exc}"[:200]
     out = {
         "metric": METRIC.replace(str(CONTEXT), str(context)), "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": round(ms8, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
@@ -343,7 +367,7 @@ def main() -> int:
                    "seq_len": context, "page_size": page, "tied": False, "parallelism": "single GPU",
                    "l2": "step inputs (15 GB of weights) exceed L2", "peaks": peak_kind},
         "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": layout_words * 4, "d2h_bytes_per_step": (8 + 2) * 4},
-        "gpu_launches": kernels_per_step * K,
+        "gpu_launches": launches_of_step,
         "prefill": {"value": round(T / (prefill_ms * 1e-3), 1), "tokens": T, "ms": round(prefill_ms, 3), "frac": round(prefill_frac, 4),
                     "attention_tflops_in_step": round(attn_flops / 1e12, 3),
                     **({"frac_of_sustained": round(flops / (prefill_ms * 1e-3) / (sustained_tflops() * 1e12), 4)} if sustained_tflops() else {})},

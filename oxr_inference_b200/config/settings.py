@@ -32,6 +32,9 @@ class EngineSettings:
     """Replay decode-only steps from CUDA graphs (oxr_runtime/decode_graph.py)."""
     dtype: str = "bfloat16"
     """``bfloat16``: the serving kernels; ``float32``: every operation in true 32-bit."""
+    profile: bool = False
+    """Keep per-stage timers and a per-step log in ``Engine.profile`` (also switched on by ``OXR_PROFILE=1`` in the
+    environment, the reference's switch, oxr_runtime/engine.py:62-63)."""
     step_tile: int | None = None
     """Rows of the widest tile of the kernels that run a step; the scheduler trims prompt portions so that a step's
     tokens come to whole tile rows. None asks the kernels (``ops.STEP_TILE_ROWS``), 0 turns the trimming off."""

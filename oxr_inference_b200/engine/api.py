@@ -10,6 +10,7 @@ until everything queued is finished. Prompts are token ids; text goes in and out
 from __future__ import annotations
 
 import logging
+import os
 import time
 from pathlib import Path
 from typing import Any, Callable, Mapping, Sequence
@@ -29,6 +30,29 @@ from oxr_inference_b200.weights.loader import load_weights
 from oxr_inference_b200.weights.random_init import fill_random
 
 log = logging.getLogger(__name__)
+
+
+class StageTimers:
+    """Per-stage counters of the engine's step, as the reference keeps them under ``OXR_PROFILE=1``
+    (oxr_runtime/engine.py:65-104: cumulative seconds and counts per stage, a ``summary()``). Host stages are wall-clock
+    (``schedule``, ``build`` = filling and copying the staging block and issuing the step, ``wait`` = blocked on the
+    step's one synchronisation, ``commit``); the device time of the step itself comes from two CUDA events around it
+    (``decode_graph`` for a replayed decode step, ``forward`` for an eager or mixed step), read after the step's own
+    synchronisation, so profiling adds no synchronisation. ``steps`` lists every step: its device milliseconds, its
+    tokens, whether it was a replayed decode step, and the tokens the running requests held in the cache."""
+
+    def __init__(self, enabled: bool):
+        self.enabled = enabled
+        self.seconds: dict[str, float] = {}
+        self.counts: dict[str, int] = {}
+        self.steps: list[dict] = []
+
+    def add(self, name: str, seconds: float, count: int = 1) -> None:
+        self.seconds[name] = self.seconds.get(name, 0.0) + seconds
+        self.counts[name] = self.counts.get(name, 0) + count
+
+    def summary(self) -> dict[str, dict[str, float]]:
+        return {k: {"s": round(v, 4), "n": self.counts[k]} for k, v in self.seconds.items()}
 
 
 class Engine:
@@ -73,6 +97,8 @@ class Engine:
 
             self.tokenizer = Tokenizer.from_file(str(Path(model_dir) / "tokenizer.json"))
         self.counters = {"steps": 0, "graph_steps": 0, "prompt_tokens": 0, "generated_tokens": 0, "step_tokens": 0}
+        self.profile = StageTimers(s.profile or os.environ.get("OXR_PROFILE") == "1")
+        self._events = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) if self.profile.enabled else None
 
     # ---- requests
     def add_request(self, prompt: Sequence[int] | str, params: SamplingParams | None = None,
@@ -101,7 +127,12 @@ class Engine:
     @torch.inference_mode()
     def step(self) -> list[Completion]:
         """Plan one batch, run it, take the sampled tokens; returns the requests that finished."""
+        prof = self.profile
+        t0 = time.perf_counter() if prof.enabled else 0.0
         plan = self.scheduler.schedule()
+        if prof.enabled:
+            prof.add("schedule", time.perf_counter() - t0)
+            held = sum(r.cache.length for r in self.scheduler.running if r.cache is not None)
         finished = list(plan.finished)
         if plan.entries:
             decode_only = plan.decode_only
@@ -129,8 +160,15 @@ class Engine:
                 finished += self.scheduler.fail_running()
                 self._finish(finished)
                 raise
+            t1 = time.perf_counter() if prof.enabled else 0.0
             wanting = [p.request for p in plan.entries if p.wants_logits]
             finished += self.scheduler.commit(plan, {r.id: t for r, t in zip(wanting, tokens)})
+            if prof.enabled:
+                prof.add("commit", time.perf_counter() - t1)
+                replayed = self._last_step_was_replayed
+                device_ms = self._events[0].elapsed_time(self._events[1])
+                prof.add("decode_graph" if replayed else "forward", device_ms * 1e-3, plan.tokens)
+                prof.steps.append({"ms": device_ms, "tokens": plan.tokens, "graph": replayed, "held": held})
             self.counters["steps"] += 1
             self.counters["step_tokens"] += plan.tokens
             self.counters["generated_tokens"] += len(wanting)
@@ -150,6 +188,11 @@ class Engine:
 
     def _run(self, plan: StepPlan, entries: list[StepEntry], decode_only: bool) -> list[int]:
         rt = self.runner.model.runtime
+        prof = self.profile
+        t0 = time.perf_counter() if prof.enabled else 0.0
+        if prof.enabled:
+            self._events[0].record()
+            self._last_step_was_replayed = False
         penalised = any(e.penalty != 1.0 for e in entries)
         if penalised:
             self._mark_new(plan)
@@ -159,7 +202,14 @@ class Engine:
             if replayed is not None:
                 # the graph copied the tokens and the status word to pinned memory itself
                 self.counters["graph_steps"] += 1
+                if prof.enabled:
+                    self._events[1].record()
+                    self._last_step_was_replayed = True
+                    t1 = time.perf_counter()
+                    prof.add("build", t1 - t0)
                 torch.cuda.current_stream().synchronize()
+                if prof.enabled:
+                    prof.add("wait", time.perf_counter() - t1)
                 host = replayed[1].tolist()
                 if host[-2] != 0:
                     ops.check_status(rt.status)
@@ -168,6 +218,10 @@ class Engine:
             ctx = self.runner.builder.build(entries)
             logits = self.runner.model.step(ctx, self.runner.cache)
             if logits.shape[0] == 0:
+                if prof.enabled:
+                    self._events[1].record()
+                    prof.add("build", time.perf_counter() - t0)
+                    torch.cuda.current_stream().synchronize()
                 return []
             s = ctx.sampling
             if penalised:
@@ -182,7 +236,13 @@ class Engine:
             self._readback = torch.empty(max(n + 2, 1026), dtype=torch.int32).pin_memory()
         self._readback[:n].copy_(tokens, non_blocking=True)
         self._readback[n:n + 2].copy_(rt.status[:2], non_blocking=True)
+        if prof.enabled:
+            self._events[1].record()
+            t1 = time.perf_counter()
+            prof.add("build", t1 - t0)
         torch.cuda.current_stream().synchronize()
+        if prof.enabled:
+            prof.add("wait", time.perf_counter() - t1)
         host = self._readback[:n + 2].tolist()
         if host[-2] != 0:
             ops.check_status(rt.status)

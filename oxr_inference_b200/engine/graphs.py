@@ -29,6 +29,8 @@ class DecodeGraphs:
         self._pool = None
         self.kernels_per_replay: dict[tuple[int, int], int] = {}
         self.replays = 0
+        self.last_key: tuple[int, int] | None = None
+        """(batch bucket, table-width bucket) of the graph that ``run`` replayed last."""
 
     def _width_bucket(self, entries: list[StepEntry]) -> int:
         need = max(len(t) for e in entries for t in e.cache.tables)
@@ -54,6 +56,7 @@ class DecodeGraphs:
         self.runner.builder.build(entries, layout=layout, device_block=block, copy=False)
         graph.replay()
         self.replays += 1
+        self.last_key = key
         ops.launch_count += self.kernels_per_replay[key]
         return tokens[:n], readback
 

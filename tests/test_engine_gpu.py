@@ -232,6 +232,25 @@ def test_text_goes_in_and_out_through_the_tokenizer_of_the_model_folder(folders,
         plain.add_request(text)
 
 
+def test_per_stage_timers_and_the_step_log(folders):
+    """With ``profile=True`` the engine keeps cumulative seconds and counts per stage and one record per step, as the
+    reference does under OXR_PROFILE=1 (oxr_runtime/engine.py:65-104); without it nothing is recorded."""
+    from oxr_inference_b200.sampling import SamplingParams
+
+    prompts = [token_ids("A", n, seed=31) for n in (3, 40)]
+    engine = _engine(folders["A"], "A", "bfloat16", profile=True)
+    engine.generate(prompts, SamplingParams(max_tokens=6, ignore_eos=True))
+    summary, steps = engine.profile.summary(), engine.profile.steps
+    assert {"schedule", "build", "wait", "commit", "forward", "decode_graph"} <= set(summary)
+    assert len(steps) == engine.counters["steps"] and sum(st["tokens"] for st in steps) == engine.counters["step_tokens"]
+    assert sum(st["graph"] for st in steps) == engine.counters["graph_steps"] > 0
+    assert all(st["ms"] > 0 for st in steps) and steps[-1]["held"] > 40
+    assert summary["decode_graph"]["n"] + summary["forward"]["n"] == engine.counters["step_tokens"]
+    quiet = _engine(folders["A"], "A", "bfloat16")
+    quiet.generate(prompts, SamplingParams(max_tokens=3, ignore_eos=True))
+    assert quiet.profile.summary() == {} and quiet.profile.steps == []
+
+
 def test_smoke_entry():
     import __graft_entry__
 
