@@ -23,6 +23,11 @@ from oxr_inference_b200.ops import build
 from oxr_inference_b200.ops.build import BuildError  # noqa: F401
 
 SKINNY_MAX_ROWS = 16
+STREAM_MAX_ROWS = 16
+STREAM_GEMM = os.environ.get("OXR_B200_STREAM", "1") != "0"
+"""Whether bf16 products of at most ``STREAM_MAX_ROWS`` rows (decode steps) run the weight-streaming kernel (a persistent
+block per SM whose producer warp fills a shared-memory ring with cp.async.bulk, also while the kernel before it still
+runs) instead of the register-fed skinny kernel. ``OXR_B200_STREAM=0`` switches back, for comparisons."""
 STATUS_NAMES = {
     1: "token id outside the vocabulary", 2: "cache slot outside the pool", 3: "position outside the rotary table",
     4: "block table names a page outside the pool", 5: "a bounded wait inside a kernel ran out",
@@ -100,6 +105,8 @@ def _lib():
         lib.oxr_gemm_f32_nt.argtypes = [p, p, p, i, i, i, p]
         lib.oxr_gemm_skinny_bf16.argtypes = [p, p, p, i, i, i, i, p]
         lib.oxr_gemm_skinny_gated_bf16.argtypes = [p, p, p, i, i, i, p]
+        lib.oxr_gemm_stream_bf16.argtypes = [p, p, p, i, i, i, i, p, p]
+        lib.oxr_gemm_stream_gated_bf16.argtypes = [p, p, p, i, i, i, p, p]
         lib.oxr_gemm_tcgen05_bf16.argtypes = [p, p, p, i, i, i, i, i, i, p, p, p, p]
         lib.oxr_gemm_tcgen05_pair_bf16.argtypes = [p, p, p, i, i, i, i, i, p, p]
         lib.oxr_gemm_tcgen05_gated_bf16.argtypes = [p, p, p, i, i, i, i, p, p]
@@ -112,7 +119,7 @@ def _lib():
         lib.oxr_repetition_penalty.argtypes = [p, p, p, p, i, i, p]
         lib.oxr_mark_seen.argtypes = [p, p, p, i, i, p]
         for name in ("oxr_embedding", "oxr_add_rms_norm", "oxr_silu_mul", "oxr_cast", "oxr_qk_norm_rope_store",
-                     "oxr_gemm_f32_nt", "oxr_gemm_skinny_bf16", "oxr_gemm_skinny_gated_bf16", "oxr_gemm_tcgen05_bf16", "oxr_gemm_tcgen05_pair_bf16", "oxr_gemm_tcgen05_gated_bf16", "oxr_gemm_few_rows_cluster_bf16", "oxr_gemm_few_rows_max_clusters",
+                     "oxr_gemm_f32_nt", "oxr_gemm_skinny_bf16", "oxr_gemm_skinny_gated_bf16", "oxr_gemm_stream_bf16", "oxr_gemm_stream_gated_bf16", "oxr_gemm_tcgen05_bf16", "oxr_gemm_tcgen05_pair_bf16", "oxr_gemm_tcgen05_gated_bf16", "oxr_gemm_few_rows_cluster_bf16", "oxr_gemm_few_rows_max_clusters",
                      "oxr_gemm_tcgen05_pair_gated_bf16", "oxr_sample", "oxr_repetition_penalty", "oxr_mark_seen"):
             getattr(lib, name).restype = c_int
         lib.oxr_set_chain.argtypes = [c_int]
@@ -270,7 +277,10 @@ def gated_silu_linear(x: torch.Tensor, weight: torch.Tensor, interleave: int = 0
     if fused:
         lib = _lib()
         out = torch.empty((m, n // 2), dtype=torch.bfloat16, device=x.device)
-        if m <= SKINNY_MAX_ROWS:
+        if STREAM_GEMM and m <= STREAM_MAX_ROWS:
+            _done(lib.oxr_gemm_stream_gated_bf16(out.data_ptr(), x.data_ptr(), weight.data_ptr(), m, n, k,
+                                                 new_status(x.device).data_ptr(), _stream()), "gemm_stream_gated")
+        elif m <= SKINNY_MAX_ROWS:
             _done(lib.oxr_gemm_skinny_gated_bf16(out.data_ptr(), x.data_ptr(), weight.data_ptr(), m, n, k, _stream()), "gemm_skinny_gated")
         elif _gemm_pair_plan(m, n, k):
             _done(lib.oxr_gemm_tcgen05_pair_gated_bf16(out.data_ptr(), x.data_ptr(), weight.data_ptr(), m, n, k, _gemm_pair_plan(m, n, k),
@@ -642,6 +652,11 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
         return cast(out, out_dtype)
     if x.dtype != torch.bfloat16:
         raise KernelError(f"linear: activations {x.dtype} with weight {weight.dtype} is not a supported pair")
+    if STREAM_GEMM and m <= STREAM_MAX_ROWS and k % 8 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0:
+        out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+        _done(lib.oxr_gemm_stream_bf16(out.data_ptr(), x.data_ptr(), weight.data_ptr(), m, n, k, _DT[out_dtype],
+                                       new_status(x.device).data_ptr(), _stream()), "gemm_stream")
+        return out
     if m <= SKINNY_MAX_ROWS and k % 8 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0:
         out = torch.empty((m, n), dtype=out_dtype, device=x.device)
         _done(lib.oxr_gemm_skinny_bf16(out.data_ptr(), x.data_ptr(), weight.data_ptr(), m, n, k, _DT[out_dtype], _stream()),

@@ -27,7 +27,7 @@ CSRC = Path(__file__).resolve().parent.parent / "csrc"
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 
-CORE_SOURCES = ["elementwise.cu", "qk_norm_rope.cu", "gemm_f32.cu", "gemm_skinny.cu", "gemm_tcgen05.cu", "gemm_tcgen05_pair.cu", "gemm_tcgen05_few_rows.cu", "sampling.cu"]
+CORE_SOURCES = ["elementwise.cu", "qk_norm_rope.cu", "gemm_f32.cu", "gemm_skinny.cu", "gemm_stream.cu", "gemm_tcgen05.cu", "gemm_tcgen05_pair.cu", "gemm_tcgen05_few_rows.cu", "sampling.cu"]
 ATTENTION_SOURCES = ["attention.cu"]
 HEADERS = ["common.cuh", "tma.cuh", "umma.cuh", "sampling_static.h"]
 

@@ -104,9 +104,12 @@ def test_silu_mul_on_interleaved_columns(ops, dtype, inter):
 
 @pytest.mark.parametrize("M", [1, 5, 8, 13, 16])
 @pytest.mark.parametrize("inter,K", [(160, 96), (24, 64), (12288, 4096), (1000, 1032)])
-def test_gated_skinny_gemm_applies_silu_in_its_epilogue(ops, M, inter, K):
+@pytest.mark.parametrize("stream", [True, False], ids=["stream", "skinny"])
+def test_gated_decode_gemm_applies_silu_in_its_epilogue(ops, monkeypatch, stream, M, inter, K):
     """silu(x Wg^T) * (x Wu^T) from ONE kernel when the weight's gate and up rows alternate in groups of 8, against the
-    plain formula; and the same call beyond the skinny kernel's rows, which runs product and SiLU kernel apart."""
+    plain formula, from the weight-streaming kernel and from the register-fed skinny kernel; and the same call with gate
+    and up side by side, which runs product and SiLU kernel apart."""
+    monkeypatch.setattr(ops, "STREAM_GEMM", stream)
     g = torch.Generator(device=DEV).manual_seed(21)
     x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
     wg = (torch.randn(inter, K, device=DEV, generator=g) * 0.05).bfloat16()
@@ -208,10 +211,35 @@ def test_gemm_f32(ops, M, N, K):
         assert torch.equal(ops.linear(x[r:r + 1].contiguous(), w)[0], got[r])
 
 
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("N,K", [(509, 96), (192, 160), (4096, 4096), (1000, 12288), (6144, 1032), (40, 520), (151936, 256)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_stream_bf16(ops, M, N, K, out_dtype):
+    """The weight-streaming kernel of decode steps: ragged N (509, 1000, 40: a last group of fewer than 16 rows), K that
+    is no multiple of the 512-wide slices (96, 160, 1032, 520) or spans many (12288), more groups than blocks and fewer,
+    one and two 8-row tiles of x. A row's result does not depend on the rows beside it."""
+    assert ops.STREAM_GEMM and M <= ops.STREAM_MAX_ROWS
+    g = torch.Generator(device=DEV).manual_seed(7)
+    x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=DEV, generator=g) * 0.05).bfloat16()
+    status = ops.new_status(DEV)
+    got = ops.linear(x, w, out_dtype)
+    ops.check_status(status)
+    assert got.dtype == out_dtype
+    want = x.float() @ w.float().T
+    if out_dtype == torch.float32:
+        torch.testing.assert_close(got, want, atol=2e-4 * math.sqrt(K) * 0.05, rtol=1e-4)
+    else:
+        torch.testing.assert_close(got.float(), want, atol=1e-2, rtol=1e-2)
+    for r in (0, M - 1):
+        assert torch.equal(ops.linear(x[r:r + 1].contiguous(), w, out_dtype)[0], got[r])
+
+
 @pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 33, 64])
 @pytest.mark.parametrize("N,K", [(509, 96), (192, 160), (4096, 4096), (1000, 12288)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 def test_gemm_skinny_bf16(ops, monkeypatch, M, N, K, out_dtype):
+    monkeypatch.setattr(ops, "STREAM_GEMM", False)    # the register-fed kernel that the streaming kernel is compared with
     monkeypatch.setattr(ops, "SKINNY_MAX_ROWS", 64)   # every row count the kernel takes, also those linear() sends elsewhere
     g = torch.Generator(device=DEV).manual_seed(6)
     x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
