@@ -119,11 +119,21 @@ __global__ void add_rms_norm_bf16x8_kernel(__nv_bfloat16* __restrict__ out, floa
                                            const int* __restrict__ rows, int hidden, float eps) {
     __shared__ float red[32];
     if (gridDim.x <= 296) pdl_trigger();   // a decode step's few blocks: the next kernel may set itself up beside them
+    const int words = hidden >> 3;
+    // the norm's weights are written by no kernel of a step: they are fetched while the kernel before still runs
+    float4 wt[VEC_PER_THREAD][2];
+#pragma unroll
+    for (int i = 0; i < VEC_PER_THREAD; ++i) {
+        const int w = threadIdx.x + i * blockDim.x;
+        if (w < words) {
+            wt[i][0] = __ldg(reinterpret_cast<const float4*>(weight + (size_t)w * 8));
+            wt[i][1] = __ldg(reinterpret_cast<const float4*>(weight + (size_t)w * 8 + 4));
+        }
+    }
     pdl_wait();
     const int r = blockIdx.x;
     const size_t src = (size_t)(rows ? rows[r] : r) * hidden;
     const size_t dst = (size_t)r * hidden;
-    const int words = hidden >> 3;
     float v[VEC_PER_THREAD][8];
     float ss = 0.f;
 #pragma unroll
@@ -158,8 +168,7 @@ __global__ void add_rms_norm_bf16x8_kernel(__nv_bfloat16* __restrict__ out, floa
                 *reinterpret_cast<float4*>(residual_out + dst + (size_t)w * 8) = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
                 *reinterpret_cast<float4*>(residual_out + dst + (size_t)w * 8 + 4) = make_float4(v[i][4], v[i][5], v[i][6], v[i][7]);
             }
-            const float4 w0 = *reinterpret_cast<const float4*>(weight + (size_t)w * 8);
-            const float4 w1 = *reinterpret_cast<const float4*>(weight + (size_t)w * 8 + 4);
+            const float4 w0 = wt[i][0], w1 = wt[i][1];
             uint4 o;
             __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
             op[0] = __floats2bfloat162_rn(v[i][0] * inv * w0.x, v[i][1] * inv * w0.y);

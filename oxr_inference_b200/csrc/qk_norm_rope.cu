@@ -107,29 +107,49 @@ __global__ void qk_norm_rope_store_bf16x2_kernel(
     const int* __restrict__ slots, int n_tokens, int H, int KV, int D, float eps, int max_positions, long long num_slots,
     int norm_q, int norm_k, int rotate, int* status) {
     if (gridDim.x <= 296) pdl_trigger();   // a decode step's few blocks: the next kernel may set itself up beside them
-    pdl_wait();
     const int warps_per_block = blockDim.x >> 5;
     const int lane = threadIdx.x & 31;
     const long long unit = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
     const int heads = H + 2 * KV;
     const int groups = (heads + HPW - 1) / HPW;
-    if (unit >= (long long)n_tokens * groups) return;
-    const int t = (int)(unit / groups), head0 = (int)(unit % groups) * HPW;
+    const bool live = unit < (long long)n_tokens * groups;
+    const int t = live ? (int)(unit / groups) : 0, head0 = (int)(unit % groups) * HPW;
     const int half = D >> 1;
-    const __nv_bfloat16* row = qkv + (size_t)t * heads * D;
-    const long long slot = slots[t];
-    if (slot >= num_slots) {
-        if (lane == 0) oxr_report(status, OXR_BAD_SLOT, t);
-    }
-    const bool can_store = slot >= 0 && slot < num_slots;
+    // ---- above the wait: what no kernel of the step writes (the step's slots and positions, the rotary tables, the norm
+    // weights); only qkv comes from the kernel before this one
+    long long slot = -1;
     int pos = 0;
-    if (rotate) {
-        pos = positions[t];
-        if (pos < 0 || pos >= max_positions) {
-            if (lane == 0) oxr_report(status, OXR_BAD_POSITION, t);
-            pos = 0;
+    bool bad_slot = false, bad_pos = false;
+    float2 c[STEPS], sn[STEPS], wq1[STEPS], wq2[STEPS], wk1[STEPS], wk2[STEPS];
+    if (live) {
+        slot = slots[t];
+        bad_slot = slot >= num_slots;
+        if (rotate) {
+            pos = positions[t];
+            bad_pos = pos < 0 || pos >= max_positions;
+            if (bad_pos) pos = 0;
+        }
+#pragma unroll
+        for (int i = 0; i < STEPS; ++i) {
+            const int j = 2 * lane + 64 * i;
+            c[i] = wq1[i] = wq2[i] = wk1[i] = wk2[i] = make_float2(1.f, 1.f);
+            sn[i] = make_float2(0.f, 0.f);
+            if (j < half) {
+                if (rotate) {
+                    c[i] = *reinterpret_cast<const float2*>(cos_table + (size_t)pos * half + j);
+                    sn[i] = *reinterpret_cast<const float2*>(sin_table + (size_t)pos * half + j);
+                }
+                if (norm_q) { wq1[i] = *reinterpret_cast<const float2*>(q_weight + j); wq2[i] = *reinterpret_cast<const float2*>(q_weight + j + half); }
+                if (norm_k) { wk1[i] = *reinterpret_cast<const float2*>(k_weight + j); wk2[i] = *reinterpret_cast<const float2*>(k_weight + j + half); }
+            }
         }
     }
+    pdl_wait();
+    if (!live) return;
+    if (bad_slot && lane == 0) oxr_report(status, OXR_BAD_SLOT, t);
+    if (bad_pos && lane == 0) oxr_report(status, OXR_BAD_POSITION, t);
+    const bool can_store = slot >= 0 && slot < num_slots;
+    const __nv_bfloat16* row = qkv + (size_t)t * heads * D;
     // ---- all loads first
     float2 x1[HPW][STEPS], x2[HPW][STEPS];
 #pragma unroll
@@ -144,17 +164,6 @@ __global__ void qk_norm_rope_store_bf16x2_kernel(
                 x1[hh][i] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(row + (size_t)head * D + j));
                 x2[hh][i] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(row + (size_t)head * D + j + half));
             }
-        }
-    }
-    float2 c[STEPS], sn[STEPS];
-#pragma unroll
-    for (int i = 0; i < STEPS; ++i) {
-        const int j = 2 * lane + 64 * i;
-        c[i] = make_float2(1.f, 1.f);
-        sn[i] = make_float2(0.f, 0.f);
-        if (rotate && j < half) {
-            c[i] = *reinterpret_cast<const float2*>(cos_table + (size_t)pos * half + j);
-            sn[i] = *reinterpret_cast<const float2*>(sin_table + (size_t)pos * half + j);
         }
     }
 #pragma unroll
@@ -173,7 +182,6 @@ __global__ void qk_norm_rope_store_bf16x2_kernel(
         if (!is_q && !can_store) continue;
         __nv_bfloat16* dst = is_q ? q_out + (size_t)t * H * D + (size_t)head * D : k_cache + (size_t)slot * KV * D + (size_t)(head - H) * D;
         const bool do_norm = is_q ? norm_q : norm_k;
-        const float* w = is_q ? q_weight : k_weight;
         float inv = 1.f;
         if (do_norm) {
             float ss = 0.f;
@@ -189,7 +197,7 @@ __global__ void qk_norm_rope_store_bf16x2_kernel(
             if (j < half) {
                 float2 y1 = x1[hh][i], y2 = x2[hh][i];
                 if (do_norm) {
-                    const float2 w1 = *reinterpret_cast<const float2*>(w + j), w2 = *reinterpret_cast<const float2*>(w + j + half);
+                    const float2 w1 = is_q ? wq1[i] : wk1[i], w2 = is_q ? wq2[i] : wk2[i];
                     y1.x = y1.x * inv * w1.x; y1.y = y1.y * inv * w1.y;
                     y2.x = y2.x * inv * w2.x; y2.y = y2.y * inv * w2.y;
                 }
