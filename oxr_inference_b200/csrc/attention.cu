@@ -13,6 +13,7 @@
 // BN = 32 that start at absolute positions 0, 32, 64, ...; because the blocks do not depend on where a portion
 // starts or on the rest of the batch, a row's result is bit-identical however the work was cut.
 #include "tma.cuh"
+OXR_TL_DEFINE(oxr_tl_read_attn)
 
 #ifndef HEAD_DIM
 #error "compile with -DHEAD_DIM=<head size>"
@@ -832,6 +833,7 @@ attn_tma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
     uint64_t* full = reinterpret_cast<uint64_t*>(stages + TILE_REGION + (size_t)DECODE_ROWS * LDS * sizeof(bf16));
     uint64_t* empty = full + TMA_STAGES;
 
+    [[maybe_unused]] unsigned long long tl_released = 0, tl_first = 0, tl_streamed = 0;   // timeline stamps of the consumer warps
     const TileGeometry g = tile_geometry(a, DECODE_ROWS);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int splits = gridDim.z, split = blockIdx.z;
@@ -914,6 +916,7 @@ attn_tma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
 
         // ---------------------------------------------------------------------- consumers (warps 0..3)
         pdl_wait();   // q comes from the kernel before this one
+        tl_released = OXR_TL_NOW();
         load_q_rows(Qs, q, a, g, DECODE_ROWS);   // strided over MMA_THREADS = the 128 consumer threads
         cp_async_commit();
         int row_pos[2];
@@ -944,6 +947,7 @@ attn_tma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
                 if (lane == 0) { atomicExch(&s_gave_up, 1); oxr_report(a.status, OXR_WAIT_EXPIRED, 11); }
                 break;
             }
+            if (b == 0) tl_first = OXR_TL_NOW();
             const bf16* Kst = reinterpret_cast<const bf16*>(stages + (size_t)st * KV_STAGE_BYTES);
             const bf16* Vst = Kst + PANELS * (PANEL_BYTES / 2);
             const int key0 = k_first + (first + b) * MMA_BN + warp * 16;
@@ -953,6 +957,7 @@ attn_tma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
             __syncwarp();
             if (lane == 0) mbar_arrive(empty + st);   // this warp is done with the stage
         }
+        tl_streamed = OXR_TL_NOW();
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
             l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
@@ -987,12 +992,19 @@ attn_tma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
     consumer_sync();
     if (threadIdx.x == 0) s_ticket = atomicAdd(&counters[unit], 1);
     consumer_sync();
-    if (s_ticket != splits - 1) return;
+    if (s_ticket != splits - 1) {
+        if (threadIdx.x == 0) OXR_TL_PUT(4, tl_released, OXR_TL_NOW(), tl_first, tl_streamed, blockIdx.x);
+        return;
+    }
     __threadfence();
     if (threadIdx.x == 0) counters[unit] = 0;
     const float* all_ml = part_ml + unit * splits * DECODE_ROWS * 2;
     const float* all_o = part_o + unit * splits * DECODE_ROWS * D;
     merge_pieces(out, all_ml, all_o, splits, rows_live, g, a);
+#ifdef OXR_TIMELINE
+    consumer_sync();
+    if (threadIdx.x == 0) OXR_TL_PUT(5, tl_released, OXR_TL_NOW(), tl_first, tl_streamed, blockIdx.x);   // id 5: the block that merged its unit
+#endif
 }
 
 // ---------------------------------------------------------------------------------------------------------------------

@@ -7,6 +7,37 @@
 
 #define OXR_API extern "C" __attribute__((visibility("default")))
 
+// ---- an optional timeline of a step's kernels (compiled in with -DOXR_TIMELINE only; see ops/microbench.py `timeline`)
+// Every block of an instrumented kernel leaves one record of six 64-bit words: a kernel id, the time its wait for the
+// kernel before it returned, the time it ended, and three more stamps or sizes of the kernel's choosing. Times are
+// %globaltimer nanoseconds, one clock for all SMs. Each source file has a buffer of its own and exports a reader.
+#ifdef OXR_TIMELINE
+#define OXR_TL_DEFINE(reader) \
+    static __device__ unsigned long long oxr_tl_buf[1 << 15]; \
+    static __device__ unsigned int oxr_tl_n; \
+    OXR_API int reader(unsigned long long* out, int words) { /* copies the records out and clears them */ \
+        if (words > (1 << 15)) words = 1 << 15; \
+        cudaMemcpyFromSymbol(out, oxr_tl_buf, (size_t)words * 8); \
+        void* p = nullptr; \
+        if (cudaGetSymbolAddress(&p, oxr_tl_buf) == cudaSuccess) cudaMemset(p, 0, sizeof(unsigned long long) << 15); \
+        if (cudaGetSymbolAddress(&p, oxr_tl_n) == cudaSuccess) cudaMemset(p, 0, 4); \
+        return words; \
+    }
+static __device__ __forceinline__ unsigned long long oxr_tl_now() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define OXR_TL_NOW() oxr_tl_now()
+#define OXR_TL_PUT(kid, a, b, c, d, e) do { \
+        const unsigned int s_ = atomicAdd(&oxr_tl_n, 1u); \
+        if (s_ < (1u << 15) / 6) { \
+            unsigned long long* r_ = oxr_tl_buf + (size_t)s_ * 6; \
+            r_[0] = (kid); r_[1] = (a); r_[2] = (b); r_[3] = (c); r_[4] = (d); r_[5] = (e); \
+        } \
+    } while (0)
+#else
+#define OXR_TL_DEFINE(reader)
+#define OXR_TL_NOW() 0ull
+#define OXR_TL_PUT(kid, a, b, c, d, e) do { } while (0)
+#endif
+
 // Error codes written to the engine's device status word (first error wins) and returned by launchers.
 enum OxrStatus : int {
     OXR_OK = 0,

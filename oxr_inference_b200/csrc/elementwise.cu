@@ -5,6 +5,7 @@
 // (oxr_runtime/language.py:102-104). Differences, all toward more exactness: the residual stream is carried
 // in fp32 whatever the activation dtype, and each result is rounded to the activation dtype once.
 #include "common.cuh"
+OXR_TL_DEFINE(oxr_tl_read_elem)
 
 // ---------------------------------------------------------------------------------------------- embedding
 template <typename TT, typename TO>
@@ -131,6 +132,7 @@ __global__ void add_rms_norm_bf16x8_kernel(__nv_bfloat16* __restrict__ out, floa
         }
     }
     pdl_wait();
+    [[maybe_unused]] const unsigned long long tl_released = OXR_TL_NOW();
     const int r = blockIdx.x;
     const size_t src = (size_t)(rows ? rows[r] : r) * hidden;
     const size_t dst = (size_t)r * hidden;
@@ -178,6 +180,10 @@ __global__ void add_rms_norm_bf16x8_kernel(__nv_bfloat16* __restrict__ out, floa
             *reinterpret_cast<uint4*>(out + dst + (size_t)w * 8) = o;
         }
     }
+#ifdef OXR_TIMELINE
+    __syncthreads();
+    if (threadIdx.x == 0) OXR_TL_PUT(2, tl_released, OXR_TL_NOW(), 0, 0, blockIdx.x);
+#endif
 }
 
 // dtype: 0 = float32, 1 = bfloat16 (of x and out). residual_in / residual_out / rows may be null.

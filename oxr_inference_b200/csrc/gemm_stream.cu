@@ -35,6 +35,7 @@
 // waiting (its output is then meaningless, which the status word says) so that every thread still reaches the end.
 #include "tma.cuh"
 
+OXR_TL_DEFINE(oxr_tl_read_stream)
 namespace {
 constexpr int ST_WARPS = 8;                          // consumer warps
 constexpr int ST_THREADS = (ST_WARPS + 1) * 32;      // + the producer warp
@@ -135,6 +136,7 @@ gemm_stream_kernel(TO* __restrict__ C, const __nv_bfloat16* __restrict__ X, cons
         }
     };
     pdl_wait();   // X comes from the kernel before this one
+    [[maybe_unused]] const unsigned long long tl_released = OXR_TL_NOW();
     // The stages of this block in the order the producer fills them: q = (group index) * slices + slice. The X words of a
     // stage depend on its slice alone; those of stage q + X_AHEAD are asked for when stage q has been multiplied: a ring
     // of X_AHEAD register buffers, indexed by q % X_AHEAD (the loop is unrolled by it).
@@ -215,6 +217,10 @@ gemm_stream_kernel(TO* __restrict__ C, const __nv_bfloat16* __restrict__ X, cons
             for (int i = 0; i < TILES; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
         }
     }
+#ifdef OXR_TIMELINE
+    consumers_sync();
+    if (threadIdx.x == 0) OXR_TL_PUT(1, tl_released, OXR_TL_NOW(), (unsigned long long)N, (unsigned long long)K, blockIdx.x);
+#endif
     // A block that gave up may still have copies in flight into its ring: give them time to land (a bounded sleep)
     // before the block's shared memory goes to someone else.
     if (s_gave_up) {

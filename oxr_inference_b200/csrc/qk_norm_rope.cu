@@ -7,6 +7,7 @@
 // to `cache + slot * KV * D` (kernels.py:84-99). Unlike the reference it takes any even head_dim, gathers
 // cos/sin by position itself, keeps the whole computation in fp32 and rounds once.
 #include "common.cuh"
+OXR_TL_DEFINE(oxr_tl_read_rope)
 
 // One warp per (token, head); heads 0..H-1 are q, H..H+KV-1 are k, H+KV..H+2KV-1 are v.
 // Lane l handles the pairs (j, j + D/2) for j = l, l + 32, ...
@@ -146,6 +147,12 @@ __global__ void qk_norm_rope_store_bf16x2_kernel(
     }
     pdl_wait();
     if (!live) return;
+#ifdef OXR_TIMELINE
+    struct TlEnd {   // this warp's record, written when the warp leaves the kernel
+        unsigned long long released;
+        __device__ ~TlEnd() { if ((threadIdx.x & 31) == 0) OXR_TL_PUT(3, released, OXR_TL_NOW(), 0, 0, blockIdx.x); }
+    } tl_end{OXR_TL_NOW()};
+#endif
     if (bad_slot && lane == 0) oxr_report(status, OXR_BAD_SLOT, t);
     if (bad_pos && lane == 0) oxr_report(status, OXR_BAD_POSITION, t);
     const bool can_store = slot >= 0 && slot < num_slots;

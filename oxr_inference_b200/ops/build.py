@@ -32,6 +32,12 @@ ATTENTION_SOURCES = ["attention.cu"]
 HEADERS = ["common.cuh", "tma.cuh", "umma.cuh", "sampling_static.h"]
 
 
+TIMELINE = os.environ.get("OXR_B200_TIMELINE") == "1"
+"""Build (as libraries of their own, ``*_tl``) with the kernels' optional timeline stamps compiled in: every block of a decode
+step's kernels then records when it was released and when it ended (``csrc/common.cuh``; read by
+``python -m oxr_inference_b200.ops.microbench timeline``). Not for serving: the stamps cost a little time."""
+
+
 class BuildError(RuntimeError):
     pass
 
@@ -152,8 +158,13 @@ def _load(lib_name: str, sources: list[str], defines: list[str]) -> ctypes.CDLL:
     return _LOADED[lib_name]
 
 
+def _variant(name: str, defines: list[str]) -> tuple[str, list[str]]:
+    return (name + "_tl", defines + ["-DOXR_TIMELINE"]) if TIMELINE else (name, defines)
+
+
 def core_library() -> ctypes.CDLL:
-    return _load("core", _existing(CORE_SOURCES), [])
+    name, defines = _variant("core", [])
+    return _load(name, _existing(CORE_SOURCES), defines)
 
 
 def check_head_dim(head_dim: int) -> None:
@@ -163,7 +174,8 @@ def check_head_dim(head_dim: int) -> None:
 
 def attention_library(head_dim: int) -> ctypes.CDLL:
     check_head_dim(head_dim)
-    return _load(f"attn_d{head_dim}", _existing(ATTENTION_SOURCES), [f"-DHEAD_DIM={head_dim}"])
+    name, defines = _variant(f"attn_d{head_dim}", [f"-DHEAD_DIM={head_dim}"])
+    return _load(name, _existing(ATTENTION_SOURCES), defines)
 
 
 def build_all(head_dims: tuple[int, ...] = (16, 32, 64, 128)) -> list[Path]:

@@ -7,6 +7,11 @@ command to put under ``ncu``.
     python -m oxr_inference_b200.ops.microbench attention --batch 1 --q-len 2048 --context 2048
     python -m oxr_inference_b200.ops.microbench norm --rows 8 --hidden 4096
     python -m oxr_inference_b200.ops.microbench rope --tokens 2048
+    OXR_B200_TIMELINE=1 python -m oxr_inference_b200.ops.microbench timeline --batch 8 --context 2048
+
+``timeline`` runs decode steps of a few layers of Qwen3-8B's sizes through the engine (CUDA graphs and all) with the kernels'
+timeline stamps compiled in, and prints, kernel by kernel in the order of one step, when its blocks were released, when
+the first and the last of them ended, and the gap since the kernel before.
 """
 
 from __future__ import annotations
@@ -133,6 +138,77 @@ def rope(args) -> dict:
             "GB/s": round(T * width * 2 * 2 / us / 1e3, 1)}
 
 
+def timeline(args) -> dict:
+    import ctypes
+
+    from oxr_inference_b200.config import EngineSettings
+    from oxr_inference_b200.engine.api import Engine
+    from oxr_inference_b200.ops import build
+    from oxr_inference_b200.sampling import SamplingParams
+
+    if not build.TIMELINE:
+        raise SystemExit("set OXR_B200_TIMELINE=1: the stamps are compiled in only then (libraries of their own, *_tl)")
+    B, ctx, D = args.batch, args.context, args.head_dim
+    cfg = {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "hidden_size": args.hidden, "intermediate_size": args.intermediate,
+           "num_hidden_layers": args.layers, "num_attention_heads": args.heads, "num_key_value_heads": args.kv_heads, "head_dim": D,
+           "rms_norm_eps": 1e-6, "rope_theta": 1000000.0, "vocab_size": args.vocab, "tie_word_embeddings": False,
+           "max_position_embeddings": ctx + 512}
+    engine = Engine(random_config=cfg, seed=0, settings=EngineSettings(
+        dtype="bfloat16", page_size=args.page_size, num_pages=B * (ctx // args.page_size + 12) + 64, max_running=max(B, 8), cuda_graphs=True,
+        max_positions=ctx + 512))
+    gen = torch.Generator().manual_seed(0)
+    for _ in range(B):
+        engine.add_request(torch.randint(0, args.vocab, (ctx,), generator=gen).tolist(), SamplingParams(max_tokens=64, ignore_eos=True))
+    while engine.scheduler.waiting or any(r.pending > 1 for r in engine.scheduler.running):
+        engine.step()
+    for _ in range(6):
+        engine.step()          # decode steps: graphs captured, clocks up
+    torch.cuda.synchronize()
+    words = 1 << 15
+    readers = [(ops._lib(), "oxr_tl_read_stream"), (ops._lib(), "oxr_tl_read_elem"), (ops._lib(), "oxr_tl_read_rope"),
+               (ops._attn_lib(D), "oxr_tl_read_attn")]
+
+    def read(lib, name):
+        buf = (ctypes.c_ulonglong * words)()
+        fn = getattr(lib, name)
+        fn.argtypes, fn.restype = [ctypes.c_void_p, ctypes.c_int], ctypes.c_int
+        fn(buf, words)
+        return [tuple(buf[i * 6 + j] for j in range(6)) for i in range(words // 6) if buf[i * 6]]
+
+    for lib, name in readers:
+        read(lib, name)        # clears
+    torch.cuda.synchronize()
+    engine.step()
+    torch.cuda.synchronize()
+    records = sorted((r for lib, name in readers for r in read(lib, name)), key=lambda r: r[1])
+    names = {1: "stream gemm", 2: "rms norm", 3: "qk norm rope", 4: "attention", 5: "attention"}
+    launches: list[dict] = []
+    for r in records:      # a launch: records of one kind released within 2.5 us of each other (and, for products, of one size)
+        kind = names.get(r[0], str(r[0]))
+        size = (r[3], r[4]) if r[0] == 1 else None
+        if launches and launches[-1]["kind"] == kind and launches[-1]["size"] == size and r[1] - launches[-1]["released"] < 2500:
+            launches[-1]["records"].append(r)
+        else:
+            launches.append({"kind": kind, "size": size, "released": r[1], "records": [r]})
+    t0, rows, before = launches[0]["released"], [], None
+    for launch in launches:
+        rs = launch["records"]
+        released, first_end, last_end = min(r[1] for r in rs), min(r[2] for r in rs), max(r[2] for r in rs)
+        row = {"kernel": launch["kind"] + (f" N={launch['size'][0]} K={launch['size'][1]}" if launch["size"] else ""), "blocks": len(rs),
+               "released_us": round((released - t0) / 1e3, 2), "first_block_ends_us": round((first_end - released) / 1e3, 2),
+               "last_block_ends_us": round((last_end - released) / 1e3, 2),
+               "gap_since_kernel_before_us": None if before is None else round((released - before) / 1e3, 2)}
+        if launch["kind"] == "attention":
+            row["first_keys_us"] = [round(min(r[3] - r[1] for r in rs if r[3]) / 1e3, 2), round(max(r[3] - r[1] for r in rs if r[3]) / 1e3, 2)]
+            row["keys_streamed_us"] = [round(min(r[4] - r[1] for r in rs if r[4]) / 1e3, 2), round(max(r[4] - r[1] for r in rs if r[4]) / 1e3, 2)]
+        rows.append(row)
+        before = last_end
+    for row in rows:
+        print(json.dumps(row))
+    return {"kernel": "timeline", "batch": B, "context": ctx, "layers": args.layers, "launches": len(rows),
+            "step_us": round((max(r[2] for r in records) - t0) / 1e3, 1)}
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="what", required=True)
@@ -164,6 +240,18 @@ def main() -> None:
     r.add_argument("--head-dim", type=int, default=128)
     r.add_argument("--page-size", type=int, default=16)
     r.set_defaults(run=rope)
+    t = sub.add_parser("timeline", help="kernel by kernel through one decode step (needs OXR_B200_TIMELINE=1)")
+    t.add_argument("--batch", type=int, default=8)
+    t.add_argument("--context", type=int, default=2048)
+    t.add_argument("--layers", type=int, default=4)
+    t.add_argument("--hidden", type=int, default=4096)
+    t.add_argument("--intermediate", type=int, default=12288)
+    t.add_argument("--heads", type=int, default=32)
+    t.add_argument("--kv-heads", type=int, default=8)
+    t.add_argument("--head-dim", type=int, default=128)
+    t.add_argument("--vocab", type=int, default=151936)
+    t.add_argument("--page-size", type=int, default=16)
+    t.set_defaults(run=timeline)
     for p in (g, a, n, r):
         p.add_argument("--reps", type=int, default=20)
     args = ap.parse_args()
