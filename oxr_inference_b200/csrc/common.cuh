@@ -102,10 +102,11 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 // before it is complete and its writes are visible (which, since that kernel waited in the same way, holds for all
 // kernels before). What stands above the wait (barrier set-up, loads of weights, which no kernel of a step writes)
 // overlaps the tail of the kernel before. Both calls do nothing in a kernel launched the ordinary way.
-// Chained: RMSNorm, q/k norm + RoPE + store, split-KV attention (which fetches the old keys above its wait) and the
-// tcgen05 GEMMs (which request the weight tiles of their first ring of stages above their wait). The skinny GEMM
-// triggers (so the small kernel after it starts early) but is itself launched the ordinary way: launched chained it
-// made the step 4 % slower on a B200, with or without weight loads above its wait.
+// Chained: RMSNorm, q/k norm + RoPE + store, split-KV attention (which fetches the old keys above its wait), the
+// weight-streaming GEMM of decode steps (whose producer warp never waits) and the tcgen05 GEMMs (which request the
+// weight tiles of their first ring of stages above their wait). The register-fed skinny GEMM triggers (so the small
+// kernel after it starts early) but is itself launched the ordinary way: launched chained it made the step 4 % slower
+// on a B200, with or without weight loads above its wait.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

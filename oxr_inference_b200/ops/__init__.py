@@ -107,6 +107,12 @@ def _lib():
         lib.oxr_gemm_skinny_gated_bf16.argtypes = [p, p, p, i, i, i, p]
         lib.oxr_gemm_stream_bf16.argtypes = [p, p, p, i, i, i, i, p, p]
         lib.oxr_gemm_stream_gated_bf16.argtypes = [p, p, p, i, i, i, p, p]
+        lib.oxr_gemm_stream_add_bf16.argtypes = [p, p, p, p, p, p, p, i, i, i, p, p]
+        lib.oxr_gemm_stream_add_bf16.restype = c_int
+        lib.oxr_gemm_stream_scaled_bf16.argtypes = [p, p, p, i, f, p, i, i, i, i, p, p]
+        lib.oxr_gemm_stream_scaled_bf16.restype = c_int
+        lib.oxr_gemm_stream_blocks.argtypes = [i]
+        lib.oxr_gemm_stream_blocks.restype = c_int
         lib.oxr_gemm_tcgen05_bf16.argtypes = [p, p, p, i, i, i, i, i, i, p, p, p, p]
         lib.oxr_gemm_tcgen05_pair_bf16.argtypes = [p, p, p, i, i, i, i, i, p, p]
         lib.oxr_gemm_tcgen05_gated_bf16.argtypes = [p, p, p, i, i, i, i, p, p]
@@ -267,7 +273,13 @@ def gated_silu_linear(x: torch.Tensor, weight: torch.Tensor, interleave: int = 0
     """``silu(x Wg^T) * (x Wu^T)`` for a weight that stacks Wg and Wu: side by side (``interleave`` 0: one product,
     then the SiLU kernel) or alternating in groups of 8 rows. With alternating rows a bf16 product runs the kernel
     ``linear`` would pick for its size (skinny, one-SM or two-SM tcgen05) with an epilogue that applies SiLU to the fp32
-    sums and writes the gated product alone; 32-bit runs the product and then the SiLU kernel on interleaved columns."""
+    sums and writes the gated product alone; 32-bit runs the product and then the SiLU kernel on interleaved columns.
+    ``x`` may be a :class:`NormedLazily`."""
+    if isinstance(x, NormedLazily):
+        out = _scaled_linear(x, weight, gated=True) if interleave == GATE_UP_INTERLEAVE else None
+        if out is not None:
+            return out
+        x = x.materialize()
     _need(x, "x")
     _need(weight, "weight")
     m, k = x.shape
@@ -637,6 +649,11 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
     16-byte words). A weight kept in float32 under bfloat16 activations is multiplied in fp32 and the result
     rounded once.
     """
+    if isinstance(x, NormedLazily):
+        out = _scaled_linear(x, weight, gated=False) if out_dtype in (None, torch.bfloat16) else None
+        if out is not None:
+            return out
+        x = x.materialize()
     _need(x, "x")
     _need(weight, "weight")
     m, k = x.shape
@@ -688,6 +705,72 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
     if out_dtype == torch.float32:
         return torch.mm(x, weight.t(), out_dtype=torch.float32)
     return torch.mm(x, weight.t())
+
+
+FUSE_MAX_ROWS = min(16, int(os.environ.get("OXR_B200_FUSE_ROWS", "16")))
+"""Decode steps of up to this many rows fold their norms into the products around them (0: never)."""
+"""Most rows for which a decode step's RMSNorms are folded into the products around them."""
+
+
+class NormedLazily:
+    """``RMSNorm(residual) * weight`` with the row's scale still to be applied: ``y = bf16(residual * weight)`` and, per block
+    of the product that wrote it, the sums of squares of the block's columns of the residual (``ops.linear_add``).
+    ``ops.linear`` and ``ops.gated_silu_linear`` take it in place of x and scale their sums by rsqrt(mean + eps) row by row;
+    ``materialize()`` runs the norm kernel on the residual for anyone else."""
+
+    def __init__(self, y: torch.Tensor, residual: torch.Tensor, sums: torch.Tensor, blocks: int, weight: torch.Tensor, eps: float):
+        self.y, self.residual, self.sums, self.blocks, self.weight, self.eps = y, residual, sums, blocks, weight, float(eps)
+
+    @property
+    def shape(self) -> torch.Size:
+        return self.y.shape
+
+    def materialize(self) -> torch.Tensor:
+        return add_rms_norm(torch.zeros_like(self.y), self.residual, self.weight, self.eps, keep_residual=False)[0]
+
+
+def linear_add(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor | None, norm_weight: torch.Tensor, eps: float
+               ) -> tuple[NormedLazily, torch.Tensor] | None:
+    """``add_rms_norm(linear(x, weight), residual, norm_weight, eps)`` for a decode step without the norm kernel: ONE kernel
+    multiplies, rounds the product to bf16 as ``linear`` would, adds it into the fp32 residual stream (in place when one is
+    given), and leaves the new residual times the norm's weight in bf16 and the rows' sums of squares, block by block; the
+    row's scale rsqrt(mean + eps) is applied by the product that takes the result (:class:`NormedLazily`) to its fp32 sums.
+    None when the sizes do not allow it (more than ``FUSE_MAX_ROWS`` rows, not bf16, ...): the caller then runs the two
+    kernels."""
+    m, k = x.shape
+    n = weight.shape[0]
+    if not (STREAM_GEMM and 0 < m <= FUSE_MAX_ROWS and x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+            and k % 8 == 0 and n % 8 == 0 and weight.shape[1] == k and x.is_contiguous() and x.data_ptr() % 16 == 0
+            and weight.data_ptr() % 16 == 0 and norm_weight.numel() == n and norm_weight.dtype == torch.float32):
+        return None
+    if residual is not None:
+        _need(residual, "residual", torch.float32)
+        if residual.shape != (m, n):
+            raise KernelError(f"residual {tuple(residual.shape)} does not match the product's {(m, n)}")
+    lib = _lib()
+    blocks = lib.oxr_gemm_stream_blocks(n)
+    res_out = residual if residual is not None else torch.empty((m, n), dtype=torch.float32, device=x.device)
+    y = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
+    sums = torch.empty((blocks, 16), dtype=torch.float32, device=x.device)
+    code = lib.oxr_gemm_stream_add_bf16(res_out.data_ptr(), _ptr(residual), y.data_ptr(), sums.data_ptr(), norm_weight.data_ptr(),
+                                        x.data_ptr(), weight.data_ptr(), m, n, k, new_status(x.device).data_ptr(), _stream())
+    _done(code, "gemm_stream_add")
+    return NormedLazily(y, res_out, sums, blocks, norm_weight, eps), res_out
+
+
+def _scaled_linear(x: NormedLazily, weight: torch.Tensor, gated: bool) -> torch.Tensor | None:
+    """``linear`` (or, ``gated``, silu(gate) * up on a weight with alternating rows) of a lazily normalised x in ONE kernel
+    that scales its sums row by row; None when the sizes do not allow it."""
+    m, k = x.y.shape
+    n = weight.shape[0]
+    if not (STREAM_GEMM and m <= STREAM_MAX_ROWS and weight.dtype == torch.bfloat16 and weight.shape[1] == k and k % 8 == 0
+            and weight.data_ptr() % 16 == 0 and x.blocks <= num_sms() and (not gated or n % 16 == 0)):
+        return None
+    out = torch.empty((m, n // 2 if gated else n), dtype=torch.bfloat16, device=weight.device)
+    code = _lib().oxr_gemm_stream_scaled_bf16(out.data_ptr(), x.y.data_ptr(), x.sums.data_ptr(), x.blocks, x.eps, weight.data_ptr(), m, n, k,
+                                              int(gated), new_status(weight.device).data_ptr(), _stream())
+    _done(code, "gemm_stream_scaled")
+    return out
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor | None = None, seed_lo: torch.Tensor | None = None,

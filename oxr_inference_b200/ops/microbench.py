@@ -198,6 +198,8 @@ def timeline(args) -> dict:
                "released_us": round((released - t0) / 1e3, 2), "first_block_ends_us": round((first_end - released) / 1e3, 2),
                "last_block_ends_us": round((last_end - released) / 1e3, 2),
                "gap_since_kernel_before_us": None if before is None else round((released - before) / 1e3, 2)}
+        if launch["kind"] == "stream gemm":   # how long before their release the blocks were resident: earliest and latest block
+            row["resident_before_release_us"] = [round(max(r[1] - r[5] for r in rs) / 1e3, 2), round(min(r[1] - r[5] for r in rs) / 1e3, 2)]
         if launch["kind"] == "attention":
             row["first_keys_us"] = [round(min(r[3] - r[1] for r in rs if r[3]) / 1e3, 2), round(max(r[3] - r[1] for r in rs if r[3]) / 1e3, 2)]
             row["keys_streamed_us"] = [round(min(r[4] - r[1] for r in rs if r[4]) / 1e3, 2), round(max(r[4] - r[1] for r in rs if r[4]) / 1e3, 2)]

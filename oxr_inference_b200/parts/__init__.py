@@ -2,7 +2,7 @@
 
 from oxr_inference_b200.parts import attention, block, mlp, norm, rope  # noqa: F401  (register themselves)
 from oxr_inference_b200.parts.base import (ARRANGEMENTS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS,
-                                           Embedding, FeedForward, GroupView, Head, LayerCache, Mixer, Norm, PagedKVNeed,
+                                           DeferredLinear, Embedding, FeedForward, GroupView, Head, LayerCache, Mixer, Norm, PagedKVNeed,
                                            ParamInfo, Part, PositionEncoding, Runtime, StateNeed, StepContext)
 from oxr_inference_b200.parts.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
 
@@ -18,7 +18,7 @@ def __getattr__(name: str):
 
 
 __all__ = [
-    "ARRANGEMENTS", "EMBEDDINGS", "FEED_FORWARDS", "HEADS", "MIXERS", "NORMS", "POSITION_ENCODINGS", "DecoderModel", "Embedding",
+    "ARRANGEMENTS", "EMBEDDINGS", "FEED_FORWARDS", "HEADS", "MIXERS", "NORMS", "POSITION_ENCODINGS", "DecoderModel", "DeferredLinear", "Embedding",
     "FeedForward", "GroupView", "Head", "LayerCache", "LayerSpec", "Mixer", "ModelSpec", "Norm", "PagedKVNeed", "ParamInfo", "Part", "PartSpec",
     "PositionEncoding", "Runtime", "ScheduleEntry", "StateNeed", "StepContext",
 ]

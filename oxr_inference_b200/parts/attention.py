@@ -5,7 +5,8 @@ from __future__ import annotations
 import torch
 
 from oxr_inference_b200 import ops
-from oxr_inference_b200.parts.base import MIXERS, LayerCache, Mixer, PagedKVNeed, ParamInfo, PositionEncoding, Runtime, StepContext
+from oxr_inference_b200.parts.base import (MIXERS, DeferredLinear, LayerCache, Mixer, PagedKVNeed, ParamInfo, PositionEncoding, Runtime,
+                                           StepContext)
 from oxr_inference_b200.parts.linear import StackedLinear
 
 
@@ -59,7 +60,16 @@ class GroupedQueryAttention(Mixer):
     def tile_specs(self) -> list[tuple[int, int, int]]:
         return ops.attention_tile_specs(self.H, self.KV, self.D, self.runtime.dtype, self.runtime.page_size)
 
+    accepts_lazy_input = True   # h goes into the q|k|v projection and nowhere else
+
     def forward(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
+        return self.o_proj(self._attend(h, ctx, cache))
+
+    def forward_deferred(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache) -> DeferredLinear:
+        return DeferredLinear(self._attend(h, ctx, cache), self.o_proj)
+
+    def _attend(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
+        """Everything up to the output projection: ``[tokens, H * D]``."""
         group = cache.group
         k_pool, v_pool = group.k_pool[cache.layer_in_group], group.v_pool[cache.layer_in_group]
         qkv = self.qkv(h)
@@ -73,4 +83,4 @@ class GroupedQueryAttention(Mixer):
                                 block_table=group.block_table, page_size=group.page_size, scale=self.scale,
                                 window=self.window, kv_len_bound=ctx.kv_len_bound, status=ctx.status,
                                 kv_maps=group.kv_maps, layer_in_pool=cache.layer_in_group)
-        return self.o_proj(o.view(ctx.n_tokens, self.H * self.D))
+        return o.view(ctx.n_tokens, self.H * self.D)

@@ -145,7 +145,26 @@ class StepContext:
 
 
 # ------------------------------------------------------------------------------------------- families
+@dataclass
+class DeferredLinear:
+    """The last projection of a mixer or feed-forward, not yet multiplied: ``linear(x)``. The norm that comes next may fold
+    the product's add into the residual stream into the product itself. Only a norm that says ``accepts_deferred`` is
+    ever handed one; anyone else who holds one calls ``materialize()``."""
+
+    x: torch.Tensor
+    linear: Callable[[torch.Tensor], torch.Tensor]
+    """The projection: callable on ``x``; norms that fuse read its ``weight`` ([out, in])."""
+
+    def materialize(self) -> torch.Tensor:
+        return self.linear(self.x)
+
+
 class Norm(Part):
+    accepts_deferred = False
+    """Whether ``forward`` takes a :class:`DeferredLinear` in place of ``x`` and a keyword ``lazy``: with ``lazy=True`` it
+    may return, in place of the normalised tensor, an object that the next part's first projection normalises by itself
+    (it has ``materialize()``); the block asks for that only when the part behind the norm says ``accepts_lazy_input``."""
+
     def forward(self, x: torch.Tensor, residual: torch.Tensor | None):
         raise NotImplementedError
 
@@ -160,6 +179,10 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    accepts_lazy_input = False
+    """Whether ``forward`` may be handed a lazily normalised ``h`` (it then passes ``h`` to its first projection and
+    does nothing else with it)."""
+
     def cache_need(self) -> PagedKVNeed | StateNeed | None:
         return None
 
@@ -171,10 +194,20 @@ class Mixer(Part):
     def forward(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
         raise NotImplementedError
 
+    def forward_deferred(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache) -> "torch.Tensor | DeferredLinear":
+        """``forward`` with the last projection left to the caller where the mixer ends in one (optional to override)."""
+        return self.forward(h, ctx, cache)
+
 
 class FeedForward(Part):
+    accepts_lazy_input = False
+
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
+
+    def forward_deferred(self, h: torch.Tensor) -> "torch.Tensor | DeferredLinear":
+        """``forward`` with the last projection left to the caller where the part ends in one (optional to override)."""
+        return self.forward(h)
 
 
 class Embedding(Part):

@@ -129,7 +129,13 @@ class DecoderModel:
         x = self.embedding.forward(ctx.token_ids)
         residual = None
         for pos, entry in enumerate(self.schedule):
-            x, residual = self.blocks[entry.layer].forward(x, residual, ctx, cache.layer_cache(pos, ctx))
+            block = self.blocks[entry.layer]
+            # a block may leave its last projection to the next block's norm, if both sides say that they can
+            after = self.blocks[self.schedule[pos + 1].layer] if pos + 1 < len(self.schedule) else None
+            if getattr(block, "supports_deferred", False) and getattr(after, "accepts_deferred_input", False):
+                x, residual = block.forward(x, residual, ctx, cache.layer_cache(pos, ctx), defer_output=True)
+            else:
+                x, residual = block.forward(x, residual, ctx, cache.layer_cache(pos, ctx))
         if ctx.logit_rows.numel() == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.runtime.device)
         h = self.final_norm.forward_rows(x, residual, ctx.logit_rows)

@@ -48,5 +48,6 @@ class StackedLinear:
         lo = self.offsets[name]
         self.weight[lo:lo + self.outs[name]].copy_(tensor)
 
-    def __call__(self, x: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    def __call__(self, x, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+        """``x`` may be a lazily normalised input (``ops.NormedLazily``): the product then normalises it itself."""
         return ops.linear(x, self.weight, out_dtype)

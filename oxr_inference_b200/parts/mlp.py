@@ -5,7 +5,7 @@ from __future__ import annotations
 import torch
 
 from oxr_inference_b200 import ops
-from oxr_inference_b200.parts.base import FEED_FORWARDS, FeedForward, ParamInfo, Runtime
+from oxr_inference_b200.parts.base import FEED_FORWARDS, DeferredLinear, FeedForward, ParamInfo, Runtime
 from oxr_inference_b200.parts.linear import StackedLinear
 
 
@@ -33,5 +33,13 @@ class SwiGLU(FeedForward):
         else:
             raise KeyError(name)
 
+    accepts_lazy_input = True   # h goes into the gate|up projection and nowhere else
+
     def forward(self, h: torch.Tensor) -> torch.Tensor:
-        return self.down(ops.gated_silu_linear(h, self.gate_up.weight, self.gate_up.interleave))
+        return self.down(self._gated(h))
+
+    def forward_deferred(self, h: torch.Tensor) -> DeferredLinear:
+        return DeferredLinear(self._gated(h), self.down)
+
+    def _gated(self, h: torch.Tensor) -> torch.Tensor:
+        return ops.gated_silu_linear(h, self.gate_up.weight, self.gate_up.interleave)

@@ -5,7 +5,7 @@ from __future__ import annotations
 import torch
 
 from oxr_inference_b200 import ops
-from oxr_inference_b200.parts.base import NORMS, Norm, ParamInfo, Runtime
+from oxr_inference_b200.parts.base import NORMS, DeferredLinear, Norm, ParamInfo, Runtime
 
 
 @NORMS.register("rms_norm")
@@ -25,8 +25,23 @@ class RMSNorm(Norm):
             raise KeyError(name)
         self.weight = tensor.to(device=self.runtime.device, dtype=torch.float32).contiguous()
 
-    def forward(self, x, residual):
+    accepts_deferred = True
+
+    def forward(self, x, residual, lazy: bool = False):
+        """``x``: a tensor, or the part before with its last projection still to do. ``lazy``: whoever takes the result
+        passes it to a product and nowhere else, so the row's scale may be left to that product."""
+        if isinstance(x, DeferredLinear):
+            weight = getattr(x.linear, "weight", None)
+            if lazy and weight is not None:
+                # a decode step: the product adds itself into the residual stream and leaves the rows' sums of squares;
+                # the next part's first projection scales its sums (no norm kernel at all)
+                fused = ops.linear_add(x.x, weight, residual, self.weight, self.eps)
+                if fused is not None:
+                    return fused
+            x = x.materialize()
         return ops.add_rms_norm(x, residual, self.weight, self.eps)
 
     def forward_rows(self, x, residual, rows):
+        if isinstance(x, DeferredLinear):
+            x = x.materialize()
         return ops.add_rms_norm(x, residual, self.weight, self.eps, rows=rows)[0]

@@ -235,6 +235,71 @@ def test_gemm_stream_bf16(ops, M, N, K, out_dtype):
         assert torch.equal(ops.linear(x[r:r + 1].contiguous(), w, out_dtype)[0], got[r])
 
 
+@pytest.mark.parametrize("M", [1, 3, 8, 13, 16])
+@pytest.mark.parametrize("N,K,N2", [(512, 96, 304), (4096, 4096, 6144), (1000, 12288, 160), (4096, 520, 24576), (136, 160, 48)])
+@pytest.mark.parametrize("gated", [False, True])
+def test_gemm_stream_with_the_norm_folded_in(ops, M, N, K, N2, gated):
+    """product + residual add + RMSNorm + next product as TWO kernels: the first adds its product into the fp32 residual
+    stream and leaves residual * norm weight and the rows' sums of squares block by block, the second scales its sums. Against
+    the three kernels they replace (same roundings: product to bf16, normalised rows to bf16), with a residual whose rows
+    differ in size by orders of magnitude so that a wrong row's inverse norm shows."""
+    g = torch.Generator(device=DEV).manual_seed(11)
+    x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=DEV, generator=g) * 0.05).bfloat16()
+    res = torch.randn(M, N, device=DEV, generator=g) * (10.0 ** torch.arange(M, device=DEV).remainder(4).float()).unsqueeze(1)
+    nw = 1 + 0.3 * torch.randn(N, device=DEV, generator=g)
+    w2 = (torch.randn(N2, N, device=DEV, generator=g) * 0.05).bfloat16()
+    eps = 1e-5
+    # the kernels they replace
+    normed, res_want = ops.add_rms_norm(ops.linear(x, w), res.clone(), nw, eps)
+    want = ops.gated_silu_linear(normed, w2, ops.GATE_UP_INTERLEAVE) if gated else ops.linear(normed, w2)
+    status = ops.new_status(DEV)
+    res_got = res.clone()
+    fused = ops.linear_add(x, w, res_got, nw, eps)
+    assert fused is not None
+    lazy, res_out = fused
+    assert res_out.data_ptr() == res_got.data_ptr()
+    assert torch.equal(res_got, res_want)                      # the same bf16 product plus the same residual, exactly
+    sums = lazy.sums[:lazy.blocks, :M].sum(0)
+    torch.testing.assert_close(sums, res_want.square().sum(1), rtol=1e-5, atol=0)
+    torch.testing.assert_close(lazy.materialize().float(), normed.float(), atol=0, rtol=2 ** -7)   # one bf16 step
+    got = ops.gated_silu_linear(lazy, w2, ops.GATE_UP_INTERLEAVE) if gated else ops.linear(lazy, w2)
+    ops.check_status(status)
+    assert got.shape == want.shape and got.dtype == want.dtype
+    scale = want.float().abs().max().item()
+    assert (got.float() - want.float()).abs().max().item() <= 2e-2 * scale
+    # against plain 32-bit arithmetic as well
+    r32 = (x.float() @ w.float().T).bfloat16().float() + res
+    n32 = (r32 * torch.rsqrt(r32.square().mean(1, keepdim=True) + eps) * nw.float()).bfloat16().float()
+    p32 = n32 @ w2.float().T
+    if gated:   # gate and up rows alternate in groups of 8
+        p32 = p32.view(M, N2 // 16, 2, 8)
+        p32 = (torch.nn.functional.silu(p32[:, :, 0]) * p32[:, :, 1]).reshape(M, N2 // 2)
+    assert (got.float() - p32).abs().max().item() <= 2e-2 * p32.abs().max().item()
+    # a row's result does not depend on the rows beside it
+    for r in (0, M - 1):
+        rr = res[r:r + 1].clone()
+        lz, _ = ops.linear_add(x[r:r + 1].contiguous(), w, rr, nw, eps)
+        one = ops.gated_silu_linear(lz, w2, ops.GATE_UP_INTERLEAVE) if gated else ops.linear(lz, w2)
+        assert torch.equal(rr[0], res_got[r]) and torch.equal(one[0], got[r])
+
+
+def test_gemm_stream_norm_folding_refuses_what_it_cannot_do(ops):
+    g = torch.Generator(device=DEV).manual_seed(12)
+    x = torch.randn(17, 64, device=DEV, generator=g).bfloat16()          # more rows than the fused kernels take
+    w = torch.randn(128, 64, device=DEV, generator=g).bfloat16()
+    nw = torch.ones(128, device=DEV)
+    assert ops.linear_add(x, w, torch.zeros(17, 128, device=DEV), nw, 1e-6) is None
+    assert ops.linear_add(x[:4].float(), w.float(), torch.zeros(4, 128, device=DEV), nw, 1e-6) is None   # 32-bit
+    # a consumer that is not a product normalises with the norm kernel; so does a 32-bit product
+    res = torch.randn(8, 128, device=DEV, generator=g)
+    normed, _ = ops.add_rms_norm(ops.linear(x[:8].contiguous(), w), res.clone(), nw, 1e-6)
+    lazy, _ = ops.linear_add(x[:8].contiguous(), w, res.clone(), nw, 1e-6)
+    torch.testing.assert_close(lazy.materialize().float(), normed.float(), atol=0, rtol=2 ** -7)
+    w32 = torch.randn(48, 128, device=DEV, generator=g)
+    torch.testing.assert_close(ops.linear(lazy, w32).float(), ops.linear(normed, w32).float(), atol=2e-2, rtol=2e-2)
+
+
 @pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 33, 64])
 @pytest.mark.parametrize("N,K", [(509, 96), (192, 160), (4096, 4096), (1000, 12288)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])

@@ -137,6 +137,93 @@ def test_block_part_carries_the_residual_like_the_plain_layer():
     torch.testing.assert_close(out + residual, want, atol=2e-5, rtol=2e-5)
 
 
+@pytest.mark.parametrize("plain_norm_in_second_block", [False, True])
+def test_blocks_hand_their_last_projection_to_the_next_norm_in_a_bf16_decode_step(monkeypatch, plain_norm_in_second_block):
+    """Two pre-norm blocks on five rows in bfloat16: with the norms folded into the products around them (the block leaves
+    its last projection to the next norm, the norm leaves the row's scale to the next product) and with every kernel on
+    its own the residual stream and the output agree within bf16 rounding; and the 32-bit plain layers say the same. A norm
+    that does not take part (defined here) gets whole tensors and the blocks around it still fold what they can."""
+    from oxr_inference_b200 import ops
+    from oxr_inference_b200.parts import ARRANGEMENTS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, DeferredLinear
+    from oxr_inference_b200.parts.base import Norm, ParamInfo
+
+    if "toy_unfused_rms" not in NORMS:
+        @NORMS.register("toy_unfused_rms")
+        class ToyNorm(Norm):
+            def __init__(self, runtime, *, size, eps):
+                self.runtime, self.size, self.eps, self.weight = runtime, size, eps, None
+
+            def parameters(self):
+                return {"weight": ParamInfo((self.size,), init="around_one", role="vector")}
+
+            def assign(self, name, tensor):
+                self.weight = tensor.to(device=self.runtime.device, dtype=torch.float32).contiguous()
+
+            def forward(self, x, residual):
+                assert isinstance(x, torch.Tensor)      # never a deferred projection, never asked to be lazy
+                return ops.add_rms_norm(x, residual, self.weight, self.eps)
+
+    rt = _runtime(torch.bfloat16)
+    hidden, inter = 96, 208
+    cfg = {"num_attention_heads": 3, "num_key_value_heads": 1, "head_dim": 32, "rms_norm_eps": 1e-5, "hidden_size": hidden,
+           "num_hidden_layers": 2}
+    rope = POSITION_ENCODINGS.build("rope_neox", rt, dim=32, theta=1e4)
+    blocks, w = [], {}
+    for layer in range(2):
+        attn = MIXERS.build("gqa_attention", rt, rope, hidden_size=hidden, num_heads=3, num_kv_heads=1, head_dim=32, scale=32 ** -0.5,
+                            eps=1e-5)
+        kind = "toy_unfused_rms" if (plain_norm_in_second_block and layer == 1) else "rms_norm"
+        n1, n2 = NORMS.build(kind, rt, size=hidden, eps=1e-5), NORMS.build("rms_norm", rt, size=hidden, eps=1e-5)
+        ff = FEED_FORWARDS.build("swiglu", rt, hidden_size=hidden, intermediate_size=inter)
+        blocks.append(ARRANGEMENTS.build("pre_norm", attn, n1, ff, n2))
+        for prefix, part, seed in ((f"model.layers.{layer}.self_attn.", attn, 10 * layer + 1), (f"model.layers.{layer}.input_layernorm.", n1, 10 * layer + 2),
+                                   (f"model.layers.{layer}.mlp.", ff, 10 * layer + 3), (f"model.layers.{layer}.post_attention_layernorm.", n2, 10 * layer + 4)):
+            # projections live in bfloat16 in the parts, norm weights in 32-bit
+            w.update({prefix + k: (v if "layernorm" in prefix else v.bfloat16().float()).to(DEV) for k, v in _fill(part, seed, 0.15).items()})
+    assert blocks[0].supports_deferred and blocks[0].accepts_deferred_input
+    assert blocks[1].accepts_deferred_input != plain_norm_in_second_block
+    rows = 5
+    x = torch.randn(rows, hidden, device=DEV).bfloat16()
+
+    def run(fold: bool):
+        monkeypatch.setattr(ops, "FUSE_MAX_ROWS", 16 if fold else 0)
+        seen = []
+        real = ops.linear_add
+        monkeypatch.setattr(ops, "linear_add", lambda *a, **k: (seen.append(1), real(*a, **k))[1])
+        from oxr_inference_b200.cache import CacheManager, make_cache_plan
+        from oxr_inference_b200.engine.batch import BatchBuilder, StepEntry
+        plan = make_cache_plan([blk.mixer.cache_need() for blk in blocks], [None, None])
+        manager = CacheManager(plan, page_size=8, num_pages=64, max_requests=8, device=rt.device, dtype=rt.dtype)
+        builder = BatchBuilder(manager, blocks[0].mixer.tile_specs(), rt.device, rt.status)
+        reqs = [manager.open(f"r{i}") for i in range(rows)]      # five requests of one token each: a decode step
+        for r in reqs:
+            assert manager.reserve(r, 1)
+        ctx = builder.build([StepEntry(r, [0], []) for r in reqs])
+        h, residual = x, None
+        defer_first = blocks[1].accepts_deferred_input
+        h, residual = blocks[0].forward(h, residual, ctx, manager.layer_cache(0, ctx), defer_output=defer_first)
+        assert isinstance(h, DeferredLinear) == defer_first
+        h, residual = blocks[1].forward(h, residual, ctx, manager.layer_cache(1, ctx))
+        ops.check_status(rt.status)
+        monkeypatch.setattr(ops, "linear_add", real)
+        return h.float() + residual, len(seen)
+
+    folded, n_folded = run(True)
+    apart, n_apart = run(False)
+    # every norm that follows a projection folds when it takes part: two inside the blocks, one between them
+    assert n_folded == (2 if plain_norm_in_second_block else 3)
+    assert n_apart == n_folded      # asked every time, refused (None) when switched off
+    scale = apart.abs().max().item()
+    assert (folded - apart).abs().max().item() <= 2e-2 * scale
+    # each request is one token at position 0: the plain layers on a one-token sequence each
+    cos, sin = QP.rope_tables(32, 1e4, 1, torch.float32)
+    for i in range(rows):
+        want = x[i:i + 1].float()
+        for layer in range(2):
+            want = QP.decoder_layer(want, w, layer, cfg, cos.to(DEV), sin.to(DEV))
+        assert (folded[i:i + 1] - want).abs().max().item() <= 3e-2 * want.abs().max().item()
+
+
 def test_embedding_and_head_parts_tied_and_untied():
     from oxr_inference_b200.parts.decoder import OutputHead, TokenEmbedding
 
