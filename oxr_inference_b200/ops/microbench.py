@@ -58,10 +58,12 @@ def gemm(args) -> dict:
     out_dtype = torch.float32 if args.fp32_out else torch.bfloat16
     if args.library:   # cuBLAS through torch.mm, for comparison
         us = _time(lambda i: torch.mm(x, ws[i % copies].t()), args.reps)
+    elif args.gated:   # silu(gate) * up of a weight whose gate and up rows alternate in groups of 8
+        us = _time(lambda i: ops.gated_silu_linear(x, ws[i % copies], ops.GATE_UP_INTERLEAVE), args.reps)
     else:
         us = _time(lambda i: ops.linear(x, ws[i % copies], out_dtype), args.reps)
     bytes_ = n * k * 2 + m * k * 2 + m * n * (4 if args.fp32_out else 2)
-    return {"kernel": "torch.mm (cuBLAS)" if args.library else "linear", "m": m, "n": n, "k": k, "us": round(us, 2), "GB/s": round(bytes_ / us / 1e3, 1),
+    return {"kernel": "torch.mm (cuBLAS)" if args.library else "gated_silu_linear" if args.gated else "linear", "m": m, "n": n, "k": k, "us": round(us, 2), "GB/s": round(bytes_ / us / 1e3, 1),
             "TFLOP/s": round(2 * m * n * k / us / 1e6, 2)}
 
 
@@ -220,6 +222,7 @@ def main() -> None:
     g.add_argument("--k", type=int, default=4096)
     g.add_argument("--fp32-out", action="store_true")
     g.add_argument("--library", action="store_true", help="time torch.mm (cuBLAS) on the same sizes instead")
+    g.add_argument("--gated", action="store_true", help="the product with the SiLU epilogue (n counts gate and up rows)")
     g.set_defaults(run=gemm)
     a = sub.add_parser("attention")
     a.add_argument("--batch", type=int, default=8)
