@@ -1305,7 +1305,7 @@ __device__ __forceinline__ float fast_exp2(float x) {
 
 __global__ void __launch_bounds__(TC_THREADS, 1)
 attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, const __grid_constant__ CUtensorMap map_k,
-                        const __grid_constant__ CUtensorMap map_v, int pool_row0, int box_rows, const AttnArgs a) {
+                        const __grid_constant__ CUtensorMap map_v, int pool_row0, int box_rows, int n_tiles, int n_y, const AttnArgs a) {
     // The kernel has no static shared memory, so the dynamic part starts at the block's shared-memory origin, which
     // is 1024-byte aligned as the swizzled tiles need (checked below).
     extern __shared__ __align__(1024) unsigned char smem_dyn[];
@@ -1320,9 +1320,14 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
     uint64_t* p_full = s_empty + 4;              // [half][2] P(b) is in shared memory and O is rescaled (4 arrivals)
     uint64_t* o_done = p_full + 4;               // [half][2] O += P(b) V(b) has completed
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 4);
+#ifdef OXR_TIMELINE
+    unsigned long long* tl = reinterpret_cast<unsigned long long*>(o_done + 5);   // five stamps in the spare bytes behind the barriers
+#endif
 
     // the list is in token order and later tiles of a prompt see more keys: start the long ones first
-    const TileGeometry g = tile_geometry(a, BIG_ROWS, (int)(gridDim.x - 1 - blockIdx.x));
+    [[maybe_unused]] const unsigned long long tl_started = OXR_TL_NOW();
+    // and all (KV head, head group) pairs of a tile side by side, so that no pair's long tiles wait behind another pair's short ones
+    const TileGeometry g = tile_geometry(a, BIG_ROWS, n_tiles - 1 - (int)(blockIdx.x / (unsigned)n_y), (int)(blockIdx.x % (unsigned)n_y));
     if (g.tok0 >= g.tok_end) return;
     if (smem_addr(base) & 1023u) {   // cannot happen without static shared memory; refuse rather than compute rubbish
         if (threadIdx.x == 0) oxr_report(a.status, OXR_BAD_ARGUMENT, 1024);
@@ -1364,6 +1369,9 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
+#ifdef OXR_TIMELINE
+    if (threadIdx.x == 0) tl[0] = OXR_TL_NOW();
+#endif
     // TMEM columns: S of half h, buffer i at (2 h + i) * 64; O of half h at 256 + h * D
     // the second half of a tile may be empty (short portions): its products and softmax are then skipped
     const bool half1_live = g.tok0 + (HALF_ROWS / g.heads_per_tile) < g.tok_end || g.heads_per_tile > HALF_ROWS;
@@ -1404,6 +1412,9 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
                     }
                 }
             }
+#ifdef OXR_TIMELINE
+            if (b == 0 && lane == 0) tl[1] = OXR_TL_NOW();
+#endif
         }
     } else if (warp == 1) {
         // ---------------------------------------------------------------------- MMA issuer
@@ -1417,6 +1428,9 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
             auto issue_s = [&](int b) -> bool {
                 const int st = b % TC_STAGES;
                 if (!mbar_wait(kv_full + st, (b / TC_STAGES) & 1)) { oxr_report(a.status, OXR_WAIT_EXPIRED, 31); return false; }
+#ifdef OXR_TIMELINE
+                if (b == 0) tl[2] = OXR_TL_NOW();
+#endif
                 const uint32_t k_addr = smem_addr(stages + (size_t)st * KV_STAGE_BYTES);
                 for (int h = 0; h < halves; ++h) {
                     if (!mbar_wait(s_empty + 2 * h + (b & 1), ((b >> 1) & 1) ^ 1)) { oxr_report(a.status, OXR_WAIT_EXPIRED, 32); return false; }
@@ -1470,6 +1484,9 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
         for (int b = 0; b < count; ++b) {
             const int key0 = k_first + b * MMA_BN;
             if (!mbar_wait(my_s_full + (b & 1), (b >> 1) & 1)) { if (lane == 0) oxr_report(a.status, OXR_WAIT_EXPIRED, 34); alive = false; break; }
+#ifdef OXR_TIMELINE
+            if (b == 0 && warp == 2 && lane == 0) tl[3] = OXR_TL_NOW();
+#endif
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             uint32_t sv[2][32];
             tc_ld32(tmem_base + lane_base + (uint32_t)((2 * half + (b & 1)) * MMA_BN), sv[0]);
@@ -1548,6 +1565,9 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
             if (!mbar_wait(my_o_done + (last & 1), (last >> 1) & 1)) { if (lane == 0) oxr_report(a.status, OXR_WAIT_EXPIRED, 37); alive = false; }
         }
         alive = __all_sync(0xffffffffu, alive);
+#ifdef OXR_TIMELINE
+        if (warp == 2 && lane == 0) tl[4] = OXR_TL_NOW();
+#endif
         if (alive) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const float inv = l > 0.f ? 1.f / l : 0.f;
@@ -1572,6 +1592,12 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+#ifdef OXR_TIMELINE
+    if (threadIdx.x == 0) {   // ids 6 and 7: a prefill tile (started, ended, set up, first S in tensor memory, epilogue begins; first loads issued, first keys landed)
+        OXR_TL_PUT(6ull | ((unsigned long long)count << 8), tl_started, OXR_TL_NOW(), tl[0], tl[3], tl[4]);
+        OXR_TL_PUT(7ull | ((unsigned long long)count << 8), tl_started, tl[1], tl[2], blockIdx.x, 0);
+    }
+#endif
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TC_TMEM_COLS) : "memory");
@@ -1640,12 +1666,12 @@ OXR_API int oxr_paged_attention_bf16(void* out, const void* q, const void* k_cac
         }
         const int hpt = G < BIG_ROWS ? G : BIG_ROWS;
         const int groups = (G + hpt - 1) / hpt;
-        if ((size_t)KV * groups > 65535) return OXR_BAD_ARGUMENT;
+        if ((size_t)KV * groups * (size_t)n_long > 0x7fffffffull) return OXR_BAD_ARGUMENT;
         a.tile_req = long_req; a.tile_tok0 = long_tok0;
         const CUtensorMap* maps = reinterpret_cast<const CUtensorMap*>(kv_maps);
         const int box_rows = page_size < MMA_BN ? page_size : MMA_BN;
-        attn_tc5_prefill_kernel<<<dim3(n_long, KV * groups), TC_THREADS, TC_SMEM, stream>>>((bf16*)out, (const bf16*)q, maps[0], maps[1],
-                                                                                             pool_row0, box_rows, a);
+        attn_tc5_prefill_kernel<<<dim3((unsigned)(n_long * KV * groups)), TC_THREADS, TC_SMEM, stream>>>(
+            (bf16*)out, (const bf16*)q, maps[0], maps[1], pool_row0, box_rows, n_long, KV * groups, a);
         int rc = oxr_launch_status();
         if (rc) return rc;
     } else if (n_long > 0) {
