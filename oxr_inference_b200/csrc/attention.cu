@@ -1242,7 +1242,7 @@ constexpr int TC_STAGES = 4;
 constexpr int TC_THREADS = 320;                                     // warp 0 TMA, warp 1 MMA, warps 2..9 softmax (4 per half)
 constexpr int Q_PANEL_BYTES = HALF_ROWS * 128;                      // 128 rows x 64 d
 constexpr int P_BYTES = HALF_ROWS * 128;                            // 128 rows x 64 keys
-constexpr size_t TC_SMEM = 2 * (size_t)PANELS * Q_PANEL_BYTES + (size_t)TC_STAGES * KV_STAGE_BYTES + 2 * P_BYTES + 256;
+constexpr size_t TC_SMEM = 2 * (size_t)PANELS * Q_PANEL_BYTES + (size_t)TC_STAGES * KV_STAGE_BYTES + 2 * P_BYTES + 512;
 constexpr uint32_t TC_TMEM_COLS = 512;                              // S[half][2] (4 x 64) | O[half] (2 x D)
 constexpr float RESCALE_THRESHOLD = 8.f;
 
@@ -1305,7 +1305,8 @@ __device__ __forceinline__ float fast_exp2(float x) {
 
 __global__ void __launch_bounds__(TC_THREADS, 1)
 attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, const __grid_constant__ CUtensorMap map_k,
-                        const __grid_constant__ CUtensorMap map_v, int pool_row0, int box_rows, int n_tiles, int n_y, const AttnArgs a) {
+                        const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_q, int q_by_tma,
+                        int pool_row0, int box_rows, int n_tiles, int n_y, const AttnArgs a) {
     // The kernel has no static shared memory, so the dynamic part starts at the block's shared-memory origin, which
     // is 1024-byte aligned as the swizzled tiles need (checked below).
     extern __shared__ __align__(1024) unsigned char smem_dyn[];
@@ -1319,13 +1320,21 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
     uint64_t* s_empty = s_full + 4;              // [half][2] the half's softmax warps have read S(b) (4 arrivals)
     uint64_t* p_full = s_empty + 4;              // [half][2] P(b) is in shared memory and O is rescaled (4 arrivals)
     uint64_t* o_done = p_full + 4;               // [half][2] O += P(b) V(b) has completed
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 4);
+    uint64_t* q_ready = o_done + 4;              // Q is in shared memory (one arrival per softmax warp)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_ready + 1);
 #ifdef OXR_TIMELINE
-    unsigned long long* tl = reinterpret_cast<unsigned long long*>(o_done + 5);   // five stamps in the spare bytes behind the barriers
+    unsigned long long* tl = reinterpret_cast<unsigned long long*>(q_ready + 2);   // eight stamps in the spare bytes behind the barriers
+    unsigned long long* tl2 = tl + 8;                                              // and sixteen inside block TLB of a long tile
+    constexpr int TLB = 10;
 #endif
 
     // the list is in token order and later tiles of a prompt see more keys: start the long ones first
     [[maybe_unused]] const unsigned long long tl_started = OXR_TL_NOW();
+    if (threadIdx.x == 0) {   // the two tensor maps are on their way before anything else
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
+        if (q_by_tma) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
+    }
     // and all (KV head, head group) pairs of a tile side by side, so that no pair's long tiles wait behind another pair's short ones
     const TileGeometry g = tile_geometry(a, BIG_ROWS, n_tiles - 1 - (int)(blockIdx.x / (unsigned)n_y), (int)(blockIdx.x % (unsigned)n_y));
     if (g.tok0 >= g.tok_end) return;
@@ -1342,29 +1351,15 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
     if (threadIdx.x == 0) {
         for (int i = 0; i < TC_STAGES; ++i) { mbar_init(kv_full + i, 1); mbar_init(kv_empty + i, 1); }
         for (int i = 0; i < 4; ++i) { mbar_init(s_full + i, 1); mbar_init(s_empty + i, 4); mbar_init(p_full + i, 4); mbar_init(o_done + i, 1); }
+        mbar_init(q_ready, q_by_tma ? 1 : TC_THREADS / 32 - 2);
         mbar_fence_init();
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(TC_TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    // The stages must hold finite numbers where pages are not fetched (they meet a probability of exactly zero).
-    for (int i = threadIdx.x; i < (int)((size_t)TC_STAGES * KV_STAGE_BYTES / 16); i += TC_THREADS)
-        reinterpret_cast<uint4*>(stages)[i] = make_uint4(0, 0, 0, 0);
-    // Q: every softmax thread copies its own row (D bf16) into the swizzled panels; rows without a (token, head) are zero.
-    if (warp >= 2) {
-        const int half = (warp - 2) >> 2, rr = (warp & 3) * 32 + lane;   // row inside the half = its TMEM lane
-        int tok, gh;
-        const bool ok = g.row(half * HALF_ROWS + rr, tok, gh);
-        const uint4* src = reinterpret_cast<const uint4*>(q + ((size_t)(g.q_begin + (ok ? tok : 0)) * a.H + (size_t)g.kvh * g.G + (ok ? gh : 0)) * D);
-        unsigned char* qh = Qs + (size_t)half * PANELS * Q_PANEL_BYTES;
-#pragma unroll
-        for (int c = 0; c < D / 8; ++c) {
-            const uint4 v = ok ? __ldg(src + c) : make_uint4(0, 0, 0, 0);
-            *reinterpret_cast<uint4*>(qh + (size_t)(c >> 3) * Q_PANEL_BYTES + (size_t)rr * 128 + (((c & 7) ^ (rr & 7)) << 4)) = v;
-        }
-    }
-    fence_proxy_async();
+    // Nothing else stands before the first loads: the producer warp goes ahead while the softmax warps bring Q in (the MMA
+    // warp waits for `q_ready` before its first product).
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -1372,6 +1367,24 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
 #ifdef OXR_TIMELINE
     if (threadIdx.x == 0) tl[0] = OXR_TL_NOW();
 #endif
+    // Q without a tensor map (a number of heads per KV head that does not divide 128): every softmax thread copies its own row
+    // (D bf16) into the swizzled panels; rows without a (token, head) are zero.
+    if (warp >= 2 && !q_by_tma) {
+        const int half = (warp - 2) >> 2, rr = (warp & 3) * 32 + lane;   // row inside the half = its TMEM lane
+        int tok, gh;
+        const bool ok = g.row(half * HALF_ROWS + rr, tok, gh);
+        const uint4* src = reinterpret_cast<const uint4*>(q + ((size_t)(g.q_begin + (ok ? tok : 0)) * a.H + (size_t)g.kvh * g.G + (ok ? gh : 0)) * D);
+        unsigned char* qh = Qs + (size_t)half * PANELS * Q_PANEL_BYTES;
+        uint4 v[D / 8];
+#pragma unroll
+        for (int c = 0; c < D / 8; ++c) v[c] = ok ? __ldg(src + c) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int c = 0; c < D / 8; ++c)
+            *reinterpret_cast<uint4*>(qh + (size_t)(c >> 3) * Q_PANEL_BYTES + (size_t)rr * 128 + (((c & 7) ^ (rr & 7)) << 4)) = v[c];
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(q_ready);
+    }
     // TMEM columns: S of half h, buffer i at (2 h + i) * 64; O of half h at 256 + h * D
     // the second half of a tile may be empty (short portions): its products and softmax are then skipped
     const bool half1_live = g.tok0 + (HALF_ROWS / g.heads_per_tile) < g.tok_end || g.heads_per_tile > HALF_ROWS;
@@ -1380,6 +1393,16 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
         // ---------------------------------------------------------------------- TMA producer (all 32 lanes issue)
         const int* table_row = a.block_table + (size_t)g.req * a.table_width;
         const int boxes = MMA_BN / box_rows, loads = boxes * 2 * PANELS;
+        if (q_by_tma && lane == 0) {
+            // Q: one box per half and 64-wide panel, rows in the order (token, head) as the tile counts them. Rows behind the
+            // request's last token are somebody else's (or zero behind the tensor): finite, and masked like the padding rows.
+            const int halves = half1_live ? 2 : 1;
+            mbar_expect_tx(q_ready, (uint32_t)(halves * PANELS * Q_PANEL_BYTES));
+            for (int h = 0; h < halves; ++h)
+                for (int pnl = 0; pnl < PANELS; ++pnl)
+                    tma_load_3d(Qs + (size_t)(h * PANELS + pnl) * Q_PANEL_BYTES, &map_q, pnl * 64, g.kvh * g.G,
+                                g.q_begin + g.tok0 + h * (HALF_ROWS / g.G), q_ready);
+        }
         for (int b = 0; b < count; ++b) {
             const int st = b % TC_STAGES;
             if (!mbar_wait(kv_empty + st, ((b / TC_STAGES) & 1) ^ 1)) { if (lane == 0) oxr_report(a.status, OXR_WAIT_EXPIRED, 30); break; }
@@ -1395,6 +1418,28 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
                 }
             }
             const int total = __reduce_add_sync(0xffffffffu, my_bytes);
+#ifdef OXR_TIMELINE
+            if (b == 0 && lane == 0) tl[5] = OXR_TL_NOW();
+#endif
+            if (total < loads * box_rows * 128) {
+                // Page pieces that are not fetched (beyond the last key, before the window, a bad page) meet a probability of
+                // exactly zero, but must hold finite numbers: zero them (the stage may hold anything from an earlier kernel).
+                for (int i = lane; i < loads; i += 32) {
+                    const int box = i / (2 * PANELS), which = i % (2 * PANELS);
+                    const int kp = k0 + box * box_rows;
+                    bool fetched = false;
+                    if (kp < k_end && kp + box_rows > k_lo) {
+                        const int page = table_row[a.page_shift >= 0 ? (kp >> a.page_shift) : (kp / a.page_size)];
+                        fetched = page >= 0 && page < a.num_pages;
+                    }
+                    if (!fetched) {
+                        uint4* z = reinterpret_cast<uint4*>(dst + (size_t)which * PANEL_BYTES + (size_t)box * box_rows * 128);
+                        for (int j = 0; j < box_rows * 8; ++j) z[j] = make_uint4(0, 0, 0, 0);
+                    }
+                }
+                fence_proxy_async();
+                __syncwarp();
+            }
             if (lane == 0) {
                 if (total > 0) mbar_expect_tx(kv_full + st, (uint32_t)total);
                 else mbar_arrive(kv_full + st);
@@ -1444,20 +1489,33 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
                 }
                 return true;
             };
-            ok = issue_s(0);
+            if (!mbar_wait(q_ready, 0)) { oxr_report(a.status, OXR_WAIT_EXPIRED, 36); ok = false; }
+            ok = ok && issue_s(0);
             for (int b = 0; b < count && ok; ++b) {
+#ifdef OXR_TIMELINE
+                if (b == TLB) tl2[0] = OXR_TL_NOW();
+#endif
                 if (b + 1 < count) ok = issue_s(b + 1);
                 if (!ok) break;
+#ifdef OXR_TIMELINE
+                if (b == TLB) tl2[1] = OXR_TL_NOW();
+#endif
                 const int st = b % TC_STAGES;
                 const uint32_t v_addr = smem_addr(stages + (size_t)st * KV_STAGE_BYTES + (size_t)PANELS * PANEL_BYTES);
                 for (int h = 0; h < halves && ok; ++h) {
                     if (!mbar_wait(p_full + 2 * h + (b & 1), (b >> 1) & 1)) { oxr_report(a.status, OXR_WAIT_EXPIRED, 33); ok = false; break; }
+#ifdef OXR_TIMELINE
+                    if (b == TLB) tl2[2 + 2 * h] = OXR_TL_NOW();
+#endif
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
                     for (int kk = 0; kk < MMA_BN / 16; ++kk)
                         tc_mma(tmem_base + 256 + (uint32_t)(h * D), desc_kmajor(p_addr + h * P_BYTES + kk * 32),
                                desc_mnmajor(v_addr + kk * 16 * 128), idesc_o, (b > 0 || kk > 0) ? 1u : 0u);
                     tc_commit(o_done + 2 * h + (b & 1));
+#ifdef OXR_TIMELINE
+                    if (b == TLB) tl2[3 + 2 * h] = OXR_TL_NOW();
+#endif
                 }
                 if (!ok) break;
                 tc_commit(kv_empty + st);       // K and V of this stage have been read by all products of the block
@@ -1486,6 +1544,8 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
             if (!mbar_wait(my_s_full + (b & 1), (b >> 1) & 1)) { if (lane == 0) oxr_report(a.status, OXR_WAIT_EXPIRED, 34); alive = false; break; }
 #ifdef OXR_TIMELINE
             if (b == 0 && warp == 2 && lane == 0) tl[3] = OXR_TL_NOW();
+            const bool tl_me = b == TLB && lane == 0 && quarter == 0;
+            if (tl_me) tl2[6 + 4 * half] = OXR_TL_NOW();
 #endif
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             uint32_t sv[2][32];
@@ -1493,6 +1553,9 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
             tc_ld32(tmem_base + lane_base + (uint32_t)((2 * half + (b & 1)) * MMA_BN + 32), sv[1]);
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
+#ifdef OXR_TIMELINE
+            if (tl_me) tl2[7 + 4 * half] = OXR_TL_NOW();
+#endif
             if (lane == 0) mbar_arrive(my_s_empty + (b & 1));    // S(b) is in registers: the buffer may take S(b + 2)
             // Blocks that this row sees in full need no per-key test; on the others the hidden keys become -inf.
             const bool whole = row_ok && key0 + MMA_BN - 1 <= row_pos && key0 >= k_lo && (a.window <= 0 || key0 > row_pos - a.window);
@@ -1523,6 +1586,9 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
             // the half's one P buffer was last read by O(b - 1), which must also be finished before a raised maximum rescales O
             const bool any_raise = __any_sync(0xffffffffu, raise && b > 0);
             if (b >= 1 && !mbar_wait(my_o_done + ((b - 1) & 1), ((b - 1) >> 1) & 1)) { if (lane == 0) oxr_report(a.status, OXR_WAIT_EXPIRED, 35); alive = false; break; }
+#ifdef OXR_TIMELINE
+            if (tl_me) tl2[8 + 4 * half] = OXR_TL_NOW();
+#endif
             if (any_raise) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
@@ -1558,6 +1624,9 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
             fence_proxy_async();                      // P is read by the tensor core through the async proxy
             __syncwarp();
             if (lane == 0) mbar_arrive(my_p_full + (b & 1));
+#ifdef OXR_TIMELINE
+            if (tl_me) tl2[9 + 4 * half] = OXR_TL_NOW();
+#endif
         }
         // ---- epilogue: O / l -> out
         if (alive && count > 0) {
@@ -1567,35 +1636,59 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
         alive = __all_sync(0xffffffffu, alive);
 #ifdef OXR_TIMELINE
         if (warp == 2 && lane == 0) tl[4] = OXR_TL_NOW();
+        if (warp == 6 && lane == 0) tl[6] = OXR_TL_NOW();
 #endif
         if (alive) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const float inv = l > 0.f ? 1.f / l : 0.f;
-            bf16* dst = out + ((size_t)(g.q_begin + (row_ok ? tok : 0)) * a.H + (size_t)g.kvh * g.G + (row_ok ? gh : 0)) * D;
+            // The row goes, as bf16, into the place of this half's Q (every product that read Q has completed), 16-byte pieces
+            // swizzled by the row; then the warp writes its 32 rows out two at a time, 256 contiguous bytes each.
+            unsigned char* oh = Qs + (size_t)half * PANELS * Q_PANEL_BYTES;
 #pragma unroll 1
             for (int c = 0; c < D / 32; ++c) {
                 uint32_t ov[32];
                 tc_ld32(tmem_o + lane_base + (uint32_t)(c * 32), ov);
-                if (row_ok) {
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        uint4 o4;
-                        __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o4);
+                for (int j = 0; j < 4; ++j) {
+                    uint4 o4;
+                    __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o4);
 #pragma unroll
-                        for (int e = 0; e < 4; ++e)
-                            op[e] = __floats2bfloat162_rn(__uint_as_float(ov[8 * j + 2 * e]) * inv, __uint_as_float(ov[8 * j + 2 * e + 1]) * inv);
-                        reinterpret_cast<uint4*>(dst + c * 32)[j] = o4;
-                    }
+                    for (int e = 0; e < 4; ++e)
+                        op[e] = __floats2bfloat162_rn(__uint_as_float(ov[8 * j + 2 * e]) * inv, __uint_as_float(ov[8 * j + 2 * e + 1]) * inv);
+                    *reinterpret_cast<uint4*>(oh + (size_t)rr * (D * 2) + (((c * 4 + j) ^ (rr & (D / 8 - 1))) << 4)) = o4;
                 }
             }
+            __syncwarp();
+            constexpr int LPR = D / 8;                 // lanes per row
+            constexpr int RPI = 32 / LPR;              // rows per instruction
+            // where this thread's row goes (null: nowhere); the copying lanes ask the row's owner
+            const unsigned long long my_dst = row_ok ? (unsigned long long)(out + ((size_t)(g.q_begin + tok) * a.H + (size_t)g.kvh * g.G + gh) * D) : 0ull;
+#pragma unroll 4
+            for (int it = 0; it < 32 / RPI; ++it) {
+                const int owner = it * RPI + lane / LPR, c2 = lane % LPR;
+                const int r2 = quarter * 32 + owner;
+                const unsigned long long dst2 = __shfl_sync(0xffffffffu, my_dst, owner);
+                if (dst2 != 0ull)
+                    reinterpret_cast<uint4*>(dst2)[c2] = *reinterpret_cast<const uint4*>(oh + (size_t)r2 * (D * 2) + ((c2 ^ (r2 & (LPR - 1))) << 4));
+            }
         }
+#ifdef OXR_TIMELINE
+        if (warp == 2 && lane == 0) tl[7] = OXR_TL_NOW();
+#endif
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
 #ifdef OXR_TIMELINE
     if (threadIdx.x == 0) {   // ids 6 and 7: a prefill tile (started, ended, set up, first S in tensor memory, epilogue begins; first loads issued, first keys landed)
         OXR_TL_PUT(6ull | ((unsigned long long)count << 8), tl_started, OXR_TL_NOW(), tl[0], tl[3], tl[4]);
-        OXR_TL_PUT(7ull | ((unsigned long long)count << 8), tl_started, tl[1], tl[2], blockIdx.x, 0);
+        OXR_TL_PUT(7ull | ((unsigned long long)count << 8), tl_started, tl[1], tl[2], tl[5], tl[6]);
+        OXR_TL_PUT(8ull | ((unsigned long long)count << 8), tl_started, tl[7], 0, 0, 0);
+        if (count > TLB + 2) {   // ids 9..11: inside block TLB: the MMA warp's loop, the first softmax warp of each half
+            OXR_TL_PUT(9ull, tl2[0], tl2[1], tl2[2], tl2[3], tl2[4]);
+            OXR_TL_PUT(10ull, tl2[0], tl2[5], tl2[6], tl2[7], tl2[8]);
+            OXR_TL_PUT(11ull, tl2[0], tl2[9], tl2[10], tl2[11], tl2[12]);
+            OXR_TL_PUT(12ull, tl2[0], tl2[13], 0, 0, 0);
+        }
     }
 #endif
     if (warp == 1) {
@@ -1630,12 +1723,13 @@ OXR_API int oxr_attn_tile_rows(int kind) {
 // kv_maps (optional): the two tensor maps of oxr_attn_make_kv_maps for the pool that k_cache / v_cache are a layer
 // of, with pool_row0 = layer * num_pages * page_size; the split-KV kernel then fetches K and V by TMA.
 // long_rows: rows per long tile the host cut the long list for: 64 (cp.async kernel) or 256 (tcgen05 kernel, needs kv_maps).
+// q_tokens: tokens (rows) of q and out, or 0 if unknown (the tcgen05 kernel then reads Q with ordinary loads).
 OXR_API int oxr_paged_attention_bf16(void* out, const void* q, const void* k_cache, const void* v_cache,
                                      const int* short_req, const int* short_tok0, int n_short, const int* long_req,
                                      const int* long_tok0, int n_long, const int* cu_q, const int* ctx_lens,
                                      const int* block_table, int table_width, int page_size, int num_pages, int H, int KV,
                                      float scale, int window, int splits, float* part_o, float* part_ml, int* counters,
-                                     const void* kv_maps, int pool_row0, int long_rows, int* status, cudaStream_t stream) {
+                                     const void* kv_maps, int pool_row0, int long_rows, int q_tokens, int* status, cudaStream_t stream) {
     if (n_short <= 0 && n_long <= 0) return 0;
     if (H <= 0 || KV <= 0 || H % KV != 0 || page_size <= 0 || table_width <= 0 || window < 0 || splits < 1) return OXR_BAD_ARGUMENT;
     if (splits > 1 && (part_o == nullptr || part_ml == nullptr || counters == nullptr)) return OXR_BAD_ARGUMENT;
@@ -1670,8 +1764,12 @@ OXR_API int oxr_paged_attention_bf16(void* out, const void* q, const void* k_cac
         a.tile_req = long_req; a.tile_tok0 = long_tok0;
         const CUtensorMap* maps = reinterpret_cast<const CUtensorMap*>(kv_maps);
         const int box_rows = page_size < MMA_BN ? page_size : MMA_BN;
+        // Q by TMA when a half's 128 rows are whole tokens (a [tokens, H, D] map made for this call: q moves from call to call)
+        CUtensorMap map_q = maps[0];
+        const int q_by_tma = (q_tokens > 0 && HALF_ROWS % G == 0 &&
+                              oxr_make_map_bf16_3d(&map_q, q, (unsigned long long)q_tokens, (unsigned long long)H, D, HALF_ROWS / G, G)) ? 1 : 0;
         attn_tc5_prefill_kernel<<<dim3((unsigned)(n_long * KV * groups)), TC_THREADS, TC_SMEM, stream>>>(
-            (bf16*)out, (const bf16*)q, maps[0], maps[1], pool_row0, box_rows, n_long, KV * groups, a);
+            (bf16*)out, (const bf16*)q, maps[0], maps[1], map_q, q_by_tma, pool_row0, box_rows, n_long, KV * groups, a);
         int rc = oxr_launch_status();
         if (rc) return rc;
     } else if (n_long > 0) {

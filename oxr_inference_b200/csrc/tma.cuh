@@ -44,6 +44,12 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(smem_addr(dst)), "l"(map), "r"(smem_addr(bar)), "r"(c0), "r"(c1) : "memory");
 }
+// One box of a 3-D tensor map (c0 innermost, its byte offset a multiple of 16).
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_addr(dst)), "l"(map), "r"(smem_addr(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
 // Orders earlier ordinary shared-memory writes before later writes by TMA to the same addresses.
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
@@ -73,5 +79,19 @@ static inline bool oxr_make_map_bf16(CUtensorMap* map, const void* base, unsigne
     const cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
     const cuuint32_t elem[2] = {1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// A [tokens, heads, d] bf16 tensor (contiguous) seen as boxes of box_tokens x box_heads x 64 d (128 bytes), 128-byte swizzle:
+// a box lands as rows of 128 bytes in the order (token, head). Elements outside the tensor read as zero.
+static inline bool oxr_make_map_bf16_3d(CUtensorMap* map, const void* base, unsigned long long tokens, unsigned long long heads,
+                                        unsigned long long d, int box_tokens, int box_heads) {
+    OxrEncodeTiledFn fn = oxr_encode_tiled();
+    if (fn == nullptr) return false;
+    const cuuint64_t dims[3] = {(cuuint64_t)d, (cuuint64_t)heads, (cuuint64_t)tokens};
+    const cuuint64_t strides[2] = {(cuuint64_t)d * 2, (cuuint64_t)d * heads * 2};
+    const cuuint32_t box[3] = {64u, (cuuint32_t)box_heads, (cuuint32_t)box_tokens};
+    const cuuint32_t elem[3] = {1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }

@@ -145,7 +145,7 @@ def _attn_lib(head_dim: int):
         p, i, f = c_void_p, c_int, c_float
         lib.oxr_paged_attention.argtypes = [p, p, p, p, p, p, i, p, p, p, i, i, i, i, i, f, i, i, p, p]
         lib.oxr_paged_attention.restype = c_int
-        lib.oxr_paged_attention_bf16.argtypes = [p, p, p, p, p, p, i, p, p, i, p, p, p, i, i, i, i, i, f, i, i, p, p, p, p, i, i, p, p]
+        lib.oxr_paged_attention_bf16.argtypes = [p, p, p, p, p, p, i, p, p, i, p, p, p, i, i, i, i, i, f, i, i, p, p, p, p, i, i, i, p, p]
         lib.oxr_attn_make_kv_maps.argtypes = [p, p, p, ctypes.c_ulonglong, i, i]
         lib.oxr_attn_make_kv_maps.restype = c_int
         lib.oxr_paged_attention_bf16.restype = c_int
@@ -492,7 +492,7 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
                                         s_tok.data_ptr(), n_short, l_req.data_ptr(), l_tok.data_ptr(), n_long, *common, splits,
                                         _ptr(part_o), _ptr(part_ml), _ptr(counters),
                                         kv_maps.address if kv_maps is not None else None,
-                                        layer_in_pool * kv_maps.rows_per_layer if kv_maps is not None else 0, long_rows,
+                                        layer_in_pool * kv_maps.rows_per_layer if kv_maps is not None else 0, long_rows, q.shape[0],
                                         status.data_ptr(), _stream())
     global launch_count
     _done(code, "paged_attention_bf16")
