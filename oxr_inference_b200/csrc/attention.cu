@@ -1222,38 +1222,47 @@ attn_tma_decode_walk_kernel(bf16* __restrict__ out, float* __restrict__ part_o, 
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// Prefill attention on tcgen05: a tile is two halves of 128 rows (one TMEM lane per row); both halves use every 64-key
-// block that arrives, so K and V are fetched once per 256 rows and eight softmax warps keep the SM busy. Per block and half
-//   S = Q K^T      tcgen05.mma, Q and K from shared memory (K-major, 128-byte swizzle), S (128 x 64 fp32) in TMEM,
-//                  double-buffered so that the next block's S is computed while this block's softmax runs;
-//   softmax        four warps, ONE THREAD PER ROW: tcgen05.ld its row of S, mask, running maximum and sum without any
-//                  shuffle, P = exp2(S - m) written as bf16 into a swizzled shared-memory tile;
-//   O += P V       tcgen05.mma, P from shared memory, V from the TMA stage as an MN-major operand, O (128 x D fp32) in TMEM.
+// Prefill attention on tcgen05: a tile is two halves of 128 rows (one TMEM lane per row); both halves use every 128-key
+// block that arrives, so K and V are fetched once per 256 rows. Per block and half
+//   S = Q K^T      tcgen05.mma 128 x 128 x 16, Q and K from shared memory (K-major, 128-byte swizzle), S (128 x 128 fp32) in TMEM;
+//   softmax        four warps, ONE THREAD PER ROW, two passes over its row of S with tcgen05.ld: the maximum, then
+//                  P = exp2(S - m), which goes back INTO TENSOR MEMORY as bf16 pairs over the columns S came from (the
+//                  pair of keys 2 j, 2 j + 1 in column j: behind what the pass has already read);
+//   O += P V       tcgen05.mma with P as the A operand FROM TENSOR MEMORY and V from the TMA stage as an MN-major operand,
+//                  O (128 x D fp32) in TMEM.
+// The tensor pipe runs one thread's products in the order they were issued, so nothing but that order keeps S(b + 1) of a
+// half off the columns that P(b) V(b) still reads: the issuing thread alternates PV0(b), S0(b + 1), PV1(b), S1(b + 1), and
+// while one half's softmax runs the pipe works for the other half.
+// Why 128 keys: measured with stamps inside the kernel, the form with 64-key blocks (S 128 x 64 x 16, P through shared
+// memory) was bound by the tensor pipe at a third of its rate: a 128 x 64 x 16 product took about 120 cycles, hardly less
+// than a 128 x 128 x 16 one, and reading P from shared memory cost the PV products another 4 KB each.
 // The running maximum is only raised when a row's maximum grows by more than 8 (in log2 units): P then stays below
 // 2^8, which bf16 and the fp32 accumulator take without loss, and the rescale of O (tcgen05.ld, multiply, tcgen05.st)
-// becomes rare. K and V blocks arrive by TMA from a producer warp exactly as in the split-KV kernel.
+// becomes rare. K and V blocks arrive by TMA from a producer warp, Q as one 3-D box per half and panel.
 // Warp roles: 0 = TMA producer, 1 = MMA issuer and owner of the TMEM allocation, 2..5 / 6..9 = softmax and epilogue of
 // the first / second half.
 // Every mbarrier wait is bounded.
 // ---------------------------------------------------------------------------------------------------------------------
 constexpr int HALF_ROWS = 128;                                      // rows of one accumulator (TMEM lanes)
 constexpr int BIG_ROWS = 2 * HALF_ROWS;                             // a tile is two such halves sharing every K/V block
-constexpr int TC_STAGES = 4;
+constexpr int TC_BN = 128;                                          // keys per block
+constexpr int TC_STAGES = 2;
 constexpr int TC_THREADS = 320;                                     // warp 0 TMA, warp 1 MMA, warps 2..9 softmax (4 per half)
 constexpr int Q_PANEL_BYTES = HALF_ROWS * 128;                      // 128 rows x 64 d
-constexpr int P_BYTES = HALF_ROWS * 128;                            // 128 rows x 64 keys
-constexpr size_t TC_SMEM = 2 * (size_t)PANELS * Q_PANEL_BYTES + (size_t)TC_STAGES * KV_STAGE_BYTES + 2 * P_BYTES + 512;
-constexpr uint32_t TC_TMEM_COLS = 512;                              // S[half][2] (4 x 64) | O[half] (2 x D)
+constexpr int TC_PANEL_BYTES = TC_BN * 128;                         // 128 keys x 64 d
+constexpr int TC_HALF_STAGE = PANELS * TC_PANEL_BYTES;              // the K (or the V) panels of a block
+constexpr size_t TC_SMEM = 2 * (size_t)PANELS * Q_PANEL_BYTES + 2 * (size_t)TC_STAGES * TC_HALF_STAGE + 512;
+constexpr uint32_t TC_TMEM_COLS = 512;                              // S | P of half h at 128 h, O of half h at 256 + h * D
 constexpr float RESCALE_THRESHOLD = 8.f;
 
-// K-major operand tile with 128-byte rows, 128-byte swizzle (Q, K, P): see gemm_tcgen05.cu
+// K-major operand tile with 128-byte rows, 128-byte swizzle (Q, K): see gemm_tcgen05.cu
 __device__ __forceinline__ uint64_t desc_kmajor(uint32_t saddr) {
     return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
-// MN-major operand (V: rows are keys = K, 64 d contiguous per 128-byte row, panels of 64 d 8 KB apart): 8 keys per
-// swizzle atom, the next 8 keys 1024 bytes on (stride byte offset), the next 64 d one panel on (leading byte offset).
+// MN-major operand (V: rows are keys = K, 64 d contiguous per 128-byte row, panels of 64 d TC_PANEL_BYTES apart): 8 keys
+// per swizzle atom, the next 8 keys 1024 bytes on (stride byte offset), the next 64 d one panel on (leading byte offset).
 __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t saddr) {
-    return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)(PANEL_BYTES >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+    return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)(TC_PANEL_BYTES >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
            ((uint64_t)2 << 61);
 }
 // kind::f16 instruction descriptor: fp32 accumulator, bf16 operands, A K-major, B K-major or MN-major
@@ -1266,6 +1275,14 @@ __device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t da, uint64_t db
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
         ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+// The same with the A operand in tensor memory (128 lanes x 8 columns of bf16 pairs per 16 k).
+__device__ __forceinline__ void tc_mma_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
 }
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
@@ -1281,6 +1298,16 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "r"(taddr));
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void tc_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]) {   // the caller issues tcgen05.wait::ld before it uses r
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
 __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -1291,6 +1318,13 @@ __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32])
           "r"(r[30]), "r"(r[31])
         : "memory");
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+          "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
 }
 __device__ __forceinline__ bool elect_one_lane() {
     uint32_t pred;
@@ -1312,25 +1346,26 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
     extern __shared__ __align__(1024) unsigned char smem_dyn[];
     unsigned char* base = smem_dyn;
     unsigned char* Qs = base;                                              // [half][PANELS] panels of [128 rows][128 B], swizzled
-    unsigned char* stages = Qs + 2 * (size_t)PANELS * Q_PANEL_BYTES;       // TC_STAGES x (K panels, V panels)
-    unsigned char* Ps = stages + (size_t)TC_STAGES * KV_STAGE_BYTES;       // [half] [128 rows][128 B], swizzled
-    uint64_t* kv_full = reinterpret_cast<uint64_t*>(Ps + 2 * P_BYTES);
-    uint64_t* kv_empty = kv_full + TC_STAGES;
-    uint64_t* s_full = kv_empty + TC_STAGES;     // [half][2] S(b) is in TMEM
-    uint64_t* s_empty = s_full + 4;              // [half][2] the half's softmax warps have read S(b) (4 arrivals)
-    uint64_t* p_full = s_empty + 4;              // [half][2] P(b) is in shared memory and O is rescaled (4 arrivals)
-    uint64_t* o_done = p_full + 4;               // [half][2] O += P(b) V(b) has completed
-    uint64_t* q_ready = o_done + 4;              // Q is in shared memory (one arrival per softmax warp)
+    unsigned char* k_ring = Qs + 2 * (size_t)PANELS * Q_PANEL_BYTES;       // TC_STAGES x K panels of [128 keys][128 B]
+    unsigned char* v_ring = k_ring + (size_t)TC_STAGES * TC_HALF_STAGE;     // TC_STAGES x V panels
+    uint64_t* k_full = reinterpret_cast<uint64_t*>(v_ring + (size_t)TC_STAGES * TC_HALF_STAGE);
+    uint64_t* k_empty = k_full + TC_STAGES;      // K(b) is free once S(b) of both halves has completed: long before V(b) is
+    uint64_t* v_full = k_empty + TC_STAGES;
+    uint64_t* v_empty = v_full + TC_STAGES;
+    uint64_t* s_full = v_empty + TC_STAGES;      // [half] S(b) is in TMEM
+    uint64_t* p_full = s_full + 2;               // [half] P(b) is in TMEM and O is rescaled (4 arrivals)
+    uint64_t* o_done = p_full + 2;               // [half] O += P(b) V(b) has completed
+    uint64_t* q_ready = o_done + 2;              // Q is in shared memory
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_ready + 1);
 #ifdef OXR_TIMELINE
     unsigned long long* tl = reinterpret_cast<unsigned long long*>(q_ready + 2);   // eight stamps in the spare bytes behind the barriers
-    unsigned long long* tl2 = tl + 8;                                              // and sixteen inside block TLB of a long tile
+    unsigned long long* tl2 = tl + 8;
     constexpr int TLB = 10;
 #endif
 
-    // the list is in token order and later tiles of a prompt see more keys: start the long ones first
+    // the list is in token order and later tiles of a prompt see more keys: start the long ones first,
     [[maybe_unused]] const unsigned long long tl_started = OXR_TL_NOW();
-    if (threadIdx.x == 0) {   // the two tensor maps are on their way before anything else
+    if (threadIdx.x == 0) {   // the tensor maps are on their way before anything else
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
         if (q_by_tma) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
@@ -1345,12 +1380,12 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int k_end = g.pos0 + g.tok_end;
     const int k_lo = a.window > 0 ? max(0, g.pos0 + g.tok0 - a.window + 1) : 0;
-    const int k_first = (k_lo / MMA_BN) * MMA_BN;
-    const int count = (k_end - k_first + MMA_BN - 1) / MMA_BN;
+    const int k_first = (k_lo / TC_BN) * TC_BN;
+    const int count = (k_end - k_first + TC_BN - 1) / TC_BN;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < TC_STAGES; ++i) { mbar_init(kv_full + i, 1); mbar_init(kv_empty + i, 1); }
-        for (int i = 0; i < 4; ++i) { mbar_init(s_full + i, 1); mbar_init(s_empty + i, 4); mbar_init(p_full + i, 4); mbar_init(o_done + i, 1); }
+        for (int i = 0; i < TC_STAGES; ++i) { mbar_init(k_full + i, 1); mbar_init(k_empty + i, 1); mbar_init(v_full + i, 1); mbar_init(v_empty + i, 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(s_full + i, 1); mbar_init(p_full + i, 4); mbar_init(o_done + i, 1); }
         mbar_init(q_ready, q_by_tma ? 1 : TC_THREADS / 32 - 2);
         mbar_fence_init();
     }
@@ -1358,8 +1393,8 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(TC_TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    // Nothing else stands before the first loads: the producer warp goes ahead while the softmax warps bring Q in (the MMA
-    // warp waits for `q_ready` before its first product).
+    // Nothing else stands before the first loads: the producer warp goes ahead while Q comes in (the MMA warp waits for
+    // `q_ready` before its first product).
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -1385,14 +1420,14 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
         __syncwarp();
         if (lane == 0) mbar_arrive(q_ready);
     }
-    // TMEM columns: S of half h, buffer i at (2 h + i) * 64; O of half h at 256 + h * D
+    // TMEM columns: S (fp32) and then P (bf16 pairs) of half h at 128 h; O of half h at 256 + h * D
     // the second half of a tile may be empty (short portions): its products and softmax are then skipped
     const bool half1_live = g.tok0 + (HALF_ROWS / g.heads_per_tile) < g.tok_end || g.heads_per_tile > HALF_ROWS;
 
     if (warp == 0) {
         // ---------------------------------------------------------------------- TMA producer (all 32 lanes issue)
         const int* table_row = a.block_table + (size_t)g.req * a.table_width;
-        const int boxes = MMA_BN / box_rows, loads = boxes * 2 * PANELS;
+        const int boxes = TC_BN / box_rows;
         if (q_by_tma && lane == 0) {
             // Q: one box per half and 64-wide panel, rows in the order (token, head) as the tile counts them. Rows behind the
             // request's last token are somebody else's (or zero behind the tensor): finite, and masked like the padding rows.
@@ -1403,122 +1438,112 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
                     tma_load_3d(Qs + (size_t)(h * PANELS + pnl) * Q_PANEL_BYTES, &map_q, pnl * 64, g.kvh * g.G,
                                 g.q_begin + g.tok0 + h * (HALF_ROWS / g.G), q_ready);
         }
-        for (int b = 0; b < count; ++b) {
-            const int st = b % TC_STAGES;
-            if (!mbar_wait(kv_empty + st, ((b / TC_STAGES) & 1) ^ 1)) { if (lane == 0) oxr_report(a.status, OXR_WAIT_EXPIRED, 30); break; }
-            const int k0 = k_first + b * MMA_BN;
-            unsigned char* dst = stages + (size_t)st * KV_STAGE_BYTES;
-            int my_bytes = 0;
-            for (int i = lane; i < loads; i += 32) {
-                const int kp = k0 + (i / (2 * PANELS)) * box_rows;
-                if (kp < k_end && kp + box_rows > k_lo) {
-                    const int page = table_row[a.page_shift >= 0 ? (kp >> a.page_shift) : (kp / a.page_size)];
-                    if (page >= 0 && page < a.num_pages) my_bytes += box_rows * 128;
-                    else oxr_report(a.status, OXR_BAD_PAGE, g.req);
-                }
+        // K(0), V(0), K(1), V(1), ...: each into its own ring. A lane fetches at most one page piece of an item (a block has at
+        // most 16 pieces of 8 keys and 2 panels), and looks its page up BEFORE it waits for the ring, so that the table's latency
+        // is not part of what the MMA warp may have to wait for.
+        const int pieces = boxes * PANELS;
+        for (int item = 0; item < 2 * count; ++item) {
+            const int b = item >> 1, is_v = item & 1, st = b % TC_STAGES;
+            const int k0 = k_first + b * TC_BN;
+            const int box = lane / PANELS, pnl = lane % PANELS;
+            const int kp = k0 + box * box_rows;
+            int row = -1;                      // the pool row of this lane's piece, or -1 if it is not fetched
+            if (lane < pieces && kp < k_end && kp + box_rows > k_lo) {
+                const int page = table_row[a.page_shift >= 0 ? (kp >> a.page_shift) : (kp / a.page_size)];
+                if (page >= 0 && page < a.num_pages)
+                    row = pool_row0 + page * a.page_size + (a.page_shift >= 0 ? (kp & (a.page_size - 1)) : (kp % a.page_size));
+                else oxr_report(a.status, OXR_BAD_PAGE, g.req);
             }
-            const int total = __reduce_add_sync(0xffffffffu, my_bytes);
+            uint64_t* full = (is_v ? v_full : k_full) + st;
+            if (!mbar_wait((is_v ? v_empty : k_empty) + st, ((b / TC_STAGES) & 1) ^ 1)) { if (lane == 0) oxr_report(a.status, OXR_WAIT_EXPIRED, 30); break; }
+            unsigned char* dst = (is_v ? v_ring : k_ring) + (size_t)st * TC_HALF_STAGE;
+            const int total = __reduce_add_sync(0xffffffffu, row >= 0 ? box_rows * 128 : 0);
 #ifdef OXR_TIMELINE
-            if (b == 0 && lane == 0) tl[5] = OXR_TL_NOW();
+            if (item == 0 && lane == 0) tl[5] = OXR_TL_NOW();
 #endif
-            if (total < loads * box_rows * 128) {
+            if (total < pieces * box_rows * 128) {
                 // Page pieces that are not fetched (beyond the last key, before the window, a bad page) meet a probability of
-                // exactly zero, but must hold finite numbers: zero them (the stage may hold anything from an earlier kernel).
-                for (int i = lane; i < loads; i += 32) {
-                    const int box = i / (2 * PANELS), which = i % (2 * PANELS);
-                    const int kp = k0 + box * box_rows;
-                    bool fetched = false;
-                    if (kp < k_end && kp + box_rows > k_lo) {
-                        const int page = table_row[a.page_shift >= 0 ? (kp >> a.page_shift) : (kp / a.page_size)];
-                        fetched = page >= 0 && page < a.num_pages;
-                    }
-                    if (!fetched) {
-                        uint4* z = reinterpret_cast<uint4*>(dst + (size_t)which * PANEL_BYTES + (size_t)box * box_rows * 128);
-                        for (int j = 0; j < box_rows * 8; ++j) z[j] = make_uint4(0, 0, 0, 0);
-                    }
+                // exactly zero, but must hold finite numbers: zero them (the ring may hold anything from an earlier kernel).
+                if (lane < pieces && row < 0) {
+                    uint4* z = reinterpret_cast<uint4*>(dst + (size_t)pnl * TC_PANEL_BYTES + (size_t)box * box_rows * 128);
+                    for (int j = 0; j < box_rows * 8; ++j) z[j] = make_uint4(0, 0, 0, 0);
                 }
                 fence_proxy_async();
                 __syncwarp();
             }
             if (lane == 0) {
-                if (total > 0) mbar_expect_tx(kv_full + st, (uint32_t)total);
-                else mbar_arrive(kv_full + st);
+                if (total > 0) mbar_expect_tx(full, (uint32_t)total);
+                else mbar_arrive(full);
             }
             __syncwarp();
-            for (int i = lane; i < loads; i += 32) {
-                const int box = i / (2 * PANELS), which = i % (2 * PANELS);
-                const int kp = k0 + box * box_rows;
-                if (kp < k_end && kp + box_rows > k_lo) {
-                    const int page = table_row[a.page_shift >= 0 ? (kp >> a.page_shift) : (kp / a.page_size)];
-                    if (page >= 0 && page < a.num_pages) {
-                        const int row = pool_row0 + page * a.page_size + (a.page_shift >= 0 ? (kp & (a.page_size - 1)) : (kp % a.page_size));
-                        tma_load_2d(dst + (size_t)which * PANEL_BYTES + (size_t)box * box_rows * 128, which < PANELS ? &map_k : &map_v,
-                                    g.kvh * D + (which % PANELS) * 64, row, kv_full + st);
-                    }
-                }
-            }
+            if (row >= 0)
+                tma_load_2d(dst + (size_t)pnl * TC_PANEL_BYTES + (size_t)box * box_rows * 128, is_v ? &map_v : &map_k, g.kvh * D + pnl * 64, row, full);
 #ifdef OXR_TIMELINE
-            if (b == 0 && lane == 0) tl[1] = OXR_TL_NOW();
+            if (item == 0 && lane == 0) tl[1] = OXR_TL_NOW();
 #endif
         }
     } else if (warp == 1) {
         // ---------------------------------------------------------------------- MMA issuer
         if (elect_one_lane()) {
-            constexpr uint32_t idesc_s = attn_idesc(HALF_ROWS, MMA_BN, false);
+            constexpr uint32_t idesc_s = attn_idesc(HALF_ROWS, TC_BN, false);
             constexpr uint32_t idesc_o = attn_idesc(HALF_ROWS, D, true);
-            const uint32_t q_addr = smem_addr(Qs), p_addr = smem_addr(Ps);
+            const uint32_t q_addr = smem_addr(Qs);
             const int halves = half1_live ? 2 : 1;
             bool ok = true;
-            // S(b) of both halves is issued one block ahead of O(b): S(0); then for each b: S(b + 1), wait P(b), O += P(b) V(b)
-            auto issue_s = [&](int b) -> bool {
-                const int st = b % TC_STAGES;
-                if (!mbar_wait(kv_full + st, (b / TC_STAGES) & 1)) { oxr_report(a.status, OXR_WAIT_EXPIRED, 31); return false; }
-#ifdef OXR_TIMELINE
-                if (b == 0) tl[2] = OXR_TL_NOW();
-#endif
-                const uint32_t k_addr = smem_addr(stages + (size_t)st * KV_STAGE_BYTES);
-                for (int h = 0; h < halves; ++h) {
-                    if (!mbar_wait(s_empty + 2 * h + (b & 1), ((b >> 1) & 1) ^ 1)) { oxr_report(a.status, OXR_WAIT_EXPIRED, 32); return false; }
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            auto issue_s = [&](int b, int h) {      // S_h(b) = Q_h K(b)^T into the half's 128 columns
+                const uint32_t k_addr = smem_addr(k_ring + (size_t)(b % TC_STAGES) * TC_HALF_STAGE);
 #pragma unroll
-                    for (int kk = 0; kk < D / 16; ++kk)
-                        tc_mma(tmem_base + (uint32_t)((2 * h + (b & 1)) * MMA_BN),
-                               desc_kmajor(q_addr + (h * PANELS + (kk >> 2)) * Q_PANEL_BYTES + (kk & 3) * 32),
-                               desc_kmajor(k_addr + (kk >> 2) * PANEL_BYTES + (kk & 3) * 32), idesc_s, kk > 0 ? 1u : 0u);
-                    tc_commit(s_full + 2 * h + (b & 1));
-                }
+                for (int kk = 0; kk < D / 16; ++kk)
+                    tc_mma(tmem_base + (uint32_t)(h * TC_BN), desc_kmajor(q_addr + (h * PANELS + (kk >> 2)) * Q_PANEL_BYTES + (kk & 3) * 32),
+                           desc_kmajor(k_addr + (kk >> 2) * TC_PANEL_BYTES + (kk & 3) * 32), idesc_s, kk > 0 ? 1u : 0u);
+                tc_commit(s_full + h);
+                if (h == halves - 1) tc_commit(k_empty + b % TC_STAGES);   // every product that reads K(b) has been issued
+            };
+            auto wait_for = [&](uint64_t* full, int b, int where) -> bool {
+                if (!mbar_wait(full + b % TC_STAGES, (b / TC_STAGES) & 1)) { oxr_report(a.status, OXR_WAIT_EXPIRED, where); return false; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 return true;
             };
             if (!mbar_wait(q_ready, 0)) { oxr_report(a.status, OXR_WAIT_EXPIRED, 36); ok = false; }
-            ok = ok && issue_s(0);
+            ok = ok && wait_for(k_full, 0, 31);
+#ifdef OXR_TIMELINE
+            tl[2] = OXR_TL_NOW();
+#endif
+            if (ok)
+                for (int h = 0; h < halves; ++h) issue_s(0, h);
+            // then, block by block and half by half: O_h += P_h(b) V(b), and at once S_h(b + 1) over the same columns
             for (int b = 0; b < count && ok; ++b) {
+                const uint32_t v_addr = smem_addr(v_ring + (size_t)(b % TC_STAGES) * TC_HALF_STAGE);
 #ifdef OXR_TIMELINE
                 if (b == TLB) tl2[0] = OXR_TL_NOW();
 #endif
-                if (b + 1 < count) ok = issue_s(b + 1);
-                if (!ok) break;
-#ifdef OXR_TIMELINE
-                if (b == TLB) tl2[1] = OXR_TL_NOW();
-#endif
-                const int st = b % TC_STAGES;
-                const uint32_t v_addr = smem_addr(stages + (size_t)st * KV_STAGE_BYTES + (size_t)PANELS * PANEL_BYTES);
                 for (int h = 0; h < halves && ok; ++h) {
-                    if (!mbar_wait(p_full + 2 * h + (b & 1), (b >> 1) & 1)) { oxr_report(a.status, OXR_WAIT_EXPIRED, 33); ok = false; break; }
+                    if (!mbar_wait(p_full + h, b & 1)) { oxr_report(a.status, OXR_WAIT_EXPIRED, 33); ok = false; break; }
 #ifdef OXR_TIMELINE
-                    if (b == TLB) tl2[2 + 2 * h] = OXR_TL_NOW();
+                    if (b == TLB) tl2[2 + 3 * h] = OXR_TL_NOW();
 #endif
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    if (h == 0 && !wait_for(v_full, b, 32)) { ok = false; break; }
 #pragma unroll
-                    for (int kk = 0; kk < MMA_BN / 16; ++kk)
-                        tc_mma(tmem_base + 256 + (uint32_t)(h * D), desc_kmajor(p_addr + h * P_BYTES + kk * 32),
-                               desc_mnmajor(v_addr + kk * 16 * 128), idesc_o, (b > 0 || kk > 0) ? 1u : 0u);
-                    tc_commit(o_done + 2 * h + (b & 1));
+                    for (int kk = 0; kk < TC_BN / 16; ++kk)
+                        tc_mma_a_tmem(tmem_base + 256 + (uint32_t)(h * D), tmem_base + (uint32_t)(h * TC_BN + kk * 8),
+                                      desc_mnmajor(v_addr + kk * 16 * 128), idesc_o, (b > 0 || kk > 0) ? 1u : 0u);
+                    tc_commit(o_done + h);
+                    if (h == halves - 1) tc_commit(v_empty + b % TC_STAGES);   // every product that reads V(b) has been issued
 #ifdef OXR_TIMELINE
-                    if (b == TLB) tl2[3 + 2 * h] = OXR_TL_NOW();
+                    if (b == TLB) tl2[3 + 3 * h] = OXR_TL_NOW();
+#endif
+                    if (b + 1 < count) {
+                        if (h == 0 && !wait_for(k_full, b + 1, 31)) { ok = false; break; }
+#ifdef OXR_TIMELINE
+                        if (b == TLB && h == 0) tl2[1] = OXR_TL_NOW();
+#endif
+                        issue_s(b + 1, h);
+                    }
+#ifdef OXR_TIMELINE
+                    if (b == TLB) tl2[4 + 3 * h] = OXR_TL_NOW();
 #endif
                 }
-                if (!ok) break;
-                tc_commit(kv_empty + st);       // K and V of this stage have been read by all products of the block
             }
         }
     } else if (warp - 2 < 4 || half1_live) {
@@ -1527,54 +1552,49 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
         const int quarter = warp & 3;                        // TMEM lanes 32 * quarter .. + 31 belong to this warp
         const int rr = quarter * 32 + lane;                  // row inside the half
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        const uint32_t tmem_s = tmem_base + lane_base + (uint32_t)(half * TC_BN);
         const uint32_t tmem_o = tmem_base + 256 + (uint32_t)(half * D);
-        uint64_t* my_s_full = s_full + 2 * half;
-        uint64_t* my_s_empty = s_empty + 2 * half;
-        uint64_t* my_p_full = p_full + 2 * half;
-        uint64_t* my_o_done = o_done + 2 * half;
         int tok, gh;
         const bool row_ok = g.row(half * HALF_ROWS + rr, tok, gh);
         const int row_pos = g.pos0 + tok;
         const float scale_log2 = a.scale * LOG2E;
         float m_used = -INFINITY, l = 0.f;                   // the maximum P is taken against, the running sum
-        unsigned char* my_p_row = Ps + (size_t)half * P_BYTES + (size_t)rr * 128;
         bool alive = true;
         for (int b = 0; b < count; ++b) {
-            const int key0 = k_first + b * MMA_BN;
-            if (!mbar_wait(my_s_full + (b & 1), (b >> 1) & 1)) { if (lane == 0) oxr_report(a.status, OXR_WAIT_EXPIRED, 34); alive = false; break; }
+            const int key0 = k_first + b * TC_BN;
+            if (!mbar_wait(s_full + half, b & 1)) { if (lane == 0) oxr_report(a.status, OXR_WAIT_EXPIRED, 34); alive = false; break; }
 #ifdef OXR_TIMELINE
             if (b == 0 && warp == 2 && lane == 0) tl[3] = OXR_TL_NOW();
             const bool tl_me = b == TLB && lane == 0 && quarter == 0;
-            if (tl_me) tl2[6 + 4 * half] = OXR_TL_NOW();
+            if (tl_me) tl2[8 + 4 * half] = OXR_TL_NOW();
 #endif
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            uint32_t sv[2][32];
-            tc_ld32(tmem_base + lane_base + (uint32_t)((2 * half + (b & 1)) * MMA_BN), sv[0]);
-            tc_ld32(tmem_base + lane_base + (uint32_t)((2 * half + (b & 1)) * MMA_BN + 32), sv[1]);
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
+            // the row's 128 scores, read once
+            uint32_t sv[TC_BN / 32][32];
+#pragma unroll
+            for (int c = 0; c < TC_BN / 32; ++c) tc_ld32_nowait(tmem_s + (uint32_t)(c * 32), sv[c]);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #ifdef OXR_TIMELINE
-            if (tl_me) tl2[7 + 4 * half] = OXR_TL_NOW();
+            if (tl_me) tl2[9 + 4 * half] = OXR_TL_NOW();
 #endif
-            if (lane == 0) mbar_arrive(my_s_empty + (b & 1));    // S(b) is in registers: the buffer may take S(b + 2)
             // Blocks that this row sees in full need no per-key test; on the others the hidden keys become -inf.
-            const bool whole = row_ok && key0 + MMA_BN - 1 <= row_pos && key0 >= k_lo && (a.window <= 0 || key0 > row_pos - a.window);
+            const bool whole = row_ok && key0 + TC_BN - 1 <= row_pos && key0 >= k_lo && (a.window <= 0 || key0 > row_pos - a.window);
             if (!whole) {
 #pragma unroll
-                for (int h = 0; h < 2; ++h)
+                for (int c = 0; c < TC_BN / 32; ++c)
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
-                        const int kp = key0 + h * 32 + j;
+                        const int kp = key0 + c * 32 + j;
                         const bool seen = row_ok && kp <= row_pos && kp >= k_lo && (a.window <= 0 || kp > row_pos - a.window);
-                        if (!seen) sv[h][j] = __float_as_uint(-INFINITY);
+                        if (!seen) sv[c][j] = __float_as_uint(-INFINITY);
                     }
             }
-            // maximum of the raw scores over four independent chains; the (positive) scale is applied once
+            // the row's maximum of the raw scores (four independent chains); the (positive) scale is applied once
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int h = 0; h < 2; ++h)
+            for (int c = 0; c < TC_BN / 32; ++c)
 #pragma unroll
-                for (int j = 0; j < 32; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(sv[h][j]));
+                for (int j = 0; j < 32; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(sv[c][j]));
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
             // raise the maximum only when it grew by more than the threshold (or there was none yet)
             float alpha = 1.f;
@@ -1583,14 +1603,8 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
                 alpha = (m_used == -INFINITY) ? 0.f : fast_exp2(m_used - mx);
                 m_used = mx;
             }
-            // the half's one P buffer was last read by O(b - 1), which must also be finished before a raised maximum rescales O
-            const bool any_raise = __any_sync(0xffffffffu, raise && b > 0);
-            if (b >= 1 && !mbar_wait(my_o_done + ((b - 1) & 1), ((b - 1) >> 1) & 1)) { if (lane == 0) oxr_report(a.status, OXR_WAIT_EXPIRED, 35); alive = false; break; }
-#ifdef OXR_TIMELINE
-            if (tl_me) tl2[8 + 4 * half] = OXR_TL_NOW();
-#endif
-            if (any_raise) {
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            // S(b) complete means that O += P(b - 1) V(b - 1), issued before it, is complete: O may be rescaled
+            if (__any_sync(0xffffffffu, raise && b > 0)) {
 #pragma unroll 1
                 for (int c = 0; c < D / 32; ++c) {
                     uint32_t ov[32];
@@ -1599,39 +1613,40 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
                     for (int j = 0; j < 32; ++j) ov[j] = __float_as_uint(__uint_as_float(ov[j]) * alpha);
                     tc_st32(tmem_o + lane_base + (uint32_t)(c * 32), ov);
                 }
-                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             }
-            // P = exp2(score * scale - m): one FMA and one ex2 per key; a row that has seen no key yet has only -inf scores
-            const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
+#ifdef OXR_TIMELINE
+            if (tl_me) tl2[10 + 4 * half] = OXR_TL_NOW();
+#endif
+            // P = exp2(score * scale - m), one FMA and one ex2 per key, written back as bf16 pairs over the columns S came from:
+            // keys 2 j and 2 j + 1 in column j
+            const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;    // a row that has seen no key yet has only -inf scores
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int h = 0; h < 2; ++h)
+            for (int c = 0; c < TC_BN / 32; ++c) {
+                uint32_t pv[16];
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {         // 8 keys = one 16-byte chunk of the row
-                    uint4 chunk;
-                    __nv_bfloat162* cp = reinterpret_cast<__nv_bfloat162*>(&chunk);
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float p0 = fast_exp2(fmaf(__uint_as_float(sv[h][c * 8 + 2 * e]), scale_log2, neg_m));
-                        const float p1 = fast_exp2(fmaf(__uint_as_float(sv[h][c * 8 + 2 * e + 1]), scale_log2, neg_m));
-                        sum4[e] += p0 + p1;
-                        cp[e] = __floats2bfloat162_rn(p0, p1);
-                    }
-                    *reinterpret_cast<uint4*>(my_p_row + ((((h * 4 + c)) ^ (rr & 7)) << 4)) = chunk;
+                for (int e = 0; e < 16; ++e) {
+                    const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c][2 * e]), scale_log2, neg_m));
+                    const float p1 = fast_exp2(fmaf(__uint_as_float(sv[c][2 * e + 1]), scale_log2, neg_m));
+                    sum4[e & 3] += p0 + p1;
+                    const __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+                    pv[e] = *reinterpret_cast<const uint32_t*>(&pk);
                 }
-            const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-            l = l * alpha + sum;
-            fence_proxy_async();                      // P is read by the tensor core through the async proxy
+                tc_st16(tmem_s + (uint32_t)(c * 16), pv);
+            }
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive(my_p_full + (b & 1));
+            if (lane == 0) mbar_arrive(p_full + half);
 #ifdef OXR_TIMELINE
-            if (tl_me) tl2[9 + 4 * half] = OXR_TL_NOW();
+            if (tl_me) tl2[11 + 4 * half] = OXR_TL_NOW();
 #endif
         }
         // ---- epilogue: O / l -> out
         if (alive && count > 0) {
             const int last = count - 1;
-            if (!mbar_wait(my_o_done + (last & 1), (last >> 1) & 1)) { if (lane == 0) oxr_report(a.status, OXR_WAIT_EXPIRED, 37); alive = false; }
+            if (!mbar_wait(o_done + half, last & 1)) { if (lane == 0) oxr_report(a.status, OXR_WAIT_EXPIRED, 37); alive = false; }
         }
         alive = __all_sync(0xffffffffu, alive);
 #ifdef OXR_TIMELINE
@@ -1679,15 +1694,15 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
 #ifdef OXR_TIMELINE
-    if (threadIdx.x == 0) {   // ids 6 and 7: a prefill tile (started, ended, set up, first S in tensor memory, epilogue begins; first loads issued, first keys landed)
+    if (threadIdx.x == 0) {   // ids 6 to 8: a prefill tile (started, ended, set up, first S in tensor memory, epilogue begins; first loads issued, first keys landed, ...)
         OXR_TL_PUT(6ull | ((unsigned long long)count << 8), tl_started, OXR_TL_NOW(), tl[0], tl[3], tl[4]);
         OXR_TL_PUT(7ull | ((unsigned long long)count << 8), tl_started, tl[1], tl[2], tl[5], tl[6]);
         OXR_TL_PUT(8ull | ((unsigned long long)count << 8), tl_started, tl[7], 0, 0, 0);
-        if (count > TLB + 2) {   // ids 9..11: inside block TLB: the MMA warp's loop, the first softmax warp of each half
+        if (count > TLB + 2) {   // ids 9 to 12: inside block TLB: the MMA warp's loop, the first softmax warp of each half
             OXR_TL_PUT(9ull, tl2[0], tl2[1], tl2[2], tl2[3], tl2[4]);
             OXR_TL_PUT(10ull, tl2[0], tl2[5], tl2[6], tl2[7], tl2[8]);
             OXR_TL_PUT(11ull, tl2[0], tl2[9], tl2[10], tl2[11], tl2[12]);
-            OXR_TL_PUT(12ull, tl2[0], tl2[13], 0, 0, 0);
+            OXR_TL_PUT(12ull, tl2[0], tl2[13], tl2[14], tl2[15], 0);
         }
     }
 #endif
