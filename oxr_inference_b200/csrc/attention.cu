@@ -1580,14 +1580,16 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
             // Blocks that this row sees in full need no per-key test; on the others the hidden keys become -inf.
             const bool whole = row_ok && key0 + TC_BN - 1 <= row_pos && key0 >= k_lo && (a.window <= 0 || key0 > row_pos - a.window);
             if (!whole) {
+                // the keys of this block that the row sees are those with index lo .. lo + span: one subtraction and one
+                // unsigned comparison per key
+                int lo = max(k_lo, a.window > 0 ? row_pos - a.window + 1 : 0) - key0;
+                int span = row_pos - key0 - lo;
+                if (!row_ok || span < 0) { lo = 1 << 30; span = 0; }
 #pragma unroll
                 for (int c = 0; c < TC_BN / 32; ++c)
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int kp = key0 + c * 32 + j;
-                        const bool seen = row_ok && kp <= row_pos && kp >= k_lo && (a.window <= 0 || kp > row_pos - a.window);
-                        if (!seen) sv[c][j] = __float_as_uint(-INFINITY);
-                    }
+                    for (int j = 0; j < 32; ++j)
+                        if ((unsigned)(c * 32 + j - lo) > (unsigned)span) sv[c][j] = __float_as_uint(-INFINITY);
             }
             // the row's maximum of the raw scores (four independent chains); the (positive) scale is applied once
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
