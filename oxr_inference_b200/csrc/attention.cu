@@ -478,13 +478,14 @@ constexpr size_t PREFILL_SMEM = (size_t)(PREFILL_ROWS + 4 * MMA_BN) * LDS * size
 
 __global__ void __launch_bounds__(MMA_THREADS)
 attn_mma_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, const bf16* __restrict__ k_cache,
-                        const bf16* __restrict__ v_cache, const AttnArgs a) {
+                        const bf16* __restrict__ v_cache, int n_tiles, int n_y, const AttnArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);
     bf16* Ks = Qs + PREFILL_ROWS * LDS;          // 2 stages
     bf16* Vs = Ks + 2 * MMA_BN * LDS;            // 2 stages
-    // the list is in token order and later tiles of a prompt see more keys: start the long ones first
-    const TileGeometry g = tile_geometry(a, PREFILL_ROWS, (int)(gridDim.x - 1 - blockIdx.x));
+    // the list is in token order and later tiles of a prompt see more keys: start the long ones first, and all (KV head,
+    // head group) pairs of a tile side by side (a one-dimensional grid), so that no pair's long tiles wait behind another's short ones
+    const TileGeometry g = tile_geometry(a, PREFILL_ROWS, n_tiles - 1 - (int)(blockIdx.x / (unsigned)n_y), (int)(blockIdx.x % (unsigned)n_y));
     if (g.tok0 >= g.tok_end) return;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int* table_row = a.block_table + (size_t)g.req * a.table_width;
@@ -1793,10 +1794,10 @@ OXR_API int oxr_paged_attention_bf16(void* out, const void* q, const void* k_cac
         if (long_rows != PREFILL_ROWS) return OXR_BAD_ARGUMENT;
         const int hpt = G < PREFILL_ROWS ? G : PREFILL_ROWS;
         const int groups = (G + hpt - 1) / hpt;
-        if ((size_t)KV * groups > 65535) return OXR_BAD_ARGUMENT;
+        if ((size_t)KV * groups * (size_t)n_long > 0x7fffffffull) return OXR_BAD_ARGUMENT;
         a.tile_req = long_req; a.tile_tok0 = long_tok0;
-        attn_mma_prefill_kernel<<<dim3(n_long, KV * groups), MMA_THREADS, PREFILL_SMEM, stream>>>(
-            (bf16*)out, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, a);
+        attn_mma_prefill_kernel<<<dim3((unsigned)(n_long * KV * groups)), MMA_THREADS, PREFILL_SMEM, stream>>>(
+            (bf16*)out, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, n_long, KV * groups, a);
         int rc = oxr_launch_status();
         if (rc) return rc;
     }
