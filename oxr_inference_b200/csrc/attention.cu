@@ -1226,9 +1226,9 @@ attn_tma_decode_walk_kernel(bf16* __restrict__ out, float* __restrict__ part_o, 
 // Prefill attention on tcgen05: a tile is two halves of 128 rows (one TMEM lane per row); both halves use every 128-key
 // block that arrives, so K and V are fetched once per 256 rows. Per block and half
 //   S = Q K^T      tcgen05.mma 128 x 128 x 16, Q and K from shared memory (K-major, 128-byte swizzle), S (128 x 128 fp32) in TMEM;
-//   softmax        four warps, ONE THREAD PER ROW, two passes over its row of S with tcgen05.ld: the maximum, then
-//                  P = exp2(S - m), which goes back INTO TENSOR MEMORY as bf16 pairs over the columns S came from (the
-//                  pair of keys 2 j, 2 j + 1 in column j: behind what the pass has already read);
+//   softmax        four warps, ONE THREAD PER ROW: tcgen05.ld of its 128 scores (read once, kept in registers), the maximum,
+//                  then P = exp2(S - m), which goes back INTO TENSOR MEMORY as bf16 pairs over the columns S came from
+//                  (keys 2 j, 2 j + 1 in column j);
 //   O += P V       tcgen05.mma with P as the A operand FROM TENSOR MEMORY and V from the TMA stage as an MN-major operand,
 //                  O (128 x D fp32) in TMEM.
 // The tensor pipe runs one thread's products in the order they were issued, so nothing but that order keeps S(b + 1) of a
