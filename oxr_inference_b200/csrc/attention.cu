@@ -1332,6 +1332,28 @@ __device__ __forceinline__ bool elect_one_lane() {
     asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
     return pred != 0;
 }
+// Two fp32 numbers in one 64-bit register pair, for the packed fp32 instructions of sm_100 (one issue slot for two results).
+__device__ __forceinline__ uint64_t pair_of(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpair(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -1597,7 +1619,7 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
 #pragma unroll
             for (int c = 0; c < TC_BN / 32; ++c)
 #pragma unroll
-                for (int j = 0; j < 32; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(sv[c][j]));
+                for (int j = 0; j < 16; ++j) mx4[j & 3] = max3(mx4[j & 3], __uint_as_float(sv[c][2 * j]), __uint_as_float(sv[c][2 * j + 1]));
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
             // raise the maximum only when it grew by more than the threshold (or there was none yet)
             float alpha = 1.f;
@@ -1623,20 +1645,26 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
             // P = exp2(score * scale - m), one FMA and one ex2 per key, written back as bf16 pairs over the columns S came from:
             // keys 2 j and 2 j + 1 in column j
             const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;    // a row that has seen no key yet has only -inf scores
-            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+            // (the scale, the shift and the sums go two keys at a time through the packed fp32 instructions)
+            const uint64_t scale2 = pair_of(scale_log2, scale_log2), neg_m2 = pair_of(neg_m, neg_m);
+            uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
             for (int c = 0; c < TC_BN / 32; ++c) {
                 uint32_t pv[16];
 #pragma unroll
                 for (int e = 0; e < 16; ++e) {
-                    const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c][2 * e]), scale_log2, neg_m));
-                    const float p1 = fast_exp2(fmaf(__uint_as_float(sv[c][2 * e + 1]), scale_log2, neg_m));
-                    sum4[e & 3] += p0 + p1;
+                    float x0, x1;
+                    unpair(fma2(pair_of(__uint_as_float(sv[c][2 * e]), __uint_as_float(sv[c][2 * e + 1])), scale2, neg_m2), x0, x1);
+                    const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+                    sum2[e & 3] = add2(sum2[e & 3], pair_of(p0, p1));
                     const __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
                     pv[e] = *reinterpret_cast<const uint32_t*>(&pk);
                 }
                 tc_st16(tmem_s + (uint32_t)(c * 16), pv);
             }
+            float sum4[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { float lo, hi; unpair(sum2[i], lo, hi); sum4[i] = lo + hi; }
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
