@@ -1405,6 +1405,23 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
     const int k_lo = a.window > 0 ? max(0, g.pos0 + g.tok0 - a.window + 1) : 0;
     const int k_first = (k_lo / TC_BN) * TC_BN;
     const int count = (k_end - k_first + TC_BN - 1) / TC_BN;
+    // A lane of the producer warp fetches one page piece of a block's K and of its V (a block has at most 16 pieces of 8 keys
+    // and 2 panels): the pool row of this lane's piece of block b, or -1 if it is not fetched. The first block's pages are
+    // looked up here, before the set-up, and every later block's while the block before it waits for its place in the rings.
+    const int* table_row = a.block_table + (size_t)g.req * a.table_width;
+    const int pieces = (TC_BN / box_rows) * PANELS;
+    const int my_box = lane / PANELS, my_pnl = lane % PANELS;
+    auto lookup = [&](int b) -> int {
+        const int kp = k_first + b * TC_BN + my_box * box_rows;
+        if (lane < pieces && kp < k_end && kp + box_rows > k_lo) {
+            const int page = table_row[a.page_shift >= 0 ? (kp >> a.page_shift) : (kp / a.page_size)];
+            if (page >= 0 && page < a.num_pages)
+                return pool_row0 + page * a.page_size + (a.page_shift >= 0 ? (kp & (a.page_size - 1)) : (kp % a.page_size));
+            oxr_report(a.status, OXR_BAD_PAGE, g.req);
+        }
+        return -1;
+    };
+    const int row_first = warp == 0 ? lookup(0) : -1;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < TC_STAGES; ++i) { mbar_init(k_full + i, 1); mbar_init(k_empty + i, 1); mbar_init(v_full + i, 1); mbar_init(v_empty + i, 1); }
@@ -1449,8 +1466,6 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
 
     if (warp == 0) {
         // ---------------------------------------------------------------------- TMA producer (all 32 lanes issue)
-        const int* table_row = a.block_table + (size_t)g.req * a.table_width;
-        const int boxes = TC_BN / box_rows;
         if (q_by_tma && lane == 0) {
             // Q: one box per half and 64-wide panel, rows in the order (token, head) as the tile counts them. Rows behind the
             // request's last token are somebody else's (or zero behind the tensor): finite, and masked like the padding rows.
@@ -1461,49 +1476,44 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
                     tma_load_3d(Qs + (size_t)(h * PANELS + pnl) * Q_PANEL_BYTES, &map_q, pnl * 64, g.kvh * g.G,
                                 g.q_begin + g.tok0 + h * (HALF_ROWS / g.G), q_ready);
         }
-        // K(0), V(0), K(1), V(1), ...: each into its own ring. A lane fetches at most one page piece of an item (a block has at
-        // most 16 pieces of 8 keys and 2 panels), and looks its page up BEFORE it waits for the ring, so that the table's latency
-        // is not part of what the MMA warp may have to wait for.
-        const int pieces = boxes * PANELS;
-        for (int item = 0; item < 2 * count; ++item) {
-            const int b = item >> 1, is_v = item & 1, st = b % TC_STAGES;
-            const int k0 = k_first + b * TC_BN;
-            const int box = lane / PANELS, pnl = lane % PANELS;
-            const int kp = k0 + box * box_rows;
-            int row = -1;                      // the pool row of this lane's piece, or -1 if it is not fetched
-            if (lane < pieces && kp < k_end && kp + box_rows > k_lo) {
-                const int page = table_row[a.page_shift >= 0 ? (kp >> a.page_shift) : (kp / a.page_size)];
-                if (page >= 0 && page < a.num_pages)
-                    row = pool_row0 + page * a.page_size + (a.page_shift >= 0 ? (kp & (a.page_size - 1)) : (kp % a.page_size));
-                else oxr_report(a.status, OXR_BAD_PAGE, g.req);
-            }
-            uint64_t* full = (is_v ? v_full : k_full) + st;
-            if (!mbar_wait((is_v ? v_empty : k_empty) + st, ((b / TC_STAGES) & 1) ^ 1)) { if (lane == 0) oxr_report(a.status, OXR_WAIT_EXPIRED, 30); break; }
-            unsigned char* dst = (is_v ? v_ring : k_ring) + (size_t)st * TC_HALF_STAGE;
+        // K(0), V(0), K(1), V(1), ...: each into its own ring
+        int row = row_first;
+        for (int b = 0; b < count; ++b) {
+            const int row_next = b + 1 < count ? lookup(b + 1) : -1;
+            const int st = b % TC_STAGES;
             const int total = __reduce_add_sync(0xffffffffu, row >= 0 ? box_rows * 128 : 0);
+            bool ok = true;
+            for (int is_v = 0; is_v < 2; ++is_v) {
+                uint64_t* full = (is_v ? v_full : k_full) + st;
+                if (!mbar_wait((is_v ? v_empty : k_empty) + st, ((b / TC_STAGES) & 1) ^ 1)) { if (lane == 0) oxr_report(a.status, OXR_WAIT_EXPIRED, 30); ok = false; break; }
+                unsigned char* dst = (is_v ? v_ring : k_ring) + (size_t)st * TC_HALF_STAGE;
 #ifdef OXR_TIMELINE
-            if (item == 0 && lane == 0) tl[5] = OXR_TL_NOW();
+                if (b == 0 && is_v == 0 && lane == 0) tl[5] = OXR_TL_NOW();
 #endif
-            if (total < pieces * box_rows * 128) {
-                // Page pieces that are not fetched (beyond the last key, before the window, a bad page) meet a probability of
-                // exactly zero, but must hold finite numbers: zero them (the ring may hold anything from an earlier kernel).
-                if (lane < pieces && row < 0) {
-                    uint4* z = reinterpret_cast<uint4*>(dst + (size_t)pnl * TC_PANEL_BYTES + (size_t)box * box_rows * 128);
-                    for (int j = 0; j < box_rows * 8; ++j) z[j] = make_uint4(0, 0, 0, 0);
+                if (total < pieces * box_rows * 128) {
+                    // Page pieces that are not fetched (beyond the last key, before the window, a bad page) meet a probability of
+                    // exactly zero, but must hold finite numbers: zero them (the ring may hold anything from an earlier kernel).
+                    if (lane < pieces && row < 0) {
+                        uint4* z = reinterpret_cast<uint4*>(dst + (size_t)my_pnl * TC_PANEL_BYTES + (size_t)my_box * box_rows * 128);
+                        for (int j = 0; j < box_rows * 8; ++j) z[j] = make_uint4(0, 0, 0, 0);
+                    }
+                    fence_proxy_async();
+                    __syncwarp();
                 }
-                fence_proxy_async();
+                if (lane == 0) {
+                    if (total > 0) mbar_expect_tx(full, (uint32_t)total);
+                    else mbar_arrive(full);
+                }
                 __syncwarp();
-            }
-            if (lane == 0) {
-                if (total > 0) mbar_expect_tx(full, (uint32_t)total);
-                else mbar_arrive(full);
-            }
-            __syncwarp();
-            if (row >= 0)
-                tma_load_2d(dst + (size_t)pnl * TC_PANEL_BYTES + (size_t)box * box_rows * 128, is_v ? &map_v : &map_k, g.kvh * D + pnl * 64, row, full);
+                if (row >= 0)
+                    tma_load_2d(dst + (size_t)my_pnl * TC_PANEL_BYTES + (size_t)my_box * box_rows * 128, is_v ? &map_v : &map_k,
+                                g.kvh * D + my_pnl * 64, row, full);
 #ifdef OXR_TIMELINE
-            if (item == 0 && lane == 0) tl[1] = OXR_TL_NOW();
+                if (b == 0 && is_v == 0 && lane == 0) tl[1] = OXR_TL_NOW();
 #endif
+            }
+            if (!ok) break;
+            row = row_next;
         }
     } else if (warp == 1) {
         // ---------------------------------------------------------------------- MMA issuer
