@@ -875,39 +875,45 @@ attn_tma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
             bool waited = false;
             for (int b = 0; b < count; ++b) {
                 const int st = b % TMA_STAGES;
+                const int k0 = k_first + (first + b) * MMA_BN;
+                // where this lane's loads come from (at most two: a block has at most 8 pieces and 4 panels), looked up before
+                // the wait for the stage so that the table's latency passes meanwhile
+                int rows[2] = {-1, -1};
+                int my_bytes = 0;
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const int i = lane + 32 * j;
+                    if (i < loads) {
+                        const int kp = piece_to_fetch(k0 + (i / (2 * PANELS)) * box_rows, box_rows, k_lo, k_end);
+                        const int page = table_row[a.page_shift >= 0 ? (kp >> a.page_shift) : (kp / a.page_size)];
+                        if (page >= 0 && page < a.num_pages) {
+                            rows[j] = pool_row0 + page * a.page_size + (a.page_shift >= 0 ? (kp & (a.page_size - 1)) : (kp % a.page_size));
+                            my_bytes += box_rows * 128;
+                        } else oxr_report(a.status, OXR_BAD_PAGE, g.req);
+                    }
+                }
                 if (!mbar_wait(empty + st, ((b / TMA_STAGES) & 1) ^ 1)) {
                     if (lane == 0) { atomicExch(&s_gave_up, 1); oxr_report(a.status, OXR_WAIT_EXPIRED, 10); }
                     break;
                 }
-                const int k0 = k_first + (first + b) * MMA_BN;
                 if (!waited && k0 + MMA_BN > g.pos0) {
                     pdl_wait();
                     waited = true;
                 }
                 unsigned char* dst = stages + (size_t)st * KV_STAGE_BYTES;
-                // where this lane's loads come from
-                int my_bytes = 0;
-                for (int i = lane; i < loads; i += 32) {
-                    const int kp = piece_to_fetch(k0 + (i / (2 * PANELS)) * box_rows, box_rows, k_lo, k_end);
-                    const int page = table_row[a.page_shift >= 0 ? (kp >> a.page_shift) : (kp / a.page_size)];
-                    if (page >= 0 && page < a.num_pages) my_bytes += box_rows * 128;
-                    else oxr_report(a.status, OXR_BAD_PAGE, g.req);
-                }
                 const int total = __reduce_add_sync(0xffffffffu, my_bytes);
                 if (lane == 0) {
                     if (total > 0) mbar_expect_tx(full + st, (uint32_t)total);
                     else mbar_arrive(full + st);
                 }
                 __syncwarp();
-                for (int i = lane; i < loads; i += 32) {
-                    const int box = i / (2 * PANELS), which = i % (2 * PANELS);     // which: K panels, then V panels
-                    const int kp = piece_to_fetch(k0 + box * box_rows, box_rows, k_lo, k_end);
-                    const int page = table_row[a.page_shift >= 0 ? (kp >> a.page_shift) : (kp / a.page_size)];
-                    if (page >= 0 && page < a.num_pages) {
-                        const int panel = which % PANELS;
-                        const int row = pool_row0 + page * a.page_size + (a.page_shift >= 0 ? (kp & (a.page_size - 1)) : (kp % a.page_size));
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const int i = lane + 32 * j;
+                    if (rows[j] >= 0) {
+                        const int box = i / (2 * PANELS), which = i % (2 * PANELS);     // which: K panels, then V panels
                         unsigned char* d2 = dst + (size_t)which * PANEL_BYTES + (size_t)box * box_rows * 128;
-                        tma_load_2d(d2, which < PANELS ? &map_k : &map_v, g.kvh * D + panel * 64, row, full + st);
+                        tma_load_2d(d2, which < PANELS ? &map_k : &map_v, g.kvh * D + (which % PANELS) * 64, rows[j], full + st);
                     }
                 }
             }
