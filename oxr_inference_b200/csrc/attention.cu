@@ -1093,39 +1093,45 @@ attn_tma_decode_walk_kernel(bf16* __restrict__ out, float* __restrict__ part_o, 
             const int* table_row = a.block_table + (size_t)p.g.req * a.table_width;
             for (int b = 0; b < p.count; ++b, ++n) {
                 const int st = n % TMA_STAGES;
+                const int k0 = p.k_first + (p.first + b) * MMA_BN;
+                // where this lane's loads come from (at most two), looked up before the wait for the stage
+                int rows[2] = {-1, -1};
+                int my_bytes = 0;
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const int i = lane + 32 * j;
+                    if (i < loads) {
+                        const int kp = piece_to_fetch(k0 + (i / (2 * PANELS)) * box_rows, box_rows, p.k_lo, p.k_end);
+                        const int page = table_row[a.page_shift >= 0 ? (kp >> a.page_shift) : (kp / a.page_size)];
+                        if (page >= 0 && page < a.num_pages) {
+                            rows[j] = pool_row0 + page * a.page_size + (a.page_shift >= 0 ? (kp & (a.page_size - 1)) : (kp % a.page_size));
+                            my_bytes += box_rows * 128;
+                        } else oxr_report(a.status, OXR_BAD_PAGE, p.g.req);
+                    }
+                }
                 if (!mbar_wait(empty + st, ((n / TMA_STAGES) & 1) ^ 1)) {
                     if (lane == 0) { atomicExch(&s_gave_up, 1); oxr_report(a.status, OXR_WAIT_EXPIRED, 20); }
                     ok = false;
                     break;
                 }
-                const int k0 = p.k_first + (p.first + b) * MMA_BN;
                 if (!waited && k0 + MMA_BN > p.g.pos0) {   // old keys are fetched while the kernel before this one may still run
                     pdl_wait();
                     waited = true;
                 }
                 unsigned char* dst = stages + (size_t)st * KV_STAGE_BYTES;
-                int my_bytes = 0;
-                for (int i = lane; i < loads; i += 32) {
-                    const int kp = piece_to_fetch(k0 + (i / (2 * PANELS)) * box_rows, box_rows, p.k_lo, p.k_end);
-                    const int page = table_row[a.page_shift >= 0 ? (kp >> a.page_shift) : (kp / a.page_size)];
-                    if (page >= 0 && page < a.num_pages) my_bytes += box_rows * 128;
-                    else oxr_report(a.status, OXR_BAD_PAGE, p.g.req);
-                }
                 const int total = __reduce_add_sync(0xffffffffu, my_bytes);
                 if (lane == 0) {
                     if (total > 0) mbar_expect_tx(full + st, (uint32_t)total);
                     else mbar_arrive(full + st);
                 }
                 __syncwarp();
-                for (int i = lane; i < loads; i += 32) {
-                    const int box = i / (2 * PANELS), which = i % (2 * PANELS);
-                    const int kp = piece_to_fetch(k0 + box * box_rows, box_rows, p.k_lo, p.k_end);
-                    const int page = table_row[a.page_shift >= 0 ? (kp >> a.page_shift) : (kp / a.page_size)];
-                    if (page >= 0 && page < a.num_pages) {
-                        const int panel = which % PANELS;
-                        const int row = pool_row0 + page * a.page_size + (a.page_shift >= 0 ? (kp & (a.page_size - 1)) : (kp % a.page_size));
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const int i = lane + 32 * j;
+                    if (rows[j] >= 0) {
+                        const int box = i / (2 * PANELS), which = i % (2 * PANELS);
                         unsigned char* d2 = dst + (size_t)which * PANEL_BYTES + (size_t)box * box_rows * 128;
-                        tma_load_2d(d2, which < PANELS ? &map_k : &map_v, p.g.kvh * D + panel * 64, row, full + st);
+                        tma_load_2d(d2, which < PANELS ? &map_k : &map_v, p.g.kvh * D + (which % PANELS) * 64, rows[j], full + st);
                     }
                 }
             }
