@@ -1024,6 +1024,7 @@ attn_tma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
 // SM, takes the tile's rows in rounds of four.
 // ---------------------------------------------------------------------------------------------------------------------
 constexpr int WALK_ROWS = 4;                                         // rows per round of the warps' merge
+constexpr int EVEN_UNITS = 512;                                      // most units for the even cut (their starts live in shared memory)
 constexpr size_t WALK_MERGE_BYTES = (size_t)4 * WALK_ROWS * MERGE_STRIDE * sizeof(float);
 constexpr size_t WALK_SMEM = 1024 + TMA_DECODE_TILES + WALK_MERGE_BYTES + (size_t)DECODE_ROWS * LDS * sizeof(bf16) + 128;
 
@@ -1041,32 +1042,71 @@ __device__ __forceinline__ bool consumer_any(bool v) {
 struct Piece {
     TileGeometry g;
     size_t unit;
-    int split, rows_live, k_end, k_lo, k_first, first, count;
+    size_t slot;       // where this piece's partial goes; the partials of a unit are `parts` consecutive slots from slot - split on
+    int split, parts, rows_live, k_end, k_lo, k_first, first, count;
 };
-__device__ __forceinline__ Piece piece_of(const AttnArgs& a, int item, int groups_y, int splits) {
-    Piece p;
-    p.split = item % splits;
-    const int y = (item / splits) % groups_y, tile = item / (splits * groups_y);
-    p.g = tile_geometry(a, DECODE_ROWS, tile, y);
-    p.unit = (size_t)tile * groups_y + y;
+// The unit's geometry and its key blocks; returns how many 64-key blocks it has (0 for a padding tile).
+__device__ __forceinline__ int unit_of(const AttnArgs& a, int unit, int groups_y, Piece& p) {
+    p.g = tile_geometry(a, DECODE_ROWS, unit / groups_y, unit % groups_y);
+    p.unit = (size_t)unit;
     p.rows_live = p.g.tok0 < p.g.tok_end ? (p.g.tok_end - p.g.tok0) * p.g.heads_per_tile : 0;
     p.k_end = p.g.pos0 + p.g.tok_end;
     p.k_lo = a.window > 0 ? max(0, p.g.pos0 + p.g.tok0 - a.window + 1) : 0;
     p.k_first = (p.k_lo / MMA_BN) * MMA_BN;
-    const int n_blocks = (p.k_end - p.k_first + MMA_BN - 1) / MMA_BN;
+    return p.rows_live > 0 ? (p.k_end - p.k_first + MMA_BN - 1) / MMA_BN : 0;
+}
+// Pieces by equal shares: every unit is cut into `splits` pieces of as many key blocks (the last may be shorter or empty).
+__device__ __forceinline__ Piece piece_of(const AttnArgs& a, int item, int groups_y, int splits) {
+    Piece p;
+    p.split = item % splits;
+    p.parts = splits;
+    const int n_blocks = unit_of(a, item / splits, groups_y, p);
+    p.slot = p.unit * splits + p.split;
     const int per = (n_blocks + splits - 1) / splits;
     p.first = p.split * per;
     p.count = p.rows_live > 0 ? max(0, min(per, n_blocks - p.first)) : 0;
     return p;
 }
+// Pieces by an even cut of ALL key blocks: the units' key blocks laid end to end (starts[u] = blocks before unit u) are
+// dealt out to the `nb` blocks of the grid in runs of q or q + 1 (the first r blocks take q + 1); a block's run may cover the
+// end of one unit and the beginning of the next, so requests of very different lengths still give every block the same
+// share. The pieces of a unit are those of consecutive blocks; piece (u, block i) has slot u + i (each new unit and each
+// new block moves the number on by one, so no two pieces share a slot).
+struct EvenCut {
+    const int* starts;   // [units + 1], in shared memory
+    int units, q, r, nb;
+    __device__ __forceinline__ int begin(int block) const { return block * q + min(block, r); }
+    __device__ __forceinline__ int block_of(int x) const { const int big = r * (q + 1); return x < big ? x / (q + 1) : r + (x - big) / q; }
+    __device__ __forceinline__ int unit_at(int x) const {    // the unit that holds key block x: the last u with starts[u] <= x
+        int lo = 0, hi = units - 1;
+        while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (starts[mid] <= x) lo = mid; else hi = mid - 1; }
+        return lo;
+    }
+};
+__device__ __forceinline__ Piece piece_even(const AttnArgs& a, const EvenCut& f, int unit, int block, int groups_y) {
+    Piece p;
+    unit_of(a, unit, groups_y, p);
+    const int u0 = f.starts[unit], u1 = f.starts[unit + 1];
+    const int lo = max(f.begin(block), u0), hi = min(f.begin(block + 1), u1);
+    p.first = lo - u0;
+    p.count = max(0, hi - lo);
+    const int b0 = u1 > u0 ? f.block_of(u0) : block, b1 = u1 > u0 ? f.block_of(u1 - 1) : block;
+    p.split = block - b0;
+    p.parts = b1 - b0 + 1;
+    p.slot = (size_t)unit + (size_t)block;
+    return p;
+}
 
-__global__ void __launch_bounds__(TMA_THREADS)
+__global__ void __launch_bounds__(TMA_THREADS, 2)   // two blocks an SM: the second bound keeps the registers within that
 attn_tma_decode_walk_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters,
                             const bf16* __restrict__ q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
-                            int pool_row0, int box_rows, int n_tiles, int groups_y, int splits, const AttnArgs a) {
+                            int pool_row0, int box_rows, int n_tiles, int groups_y, int splits, int cut, const AttnArgs a) {
+    // cut 0: every unit in `splits` equal pieces, dealt out piece by piece. cut 1: the even cut of all key blocks (EvenCut; at
+    // most EVEN_UNITS units), which the host asks for when the requests' lengths differ much.
     extern __shared__ unsigned char smem_dyn[];
     __shared__ int s_ticket;
     __shared__ int s_gave_up;
+    __shared__ int s_starts[EVEN_UNITS + 1];
     unsigned char* stages = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
     float* mo = reinterpret_cast<float*>(stages + TMA_DECODE_TILES);        // [4 warps][WALK_ROWS][MERGE_STRIDE]
     bf16* Qs = reinterpret_cast<bf16*>(stages + TMA_DECODE_TILES + WALK_MERGE_BYTES);
@@ -1074,6 +1114,7 @@ attn_tma_decode_walk_kernel(bf16* __restrict__ out, float* __restrict__ part_o, 
     uint64_t* empty = full + TMA_STAGES;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int items = n_tiles * groups_y * splits;
+    const int units = n_tiles * groups_y;
 
     if (threadIdx.x == 0) {
         for (int s2 = 0; s2 < TMA_STAGES; ++s2) { mbar_init(full + s2, 1); mbar_init(empty + s2, 4); }
@@ -1081,6 +1122,43 @@ attn_tma_decode_walk_kernel(bf16* __restrict__ out, float* __restrict__ part_o, 
         mbar_fence_init();
     }
     __syncthreads();
+    EvenCut even;
+    even.starts = s_starts; even.units = units; even.q = even.r = 0; even.nb = 1;
+    int u_first = 0, u_last = -1;      // even cut: the units this block's run touches
+    const bool flat = cut != 0;
+    if (flat) {
+        // what no kernel of a step writes (lengths, tile lists) is read above the wait: every block counts every unit's key
+        // blocks, warp 0 turns the counts into starts (each lane sixteen of them, then a scan over the lanes)
+        for (int u = threadIdx.x; u < EVEN_UNITS; u += blockDim.x) {
+            Piece tmp;
+            s_starts[u + 1] = u < units ? unit_of(a, u, groups_y, tmp) : 0;
+        }
+        if (threadIdx.x == 0) s_starts[0] = 0;
+        __syncthreads();
+        if (warp == 0) {
+            constexpr int PER = EVEN_UNITS / 32;
+            int v[PER], sum = 0;
+#pragma unroll
+            for (int j = 0; j < PER; ++j) { v[j] = s_starts[1 + lane * PER + j]; sum += v[j]; }
+            int before = sum;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) { const int t = __shfl_up_sync(0xffffffffu, before, o); if (lane >= o) before += t; }
+            before -= sum;
+#pragma unroll
+            for (int j = 0; j < PER; ++j) { before += v[j]; s_starts[1 + lane * PER + j] = before; }
+        }
+        __syncthreads();
+        const int total = s_starts[units];
+        even.nb = min((int)gridDim.x, total);
+        if (even.nb > 0) { even.q = total / even.nb; even.r = total % even.nb; }
+        if ((int)blockIdx.x < even.nb) {
+            u_first = even.unit_at(even.begin(blockIdx.x));
+            u_last = even.unit_at(even.begin(blockIdx.x + 1) - 1);
+        }
+    }
+    // one walk for both forms: `it` is an item (equal shares) or a unit (even cut)
+    const int it_begin = flat ? u_first : (int)blockIdx.x, it_end = flat ? u_last + 1 : items, it_step = flat ? 1 : (int)gridDim.x;
+    auto piece_at = [&](int it) { return flat ? piece_even(a, even, it, blockIdx.x, groups_y) : piece_of(a, it, groups_y, splits); };
 
     if (warp == 4) {
         // ---------------------------------------------------------------------- producer: piece after piece, one ring
@@ -1088,8 +1166,8 @@ attn_tma_decode_walk_kernel(bf16* __restrict__ out, float* __restrict__ part_o, 
         const int loads = boxes * 2 * PANELS;
         uint32_t n = 0;          // blocks requested so far: stage n % TMA_STAGES, use n / TMA_STAGES of that stage
         bool waited = false, ok = true;
-        for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
-            const Piece p = piece_of(a, item, groups_y, splits);
+        for (int item = it_begin; item < it_end && ok; item += it_step) {
+            const Piece p = piece_at(item);
             const int* table_row = a.block_table + (size_t)p.g.req * a.table_width;
             for (int b = 0; b < p.count; ++b, ++n) {
                 const int st = n % TMA_STAGES;
@@ -1145,15 +1223,16 @@ attn_tma_decode_walk_kernel(bf16* __restrict__ out, float* __restrict__ part_o, 
     const float scale_log2 = a.scale * LOG2E;
     constexpr int MS = MERGE_STRIDE;
     uint32_t n = 0;
-    for (int item = blockIdx.x; item < items; item += gridDim.x) {
+    for (int item = it_begin; item < it_end; item += it_step) {
         // the barrier frees Qs, the merge area and s_ticket of the piece before; all warps leave together once a wait
         // has run out anywhere in the block
         if (consumer_any(*reinterpret_cast<volatile int*>(&s_gave_up) != 0)) return;
-        const Piece p = piece_of(a, item, groups_y, splits);
+        const Piece p = piece_at(item);
         if (p.rows_live == 0) continue;   // every piece of this unit passes here: no tickets are drawn
+        if (flat && p.count == 0) continue;   // the even cut gives a unit no empty pieces (and counts none)
         const TileGeometry& g = p.g;
-        float* my_ml = part_ml + (p.unit * splits + p.split) * DECODE_ROWS * 2;
-        float* my_o = part_o + (p.unit * splits + p.split) * DECODE_ROWS * D;
+        float* my_ml = part_ml + p.slot * DECODE_ROWS * 2;
+        float* my_o = part_o + p.slot * DECODE_ROWS * D;
         if (p.count > 0) {
             load_q_rows(Qs, q, a, g, DECODE_ROWS);
             cp_async_commit();
@@ -1215,21 +1294,22 @@ attn_tma_decode_walk_kernel(bf16* __restrict__ out, float* __restrict__ part_o, 
                     }
                 }
                 consumer_sync();
-                merge_warps(mo, min(WALK_ROWS, p.rows_live - r0), splits, out, my_o, my_ml, g, a, r0, WALK_ROWS);
+                merge_warps(mo, min(WALK_ROWS, p.rows_live - r0), p.parts, out, my_o, my_ml, g, a, r0, WALK_ROWS);
             }
-        } else if (splits > 1) {   // nothing for this piece: an empty partial
+        } else if (p.parts > 1) {   // nothing for this piece: an empty partial
             for (int i = threadIdx.x; i < p.rows_live; i += MMA_THREADS) { my_ml[2 * i] = -INFINITY; my_ml[2 * i + 1] = 0.f; }
         }
-        if (splits == 1) continue;
+        if (p.parts == 1) continue;
         // ---- ticket: the last piece of a unit to finish merges them all
         __threadfence();
         consumer_sync();
         if (threadIdx.x == 0) s_ticket = atomicAdd(&counters[p.unit], 1);
         consumer_sync();
-        if (s_ticket == splits - 1) {
+        if (s_ticket == p.parts - 1) {
             __threadfence();
             if (threadIdx.x == 0) counters[p.unit] = 0;
-            merge_pieces(out, part_ml + p.unit * splits * DECODE_ROWS * 2, part_o + p.unit * splits * DECODE_ROWS * D, splits, p.rows_live, g, a);
+            const size_t slot0 = p.slot - (size_t)p.split;
+            merge_pieces(out, part_ml + slot0 * DECODE_ROWS * 2, part_o + slot0 * DECODE_ROWS * D, p.parts, p.rows_live, g, a);
         }
     }
 }
@@ -1766,9 +1846,32 @@ attn_tc5_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
 }
 }  // namespace
 
+// Blocks of the walking split-KV kernel that the GPU holds at once (0 if it cannot run here).
+static int walk_slots() {
+    static int slots = 0;
+    if (slots == 0 && TMA_OK) {
+        int dev = 0, sms = 0, per_sm = 0;
+        if (cudaFuncSetAttribute(attn_tma_decode_walk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WALK_SMEM) != cudaSuccess ||
+            cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_tma_decode_walk_kernel, TMA_THREADS, WALK_SMEM) != cudaSuccess ||
+            sms <= 0 || per_sm <= 0)
+            return 0;
+        slots = sms * per_sm;
+    }
+    return slots;
+}
+// For `cut` 1 of oxr_paged_attention_bf16: how many partial slots the scratch must have for
+// `units` = short tiles x KV heads x head groups (part_o: slots x 16 x D floats, part_ml: slots x 16 x 2): units + the
+// blocks of one round, or 0 if the even cut cannot be used for so many units or on this head size.
+OXR_API int oxr_attn_even_cut_slots(int units) {
+    const int slots = walk_slots();
+    return (slots > 0 && units > 0 && units <= EVEN_UNITS) ? units + slots : 0;
+}
+
 OXR_API int oxr_attn_head_dim() { return D; }
 // Which split-KV kernel the last call with short tiles launched: 0 none yet, 1 cp.async gathers, 2 TMA gathers with one
-// block per piece, 3 TMA gathers with one round of blocks that walk over the pieces. For tests and profiles.
+// block per piece, 3 TMA gathers with one round of blocks that walk over the pieces, 4 the same with the even cut of all key
+// blocks. For tests and profiles.
 static int oxr_last_short_kernel = 0;
 OXR_API int oxr_attn_last_short_kernel() { return oxr_last_short_kernel; }
 // Rows of a tile for each kind of tile list that the host builds: 0 generic, 1 decode, 2 prefill (mma.sync), 3 prefill
@@ -1792,15 +1895,18 @@ OXR_API int oxr_attn_tile_rows(int kind) {
 // of, with pool_row0 = layer * num_pages * page_size; the split-KV kernel then fetches K and V by TMA.
 // long_rows: rows per long tile the host cut the long list for: 64 (cp.async kernel) or 256 (tcgen05 kernel, needs kv_maps).
 // q_tokens: tokens (rows) of q and out, or 0 if unknown (the tcgen05 kernel then reads Q with ordinary loads).
+// cut (split-KV with TMA gathers only): 0 every request in `splits` equal pieces; 1 all key blocks of the step dealt out
+// evenly to one round of blocks, for requests of very different lengths (the scratch must then have
+// oxr_attn_even_cut_slots(units) slots, also with splits == 1).
 OXR_API int oxr_paged_attention_bf16(void* out, const void* q, const void* k_cache, const void* v_cache,
                                      const int* short_req, const int* short_tok0, int n_short, const int* long_req,
                                      const int* long_tok0, int n_long, const int* cu_q, const int* ctx_lens,
                                      const int* block_table, int table_width, int page_size, int num_pages, int H, int KV,
                                      float scale, int window, int splits, float* part_o, float* part_ml, int* counters,
-                                     const void* kv_maps, int pool_row0, int long_rows, int q_tokens, int* status, cudaStream_t stream) {
+                                     const void* kv_maps, int pool_row0, int long_rows, int q_tokens, int cut, int* status, cudaStream_t stream) {
     if (n_short <= 0 && n_long <= 0) return 0;
     if (H <= 0 || KV <= 0 || H % KV != 0 || page_size <= 0 || table_width <= 0 || window < 0 || splits < 1) return OXR_BAD_ARGUMENT;
-    if (splits > 1 && (part_o == nullptr || part_ml == nullptr || counters == nullptr)) return OXR_BAD_ARGUMENT;
+    if ((splits > 1 || cut != 0) && n_short > 0 && (part_o == nullptr || part_ml == nullptr || counters == nullptr)) return OXR_BAD_ARGUMENT;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_mma_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PREFILL_SMEM);
@@ -1868,22 +1974,21 @@ OXR_API int oxr_paged_attention_bf16(void* out, const void* q, const void* k_cac
             const int box_rows = page_size < MMA_BN ? page_size : MMA_BN;
             const long long pieces = (long long)n_short * KV * groups * splits;
             if (pieces > 0x7fffffffLL) return OXR_BAD_ARGUMENT;
-            static int slots = 0;   // blocks of this kernel that the GPU holds at once
-            if (slots == 0) {
-                cudaError_t e = cudaFuncSetAttribute(attn_tma_decode_walk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WALK_SMEM);
-                if (e != cudaSuccess) return 1000 + (int)e;
-                int dev = 0, sms = 0, per_sm = 0;
-                if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
-                    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_tma_decode_walk_kernel, TMA_THREADS, WALK_SMEM) != cudaSuccess ||
-                    sms <= 0 || per_sm <= 0)
-                    return OXR_BAD_ARGUMENT;
-                slots = sms * per_sm;
+            const int slots = walk_slots();   // blocks of the walking kernel that the GPU holds at once
+            if (slots <= 0) return OXR_BAD_ARGUMENT;
+            if (cut != 0) {
+                // one round of blocks and the even cut of all key blocks
+                if (cut != 1 || (long long)n_short * KV * groups > EVEN_UNITS) return OXR_BAD_ARGUMENT;
+                oxr_last_short_kernel = 4;
+                oxr_launch(attn_tma_decode_walk_kernel, dim3(slots), dim3(TMA_THREADS), WALK_SMEM, stream, true,
+                    (bf16*)out, part_o, part_ml, counters, (const bf16*)q, maps[0], maps[1], pool_row0, box_rows, n_short, KV * groups, splits, cut, a);
+                return oxr_launch_status();
             }
             if (pieces > slots) {
                 // more pieces than fit at once: one round of blocks that walk over them
                 oxr_last_short_kernel = 3;
                 oxr_launch(attn_tma_decode_walk_kernel, dim3(slots), dim3(TMA_THREADS), WALK_SMEM, stream, true,
-                    (bf16*)out, part_o, part_ml, counters, (const bf16*)q, maps[0], maps[1], pool_row0, box_rows, n_short, KV * groups, splits, a);
+                    (bf16*)out, part_o, part_ml, counters, (const bf16*)q, maps[0], maps[1], pool_row0, box_rows, n_short, KV * groups, splits, 0, a);
                 return oxr_launch_status();
             }
             oxr_last_short_kernel = 2;

@@ -17,7 +17,7 @@ import numpy as np
 import torch
 
 from oxr_inference_b200.cache.manager import CacheManager, RequestCache
-from oxr_inference_b200.parts.base import StepContext
+from oxr_inference_b200.parts.base import StepContext, uneven_lengths
 
 
 @dataclass(slots=True)
@@ -272,7 +272,9 @@ class BatchBuilder:
                 ctx = self._fixed_views[id(device_block)] = self.views(layout, device_block, tiles_n, q_lens, ctx_lens, max(layout.widths) * P)
             ctx.q_lens, ctx.ctx_lens_host = q_lens, ctx_lens
             return ctx
-        return self.views(layout, device_block, tiles_n, q_lens, ctx_lens, max(ctx_lens))
+        ctx = self.views(layout, device_block, tiles_n, q_lens, ctx_lens, max(ctx_lens))
+        ctx.uneven = uneven_lengths(ctx_lens)
+        return ctx
 
     def _advance_fixed(self, entries: list[StepEntry], layout: Layout, device_block: torch.Tensor, pinned: torch.Tensor, seg,
                        copy: bool) -> StepContext:

@@ -4,7 +4,8 @@ As in the reference (oxr_runtime/decode_graph.py:33-119): batch sizes are rounde
 in fixed device memory filled from pinned host memory before each replay, rows beyond the real requests point at
 a scratch page, and the graph holds the whole step: embedding, every layer, output head and the choice of the
 next token. Differences: graphs are captured at first use instead of all at start-up, a graph is keyed by
-(batch bucket, block-table width bucket) so that short contexts do not pay for the widest possible table, and the
+(batch bucket, block-table width bucket, whether the requests' lengths differ much) so that short contexts do not pay for
+the widest possible table and uneven batches get kernels that deal work out by keys rather than by requests, and the
 graph also holds the copy of its inputs from pinned memory and the copy of the chosen tokens and the kernels'
 status word back to pinned memory: a step is one launch and one synchronisation for the host.
 """
@@ -16,6 +17,7 @@ import torch
 from oxr_inference_b200 import ops
 from oxr_inference_b200.engine.batch import Layout, StepEntry
 from oxr_inference_b200.engine.runtime import ModelRunner
+from oxr_inference_b200.parts.base import uneven_lengths
 
 BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 192, 256, 384, 512, 768, 1024)  # oxr_runtime/decode_graph.py:30
 
@@ -29,8 +31,8 @@ class DecodeGraphs:
         self._pool = None
         self.kernels_per_replay: dict[tuple[int, int], int] = {}
         self.replays = 0
-        self.last_key: tuple[int, int] | None = None
-        """(batch bucket, table-width bucket) of the graph that ``run`` replayed last."""
+        self.last_key: tuple[int, int, bool] | None = None
+        """(batch bucket, table-width bucket, lengths uneven) of the graph that ``run`` replayed last."""
 
     def _width_bucket(self, entries: list[StepEntry]) -> int:
         need = max(len(t) for e in entries for t in e.cache.tables)
@@ -49,7 +51,7 @@ class DecodeGraphs:
         bucket = next((b for b in self.buckets if b >= n), None)
         if bucket is None:
             return None
-        key = (bucket, self._width_bucket(entries))
+        key = (bucket, self._width_bucket(entries), uneven_lengths([e.cache.length + 1 for e in entries]))
         if key not in self._graphs:
             self._capture(key)
         graph, layout, block, tokens, readback = self._graphs[key]
@@ -66,8 +68,8 @@ class DecodeGraphs:
         return ops.sample(logits, s["temperature"], s["seed_lo"], s["seed_hi"], s["counter"])
 
     @torch.inference_mode()
-    def _capture(self, key: tuple[int, int]) -> None:
-        bucket, width = key
+    def _capture(self, key: tuple[int, int, bool]) -> None:
+        bucket, width, uneven = key
         b = self.runner.builder
         m = self.runner.cache
         layout = Layout(bucket, bucket, bucket, [width] * len(m.pools), b.decode_tile_caps(bucket))
@@ -78,6 +80,7 @@ class DecodeGraphs:
         # mixer that keeps per-request state must not see a token twice (oxr_runtime/decode_graph.py:84-90 warms up on
         # whatever its static buffers hold, which at start-up is the scratch page as well).
         ctx = b.build([], layout=layout, device_block=block)
+        ctx.uneven = uneven      # the fixed block's context keeps it: every replay of this graph has requests of that kind
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):

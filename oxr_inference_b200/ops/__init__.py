@@ -145,9 +145,11 @@ def _attn_lib(head_dim: int):
         p, i, f = c_void_p, c_int, c_float
         lib.oxr_paged_attention.argtypes = [p, p, p, p, p, p, i, p, p, p, i, i, i, i, i, f, i, i, p, p]
         lib.oxr_paged_attention.restype = c_int
-        lib.oxr_paged_attention_bf16.argtypes = [p, p, p, p, p, p, i, p, p, i, p, p, p, i, i, i, i, i, f, i, i, p, p, p, p, i, i, i, p, p]
+        lib.oxr_paged_attention_bf16.argtypes = [p, p, p, p, p, p, i, p, p, i, p, p, p, i, i, i, i, i, f, i, i, p, p, p, p, i, i, i, i, p, p]
         lib.oxr_attn_make_kv_maps.argtypes = [p, p, p, ctypes.c_ulonglong, i, i]
         lib.oxr_attn_make_kv_maps.restype = c_int
+        lib.oxr_attn_even_cut_slots.argtypes = [i]
+        lib.oxr_attn_even_cut_slots.restype = c_int
         lib.oxr_paged_attention_bf16.restype = c_int
         lib.oxr_attn_tile_rows.argtypes = [i]
         lib.oxr_attn_tile_rows.restype = c_int
@@ -166,7 +168,8 @@ def _attn_lib(head_dim: int):
     return lib
 
 
-SHORT_KERNELS = {0: None, 1: "attn_mma_decode_kernel", 2: "attn_tma_decode_kernel", 3: "attn_tma_decode_walk_kernel"}
+SHORT_KERNELS = {0: None, 1: "attn_mma_decode_kernel", 2: "attn_tma_decode_kernel", 3: "attn_tma_decode_walk_kernel",
+                 4: "attn_tma_decode_walk_kernel (one round)"}
 
 
 def last_short_attention_kernel(head_dim: int) -> str | None:
@@ -401,6 +404,14 @@ DECODE_BLOCKS_PER_SM = 2
 """Blocks of the split-KV kernel that fit on one SM (its shared memory is the limit)."""
 
 
+DECODE_CUT = os.environ.get("OXR_B200_DECODE_CUT", "auto")
+"""How the split-KV kernel with TMA gathers cuts a step's keys (up to 512 (request, KV head) units): ``equal``: every request
+into the same number of pieces; ``even``: ALL key blocks of the step dealt out evenly to one round of blocks, so that
+requests of very different lengths still give every block the same share (a block's run may end one request and begin the
+next); ``auto`` (default): the even cut for the steps whose caller says that the lengths differ much (``uneven``), equal
+pieces otherwise (with lengths alike the even cut only costs: 3 us per layer at batch 8)."""
+
+
 def attention_splits(n_short_tiles: int, num_heads: int, num_kv_heads: int, kv_len_bound: int) -> int:
     """Into how many pieces the split-KV kernel cuts each request's keys. Blocks run in waves of
     ``num_sms() * DECODE_BLOCKS_PER_SM``; a block walks its piece's 64-key blocks one after the other and spends about
@@ -446,14 +457,15 @@ def make_kv_maps(k_pool: torch.Tensor, v_pool: torch.Tensor, page_size: int) -> 
 def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, *, tiles: dict, cu_q: torch.Tensor,
                     ctx_lens: torch.Tensor, block_table: torch.Tensor, page_size: int, scale: float, window: int,
                     kv_len_bound: int, status: torch.Tensor, generic: bool = False, kv_maps: KVMaps | None = None,
-                    layer_in_pool: int = 0) -> torch.Tensor:
+                    layer_in_pool: int = 0, uneven: bool = False) -> torch.Tensor:
     """Causal grouped-query attention of the step's new tokens over the paged cache
     (oxr_runtime/attention.py:47-109). ``q`` is ``[tokens, H, D]``; ``k_cache`` / ``v_cache`` are one layer's pool
     ``[pages, page_size, KV, D]``; ``window`` > 0 limits a query to its last ``window`` keys; ``tiles`` maps each
     spec of :func:`attention_tile_specs` to ``(tile_req, tile_tok0, count)``; ``kv_len_bound`` is an upper bound of
     the context lengths. float32 runs the fp32 CUDA-core kernel, bfloat16 the tensor-core kernels (``generic``
     forces the CUDA-core kernel, which then needs the float32 tile spec). With ``kv_maps`` (of the pool that
-    ``k_cache`` / ``v_cache`` are layer ``layer_in_pool`` of) the split-KV kernel fetches K and V by TMA."""
+    ``k_cache`` / ``v_cache`` are layer ``layer_in_pool`` of) the split-KV kernel fetches K and V by TMA. ``uneven``: the
+    caller knows that the requests' lengths differ much (see ``DECODE_CUT``)."""
     _need(q, "q")
     _need(k_cache, "k_cache", q.dtype)
     _need(v_cache, "v_cache", q.dtype)
@@ -482,17 +494,25 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     l_req, l_tok, n_long = tiles[long_]
     splits = attention_splits(n_short, num_heads, num_kv_heads, kv_len_bound) if n_short else 1
     part_o = part_ml = counters = None
-    if splits > 1:
-        group = num_heads // num_kv_heads
-        units = n_short * num_kv_heads * -(-group // min(group, DECODE_ROWS))
-        part_o = torch.empty(units * splits * DECODE_ROWS * head_dim, dtype=torch.float32, device=q.device)
-        part_ml = torch.empty(units * splits * DECODE_ROWS * 2, dtype=torch.float32, device=q.device)
+    cut = 0
+    group = num_heads // num_kv_heads
+    units = n_short * num_kv_heads * -(-group // min(group, DECODE_ROWS))
+    slots = units * splits if splits > 1 else 0
+    if n_short and kv_maps is not None and (DECODE_CUT == "even" or (DECODE_CUT == "auto" and uneven)):
+        # all key blocks of the step dealt out evenly to one round of blocks (requests of any mix of lengths): the library
+        # says how many partial results that can make, or 0 if it cannot do it for so many units
+        even = lib.oxr_attn_even_cut_slots(units)
+        if even > 0:
+            cut, slots = 1, max(slots, even)
+    if slots:
+        part_o = torch.empty(slots * DECODE_ROWS * head_dim, dtype=torch.float32, device=q.device)
+        part_ml = torch.empty(slots * DECODE_ROWS * 2, dtype=torch.float32, device=q.device)
         counters = _ticket_counters(q.device, units)
     code = lib.oxr_paged_attention_bf16(out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), s_req.data_ptr(),
                                         s_tok.data_ptr(), n_short, l_req.data_ptr(), l_tok.data_ptr(), n_long, *common, splits,
                                         _ptr(part_o), _ptr(part_ml), _ptr(counters),
                                         kv_maps.address if kv_maps is not None else None,
-                                        layer_in_pool * kv_maps.rows_per_layer if kv_maps is not None else 0, long_rows, q.shape[0],
+                                        layer_in_pool * kv_maps.rows_per_layer if kv_maps is not None else 0, long_rows, q.shape[0], cut,
                                         status.data_ptr(), _stream())
     global launch_count
     _done(code, "paged_attention_bf16")

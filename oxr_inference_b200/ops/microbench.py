@@ -79,6 +79,9 @@ def attention(args) -> dict:
     q = torch.randn(B * q_len, H, D, device="cuda").bfloat16()
     cu = torch.arange(0, (B + 1) * q_len, q_len, dtype=torch.int32, device="cuda")
     ctx_lens = torch.full((B,), ctx, dtype=torch.int32, device="cuda")
+    if args.ragged:   # decoding requests of very different lengths: from q_len + 16 keys up to the given context
+        gen = torch.Generator().manual_seed(1)
+        ctx_lens = torch.randint(q_len + 16, ctx + 1, (B,), generator=gen).int().cuda()
     tiles = {}
     for spec in ops.attention_tile_specs(H, KV, D, torch.bfloat16, None if args.no_tma else P):
         tpt, lo, hi = spec
@@ -95,15 +98,19 @@ def attention(args) -> dict:
     del pools
     maps = None if args.no_tma else ops.make_kv_maps(k_pool, v_pool, P)
 
+    from oxr_inference_b200.parts.base import uneven_lengths
+    uneven = uneven_lengths(ctx_lens.tolist())     # what the engine tells the kernel about such a step
+
     def run(i):
         layer = i % layers
         ops.paged_attention(q, k_pool[layer], v_pool[layer], tiles=tiles, cu_q=cu, ctx_lens=ctx_lens, block_table=table, page_size=P,
-                            scale=D ** -0.5, window=0, kv_len_bound=ctx, status=status, kv_maps=maps, layer_in_pool=layer)
+                            scale=D ** -0.5, window=0, kv_len_bound=ctx, status=status, kv_maps=maps, layer_in_pool=layer, uneven=uneven)
     us = _time(run, args.reps)
     ops.check_status(status)
-    kv_bytes = B * ctx * KV * D * 2 * 2
-    flops = sum(4 * H * D * (ctx - q_len + i + 1) for i in range(q_len)) * B
-    return {"kernel": "paged_attention", "batch": B, "q_len": q_len, "context": ctx, "heads": H, "kv_heads": KV, "head_dim": D,
+    lens = ctx_lens.tolist()
+    kv_bytes = sum(lens) * KV * D * 2 * 2
+    flops = sum(4 * H * D * (c - q_len + i + 1) for c in lens for i in range(q_len))
+    return {"kernel": "paged_attention", "batch": B, "q_len": q_len, "context": ctx if not args.ragged else f"{min(lens)}..{max(lens)}", "heads": H, "kv_heads": KV, "head_dim": D,
             "us": round(us, 2), "KV GB/s": round(kv_bytes / us / 1e3, 1), "TFLOP/s": round(flops / us / 1e6, 2)}
 
 
@@ -233,6 +240,7 @@ def main() -> None:
     a.add_argument("--head-dim", type=int, default=128)
     a.add_argument("--page-size", type=int, default=16)
     a.add_argument("--no-tma", action="store_true", help="gather K and V with cp.async instead of TMA")
+    a.add_argument("--ragged", action="store_true", help="contexts drawn between q_len + 16 and --context instead of all equal")
     a.set_defaults(run=attention)
     n = sub.add_parser("norm")
     n.add_argument("--rows", type=int, default=8)

@@ -82,5 +82,5 @@ class GroupedQueryAttention(Mixer):
         o = ops.paged_attention(q, k_pool, v_pool, tiles=ctx.tiles, cu_q=ctx.cu_q, ctx_lens=ctx.ctx_lens,
                                 block_table=group.block_table, page_size=group.page_size, scale=self.scale,
                                 window=self.window, kv_len_bound=ctx.kv_len_bound, status=ctx.status,
-                                kv_maps=group.kv_maps, layer_in_pool=cache.layer_in_group)
+                                kv_maps=group.kv_maps, layer_in_pool=cache.layer_in_group, uneven=ctx.uneven)
         return o.view(ctx.n_tokens, self.H * self.D)

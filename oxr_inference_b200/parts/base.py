@@ -139,9 +139,20 @@ class StepContext:
     """No request's context is longer than this; fixed for a CUDA graph, else the step's longest context."""
     q_lens: list[int] = field(default_factory=list)       # host copies, for parts that plan on the host
     ctx_lens_host: list[int] = field(default_factory=list)
+    uneven: bool = False
+    """The requests' context lengths differ much (``uneven_lengths``): a mixer may then deal its work out by keys rather than by
+    requests. Fixed for a captured CUDA graph (it is part of the graph's key)."""
     status: torch.Tensor | None = None
     sampling: dict[str, torch.Tensor] = field(default_factory=dict)
     """Per logit row: temperature (fp32), seed_lo, seed_hi, counter, row_slot (the row's state slot)."""
+
+
+def uneven_lengths(ctx_lens: list[int]) -> bool:
+    """Whether a step's requests differ so much in length that work dealt out request by request would leave most of the GPU
+    waiting for the longest: the longest is more than a quarter (and 128 keys) above the mean."""
+    if len(ctx_lens) < 2:
+        return False
+    return max(ctx_lens) > 1.25 * (sum(ctx_lens) / len(ctx_lens)) + 128
 
 
 # ------------------------------------------------------------------------------------------- families

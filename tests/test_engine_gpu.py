@@ -70,6 +70,49 @@ def test_greedy_generation_bfloat16_picks_near_maxima_of_the_plain_logits(folder
             assert row[tok] >= row.max() - 2 * 2.5e-2 * scale, f"token {i} = {tok} is not near the plain maximum"
 
 
+def test_requests_of_very_different_lengths_decode_with_the_even_cut(tmp_path):
+    """Head size 64 and pages of 8 tokens (TMA gathers), one layer with a window: four requests of 6 to 900 tokens decode
+    together. The engine notices that their lengths differ much, keys its CUDA graph by that, and the split-KV kernel deals
+    all key blocks out evenly instead of cutting every request alike; the tokens lie near the plain maxima, with graphs and
+    without, and a batch of requests of one length keeps the equal pieces."""
+    from oxr_inference_b200 import ops
+    from oxr_inference_b200.config import EngineSettings
+    from oxr_inference_b200.engine.api import Engine
+    from oxr_inference_b200.sampling import SamplingParams
+
+    name = "uneven64"
+    util.CONFIGS[name] = {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "hidden_size": 128, "intermediate_size": 96,
+                          "num_hidden_layers": 2, "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64, "rms_norm_eps": 1e-6,
+                          "rope_theta": 1e4, "vocab_size": 300, "tie_word_embeddings": False, "max_position_embeddings": 1024,
+                          "eos_token_id": 299, "use_sliding_window": True, "sliding_window": 400,
+                          "layer_types": ["full_attention", "sliding_attention"]}
+    try:
+        folder = make_folder(tmp_path, name, seed=5)
+        prompts = [token_ids(name, n, seed=31) for n in (6, 900, 40, 333)]
+        same = [token_ids(name, 200, seed=32 + i) for i in range(4)]
+    finally:
+        del util.CONFIGS[name]
+    for graphs in (True, False):
+        engine = Engine(folder, EngineSettings(dtype="bfloat16", page_size=8, num_pages=400, max_running=4, cuda_graphs=graphs,
+                                               max_step_tokens=2048))
+        got = engine.generate(prompts, SamplingParams(max_tokens=12, ignore_eos=True))
+        assert ops.last_short_attention_kernel(64) == "attn_tma_decode_walk_kernel (one round)"
+        if graphs:
+            assert engine.graphs.last_key[2] is True
+        for prompt, c in zip(prompts, got):
+            seq = prompt + c.token_ids
+            logits = plain_logits(folder, seq[:-1])
+            scale = logits.abs().max().item()
+            for i, tok in enumerate(c.token_ids):
+                row = logits[len(prompt) - 1 + i]
+                assert row[tok] >= row.max() - 2 * 2.5e-2 * scale, f"token {i} = {tok} is not near the plain maximum"
+        engine.generate(same, SamplingParams(max_tokens=4, ignore_eos=True))
+        assert ops.last_short_attention_kernel(64) == "attn_tma_decode_kernel"
+        if graphs:
+            assert engine.graphs.last_key[2] is False
+        engine.runner.cache.check()
+
+
 def test_cuda_graph_replay_equals_eager_steps(folders):
     from oxr_inference_b200.sampling import SamplingParams
 

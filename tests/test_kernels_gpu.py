@@ -679,9 +679,12 @@ def test_no_cpu_path(ops):
 
 @pytest.mark.parametrize("H,KV,D,P", [(32, 8, 128, 16), (8, 2, 64, 8), (4, 4, 128, 64), (16, 1, 64, 256), (2, 2, 256, 32)])
 @pytest.mark.parametrize("window", [0, 300])
-def test_split_kv_decode_with_tma_gathers(ops, H, KV, D, P, window):
+@pytest.mark.parametrize("uneven", [False, True])
+def test_split_kv_decode_with_tma_gathers(ops, H, KV, D, P, window, uneven):
     """The split-KV kernel fetching K and V by TMA from a pool of several layers (the layer is chosen by a row offset
-    into the pool's tensor map): against the plain statement, and against the cp.async version of the same kernel."""
+    into the pool's tensor map): against the plain statement, and against the cp.async version of the same kernel. Every
+    request cut into the same number of pieces, and (``uneven``: what the engine says of such lengths) all key blocks dealt
+    out evenly to one round of blocks."""
     g = torch.Generator(device=DEV).manual_seed(70 + D)
     q_lens = [1, 1, 1, 5, 2]
     ctx_lens = [1500, 333, 1, 1029, 64]
@@ -699,8 +702,8 @@ def test_split_kv_decode_with_tma_gathers(ops, H, KV, D, P, window):
     status = ops.new_status(DEV)
     common = dict( cu_q=torch.tensor(cu, dtype=torch.int32, device=DEV), ctx_lens=torch.tensor(ctx_lens, dtype=torch.int32, device=DEV),
                   block_table=table, page_size=P, scale=D ** -0.5, window=window, kv_len_bound=max(ctx_lens), status=status)
-    got = ops.paged_attention(q, k_pool[layer], v_pool[layer], tiles=tma_tiles, kv_maps=maps, layer_in_pool=layer, **common)
-    assert ops.last_short_attention_kernel(D) == "attn_tma_decode_kernel"
+    got = ops.paged_attention(q, k_pool[layer], v_pool[layer], tiles=tma_tiles, kv_maps=maps, layer_in_pool=layer, uneven=uneven, **common)
+    assert ops.last_short_attention_kernel(D) == ("attn_tma_decode_walk_kernel (one round)" if uneven else "attn_tma_decode_kernel")
     plain_gather = ops.paged_attention(q, k_pool[layer], v_pool[layer], tiles=tiles, **common)
     ops.check_status(status)
     want = KP.paged_attention(q, k_cache, v_cache, cu, ctx_lens, table, D ** -0.5, window)
@@ -762,6 +765,45 @@ def test_split_kv_decode_walking_over_more_pieces_than_blocks_fit(ops, H, KV, D,
                               scale=D ** -0.5, window=window, kv_len_bound=max(ctx_lens), status=status, kv_maps=maps, layer_in_pool=0)
     ops.check_status(status)
     assert ops.last_short_attention_kernel(D) == "attn_tma_decode_walk_kernel"
+    want = KP.paged_attention(q, k_cache, v_cache, cu, ctx_lens, table, D ** -0.5, window)
+    torch.testing.assert_close(got.float(), want, atol=2e-2, rtol=2e-2)
+    # told that the lengths differ much (they do), up to 512 (request, KV head) units take the even cut instead: the same
+    # kernel, every block with the same share of all keys
+    units = tiles[short][2] * KV
+    again = ops.paged_attention(q, k_cache, v_cache, tiles=tiles, cu_q=torch.tensor(cu, dtype=torch.int32, device=DEV),
+                                ctx_lens=torch.tensor(ctx_lens, dtype=torch.int32, device=DEV), block_table=released, page_size=P,
+                                scale=D ** -0.5, window=window, kv_len_bound=max(ctx_lens), status=status, kv_maps=maps, layer_in_pool=0,
+                                uneven=True)
+    ops.check_status(status)
+    assert ops.last_short_attention_kernel(D) == ("attn_tma_decode_walk_kernel (one round)" if units <= 512 else "attn_tma_decode_walk_kernel")
+    assert (n_req == 80) == (units > 512)
+    torch.testing.assert_close(again.float(), want, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("H,KV,D,P", [(32, 8, 128, 16), (4, 2, 64, 8), (6, 1, 128, 128)])
+@pytest.mark.parametrize("window", [0, 300])
+def test_split_kv_decode_even_cut_of_very_different_lengths(ops, H, KV, D, P, window):
+    """The even cut: one key beside eight thousand, a block's run ending exactly at a request's end (64, 128 keys), requests
+    that get one piece and requests that get dozens, short portions among the decoded tokens; with a window the tables name
+    released pages. A far key is made to stand out in the longest request so that a lost piece shows."""
+    g = torch.Generator(device=DEV).manual_seed(95 + D)
+    ctx_lens = [1, 5000, 64, 65, 3000, 129, 2, 700, 8000, 63, 128, 256]
+    q_lens = [1, 1, 1, 3, 1, 1, 2, 8, 1, 1, 1, 1]
+    q, k_cache, v_cache, table, cu = _paged_case(g, q_lens, ctx_lens, H, KV, D, P, torch.bfloat16)
+    if window == 0:      # request 8's key 1234 answers its query: without it the output is another
+        page = int(table[8, 1234 // P])
+        k_cache[page, 1234 % P] = (q[cu[8], ::H // KV] * 3).to(k_cache.dtype)
+    released = _release_behind_window(table, q_lens, ctx_lens, P, window)
+    maps = ops.make_kv_maps(k_cache[None], v_cache[None], P)
+    assert maps is not None
+    tiles = _tiles(ops, q_lens, H, KV, D, torch.bfloat16, P)
+    status = ops.new_status(DEV)
+    got = ops.paged_attention(q, k_cache, v_cache, tiles=tiles, cu_q=torch.tensor(cu, dtype=torch.int32, device=DEV),
+                              ctx_lens=torch.tensor(ctx_lens, dtype=torch.int32, device=DEV), block_table=released, page_size=P,
+                              scale=D ** -0.5, window=window, kv_len_bound=max(ctx_lens), status=status, kv_maps=maps, layer_in_pool=0,
+                              uneven=True)
+    ops.check_status(status)
+    assert ops.last_short_attention_kernel(D) == "attn_tma_decode_walk_kernel (one round)"
     want = KP.paged_attention(q, k_cache, v_cache, cu, ctx_lens, table, D ** -0.5, window)
     torch.testing.assert_close(got.float(), want, atol=2e-2, rtol=2e-2)
 
