@@ -70,7 +70,7 @@ def test_greedy_generation_bfloat16_picks_near_maxima_of_the_plain_logits(folder
             assert row[tok] >= row.max() - 2 * 2.5e-2 * scale, f"token {i} = {tok} is not near the plain maximum"
 
 
-def test_requests_of_very_different_lengths_decode_with_the_even_cut(tmp_path):
+def test_requests_of_very_different_lengths_decode_with_the_even_cut(tmp_path, monkeypatch):
     """Head size 64 and pages of 8 tokens (TMA gathers), one layer with a window: four requests of 6 to 900 tokens decode
     together. The engine notices that their lengths differ much, keys its CUDA graph by that, and the split-KV kernel deals
     all key blocks out evenly instead of cutting every request alike; the tokens lie near the plain maxima, with graphs and
@@ -80,6 +80,7 @@ def test_requests_of_very_different_lengths_decode_with_the_even_cut(tmp_path):
     from oxr_inference_b200.engine.api import Engine
     from oxr_inference_b200.sampling import SamplingParams
 
+    monkeypatch.setattr(ops, "DECODE_CUT", "auto")     # the default: the engine decides (an environment variable may say otherwise)
     name = "uneven64"
     util.CONFIGS[name] = {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "hidden_size": 128, "intermediate_size": 96,
                           "num_hidden_layers": 2, "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64, "rms_norm_eps": 1e-6,
