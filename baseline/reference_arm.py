@@ -18,6 +18,7 @@ its last token, points at batch 1 and 64.
 from __future__ import annotations
 
 import json
+import os
 import shutil
 import statistics
 import sys
@@ -37,7 +38,7 @@ def _ensure_copy() -> str | None:
     """The reference's package under baseline/_ref; copied from the mounted reference tree if it is not there yet."""
     if (REF / "oxr_runtime" / "language.py").is_file():
         return None
-    for src in (Path("/root/reference/oxr_runtime"),):
+    for src in (Path(os.environ.get("OXR_REFERENCE_TREE", "/root/reference")) / "oxr_runtime",):
         if (src / "language.py").is_file():
             REF.mkdir(parents=True, exist_ok=True)
             shutil.copytree(src, REF / "oxr_runtime", dirs_exist_ok=True)
