@@ -1024,7 +1024,8 @@ attn_tma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
 // SM, takes the tile's rows in rounds of four.
 // ---------------------------------------------------------------------------------------------------------------------
 constexpr int WALK_ROWS = 4;                                         // rows per round of the warps' merge
-constexpr int EVEN_UNITS = 512;                                      // most units for the even cut (their starts live in shared memory)
+constexpr int EVEN_MAX_UNITS = 16384;                                // most units for the even cut (32 of them then share a start)
+constexpr int EVEN_STARTS = 512;                                     // starts kept in shared memory for the even cut (of every unit, or every n-th)
 constexpr size_t WALK_MERGE_BYTES = (size_t)4 * WALK_ROWS * MERGE_STRIDE * sizeof(float);
 constexpr size_t WALK_SMEM = 1024 + TMA_DECODE_TILES + WALK_MERGE_BYTES + (size_t)DECODE_ROWS * LDS * sizeof(bf16) + 128;
 
@@ -1067,30 +1068,53 @@ __device__ __forceinline__ Piece piece_of(const AttnArgs& a, int item, int group
     p.count = p.rows_live > 0 ? max(0, min(per, n_blocks - p.first)) : 0;
     return p;
 }
-// Pieces by an even cut of ALL key blocks: the units' key blocks laid end to end (starts[u] = blocks before unit u) are
-// dealt out to the `nb` blocks of the grid in runs of q or q + 1 (the first r blocks take q + 1); a block's run may cover the
-// end of one unit and the beginning of the next, so requests of very different lengths still give every block the same
-// share. The pieces of a unit are those of consecutive blocks; piece (u, block i) has slot u + i (each new unit and each
-// new block moves the number on by one, so no two pieces share a slot).
+// Pieces by an even cut of ALL key blocks: the units' key blocks (with the slots of even_cost) laid end to end are dealt out to the `nb` blocks of the grid
+// in runs of q or q + 1 (the first r blocks take q + 1); a block's run may cover the end of one unit and the beginning of
+// the next, so requests of very different lengths still give every block the same share. The pieces of a unit are those of
+// consecutive blocks; piece (u, block i) has slot u + i (each new unit and each new block moves the number on by one, so
+// no two pieces share a slot). The units of one tile (its KV heads and head groups, `per_tile` of them, consecutive) have the
+// same number of key blocks, so shared memory holds per TILE the key blocks of one unit of all tiles before it, and only of
+// every `grp`-th tile, so that any number of tiles fits EVEN_STARTS entries (the tiles in between are counted again when a
+// run is looked up).
+// What is dealt out evenly are not the key blocks alone: a piece costs a block about as much as three key blocks beside its
+// streaming (its Q, the warps' merge, perhaps a ticket and the merge of a request's pieces), and requests come longest first, so
+// that a run of key blocks alone at the short end would be a hundred one-block pieces. Every unit therefore counts for its
+// key blocks and EVEN_PIECE_COST slots before them that hold no work.
+constexpr int EVEN_PIECE_COST = 3;
+__device__ __forceinline__ int even_cost(int n_blocks) { return n_blocks > 0 ? n_blocks + EVEN_PIECE_COST : 0; }
+
 struct EvenCut {
-    const int* starts;   // [units + 1], in shared memory
-    int units, q, r, nb;
+    const int* starts;   // [ceil(tiles / grp) + 1], in shared memory: starts[c] = key blocks of ONE unit each of the tiles before c * grp
+    int tiles, per_tile, grp, q, r, nb;
     __device__ __forceinline__ int begin(int block) const { return block * q + min(block, r); }
     __device__ __forceinline__ int block_of(int x) const { const int big = r * (q + 1); return x < big ? x / (q + 1) : r + (x - big) / q; }
-    __device__ __forceinline__ int unit_at(int x) const {    // the unit that holds key block x: the last u with starts[u] <= x
-        int lo = 0, hi = units - 1;
-        while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (starts[mid] <= x) lo = mid; else hi = mid - 1; }
-        return lo;
+    // the unit that holds key block x of the step, and that unit's first key block
+    __device__ __forceinline__ int unit_at(const AttnArgs& a, int x, int& start) const {
+        int lo = 0, hi = (tiles - 1) / grp;
+        while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (starts[mid] * per_tile <= x) lo = mid; else hi = mid - 1; }
+        int t = lo * grp, n = 0;
+        start = starts[lo] * per_tile;
+        for (;; ++t) {
+            Piece tmp;
+            n = even_cost(unit_of(a, t * per_tile, per_tile, tmp));
+            if (x < start + n * per_tile || t + 1 >= tiles) break;
+            start += n * per_tile;
+        }
+        const int y = n > 0 ? min((x - start) / n, per_tile - 1) : 0;
+        start += y * n;
+        return t * per_tile + y;
     }
 };
-__device__ __forceinline__ Piece piece_even(const AttnArgs& a, const EvenCut& f, int unit, int block, int groups_y) {
+// The piece of `unit` (whose slots begin at number u0 of the step) that falls into `block`'s run; slots: how many the unit has.
+__device__ __forceinline__ Piece piece_even(const AttnArgs& a, const EvenCut& f, int unit, int u0, int block, int groups_y, int& slots) {
     Piece p;
-    unit_of(a, unit, groups_y, p);
-    const int u0 = f.starts[unit], u1 = f.starts[unit + 1];
-    const int lo = max(f.begin(block), u0), hi = min(f.begin(block + 1), u1);
-    p.first = lo - u0;
+    const int n_blocks = unit_of(a, unit, groups_y, p);
+    slots = even_cost(n_blocks);
+    const int k0 = u0 + EVEN_PIECE_COST, k1 = k0 + n_blocks;      // the unit's key blocks among its slots
+    const int lo = max(f.begin(block), k0), hi = min(f.begin(block + 1), k1);
+    p.first = max(0, lo - k0);
     p.count = max(0, hi - lo);
-    const int b0 = u1 > u0 ? f.block_of(u0) : block, b1 = u1 > u0 ? f.block_of(u1 - 1) : block;
+    const int b0 = n_blocks > 0 ? f.block_of(k0) : block, b1 = n_blocks > 0 ? f.block_of(k1 - 1) : block;
     p.split = block - b0;
     p.parts = b1 - b0 + 1;
     p.slot = (size_t)unit + (size_t)block;
@@ -1101,12 +1125,12 @@ __global__ void __launch_bounds__(TMA_THREADS, 2)   // two blocks an SM: the sec
 attn_tma_decode_walk_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters,
                             const bf16* __restrict__ q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                             int pool_row0, int box_rows, int n_tiles, int groups_y, int splits, int cut, const AttnArgs a) {
-    // cut 0: every unit in `splits` equal pieces, dealt out piece by piece. cut 1: the even cut of all key blocks (EvenCut; at
-    // most EVEN_UNITS units), which the host asks for when the requests' lengths differ much.
+    // cut 0: every unit in `splits` equal pieces, dealt out piece by piece. cut 1: the even cut of all key blocks (EvenCut),
+    // which the host asks for when the requests' lengths differ much.
     extern __shared__ unsigned char smem_dyn[];
     __shared__ int s_ticket;
     __shared__ int s_gave_up;
-    __shared__ int s_starts[EVEN_UNITS + 1];
+    __shared__ int s_starts[EVEN_STARTS + 1];
     unsigned char* stages = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
     float* mo = reinterpret_cast<float*>(stages + TMA_DECODE_TILES);        // [4 warps][WALK_ROWS][MERGE_STRIDE]
     bf16* Qs = reinterpret_cast<bf16*>(stages + TMA_DECODE_TILES + WALK_MERGE_BYTES);
@@ -1123,20 +1147,30 @@ attn_tma_decode_walk_kernel(bf16* __restrict__ out, float* __restrict__ part_o, 
     }
     __syncthreads();
     EvenCut even;
-    even.starts = s_starts; even.units = units; even.q = even.r = 0; even.nb = 1;
+    even.starts = s_starts; even.tiles = n_tiles; even.per_tile = groups_y; even.q = even.r = 0; even.nb = 1;
+    even.grp = (n_tiles + EVEN_STARTS - 1) / EVEN_STARTS;
+    if (even.grp < 1) even.grp = 1;
     int u_first = 0, u_last = -1;      // even cut: the units this block's run touches
+    int run_start = 0, run_n = 0;      // even cut: the first key block of the unit a walk stands at, and that unit's count
     const bool flat = cut != 0;
     if (flat) {
-        // what no kernel of a step writes (lengths, tile lists) is read above the wait: every block counts every unit's key
-        // blocks, warp 0 turns the counts into starts (each lane sixteen of them, then a scan over the lanes)
-        for (int u = threadIdx.x; u < EVEN_UNITS; u += blockDim.x) {
-            Piece tmp;
-            s_starts[u + 1] = u < units ? unit_of(a, u, groups_y, tmp) : 0;
+        // what no kernel of a step writes (lengths, tile lists) is read above the wait: every block counts every tile's key
+        // blocks (a thread `grp` consecutive tiles at a time), warp 0 turns the counts into starts (each lane sixteen of them,
+        // then a scan over the lanes)
+        const int coarse = (n_tiles + even.grp - 1) / even.grp;
+        for (int c = threadIdx.x; c < EVEN_STARTS; c += blockDim.x) {
+            int sum = 0;
+            if (c < coarse)
+                for (int t = c * even.grp; t < min(n_tiles, (c + 1) * even.grp); ++t) {
+                    Piece tmp;
+                    sum += even_cost(unit_of(a, t * groups_y, groups_y, tmp));
+                }
+            s_starts[c + 1] = sum;
         }
         if (threadIdx.x == 0) s_starts[0] = 0;
         __syncthreads();
         if (warp == 0) {
-            constexpr int PER = EVEN_UNITS / 32;
+            constexpr int PER = EVEN_STARTS / 32;
             int v[PER], sum = 0;
 #pragma unroll
             for (int j = 0; j < PER; ++j) { v[j] = s_starts[1 + lane * PER + j]; sum += v[j]; }
@@ -1148,17 +1182,20 @@ attn_tma_decode_walk_kernel(bf16* __restrict__ out, float* __restrict__ part_o, 
             for (int j = 0; j < PER; ++j) { before += v[j]; s_starts[1 + lane * PER + j] = before; }
         }
         __syncthreads();
-        const int total = s_starts[units];
+        const int total = s_starts[coarse] * groups_y;
         even.nb = min((int)gridDim.x, total);
         if (even.nb > 0) { even.q = total / even.nb; even.r = total % even.nb; }
         if ((int)blockIdx.x < even.nb) {
-            u_first = even.unit_at(even.begin(blockIdx.x));
-            u_last = even.unit_at(even.begin(blockIdx.x + 1) - 1);
+            int last_start;
+            u_first = even.unit_at(a, even.begin(blockIdx.x), run_start);
+            u_last = even.unit_at(a, even.begin(blockIdx.x + 1) - 1, last_start);
         }
     }
-    // one walk for both forms: `it` is an item (equal shares) or a unit (even cut)
+    // one walk for both forms: `it` is an item (equal shares) or a unit (even cut); in the even cut a walk carries the
+    // start of the unit it stands at (run_start), moved on by the unit's count when the walk steps
     const int it_begin = flat ? u_first : (int)blockIdx.x, it_end = flat ? u_last + 1 : items, it_step = flat ? 1 : (int)gridDim.x;
-    auto piece_at = [&](int it) { return flat ? piece_even(a, even, it, blockIdx.x, groups_y) : piece_of(a, it, groups_y, splits); };
+    const int run_start0 = run_start;
+    auto piece_at = [&](int it) { return flat ? piece_even(a, even, it, run_start, blockIdx.x, groups_y, run_n) : piece_of(a, it, groups_y, splits); };
 
     if (warp == 4) {
         // ---------------------------------------------------------------------- producer: piece after piece, one ring
@@ -1166,7 +1203,8 @@ attn_tma_decode_walk_kernel(bf16* __restrict__ out, float* __restrict__ part_o, 
         const int loads = boxes * 2 * PANELS;
         uint32_t n = 0;          // blocks requested so far: stage n % TMA_STAGES, use n / TMA_STAGES of that stage
         bool waited = false, ok = true;
-        for (int item = it_begin; item < it_end && ok; item += it_step) {
+        run_start = run_start0;
+        for (int item = it_begin; item < it_end && ok; item += it_step, run_start += run_n) {
             const Piece p = piece_at(item);
             const int* table_row = a.block_table + (size_t)p.g.req * a.table_width;
             for (int b = 0; b < p.count; ++b, ++n) {
@@ -1223,7 +1261,8 @@ attn_tma_decode_walk_kernel(bf16* __restrict__ out, float* __restrict__ part_o, 
     const float scale_log2 = a.scale * LOG2E;
     constexpr int MS = MERGE_STRIDE;
     uint32_t n = 0;
-    for (int item = it_begin; item < it_end; item += it_step) {
+    run_start = run_start0;
+    for (int item = it_begin; item < it_end; item += it_step, run_start += run_n) {
         // the barrier frees Qs, the merge area and s_ticket of the piece before; all warps leave together once a wait
         // has run out anywhere in the block
         if (consumer_any(*reinterpret_cast<volatile int*>(&s_gave_up) != 0)) return;
@@ -1865,7 +1904,7 @@ static int walk_slots() {
 // blocks of one round, or 0 if the even cut cannot be used for so many units or on this head size.
 OXR_API int oxr_attn_even_cut_slots(int units) {
     const int slots = walk_slots();
-    return (slots > 0 && units > 0 && units <= EVEN_UNITS) ? units + slots : 0;
+    return (slots > 0 && units > 0 && units <= EVEN_MAX_UNITS) ? units + slots : 0;
 }
 
 OXR_API int oxr_attn_head_dim() { return D; }
@@ -1978,7 +2017,7 @@ OXR_API int oxr_paged_attention_bf16(void* out, const void* q, const void* k_cac
             if (slots <= 0) return OXR_BAD_ARGUMENT;
             if (cut != 0) {
                 // one round of blocks and the even cut of all key blocks
-                if (cut != 1 || (long long)n_short * KV * groups > EVEN_UNITS) return OXR_BAD_ARGUMENT;
+                if (cut != 1 || (long long)n_short * KV * groups > EVEN_MAX_UNITS) return OXR_BAD_ARGUMENT;
                 oxr_last_short_kernel = 4;
                 oxr_launch(attn_tma_decode_walk_kernel, dim3(slots), dim3(TMA_THREADS), WALK_SMEM, stream, true,
                     (bf16*)out, part_o, part_ml, counters, (const bf16*)q, maps[0], maps[1], pool_row0, box_rows, n_short, KV * groups, splits, cut, a);

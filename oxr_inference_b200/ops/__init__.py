@@ -405,11 +405,15 @@ DECODE_BLOCKS_PER_SM = 2
 
 
 DECODE_CUT = os.environ.get("OXR_B200_DECODE_CUT", "auto")
-"""How the split-KV kernel with TMA gathers cuts a step's keys (up to 512 (request, KV head) units): ``equal``: every request
+"""How the split-KV kernel with TMA gathers cuts a step's keys: ``equal``: every request
 into the same number of pieces; ``even``: ALL key blocks of the step dealt out evenly to one round of blocks, so that
 requests of very different lengths still give every block the same share (a block's run may end one request and begin the
 next); ``auto`` (default): the even cut for the steps whose caller says that the lengths differ much (``uneven``), equal
-pieces otherwise (with lengths alike the even cut only costs: 3 us per layer at batch 8)."""
+pieces otherwise (with lengths alike the even cut only costs: 3 us per layer at batch 8), and equal pieces also for more than
+``EVEN_CUT_MAX_TILES`` requests: the engine runs a decode step's requests longest first, so that hundreds of them dealt out
+piece by piece come out even by themselves (decode steps of Qwen3-4B sizes, contexts drawn up to 2,048 to 8,192 keys, eight
+layers: 8 requests 0.98 against 1.05 ms, 64: 1.83 against 2.10, 128: 1.97 against 2.30, 256: 3.34 against 3.24)."""
+EVEN_CUT_MAX_TILES = 192
 
 
 def attention_splits(n_short_tiles: int, num_heads: int, num_kv_heads: int, kv_len_bound: int) -> int:
@@ -498,7 +502,7 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     group = num_heads // num_kv_heads
     units = n_short * num_kv_heads * -(-group // min(group, DECODE_ROWS))
     slots = units * splits if splits > 1 else 0
-    if n_short and kv_maps is not None and (DECODE_CUT == "even" or (DECODE_CUT == "auto" and uneven)):
+    if n_short and kv_maps is not None and (DECODE_CUT == "even" or (DECODE_CUT == "auto" and uneven and n_short <= EVEN_CUT_MAX_TILES)):
         # all key blocks of the step dealt out evenly to one round of blocks (requests of any mix of lengths): the library
         # says how many partial results that can make, or 0 if it cannot do it for so many units
         even = lib.oxr_attn_even_cut_slots(units)

@@ -81,7 +81,10 @@ def attention(args) -> dict:
     ctx_lens = torch.full((B,), ctx, dtype=torch.int32, device="cuda")
     if args.ragged:   # decoding requests of very different lengths: from q_len + 16 keys up to the given context
         gen = torch.Generator().manual_seed(1)
-        ctx_lens = torch.randint(q_len + 16, ctx + 1, (B,), generator=gen).int().cuda()
+        ctx_lens = torch.randint(q_len + 16, ctx + 1, (B,), generator=gen).int()
+        if not args.unsorted:      # the engine runs a decode step's requests longest context first
+            ctx_lens = ctx_lens.sort(descending=True).values
+        ctx_lens = ctx_lens.cuda()
     tiles = {}
     for spec in ops.attention_tile_specs(H, KV, D, torch.bfloat16, None if args.no_tma else P):
         tpt, lo, hi = spec
@@ -241,6 +244,7 @@ def main() -> None:
     a.add_argument("--page-size", type=int, default=16)
     a.add_argument("--no-tma", action="store_true", help="gather K and V with cp.async instead of TMA")
     a.add_argument("--ragged", action="store_true", help="contexts drawn between q_len + 16 and --context instead of all equal")
+    a.add_argument("--unsorted", action="store_true", help="with --ragged: leave the requests in the order drawn")
     a.set_defaults(run=attention)
     n = sub.add_parser("norm")
     n.add_argument("--rows", type=int, default=8)

@@ -767,16 +767,15 @@ def test_split_kv_decode_walking_over_more_pieces_than_blocks_fit(ops, H, KV, D,
     assert ops.last_short_attention_kernel(D) == "attn_tma_decode_walk_kernel"
     want = KP.paged_attention(q, k_cache, v_cache, cu, ctx_lens, table, D ** -0.5, window)
     torch.testing.assert_close(got.float(), want, atol=2e-2, rtol=2e-2)
-    # told that the lengths differ much (they do), up to 512 (request, KV head) units take the even cut instead: the same
-    # kernel, every block with the same share of all keys
-    units = tiles[short][2] * KV
+    # told that the lengths differ much (they do), the step takes the even cut instead: the same kernel, every block with the
+    # same share of all keys (640 (request, KV head) units in the first shape: two units share a start in shared memory)
     again = ops.paged_attention(q, k_cache, v_cache, tiles=tiles, cu_q=torch.tensor(cu, dtype=torch.int32, device=DEV),
                                 ctx_lens=torch.tensor(ctx_lens, dtype=torch.int32, device=DEV), block_table=released, page_size=P,
                                 scale=D ** -0.5, window=window, kv_len_bound=max(ctx_lens), status=status, kv_maps=maps, layer_in_pool=0,
                                 uneven=True)
     ops.check_status(status)
-    assert ops.last_short_attention_kernel(D) == ("attn_tma_decode_walk_kernel (one round)" if units <= 512 else "attn_tma_decode_walk_kernel")
-    assert (n_req == 80) == (units > 512)
+    assert ops.last_short_attention_kernel(D) == "attn_tma_decode_walk_kernel (one round)"
+    assert (n_req == 80) == (tiles[short][2] * KV > 512)
     torch.testing.assert_close(again.float(), want, atol=2e-2, rtol=2e-2)
 
 
