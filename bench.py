@@ -6,7 +6,8 @@
 Prints ONE JSON line. ``value`` is decoded tokens per second at batch 8 with 2,048 tokens of context per request,
 timed on the device over K replays of the decode step; ``e2e`` is the same through ``Engine.step`` (host token ids
 in through pinned memory, sampled token ids out, every step). ``prefill`` is one 2,048-token prompt in one step;
-``points`` holds decode at batch 1 and 64; ``roofline`` divides the bytes a decode step has to read (every weight
+``points`` holds decode at batch 1 and 64, at longer contexts and for 32 requests of very different lengths, a longer prefill
+and the two serving workloads; ``roofline`` divides the bytes a decode step has to read (every weight
 once, plus the cache of the live requests) by its time. A step's inputs (15 GB of weights) are far larger than L2,
 so nothing is cached between timed iterations.
 """
@@ -44,6 +45,7 @@ CONTEXT = 2048
 PREFILL_TOKENS = 2048
 LONG_CONTEXTS = (8192, 32768)      # further decode points at batch 8
 LONG_PREFILL_TOKENS = 8192         # a further prefill point
+UNEVEN_CONTEXTS = [256 + round(i * (8192 - 256) / 31) for i in range(32)]   # a decode point with requests of very different lengths
 METRIC = "Qwen3-8B bf16 decode tok/s at batch 8 (context 2048)"
 
 
@@ -226,7 +228,8 @@ def main() -> int:
     long_contexts = () if args.skip_points else LONG_CONTEXTS
     long_prefill = 0 if args.skip_points else LONG_PREFILL_TOKENS
     spare = 2 * (K + W) + 64
-    pages = max([max(batches) * ((context + spare) // page + 2)] + [8 * ((c + spare) // page + 2) for c in long_contexts]) + 64
+    pages = max([max(batches) * ((context + spare) // page + 2)] + [8 * ((c + spare) // page + 2) for c in long_contexts] +
+                ([sum((c + spare) // page + 2 for c in UNEVEN_CONTEXTS)] if long_contexts else [])) + 64
     engine = Engine(random_config=cfg, seed=0, settings=EngineSettings(
         dtype="bfloat16", page_size=page, num_pages=pages, max_running=64, max_step_tokens=8192, prefill_chunk=2048,
         max_positions=max([4096, context + spare + 64, long_prefill + 64] + [c + spare + 64 for c in long_contexts]), cuda_graphs=True))
@@ -240,20 +243,20 @@ def main() -> int:
     weight_bytes = 2 * (L * layer_params + V * h) + 4 * (L * (2 * h + 2 * D) + h)
     kv_bytes_per_token = 2 * L * KV * D * 2
 
-    def fill(batch: int, budget: int, tokens: int) -> None:
-        """`batch` requests, each with `tokens` tokens in the cache and one token left to decode."""
+    def fill(batch: int, budget: int, tokens) -> None:
+        """`batch` requests, each with `tokens` tokens (one number, or one for each) in the cache and one token left to decode."""
         for r in list(engine.scheduler.running) + list(engine.scheduler.waiting):
             r.cancelled = True
         engine.step()
-        for _ in range(batch):
-            p = torch.randint(0, V, (tokens,), generator=gen).tolist()
+        for i in range(batch):
+            p = torch.randint(0, V, (tokens if isinstance(tokens, int) else tokens[i],), generator=gen).tolist()
             engine.add_request(p, SamplingParams(max_tokens=budget, ignore_eos=True))
         while engine.scheduler.waiting or any(r.pending > 1 for r in engine.scheduler.running):
             engine.step()
         assert len(engine.scheduler.running) == batch
 
-    def decode_device(batch: int, tokens: int = context) -> tuple[float, int, int]:
-        """ms per decode step on the device (K replays after W), kernels per step, context length."""
+    def decode_device(batch: int, tokens=context) -> tuple[float, int, int]:
+        """ms per decode step on the device (K replays after W), kernels per step, context length (of the first request)."""
         fill(batch, 2 * (K + W) + 8, tokens)
         plan = engine.scheduler.schedule()
         assert plan.decode_only and len(plan.entries) == batch
@@ -306,6 +309,13 @@ def main() -> int:
         ms, _, ctx = decode_device(8, c)
         points[f"decode_b8_ctx{c}"] = round(8 * 1000.0 / ms, 1)
         points[f"decode_b8_ctx{c}_hbm_frac"] = round((weight_bytes + 8 * ctx * kv_bytes_per_token) / (ms * 1e-3) / 1e9 / hbm_gbs, 4)
+
+    if long_contexts:
+        # requests of very different lengths, as a serving engine has them: 32 contexts evenly spaced from 256 to 8,192 tokens
+        lens = UNEVEN_CONTEXTS
+        ms, _, _ = decode_device(32, lens)
+        points["decode_b32_ctx256_to_8192"] = round(32 * 1000.0 / ms, 1)
+        points["decode_b32_ctx256_to_8192_hbm_frac"] = round((weight_bytes + (sum(lens) + 32) * kv_bytes_per_token) / (ms * 1e-3) / 1e9 / hbm_gbs, 4)
 
     # ---- prefill: one prompt in one step
     for r in list(engine.scheduler.running):
