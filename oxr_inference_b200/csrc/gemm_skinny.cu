@@ -101,7 +101,7 @@ gemm_skinny_kernel(TO* __restrict__ C, const __nv_bfloat16* __restrict__ X, cons
                 float gate = 0.f, up = 0.f;
 #pragma unroll
                 for (int w = 0; w < SKINNY_WARPS; ++w) { gate += partial[w][r][m]; up += partial[w][r + 8][m]; }
-                C[(size_t)m * (N / 2) + n0 / 2 + r] = Num<TO>::from_f32(gate / (1.f + __expf(-gate)) * up);
+                C[(size_t)m * (N / 2) + n0 / 2 + r] = Num<TO>::from_f32(__fdividef(gate, 1.f + __expf(-gate)) * up);
             }
         }
     } else {

@@ -275,7 +275,7 @@ gemm_stream_kernel(TO* __restrict__ C, const __nv_bfloat16* __restrict__ X, cons
 #pragma unroll
                     for (int w = 0; w < ST_WARPS; ++w) { gate += partial[(w * 16 + r) * PW + m]; up += partial[(w * 16 + r + 8) * PW + m]; }
                     if constexpr (SCALED) { gate *= s_inv[m]; up *= s_inv[m]; }
-                    C[(size_t)m * (N / 2) + n0 / 2 + r] = Num<TO>::from_f32(gate / (1.f + __expf(-gate)) * up);
+                    C[(size_t)m * (N / 2) + n0 / 2 + r] = Num<TO>::from_f32(__fdividef(gate, 1.f + __expf(-gate)) * up);
                 }
             }
         } else if constexpr (ADD) {
