@@ -808,8 +808,177 @@ constexpr int KV_STAGE_BYTES = 2 * PANELS * PANEL_BYTES;     // K panels then V 
 constexpr int TMA_STAGES = 3;
 constexpr int TMA_THREADS = 160;                             // 4 consumer warps + 1 producer warp
 constexpr size_t TMA_DECODE_TILES = (size_t)TMA_STAGES * KV_STAGE_BYTES;
+constexpr size_t NEW_KV_BYTES = 2 * (size_t)D * sizeof(bf16);   // the new token's k and v head (fused form), behind the barriers
 constexpr size_t TMA_DECODE_SMEM = 1024 + (TMA_DECODE_TILES > DECODE_MERGE_SMEM ? TMA_DECODE_TILES : DECODE_MERGE_SMEM) +
-                                   (size_t)DECODE_ROWS * LDS * sizeof(bf16) + 128;
+                                   (size_t)DECODE_ROWS * LDS * sizeof(bf16) + 128 + NEW_KV_BYTES;
+
+// ---------------------------------------------------------------------------------------------------------------------
+// A decode step without the q/k norm + rotation + store kernel (qk_norm_rope.cu; oxr_runtime/kernels.py:66-99): when every
+// request brings ONE token, the split-KV kernel with TMA gathers (a block per piece) can take the raw q|k|v projections itself. The
+// consumer warps normalise and rotate the tile's q heads on their way into shared memory; the warp that owns the new
+// token's key in the last key block does the same for the k head, copies the v head, writes both to the cache for the steps
+// to come, and puts them over that row of the stage when the block has arrived (whatever the TMA copy found in the cache
+// row of a token that nobody had stored yet). The arithmetic is that of the stand-alone kernel: fp32 from the bf16
+// projections, one rounding.
+// ---------------------------------------------------------------------------------------------------------------------
+struct FuseQkv {
+    const bf16* qkv;          // [requests, (H + 2 KV) * D]: null = q is given, the cache is complete
+    bf16* k_cache;            // this layer's pool, written at the new token's row; null = the layer stores nothing and
+    bf16* v_cache;            //   attends to what the cache holds (a layer that reads another layer's cache)
+    const float* q_weight;    // [D] or null: no norm
+    const float* k_weight;
+    const float* cos_table;   // [max_positions, D / 2] or null: no rotation
+    const float* sin_table;
+    float eps;
+    int max_positions;
+};
+constexpr int QK_STEPS = (D / 2 + 63) / 64;   // lane l holds elements 2 l, 2 l + 1 (+ 64 i) of a head's first half and their partners
+
+struct HeadWords {
+    float2 x1[QK_STEPS], x2[QK_STEPS];
+};
+__device__ __forceinline__ void load_head(HeadWords& w, const bf16* __restrict__ src, int lane) {
+#pragma unroll
+    for (int i = 0; i < QK_STEPS; ++i) {
+        const int j = 2 * lane + 64 * i;
+        w.x1[i] = w.x2[i] = make_float2(0.f, 0.f);
+        if (j < D / 2) {
+            w.x1[i] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + j));
+            w.x2[i] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + j + D / 2));
+        }
+    }
+}
+// One warp, one head: RMSNorm over the head with `weight` (null: none), then the half-split rotation with the rows
+// `cos_row`, `sin_row` of the tables (null: none). o1[i], o2[i]: the lane's elements as load_head holds them.
+__device__ __forceinline__ void norm_rope_head(const HeadWords& w, const float* __restrict__ weight, const float* __restrict__ cos_row,
+                                               const float* __restrict__ sin_row, float eps, int lane, __nv_bfloat162 (&o1)[QK_STEPS],
+                                               __nv_bfloat162 (&o2)[QK_STEPS]) {
+    constexpr int half = D / 2;
+    float inv = 1.f;
+    if (weight != nullptr) {
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < QK_STEPS; ++i)
+            ss += w.x1[i].x * w.x1[i].x + w.x1[i].y * w.x1[i].y + w.x2[i].x * w.x2[i].x + w.x2[i].y * w.x2[i].y;
+        ss = warp_sum(ss);
+        inv = rsqrtf(ss / (float)D + eps);
+    }
+#pragma unroll
+    for (int i = 0; i < QK_STEPS; ++i) {
+        const int j = 2 * lane + 64 * i;
+        float2 y1 = w.x1[i], y2 = w.x2[i];
+        if (j < half) {
+            if (weight != nullptr) {
+                const float2 w1 = *reinterpret_cast<const float2*>(weight + j), w2 = *reinterpret_cast<const float2*>(weight + j + half);
+                y1.x = y1.x * inv * w1.x; y1.y = y1.y * inv * w1.y;
+                y2.x = y2.x * inv * w2.x; y2.y = y2.y * inv * w2.y;
+            }
+            if (cos_row != nullptr) {
+                const float2 c = *reinterpret_cast<const float2*>(cos_row + j), sn = *reinterpret_cast<const float2*>(sin_row + j);
+                const float2 r1 = make_float2(y1.x * c.x - y2.x * sn.x, y1.y * c.y - y2.y * sn.y);
+                const float2 r2 = make_float2(y1.x * sn.x + y2.x * c.x, y1.y * sn.y + y2.y * c.y);
+                y1 = r1;
+                y2 = r2;
+            }
+        }
+        o1[i] = __float22bfloat162_rn(y1);
+        o2[i] = __float22bfloat162_rn(y2);
+    }
+}
+// The position of a request's one new token, checked against the rotary table.
+__device__ __forceinline__ int checked_position(const FuseQkv& f, const AttnArgs& a, int pos, int req, int lane) {
+    if (f.cos_table != nullptr && (pos < 0 || pos >= f.max_positions)) {
+        if (lane == 0) oxr_report(a.status, OXR_BAD_POSITION, req);
+        return 0;
+    }
+    return pos;
+}
+// The tile's q rows from the raw projections into shared memory, normalised and rotated (zeros for rows without a head):
+// consumer warp w takes rows w, w + 4, ..., all their loads first.
+__device__ __forceinline__ void fused_q_rows(bf16* Qs, const FuseQkv& f, const AttnArgs& a, const TileGeometry& g, int warp, int lane) {
+    constexpr int RPW = DECODE_ROWS / 4;
+    const int heads = a.H + 2 * a.KV;
+    HeadWords w[RPW];
+    bool ok[RPW];
+    const int pos = checked_position(f, a, g.pos0 + g.tok0, g.req, lane);
+    const bf16* token = f.qkv + (size_t)(g.q_begin + g.tok0) * heads * D;
+#pragma unroll
+    for (int i = 0; i < RPW; ++i) {
+        int tok, gh;
+        ok[i] = g.row(warp + 4 * i, tok, gh) && tok == g.tok0;   // one token per request
+        if (ok[i]) load_head(w[i], token + (size_t)(g.kvh * g.G + gh) * D, lane);
+    }
+    const float* cos_row = f.cos_table != nullptr ? f.cos_table + (size_t)pos * (D / 2) : nullptr;
+    const float* sin_row = f.cos_table != nullptr ? f.sin_table + (size_t)pos * (D / 2) : nullptr;
+#pragma unroll
+    for (int i = 0; i < RPW; ++i) {
+        __nv_bfloat162 o1[QK_STEPS], o2[QK_STEPS];
+        if (ok[i]) {
+            norm_rope_head(w[i], f.q_weight, cos_row, sin_row, f.eps, lane, o1, o2);
+        } else {
+#pragma unroll
+            for (int s = 0; s < QK_STEPS; ++s) o1[s] = o2[s] = __floats2bfloat162_rn(0.f, 0.f);
+        }
+        bf16* dst = Qs + (warp + 4 * i) * LDS;
+#pragma unroll
+        for (int s = 0; s < QK_STEPS; ++s) {
+            const int j = 2 * lane + 64 * s;
+            if (j < D / 2) {
+                *reinterpret_cast<__nv_bfloat162*>(dst + j) = o1[s];
+                *reinterpret_cast<__nv_bfloat162*>(dst + j + D / 2) = o2[s];
+            }
+        }
+    }
+}
+// One warp: the new token's k head (normalised, rotated) and v head into `newkv` ([2][D] in shared memory) and into the
+// cache row that the block table names for position `pos`.
+__device__ __forceinline__ void fused_new_kv(bf16* newkv, const FuseQkv& f, const AttnArgs& a, const TileGeometry& g, int lane) {
+    const int heads = a.H + 2 * a.KV;
+    const int pos_raw = g.pos0 + g.tok0;
+    const int pos = checked_position(f, a, pos_raw, g.req, lane);
+    const bf16* token = f.qkv + (size_t)(g.q_begin + g.tok0) * heads * D;
+    HeadWords w;
+    load_head(w, token + (size_t)(a.H + g.kvh) * D, lane);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (lane < D / 8) v = *reinterpret_cast<const uint4*>(token + (size_t)(a.H + a.KV + g.kvh) * D + 8 * lane);
+    const int page = a.block_table[(size_t)g.req * a.table_width + (a.page_shift >= 0 ? (pos_raw >> a.page_shift) : (pos_raw / a.page_size))];
+    const bool page_ok = page >= 0 && page < a.num_pages;
+    if (!page_ok && lane == 0) oxr_report(a.status, OXR_BAD_PAGE, g.req);
+    const size_t row = (size_t)(page_ok ? page : 0) * a.page_size + (a.page_shift >= 0 ? (pos_raw & (a.page_size - 1)) : (pos_raw % a.page_size));
+    __nv_bfloat162 o1[QK_STEPS], o2[QK_STEPS];
+    norm_rope_head(w, f.k_weight, f.cos_table != nullptr ? f.cos_table + (size_t)pos * (D / 2) : nullptr,
+                   f.cos_table != nullptr ? f.sin_table + (size_t)pos * (D / 2) : nullptr, f.eps, lane, o1, o2);
+    bf16* k_row = f.k_cache + (row * a.KV + g.kvh) * D;
+    bf16* v_row = f.v_cache + (row * a.KV + g.kvh) * D;
+#pragma unroll
+    for (int s = 0; s < QK_STEPS; ++s) {
+        const int j = 2 * lane + 64 * s;
+        if (j < D / 2) {
+            *reinterpret_cast<__nv_bfloat162*>(newkv + j) = o1[s];
+            *reinterpret_cast<__nv_bfloat162*>(newkv + j + D / 2) = o2[s];
+            if (page_ok) {
+                *reinterpret_cast<__nv_bfloat162*>(k_row + j) = o1[s];
+                *reinterpret_cast<__nv_bfloat162*>(k_row + j + D / 2) = o2[s];
+            }
+        }
+    }
+    if (lane < D / 8) {
+        *reinterpret_cast<uint4*>(newkv + D + 8 * lane) = v;
+        if (page_ok) *reinterpret_cast<uint4*>(v_row + 8 * lane) = v;
+    }
+    __syncwarp();
+}
+
+// The same warp, once the key block with the new token's row has arrived: k and v over that row of the stage (16-byte
+// words at their swizzled places). The fence orders these writes before the TMA copy that fills the stage next.
+__device__ __forceinline__ void patch_new_kv(const bf16* Kst, const bf16* Vst, const bf16* newkv, int row, int lane) {
+    if (lane < D / 8) {
+        *reinterpret_cast<uint4*>(const_cast<bf16*>(kv_elem<true>(Kst, row, 8 * lane))) = *reinterpret_cast<const uint4*>(newkv + 8 * lane);
+        *reinterpret_cast<uint4*>(const_cast<bf16*>(kv_elem<true>(Vst, row, 8 * lane))) = *reinterpret_cast<const uint4*>(newkv + D + 8 * lane);
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+}
 
 // First key of the page piece to fetch for the piece that starts at key `kp`: itself when any of its `box_rows` keys
 // is visible (k_lo <= key < k_end), else the piece that holds the nearest visible key.
@@ -821,10 +990,11 @@ __device__ __forceinline__ int piece_to_fetch(int kp, int box_rows, int k_lo, in
 
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
+template <bool FUSED>
 __global__ void __launch_bounds__(TMA_THREADS)
 attn_tma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters,
                        const bf16* __restrict__ q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
-                       int pool_row0, int box_rows, const AttnArgs a) {
+                       int pool_row0, int box_rows, const AttnArgs a, const FuseQkv f) {
     extern __shared__ unsigned char smem_dyn[];
     __shared__ int s_ticket;
     __shared__ int s_gave_up;
@@ -833,6 +1003,7 @@ attn_tma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
     bf16* Qs = reinterpret_cast<bf16*>(stages + TILE_REGION);
     uint64_t* full = reinterpret_cast<uint64_t*>(stages + TILE_REGION + (size_t)DECODE_ROWS * LDS * sizeof(bf16));
     uint64_t* empty = full + TMA_STAGES;
+    [[maybe_unused]] bf16* newkv = reinterpret_cast<bf16*>(stages + TILE_REGION + (size_t)DECODE_ROWS * LDS * sizeof(bf16) + 128);
 
     [[maybe_unused]] unsigned long long tl_released = 0, tl_first = 0, tl_streamed = 0;   // timeline stamps of the consumer warps
     const TileGeometry g = tile_geometry(a, DECODE_ROWS);
@@ -851,6 +1022,9 @@ attn_tma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
     const int per = (n_blocks + splits - 1) / splits;
     const int first = split * per;
     const int count = max(0, min(per, n_blocks - first));
+    // fused form: the key block and the row in it of the request's new token, and whether this piece holds it
+    [[maybe_unused]] const int new_blk = (g.pos0 + g.tok0 - k_first) / MMA_BN, new_row = (g.pos0 + g.tok0 - k_first) % MMA_BN;
+    [[maybe_unused]] const bool has_new = FUSED && f.k_cache != nullptr && new_blk >= first && new_blk < first + count;
 
     if (count > 0) {
         if (threadIdx.x == 0) {
@@ -896,7 +1070,7 @@ attn_tma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
                     if (lane == 0) { atomicExch(&s_gave_up, 1); oxr_report(a.status, OXR_WAIT_EXPIRED, 10); }
                     break;
                 }
-                if (!waited && k0 + MMA_BN > g.pos0) {
+                if (!FUSED && !waited && k0 + MMA_BN > g.pos0) {   // fused form: no kernel of the step wrote the cache before this one
                     pdl_wait();
                     waited = true;
                 }
@@ -924,7 +1098,12 @@ attn_tma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
         // ---------------------------------------------------------------------- consumers (warps 0..3)
         pdl_wait();   // q comes from the kernel before this one
         tl_released = OXR_TL_NOW();
-        load_q_rows(Qs, q, a, g, DECODE_ROWS);   // strided over MMA_THREADS = the 128 consumer threads
+        if constexpr (FUSED) {
+            fused_q_rows(Qs, f, a, g, warp, lane);
+            if (has_new && warp == new_row / 16) fused_new_kv(newkv, f, a, g, lane);
+        } else {
+            load_q_rows(Qs, q, a, g, DECODE_ROWS);   // strided over MMA_THREADS = the 128 consumer threads
+        }
         cp_async_commit();
         int row_pos[2];
         bool row_ok[2];
@@ -957,6 +1136,9 @@ attn_tma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
             if (b == 0) tl_first = OXR_TL_NOW();
             const bf16* Kst = reinterpret_cast<const bf16*>(stages + (size_t)st * KV_STAGE_BYTES);
             const bf16* Vst = Kst + PANELS * (PANEL_BYTES / 2);
+            if constexpr (FUSED) {
+                if (has_new && first + b == new_blk && warp == new_row / 16) patch_new_kv(Kst, Vst, newkv, new_row, lane);
+            }
             const int key0 = k_first + (first + b) * MMA_BN + warp * 16;
             const bool full_block = key0 + 15 <= tile_first_pos && key0 >= k_lo && (a.window <= 0 || key0 > tile_last_pos - a.window);
             warp_block<16, true>(qf, Qs, Kst + warp * 16 * 64, Vst + warp * 16 * 64, key0, row_pos, row_ok, a.window, full_block,
@@ -1907,12 +2089,57 @@ OXR_API int oxr_attn_even_cut_slots(int units) {
     return (slots > 0 && units > 0 && units <= EVEN_MAX_UNITS) ? units + slots : 0;
 }
 
+// Pieces that the split-KV kernel with TMA gathers runs with a block each (beyond it, one round of blocks walks over them).
+OXR_API int oxr_attn_one_round_of_pieces() { return walk_slots(); }
+
 OXR_API int oxr_attn_head_dim() { return D; }
 // Which split-KV kernel the last call with short tiles launched: 0 none yet, 1 cp.async gathers, 2 TMA gathers with one
 // block per piece, 3 TMA gathers with one round of blocks that walk over the pieces, 4 the same with the even cut of all key
 // blocks. For tests and profiles.
 static int oxr_last_short_kernel = 0;
 OXR_API int oxr_attn_last_short_kernel() { return oxr_last_short_kernel; }
+
+// The split-KV kernels with TMA gathers for the short tiles: kv_maps holds the group's two tensor maps (K, V) made by
+// oxr_attn_make_kv_maps. FUSED: the tiles are single tokens and `f` names their raw projections (FuseQkv); only the form with
+// a block per piece does that (a block that walks over many pieces would prepare q again for each, which at 64 requests of
+// 2,048 keys cost more than the kernel it saves: 7.21 against 7.14 ms for a Qwen3-8B decode step), so more pieces than one
+// round of blocks, or the even cut, are refused.
+template <bool FUSED>
+static int launch_tma_decode(void* out, const void* q, int n_short, int groups_y, int splits, float* part_o, float* part_ml, int* counters,
+                             const void* kv_maps, int pool_row0, int cut, const AttnArgs& a, const FuseQkv& f, cudaStream_t stream) {
+    static bool tma_configured = false;
+    if (!tma_configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_tma_decode_kernel<FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TMA_DECODE_SMEM);
+        if (e != cudaSuccess) return 1000 + (int)e;
+        tma_configured = true;
+    }
+    const CUtensorMap* maps = reinterpret_cast<const CUtensorMap*>(kv_maps);
+    const int box_rows = a.page_size < MMA_BN ? a.page_size : MMA_BN;
+    const long long pieces = (long long)n_short * groups_y * splits;
+    if (pieces > 0x7fffffffLL) return OXR_BAD_ARGUMENT;
+    const int slots = walk_slots();   // blocks of the walking kernel that the GPU holds at once
+    if (slots <= 0) return OXR_BAD_ARGUMENT;
+    if (FUSED && (cut != 0 || pieces > slots)) return OXR_BAD_ARGUMENT;
+    if (cut != 0) {
+        // one round of blocks and the even cut of all key blocks
+        if (cut != 1 || (long long)n_short * groups_y > EVEN_MAX_UNITS) return OXR_BAD_ARGUMENT;
+        oxr_last_short_kernel = 4;
+        oxr_launch(attn_tma_decode_walk_kernel, dim3(slots), dim3(TMA_THREADS), WALK_SMEM, stream, true,
+            (bf16*)out, part_o, part_ml, counters, (const bf16*)q, maps[0], maps[1], pool_row0, box_rows, n_short, groups_y, splits, cut, a);
+        return oxr_launch_status();
+    }
+    if (pieces > slots) {
+        // more pieces than fit at once: one round of blocks that walk over them
+        oxr_last_short_kernel = 3;
+        oxr_launch(attn_tma_decode_walk_kernel, dim3(slots), dim3(TMA_THREADS), WALK_SMEM, stream, true,
+            (bf16*)out, part_o, part_ml, counters, (const bf16*)q, maps[0], maps[1], pool_row0, box_rows, n_short, groups_y, splits, 0, a);
+        return oxr_launch_status();
+    }
+    oxr_last_short_kernel = 2;
+    oxr_launch(attn_tma_decode_kernel<FUSED>, dim3(n_short, groups_y, splits), dim3(TMA_THREADS), TMA_DECODE_SMEM, stream, true,
+        (bf16*)out, part_o, part_ml, counters, (const bf16*)q, maps[0], maps[1], pool_row0, box_rows, a, f);
+    return oxr_launch_status();
+}
 // Rows of a tile for each kind of tile list that the host builds: 0 generic, 1 decode, 2 prefill (mma.sync), 3 prefill
 // (tcgen05). The host keeps the same numbers and compares them when it loads the library.
 OXR_API int oxr_attn_tile_rows(int kind) {
@@ -2001,40 +2228,8 @@ OXR_API int oxr_paged_attention_bf16(void* out, const void* q, const void* k_cac
         const int groups = (G + hpt - 1) / hpt;
         if ((size_t)KV * groups > 65535 || splits > 65535) return OXR_BAD_ARGUMENT;
         a.tile_req = short_req; a.tile_tok0 = short_tok0;
-        if (TMA_OK && kv_maps != nullptr && a.page_shift >= 3) {
-            // K/V blocks by TMA: kv_maps holds the group's two tensor maps (K, V) made by oxr_attn_make_kv_maps
-            static bool tma_configured = false;
-            if (!tma_configured) {
-                cudaError_t e = cudaFuncSetAttribute(attn_tma_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TMA_DECODE_SMEM);
-                if (e != cudaSuccess) return 1000 + (int)e;
-                tma_configured = true;
-            }
-            const CUtensorMap* maps = reinterpret_cast<const CUtensorMap*>(kv_maps);
-            const int box_rows = page_size < MMA_BN ? page_size : MMA_BN;
-            const long long pieces = (long long)n_short * KV * groups * splits;
-            if (pieces > 0x7fffffffLL) return OXR_BAD_ARGUMENT;
-            const int slots = walk_slots();   // blocks of the walking kernel that the GPU holds at once
-            if (slots <= 0) return OXR_BAD_ARGUMENT;
-            if (cut != 0) {
-                // one round of blocks and the even cut of all key blocks
-                if (cut != 1 || (long long)n_short * KV * groups > EVEN_MAX_UNITS) return OXR_BAD_ARGUMENT;
-                oxr_last_short_kernel = 4;
-                oxr_launch(attn_tma_decode_walk_kernel, dim3(slots), dim3(TMA_THREADS), WALK_SMEM, stream, true,
-                    (bf16*)out, part_o, part_ml, counters, (const bf16*)q, maps[0], maps[1], pool_row0, box_rows, n_short, KV * groups, splits, cut, a);
-                return oxr_launch_status();
-            }
-            if (pieces > slots) {
-                // more pieces than fit at once: one round of blocks that walk over them
-                oxr_last_short_kernel = 3;
-                oxr_launch(attn_tma_decode_walk_kernel, dim3(slots), dim3(TMA_THREADS), WALK_SMEM, stream, true,
-                    (bf16*)out, part_o, part_ml, counters, (const bf16*)q, maps[0], maps[1], pool_row0, box_rows, n_short, KV * groups, splits, 0, a);
-                return oxr_launch_status();
-            }
-            oxr_last_short_kernel = 2;
-            oxr_launch(attn_tma_decode_kernel, dim3(n_short, KV * groups, splits), dim3(TMA_THREADS), TMA_DECODE_SMEM, stream, true,
-                (bf16*)out, part_o, part_ml, counters, (const bf16*)q, maps[0], maps[1], pool_row0, box_rows, a);
-            return oxr_launch_status();
-        }
+        if (TMA_OK && kv_maps != nullptr && a.page_shift >= 3)
+            return launch_tma_decode<false>(out, q, n_short, KV * groups, splits, part_o, part_ml, counters, kv_maps, pool_row0, cut, a, FuseQkv{}, stream);
         oxr_last_short_kernel = 1;
         attn_mma_decode_kernel<<<dim3(n_short, KV * groups, splits), MMA_THREADS, DECODE_SMEM, stream>>>(
             (bf16*)out, part_o, part_ml, counters, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, a);
@@ -2042,6 +2237,49 @@ OXR_API int oxr_paged_attention_bf16(void* out, const void* q, const void* k_cac
         if (rc) return rc;
     }
     return 0;
+}
+
+// A decode step's attention straight from the raw projections: every request brings ONE token (row r of qkv
+// [n, (H + 2 KV) * D] is request r's; cu_q = 0, 1, 2, ...), `short_req` / `short_tok0` are the n tiles of the short list. The
+// kernel normalises q and k per head (q_weight / k_weight [D] fp32, null: no norm), rotates them by the rows of the tables
+// [max_positions, D / 2] at each request's last position (null tables: no rotation), writes k and v into the cache
+// (store = 0: writes nothing and attends to what the cache holds) and attends, as oxr_qk_norm_rope_store followed by
+// oxr_paged_attention_bf16 would. Needs kv_maps, a head size that is a multiple of 64 and pages of 8 * 2^k tokens
+// and no more pieces (n_short * KV * head groups * splits) than oxr_attn_one_round_of_pieces(), cut 0 (OXR_BAD_ARGUMENT
+// otherwise); splits and scratch as in oxr_paged_attention_bf16.
+OXR_API int oxr_paged_attention_fused_decode_bf16(void* out, const void* qkv, void* k_cache, void* v_cache, const int* short_req,
+                                                  const int* short_tok0, int n_short, const int* cu_q, const int* ctx_lens,
+                                                  const int* block_table, int table_width, int page_size, int num_pages, int H, int KV,
+                                                  float scale, int window, int splits, float* part_o, float* part_ml, int* counters,
+                                                  const void* kv_maps, int pool_row0, int cut, const float* q_weight, const float* k_weight,
+                                                  const float* cos_table, const float* sin_table, float eps, int max_positions, int store,
+                                                  int* status, cudaStream_t stream) {
+    if (n_short <= 0) return 0;
+    if (H <= 0 || KV <= 0 || H % KV != 0 || page_size <= 0 || table_width <= 0 || window < 0 || splits < 1) return OXR_BAD_ARGUMENT;
+    if ((splits > 1 || cut != 0) && (part_o == nullptr || part_ml == nullptr || counters == nullptr)) return OXR_BAD_ARGUMENT;
+    if (!TMA_OK || kv_maps == nullptr || qkv == nullptr || (uintptr_t)qkv % 16 != 0 || (cos_table == nullptr) != (sin_table == nullptr) ||
+        (cos_table != nullptr && max_positions <= 0))
+        return OXR_BAD_ARGUMENT;
+    const int G = H / KV;
+    AttnArgs a;
+    a.cu_q = cu_q; a.ctx_lens = ctx_lens; a.block_table = block_table;
+    a.table_width = table_width; a.page_size = page_size; a.num_pages = num_pages; a.H = H; a.KV = KV;
+    a.page_shift = -1;
+    for (int sh = 0; sh < 30; ++sh) if ((1 << sh) == page_size) a.page_shift = sh;
+    if (a.page_shift < 3) return OXR_BAD_ARGUMENT;
+    a.heads_per_tile = a.tokens_per_tile = a.head_groups = 0;
+    a.scale = scale; a.window = window; a.status = status;
+    a.tile_req = short_req; a.tile_tok0 = short_tok0;
+    const int hpt = G < DECODE_ROWS ? G : DECODE_ROWS;
+    const int groups = (G + hpt - 1) / hpt;
+    if ((size_t)KV * groups > 65535 || splits > 65535) return OXR_BAD_ARGUMENT;
+    FuseQkv f;
+    f.qkv = (const bf16*)qkv;
+    f.k_cache = store ? (bf16*)k_cache : nullptr;
+    f.v_cache = store ? (bf16*)v_cache : nullptr;
+    f.q_weight = q_weight; f.k_weight = k_weight; f.cos_table = cos_table; f.sin_table = sin_table;
+    f.eps = eps; f.max_positions = max_positions;
+    return launch_tma_decode<true>(out, nullptr, n_short, KV * groups, splits, part_o, part_ml, counters, kv_maps, pool_row0, cut, a, f, stream);
 }
 
 // dtype: 0 = float32, 1 = bfloat16 (q, out and the cache). q, out: [tokens, H, D]. k_cache, v_cache: one layer's

@@ -76,6 +76,16 @@ class GroupedQueryAttention(Mixer):
         if qkv.dtype != k_pool.dtype:  # weights kept in 32-bit under 16-bit activations
             qkv = ops.cast(qkv, k_pool.dtype)
         cos, sin = self.position.tables() if self.position is not None else (None, None)
+        if ctx.single_tokens and ops.attention_takes_projections(self.D, qkv.dtype, group.page_size, group.kv_maps, requests=ctx.n_requests,
+                                                                 num_heads=self.H, num_kv_heads=self.KV, kv_len_bound=ctx.kv_len_bound,
+                                                                 uneven=ctx.uneven):
+            # a decode step: the attention kernel normalises, rotates and stores the one new token of each request itself
+            o = ops.decode_attention_from_projections(
+                qkv, self.q_norm, self.k_norm, cos, sin, k_pool, v_pool, store=cache.store, num_heads=self.H, num_kv_heads=self.KV,
+                head_dim=self.D, eps=self.eps, tiles=ctx.tiles, cu_q=ctx.cu_q, ctx_lens=ctx.ctx_lens, block_table=group.block_table,
+                page_size=group.page_size, scale=self.scale, window=self.window, kv_len_bound=ctx.kv_len_bound, status=ctx.status,
+                kv_maps=group.kv_maps, layer_in_pool=cache.layer_in_group, uneven=ctx.uneven)
+            return o.view(ctx.n_tokens, self.H * self.D)
         q = ops.qk_norm_rope_store(qkv, self.q_norm, self.k_norm, cos, sin, ctx.positions,
                                    group.slots if cache.store else ctx.no_store_slots, k_pool, v_pool,
                                    self.H, self.KV, self.D, self.eps, ctx.status)

@@ -146,6 +146,12 @@ class StepContext:
     sampling: dict[str, torch.Tensor] = field(default_factory=dict)
     """Per logit row: temperature (fp32), seed_lo, seed_hi, counter, row_slot (the row's state slot)."""
 
+    @property
+    def single_tokens(self) -> bool:
+        """Every request of the step brings exactly one token (a decode step): token r is request r's, at position
+        ``ctx_lens[r] - 1``."""
+        return self.n_tokens == self.n_requests and all(q == 1 for q in self.q_lens)
+
 
 def uneven_lengths(ctx_lens: list[int]) -> bool:
     """Whether a step's requests differ so much in length that work dealt out request by request would leave most of the GPU

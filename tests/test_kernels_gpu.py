@@ -807,6 +807,111 @@ def test_split_kv_decode_even_cut_of_very_different_lengths(ops, H, KV, D, P, wi
     torch.testing.assert_close(got.float(), want, atol=2e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("H,KV,D,P", [(32, 8, 128, 16), (8, 2, 64, 8), (2, 2, 256, 32), (40, 1, 64, 16), (6, 3, 192, 64)])
+@pytest.mark.parametrize("window", [0, 300])
+@pytest.mark.parametrize("norm,rotate,store", [(True, True, True), (False, True, True), (True, False, True), (True, True, False)])
+def test_decode_attention_takes_the_raw_projections(ops, monkeypatch, H, KV, D, P, window, norm, rotate, store):
+    """A step of one token per request given to the split-KV kernel as raw q|k|v projections: the kernel normalises and
+    rotates q and the new k itself, stores k and v, and attends. Against the stand-alone q/k norm + rotation + store kernel
+    followed by the same attention kernel on a copy of the pool: the same cache afterwards (every other row untouched) and
+    the same output. New tokens at a key block's first and last row, as a request's only key, behind thousands of keys;
+    more q heads per KV head than a tile has rows; without norm, without rotation, and for a layer that stores nothing."""
+    monkeypatch.setattr(ops, "FUSE_QKV", True)     # whatever the environment's switches say
+    monkeypatch.setattr(ops, "DECODE_CUT", "auto")
+    g = torch.Generator(device=DEV).manual_seed(170 + D + H)
+    ctx_lens = [65, 1500, 64, 1, 333, 129, 2, 700, 1029, 63, 128, 256]
+    if D == 256:      # one block per SM at this head size: a round of blocks holds half as many pieces
+        ctx_lens = ctx_lens[:6]
+    n = len(ctx_lens)
+    q_lens = [1] * n
+    layers, layer, eps, maxpos = 2, 1, 1e-5, max(ctx_lens) + 3
+    _, k_cache, v_cache, table, cu = _paged_case(g, q_lens, ctx_lens, H, KV, D, P, torch.bfloat16)
+    table = _release_behind_window(table, q_lens, ctx_lens, P, window)
+    k_pool = torch.randn(layers, *k_cache.shape, device=DEV, generator=g).bfloat16()
+    v_pool = torch.randn(layers, *v_cache.shape, device=DEV, generator=g).bfloat16()
+    k_pool[layer], v_pool[layer] = k_cache, v_cache
+    qkv = torch.randn(n, (H + 2 * KV) * D, device=DEV, generator=g).bfloat16()
+    qw = 1 + 0.2 * torch.randn(D, device=DEV, generator=g) if norm else None
+    kw = 1 + 0.2 * torch.randn(D, device=DEV, generator=g) if norm else None
+    inv = 1.0 / (1e4 ** (torch.arange(0, D, 2, dtype=torch.float) / D))
+    fr = torch.outer(torch.arange(maxpos, dtype=torch.float), inv)
+    cos, sin = (fr.cos().to(DEV), fr.sin().to(DEV)) if rotate else (None, None)
+    positions = torch.tensor([c - 1 for c in ctx_lens], dtype=torch.int32, device=DEV)
+    slots = torch.tensor([int(table[r, (c - 1) // P]) * P + (c - 1) % P for r, c in enumerate(ctx_lens)], dtype=torch.int32, device=DEV)
+    tiles = _tiles(ops, q_lens, H, KV, D, torch.bfloat16, P)
+    short = ops.attention_tile_specs(H, KV, D, torch.bfloat16, P)[0]
+    assert ops.attention_splits(tiles[short][2], H, KV, max(ctx_lens)) > 1, "the new token's piece is to be one of several"
+    status = ops.new_status(DEV)
+    common = dict(tiles=tiles, cu_q=torch.tensor(cu, dtype=torch.int32, device=DEV), ctx_lens=torch.tensor(ctx_lens, dtype=torch.int32, device=DEV),
+                  block_table=table, page_size=P, scale=D ** -0.5, window=window, kv_len_bound=max(ctx_lens), status=status, layer_in_pool=layer,
+                  uneven=False)
+    name = "attn_tma_decode_kernel"
+    # the two kernels, on a copy of the pool
+    k_two, v_two = k_pool.clone(), v_pool.clone()
+    q = ops.qk_norm_rope_store(qkv, qw, kw, cos, sin, positions, slots if store else torch.full_like(slots, -1), k_two[layer], v_two[layer],
+                               H, KV, D, eps, status)
+    want = ops.paged_attention(q, k_two[layer], v_two[layer], kv_maps=ops.make_kv_maps(k_two, v_two, P), **common)
+    assert ops.last_short_attention_kernel(D) == name
+    # the one kernel
+    maps = ops.make_kv_maps(k_pool, v_pool, P)
+    assert ops.attention_takes_projections(D, torch.bfloat16, P, maps, requests=n, num_heads=H, num_kv_heads=KV, kv_len_bound=max(ctx_lens))
+    before = (k_pool.clone(), v_pool.clone())
+    got = ops.decode_attention_from_projections(qkv, qw, kw, cos, sin, k_pool[layer], v_pool[layer], store=store, num_heads=H, num_kv_heads=KV,
+                                                head_dim=D, eps=eps, kv_maps=maps, **common)
+    ops.check_status(status)
+    assert ops.last_short_attention_kernel(D) == name
+    # v is a copy; k is computed in fp32 and rounded once by both kernels, whose compiled sums may differ in the last bit of
+    # fp32: at most one bf16 step apart; every row but the new tokens' stays as it was
+    assert torch.equal(v_pool, v_two)
+    torch.testing.assert_close(k_pool.float(), k_two.float(), rtol=2.0 ** -7, atol=1e-6)
+    new_rows = torch.zeros(k_pool[layer].numel() // (KV * D), dtype=torch.bool, device=DEV)
+    if store:
+        new_rows[slots.long()] = True
+    for now, was in ((k_pool, before[0]), (v_pool, before[1])):
+        assert torch.equal(now[0], was[0]), "another layer of the pool was written"
+        assert torch.equal(now[layer].view(-1, KV * D)[~new_rows], was[layer].view(-1, KV * D)[~new_rows]), "a row of another token was written"
+    if store:
+        assert not torch.equal(k_pool[layer].view(-1, KV * D)[new_rows], before[0][layer].view(-1, KV * D)[new_rows])
+    torch.testing.assert_close(got.float(), want.float(), atol=4e-3, rtol=2.0 ** -7)   # one bf16 step where a key moved by one
+    if not norm:
+        return
+    # and against the plain statement of both steps
+    wq, wk, wv = KP.qk_norm_rope(qkv, qw, kw, cos, sin, positions, H, KV, D, eps)
+    if store:
+        kc, vc = before[0][layer].clone().view(-1, KV, D), before[1][layer].clone().view(-1, KV, D)
+        kc[slots.long()], vc[slots.long()] = wk.bfloat16(), wv.bfloat16()
+    else:
+        kc, vc = before[0][layer], before[1][layer]
+    plain = KP.paged_attention(wq.bfloat16(), kc.view_as(k_cache), vc.view_as(v_cache), cu, ctx_lens, table, D ** -0.5, window)
+    torch.testing.assert_close(got.float(), plain, atol=2e-2, rtol=2e-2)
+
+
+def test_decode_attention_from_projections_refuses_what_it_cannot_do(ops, monkeypatch):
+    monkeypatch.setattr(ops, "FUSE_QKV", True)
+    monkeypatch.setattr(ops, "DECODE_CUT", "auto")
+    H, KV, D, P, n = 4, 2, 64, 16, 3
+    k_pool = torch.zeros(1, 8, P, KV, D, device=DEV, dtype=torch.bfloat16)
+    v_pool = torch.zeros_like(k_pool)
+    maps = ops.make_kv_maps(k_pool, v_pool, P)
+    assert not ops.attention_takes_projections(48, torch.bfloat16, P, maps)       # head size not a multiple of 64
+    assert not ops.attention_takes_projections(D, torch.float32, P, maps)
+    assert not ops.attention_takes_projections(D, torch.bfloat16, 4, maps)        # pages too small for a TMA box
+    assert not ops.attention_takes_projections(D, torch.bfloat16, P, None)
+    # only with a block for every piece: not when a round of blocks walks over more pieces, nor with the even cut
+    assert ops.attention_takes_projections(D, torch.bfloat16, P, maps, requests=8, num_heads=H, num_kv_heads=KV, kv_len_bound=2048)
+    assert not ops.attention_takes_projections(D, torch.bfloat16, P, maps, requests=400, num_heads=H, num_kv_heads=KV, kv_len_bound=2048)
+    assert not ops.attention_takes_projections(D, torch.bfloat16, P, maps, requests=8, num_heads=H, num_kv_heads=KV, kv_len_bound=8192, uneven=True)
+    q_lens, ctx_lens = [1, 2, 1], [5, 9, 3]       # one request brings two tokens
+    tiles = _tiles(ops, q_lens, H, KV, D, torch.bfloat16, P)
+    qkv = torch.zeros(sum(q_lens), (H + 2 * KV) * D, device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(ops.KernelError, match="one token per request"):
+        ops.decode_attention_from_projections(qkv, None, None, None, None, k_pool[0], v_pool[0], store=True, num_heads=H, num_kv_heads=KV,
+                                              head_dim=D, eps=1e-6, tiles=tiles, cu_q=torch.tensor([0, 1, 3, 4], dtype=torch.int32, device=DEV),
+                                              ctx_lens=torch.tensor(ctx_lens, dtype=torch.int32, device=DEV),
+                                              block_table=torch.zeros(n, 2, dtype=torch.int32, device=DEV), page_size=P, scale=1.0, window=0,
+                                              kv_len_bound=16, status=ops.new_status(DEV), kv_maps=maps)
+
+
 def test_tma_gathers_are_refused_for_sizes_they_cannot_do(ops):
     pool = torch.zeros(1, 4, 4, 2, 128, device=DEV, dtype=torch.bfloat16)
     assert ops.make_kv_maps(pool, pool, 4) is None          # pages of 4 tokens
