@@ -820,9 +820,12 @@ def test_decode_attention_takes_the_raw_projections(ops, monkeypatch, H, KV, D, 
     monkeypatch.setattr(ops, "DECODE_CUT", "auto")
     g = torch.Generator(device=DEV).manual_seed(170 + D + H)
     ctx_lens = [65, 1500, 64, 1, 333, 129, 2, 700, 1029, 63, 128, 256]
-    if D == 256:      # one block per SM at this head size: a round of blocks holds half as many pieces
-        ctx_lens = ctx_lens[:6]
     n = len(ctx_lens)
+    # as many of them as get a block for each of their pieces (at head sizes of 192 and more an SM holds one block, not two)
+    while not ops.attention_takes_projections(D, torch.bfloat16, P, True, requests=n, num_heads=H, num_kv_heads=KV, kv_len_bound=max(ctx_lens[:n])):
+        n -= 1
+    assert n >= 6
+    ctx_lens = ctx_lens[:n]
     q_lens = [1] * n
     layers, layer, eps, maxpos = 2, 1, 1e-5, max(ctx_lens) + 3
     _, k_cache, v_cache, table, cu = _paged_case(g, q_lens, ctx_lens, H, KV, D, P, torch.bfloat16)

@@ -110,6 +110,72 @@ def test_attention_part_in_portions_equals_the_plain_whole_sequence(window):
     torch.testing.assert_close(torch.cat(outs), want, atol=2e-5, rtol=2e-5)
 
 
+@pytest.mark.parametrize("window", [0, 9])
+def test_attention_part_decodes_from_the_raw_projections_in_bfloat16(monkeypatch, window):
+    """Two requests, a portion of a prompt each and then one token at a time: at a head size and page size where the
+    split-KV kernel takes the raw projections itself (norm, rotation and cache store inside it), the part must take that
+    path for the single-token steps and give what it gives with the stand-alone kernel before the attention, and what the
+    plain implementation gives on the whole sequences."""
+    from oxr_inference_b200 import ops
+    from oxr_inference_b200.parts import MIXERS, POSITION_ENCODINGS
+
+    D, H, KV, hidden = 64, 6, 2, 96
+    cfg = {"num_attention_heads": H, "num_key_value_heads": KV, "head_dim": D, "rms_norm_eps": 1e-5}
+    lens, first = (41, 30), (20, 11)
+    hs = [torch.randn(n, hidden, device=DEV).bfloat16() for n in lens]
+    taken = {"fused": 0}
+    real = ops.decode_attention_from_projections
+
+    def counting(*a, **k):
+        taken["fused"] += 1
+        return real(*a, **k)
+
+    monkeypatch.setattr(ops, "decode_attention_from_projections", counting)
+    monkeypatch.setattr(ops, "DECODE_CUT", "auto")
+    outs = {}
+    for fuse in (True, False):
+        monkeypatch.setattr(ops, "FUSE_QKV", fuse)
+        rt = _runtime(torch.bfloat16)
+        rope = POSITION_ENCODINGS.build("rope_neox", rt, dim=D, theta=1e4)
+        attn = MIXERS.build("gqa_attention", rt, rope, hidden_size=hidden, num_heads=H, num_kv_heads=KV, head_dim=D, scale=D ** -0.5,
+                            qk_norm=True, eps=1e-5, window=window)
+        w = {"p." + k: v.to(DEV).bfloat16().float() for k, v in _fill(attn, scale=0.15).items()}
+        manager, builder, StepEntry = _one_layer_context(attn, rt, None, None)
+        rcs = [manager.open("a"), manager.open("b")]
+        got = [[], []]
+        pos = [0, 0]
+
+        def step(counts):
+            entries = []
+            for i, c in enumerate(counts):
+                if c:
+                    assert manager.reserve(rcs[i], pos[i] + c)
+                    entries.append((i, c, StepEntry(rcs[i], [0] * c, [])))
+            ctx = builder.build([e for _, _, e in entries])
+            x = torch.cat([hs[i][pos[i]:pos[i] + c] for i, c, _ in entries]).contiguous()
+            o = attn.forward(x, ctx, manager.layer_cache(0, ctx))
+            at = 0
+            for i, c, _ in entries:
+                got[i].append(o[at:at + c])
+                manager.advance(rcs[i], pos[i] + c)
+                pos[i] += c
+                at += c
+
+        step(first)
+        before = taken["fused"]
+        while pos[0] < lens[0] or pos[1] < lens[1]:
+            step([1 if pos[i] < lens[i] else 0 for i in range(2)])
+        ops.check_status(rt.status)
+        assert (taken["fused"] - before == lens[0] - first[0]) == fuse, "the single-token steps did not take the expected path"
+        outs[fuse] = [torch.cat(g).float() for g in got]
+        for i, n in enumerate(lens):
+            cos, sin = QP.rope_tables(D, 1e4, n, torch.float32)
+            want = QP.attention_block(hs[i].float(), w, "p.", cfg, cos.to(DEV), sin.to(DEV), window)
+            torch.testing.assert_close(outs[fuse][i], want, atol=3e-2, rtol=3e-2)
+    for a, b in zip(outs[True], outs[False]):     # the same arithmetic up to the last bit of fp32 before a rounding to bf16
+        torch.testing.assert_close(a, b, atol=4e-3, rtol=2.0 ** -6)
+
+
 def test_block_part_carries_the_residual_like_the_plain_layer():
     from oxr_inference_b200.parts import ARRANGEMENTS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS
 
