@@ -104,16 +104,40 @@ def attention(args) -> dict:
     from oxr_inference_b200.parts.base import uneven_lengths
     uneven = uneven_lengths(ctx_lens.tolist())     # what the engine tells the kernel about such a step
 
+    common = dict(tiles=tiles, cu_q=cu, ctx_lens=ctx_lens, block_table=table, page_size=P, scale=D ** -0.5, window=0, kv_len_bound=ctx,
+                  status=status, kv_maps=maps, uneven=uneven)
+    if args.from_projections or args.with_rope_kernel:
+        # a decode step's attention from the raw q|k|v projections: in one kernel, or behind the q/k norm + RoPE + store kernel
+        if q_len != 1:
+            raise SystemExit("--from-projections / --with-rope-kernel: a step of one token per request (--q-len 1)")
+        qkv = torch.randn(B, (H + 2 * KV) * D, device="cuda").bfloat16()
+        qw, kw = torch.ones(D, device="cuda"), torch.ones(D, device="cuda")
+        angles = torch.outer(torch.arange(ctx + 1, dtype=torch.float), 1.0 / (1e6 ** (torch.arange(0, D, 2, dtype=torch.float) / D)))
+        cos, sin = angles.cos().cuda(), angles.sin().cuda()
+        positions = (ctx_lens - 1).int()
+        slots = (table.gather(1, (positions // P).long()[:, None])[:, 0] * P + positions % P).int()
+        if args.from_projections and not ops.attention_takes_projections(D, torch.bfloat16, P, maps, requests=B, num_heads=H, num_kv_heads=KV,
+                                                                         kv_len_bound=ctx, uneven=uneven):
+            raise SystemExit("the attention kernel does not take the projections itself for this step")
+
     def run(i):
         layer = i % layers
-        ops.paged_attention(q, k_pool[layer], v_pool[layer], tiles=tiles, cu_q=cu, ctx_lens=ctx_lens, block_table=table, page_size=P,
-                            scale=D ** -0.5, window=0, kv_len_bound=ctx, status=status, kv_maps=maps, layer_in_pool=layer, uneven=uneven)
+        if args.from_projections:
+            ops.decode_attention_from_projections(qkv, qw, kw, cos, sin, k_pool[layer], v_pool[layer], store=True, num_heads=H, num_kv_heads=KV,
+                                                  head_dim=D, eps=1e-6, layer_in_pool=layer, **common)
+            return
+        x = q
+        if args.with_rope_kernel:
+            x = ops.qk_norm_rope_store(qkv, qw, kw, cos, sin, positions, slots, k_pool[layer], v_pool[layer], H, KV, D, 1e-6, status)
+        ops.paged_attention(x, k_pool[layer], v_pool[layer], layer_in_pool=layer, **common)
     us = _time(run, args.reps)
     ops.check_status(status)
     lens = ctx_lens.tolist()
     kv_bytes = sum(lens) * KV * D * 2 * 2
     flops = sum(4 * H * D * (c - q_len + i + 1) for c in lens for i in range(q_len))
-    return {"kernel": "paged_attention", "batch": B, "q_len": q_len, "context": ctx if not args.ragged else f"{min(lens)}..{max(lens)}", "heads": H, "kv_heads": KV, "head_dim": D,
+    name = ("decode_attention_from_projections" if args.from_projections else
+            "qk_norm_rope_store + paged_attention" if args.with_rope_kernel else "paged_attention")
+    return {"kernel": name, "batch": B, "q_len": q_len, "context": ctx if not args.ragged else f"{min(lens)}..{max(lens)}", "heads": H, "kv_heads": KV, "head_dim": D,
             "us": round(us, 2), "KV GB/s": round(kv_bytes / us / 1e3, 1), "TFLOP/s": round(flops / us / 1e6, 2)}
 
 
@@ -245,6 +269,9 @@ def main() -> None:
     a.add_argument("--no-tma", action="store_true", help="gather K and V with cp.async instead of TMA")
     a.add_argument("--ragged", action="store_true", help="contexts drawn between q_len + 16 and --context instead of all equal")
     a.add_argument("--unsorted", action="store_true", help="with --ragged: leave the requests in the order drawn")
+    a.add_argument("--from-projections", action="store_true",
+                   help="a decode step's attention from raw q|k|v projections: norm, rotation and cache store inside the attention kernel")
+    a.add_argument("--with-rope-kernel", action="store_true", help="the same work as two kernels: q/k norm + RoPE + store, then attention")
     a.set_defaults(run=attention)
     n = sub.add_parser("norm")
     n.add_argument("--rows", type=int, default=8)
