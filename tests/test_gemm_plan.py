@@ -51,3 +51,55 @@ def test_few_rows_form_where_w_is_narrow_and_rows_are_few(monkeypatch):
     assert ops._gemm_few_rows_plan(64, 2560, 9728) == 4        # 20 tiles: 6 shares would run, 4 are as fast or faster
     assert ops._gemm_few_rows_plan(256, 2560, 9728) == 6       # many rows and a long k: more shares pay
     assert ops._gemm_few_rows_plan(256, 2560, 4096) == 4
+
+
+class _FakeAttnLib:
+    """Stands in for the attention library's one question that the plan asks: how many pieces get a block each."""
+
+    def __init__(self, pieces):
+        self.pieces = pieces
+
+    def oxr_attn_one_round_of_pieces(self):
+        return self.pieces
+
+
+def test_decode_attention_takes_projections_only_with_a_block_per_piece(monkeypatch):
+    """The plan that decides whether a step of single tokens hands its raw q|k|v to the attention kernel: the sizes TMA gathers need, no
+    more pieces than one round of blocks, not the even cut, and the switch."""
+    import torch
+
+    monkeypatch.setattr(ops, "FUSE_QKV", True)
+    monkeypatch.setattr(ops, "DECODE_CUT", "auto")
+    monkeypatch.setattr(ops, "_attn_lib", lambda d: _FakeAttnLib(296))
+    maps = object()
+    step = dict(num_heads=32, num_kv_heads=8, kv_len_bound=2048)
+    assert ops.attention_takes_projections(128, torch.bfloat16, 16, maps)
+    assert ops.attention_takes_projections(128, torch.bfloat16, 16, maps, requests=8, **step)        # 64 units x 4 pieces
+    assert not ops.attention_takes_projections(128, torch.bfloat16, 16, maps, requests=64, **step)   # 512 units
+    assert not ops.attention_takes_projections(128, torch.bfloat16, 16, maps, requests=8, uneven=True, **step)
+    assert not ops.attention_takes_projections(128, torch.float32, 16, maps, requests=8, **step)
+    assert not ops.attention_takes_projections(80, torch.bfloat16, 16, maps, requests=8, **step)
+    assert not ops.attention_takes_projections(128, torch.bfloat16, 4, maps, requests=8, **step)
+    assert not ops.attention_takes_projections(128, torch.bfloat16, 24, maps, requests=8, **step)     # not a power of two
+    assert not ops.attention_takes_projections(128, torch.bfloat16, 16, None, requests=8, **step)
+    monkeypatch.setattr(ops, "_attn_lib", lambda d: _FakeAttnLib(148))                                # one block per SM
+    assert not ops.attention_takes_projections(128, torch.bfloat16, 16, maps, requests=8, **step)
+    monkeypatch.setattr(ops, "FUSE_QKV", False)
+    assert not ops.attention_takes_projections(128, torch.bfloat16, 16, maps)
+
+
+def test_a_step_of_single_tokens_knows_itself():
+    import torch
+
+    from oxr_inference_b200.parts.base import StepContext
+
+    z = torch.zeros(0, dtype=torch.int32)
+
+    def ctx(q_lens):
+        return StepContext(n_tokens=sum(q_lens), n_requests=len(q_lens), token_ids=z, positions=z, req_of_token=z, cu_q=z, ctx_lens=z, state_slots=z,
+                           logit_rows=z, no_store_slots=z, groups=[], q_lens=q_lens)
+
+    assert ctx([1, 1, 1]).single_tokens
+    assert not ctx([1, 2, 1]).single_tokens
+    assert not ctx([3]).single_tokens
+    assert not ctx([2, 0]).single_tokens       # as many tokens as requests, but not one each
